@@ -1,0 +1,397 @@
+// Cast family: amax, high precision -> FP8 (optionally with a transposed copy), FP8 -> high
+// precision, byte transpose and the vectorised scale update.  All kernels are bandwidth bound;
+// they use 16-byte accesses when the pointers allow it and a grid sized from the SM count.
+#include "common.cuh"
+
+namespace {
+
+constexpr int kThreads = 256;
+
+template <typename T>
+struct VecOf {
+  static constexpr int N = 16 / sizeof(T);
+};
+
+// ---- amax (+ optional scale update by the last block to finish) -------------------------------
+template <typename T, bool VEC>
+__global__ void __launch_bounds__(kThreads) amax_kernel(const T* __restrict__ x, int64_t n, float* amax, float* scale,
+                                                         float* scale_inv, float fp_max, int margin, float prescale,
+                                                         unsigned int* counter) {
+  __shared__ float red[32];
+  float m = 0.0f;
+  int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  if (VEC) {
+    constexpr int N = VecOf<T>::N;
+    int64_t nv = n / N;
+    const Bytes16* xv = reinterpret_cast<const Bytes16*>(x);
+    for (int64_t i = tid; i < nv; i += stride) {
+      Bytes16 v = xv[i];
+      const T* e = reinterpret_cast<const T*>(&v);
+#pragma unroll
+      for (int j = 0; j < N; ++j) m = fmaxf(m, abs_nan_to_inf(to_f32<T>(e[j])));
+    }
+    for (int64_t i = nv * N + tid; i < n; i += stride) m = fmaxf(m, abs_nan_to_inf(to_f32<T>(x[i])));
+  } else {
+    for (int64_t i = tid; i < n; i += stride) m = fmaxf(m, abs_nan_to_inf(to_f32<T>(x[i])));
+  }
+  m = block_max(m, red);
+  if (threadIdx.x == 0) {
+    atomic_max_nonneg(amax, m);
+    if (counter != nullptr) {
+      __threadfence();
+      unsigned int done = atomicAdd(counter, 1u);
+      if (done == gridDim.x - 1) {
+        // Every other block has published its maximum: derive the scale once.
+        __threadfence();
+        float a = *(volatile float*)amax;
+        float s = msamp_compute_scale(a, *scale, fp_max, margin) * prescale;
+        *scale = s;
+        *scale_inv = __frcp_rn(s);
+        *counter = 0;    // ready for the next launch on this stream
+      }
+    }
+  }
+}
+
+// ---- high precision -> fp8 ------------------------------------------------------------------------
+template <typename T, int FMT, bool VEC>
+__global__ void __launch_bounds__(kThreads) cast_to_fp8_kernel(const T* __restrict__ x, uint8_t* __restrict__ out, int64_t n,
+                                                                const float* __restrict__ scale_ptr, float* amax) {
+  __shared__ float red[32];
+  const float scale = *scale_ptr;
+  float m = 0.0f;
+  int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  if (VEC) {
+    constexpr int N = VecOf<T>::N;    // 8 (16-bit) or 4 (fp32) inputs -> N bytes out
+    int64_t nv = n / N;
+    const Bytes16* xv = reinterpret_cast<const Bytes16*>(x);
+    for (int64_t i = tid; i < nv; i += stride) {
+      Bytes16 v = xv[i];
+      const T* e = reinterpret_cast<const T*>(&v);
+      uint16_t o[N / 2];
+#pragma unroll
+      for (int j = 0; j < N; j += 2) {
+        float a = to_f32<T>(e[j]), b = to_f32<T>(e[j + 1]);
+        m = fmaxf(m, fmaxf(abs_nan_to_inf(a), abs_nan_to_inf(b)));
+        o[j / 2] = f32x2_to_fp8x2<FMT>(a * scale, b * scale);
+      }
+      if (N == 8) {
+        reinterpret_cast<Bytes8*>(out)[i] = *reinterpret_cast<Bytes8*>(o);
+      } else {
+        reinterpret_cast<uint32_t*>(out)[i] = *reinterpret_cast<uint32_t*>(o);
+      }
+    }
+    for (int64_t i = nv * N + tid; i < n; i += stride) {
+      float a = to_f32<T>(x[i]);
+      m = fmaxf(m, abs_nan_to_inf(a));
+      out[i] = f32_to_fp8<FMT>(a * scale);
+    }
+  } else {
+    for (int64_t i = tid; i < n; i += stride) {
+      float a = to_f32<T>(x[i]);
+      m = fmaxf(m, abs_nan_to_inf(a));
+      out[i] = f32_to_fp8<FMT>(a * scale);
+    }
+  }
+  if (amax != nullptr) {
+    m = block_max(m, red);
+    if (threadIdx.x == 0) atomic_max_nonneg(amax, m);
+  }
+}
+
+// ---- fp8 -> high precision ------------------------------------------------------------------------
+template <typename T, int FMT, bool VEC>
+__global__ void __launch_bounds__(kThreads) cast_from_fp8_kernel(const uint8_t* __restrict__ in, T* __restrict__ out, int64_t n,
+                                                                  const float* __restrict__ scale_inv_ptr) {
+  const float si = *scale_inv_ptr;
+  int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  if (VEC) {
+    constexpr int N = VecOf<T>::N;
+    int64_t nv = n / N;
+    for (int64_t i = tid; i < nv; i += stride) {
+      uint8_t b[N];
+      if (N == 8) {
+        *reinterpret_cast<Bytes8*>(b) = reinterpret_cast<const Bytes8*>(in)[i];
+      } else {
+        *reinterpret_cast<uint32_t*>(b) = reinterpret_cast<const uint32_t*>(in)[i];
+      }
+      Bytes16 o;
+      T* e = reinterpret_cast<T*>(&o);
+#pragma unroll
+      for (int j = 0; j < N; ++j) e[j] = from_f32<T>(fp8_to_f32<FMT>(b[j]) * si);
+      reinterpret_cast<Bytes16*>(out)[i] = o;
+    }
+    for (int64_t i = nv * N + tid; i < n; i += stride) out[i] = from_f32<T>(fp8_to_f32<FMT>(in[i]) * si);
+  } else {
+    for (int64_t i = tid; i < n; i += stride) out[i] = from_f32<T>(fp8_to_f32<FMT>(in[i]) * si);
+  }
+}
+
+// ---- cast + transpose -----------------------------------------------------------------------------
+// One CTA converts a 64x64 tile. The row-major copy is written straight from registers; the
+// transposed copy goes through shared memory so that both outputs are written in 64-byte runs.
+constexpr int kTile = 64;
+constexpr int kTStride = kTile + 4;    // bytes; keeps 4-byte alignment and spreads banks
+
+template <typename T, int FMT, bool WRITE_ROWMAJOR>
+__global__ void __launch_bounds__(kThreads) cast_transpose_kernel(const T* __restrict__ x, uint8_t* __restrict__ out,
+                                                                   uint8_t* __restrict__ out_t, int rows, int cols,
+                                                                   const float* __restrict__ scale_ptr, float* amax,
+                                                                   bool aligned) {
+  __shared__ __align__(16) uint8_t tile_t[kTile * kTStride];    // [c][r]
+  __shared__ float red[32];
+  const float scale = *scale_ptr;
+  const int tiles_c = (cols + kTile - 1) / kTile;
+  const int tiles_r = (rows + kTile - 1) / kTile;
+  const int64_t ntiles = (int64_t)tiles_c * tiles_r;
+  float m = 0.0f;
+  for (int64_t t = blockIdx.x; t < ntiles; t += gridDim.x) {
+    const int r0 = (int)(t / tiles_c) * kTile;
+    const int c0 = (int)(t % tiles_c) * kTile;
+    const bool full = aligned && (r0 + kTile <= rows) && (c0 + kTile <= cols);
+    if (full) {
+      // 8 threads cover a row of 64 elements (8 each); 32 rows per pass.
+      const int cr = threadIdx.x >> 3, cc = (threadIdx.x & 7) * 8;
+#pragma unroll
+      for (int p = 0; p < 2; ++p) {
+        const int r = cr + p * 32;
+        const T* src = x + (int64_t)(r0 + r) * cols + c0 + cc;
+        T e[8];
+        if constexpr (sizeof(T) == 2) {
+          *reinterpret_cast<Bytes16*>(e) = *reinterpret_cast<const Bytes16*>(src);
+        } else {
+          *reinterpret_cast<Bytes16*>(e) = *reinterpret_cast<const Bytes16*>(src);
+          *reinterpret_cast<Bytes16*>(e + 4) = *reinterpret_cast<const Bytes16*>(src + 4);
+        }
+        uint8_t b[8];
+#pragma unroll
+        for (int j = 0; j < 8; j += 2) {
+          float a0 = to_f32<T>(e[j]), a1 = to_f32<T>(e[j + 1]);
+          m = fmaxf(m, fmaxf(abs_nan_to_inf(a0), abs_nan_to_inf(a1)));
+          uint16_t q = f32x2_to_fp8x2<FMT>(a0 * scale, a1 * scale);
+          b[j] = (uint8_t)(q & 0xff);
+          b[j + 1] = (uint8_t)(q >> 8);
+        }
+        if (WRITE_ROWMAJOR) *reinterpret_cast<Bytes8*>(out + (int64_t)(r0 + r) * cols + c0 + cc) = *reinterpret_cast<Bytes8*>(b);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) tile_t[(cc + j) * kTStride + r] = b[j];
+      }
+      __syncthreads();
+      {
+        const int c = threadIdx.x >> 2, rr = (threadIdx.x & 3) * 16;
+        Bytes16 o;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) o.w[j] = *reinterpret_cast<const uint32_t*>(&tile_t[c * kTStride + rr + 4 * j]);
+        *reinterpret_cast<Bytes16*>(out_t + (int64_t)(c0 + c) * rows + r0 + rr) = o;
+      }
+      __syncthreads();
+    } else {
+      for (int i = threadIdx.x; i < kTile * kTile; i += blockDim.x) {
+        const int r = i / kTile, c = i % kTile;
+        uint8_t q = 0;
+        if (r0 + r < rows && c0 + c < cols) {
+          float a = to_f32<T>(x[(int64_t)(r0 + r) * cols + c0 + c]);
+          m = fmaxf(m, abs_nan_to_inf(a));
+          q = f32_to_fp8<FMT>(a * scale);
+          if (WRITE_ROWMAJOR) out[(int64_t)(r0 + r) * cols + c0 + c] = q;
+        }
+        tile_t[c * kTStride + r] = q;
+      }
+      __syncthreads();
+      for (int i = threadIdx.x; i < kTile * kTile; i += blockDim.x) {
+        const int c = i / kTile, r = i % kTile;
+        if (r0 + r < rows && c0 + c < cols) out_t[(int64_t)(c0 + c) * rows + r0 + r] = tile_t[c * kTStride + r];
+      }
+      __syncthreads();
+    }
+  }
+  if (amax != nullptr) {
+    m = block_max(m, red);
+    if (threadIdx.x == 0) atomic_max_nonneg(amax, m);
+  }
+}
+
+// ---- byte transpose ---------------------------------------------------------------------------------
+__global__ void __launch_bounds__(kThreads) transpose_bytes_kernel(const uint8_t* __restrict__ in, uint8_t* __restrict__ out,
+                                                                    int rows, int cols, bool aligned) {
+  __shared__ __align__(16) uint8_t tile_t[kTile * kTStride];
+  const int tiles_c = (cols + kTile - 1) / kTile;
+  const int tiles_r = (rows + kTile - 1) / kTile;
+  const int64_t ntiles = (int64_t)tiles_c * tiles_r;
+  for (int64_t t = blockIdx.x; t < ntiles; t += gridDim.x) {
+    const int r0 = (int)(t / tiles_c) * kTile;
+    const int c0 = (int)(t % tiles_c) * kTile;
+    const bool full = aligned && (r0 + kTile <= rows) && (c0 + kTile <= cols);
+    if (full) {
+      // 4 threads cover a 64-byte row (16 bytes each); 64 rows in one pass.
+      const int r = threadIdx.x >> 2, cc = (threadIdx.x & 3) * 16;
+      Bytes16 v = *reinterpret_cast<const Bytes16*>(in + (int64_t)(r0 + r) * cols + c0 + cc);
+      const uint8_t* b = reinterpret_cast<const uint8_t*>(&v);
+#pragma unroll
+      for (int j = 0; j < 16; ++j) tile_t[(cc + j) * kTStride + r] = b[j];
+      __syncthreads();
+      Bytes16 o;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) o.w[j] = *reinterpret_cast<const uint32_t*>(&tile_t[r * kTStride + cc + 4 * j]);
+      *reinterpret_cast<Bytes16*>(out + (int64_t)(c0 + r) * rows + r0 + cc) = o;
+      __syncthreads();
+    } else {
+      for (int i = threadIdx.x; i < kTile * kTile; i += blockDim.x) {
+        const int r = i / kTile, c = i % kTile;
+        tile_t[c * kTStride + r] = (r0 + r < rows && c0 + c < cols) ? in[(int64_t)(r0 + r) * cols + c0 + c] : 0;
+      }
+      __syncthreads();
+      for (int i = threadIdx.x; i < kTile * kTile; i += blockDim.x) {
+        const int c = i / kTile, r = i % kTile;
+        if (r0 + r < rows && c0 + c < cols) out[(int64_t)(c0 + c) * rows + r0 + r] = tile_t[c * kTStride + r];
+      }
+      __syncthreads();
+    }
+  }
+}
+
+// ---- vectorised scale update ------------------------------------------------------------------------
+__global__ void update_scales_kernel(const float* __restrict__ amax, int64_t amax_stride, float* scale, float* scale_inv,
+                                     int n, float fp_max, int margin) {
+  int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) {
+    float s = msamp_compute_scale(amax[(int64_t)i * amax_stride], scale[i], fp_max, margin);
+    scale[i] = s;
+    scale_inv[i] = __frcp_rn(s);
+  }
+}
+
+// Delayed-scaling bookkeeping for n metas that share flat buffers (one launch for all layers),
+// amax is [n, window]: a non-finite newest entry is dropped, the scale is recomputed from the
+// window maximum, the window moves by one slot with slot 0 cleared, and the step counter advances
+// (or restarts after a non-finite entry).  scale_inv is left alone: it belongs to the tensors that
+// were quantised with the old scale and is refreshed by the next cast.
+__global__ void roll_windows_kernel(float* amax, float* scale, int* counters, int n, int window, float fp_max, int margin) {
+  int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  float* a = amax + (int64_t)i * window;
+  const bool finite = !(isinf(a[0]) || isnan(a[0]));
+  if (!finite) a[0] = 0.0f;
+  float mx = 0.0f;
+  for (int j = 0; j < window; ++j) mx = fmaxf(mx, a[j]);
+  scale[i] = msamp_compute_scale(mx, scale[i], fp_max, margin);
+  for (int j = window - 1; j > 0; --j) a[j] = a[j - 1];
+  a[0] = 0.0f;
+  counters[i] = finite ? counters[i] + 1 : 0;
+}
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+inline bool aligned8(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 7) == 0; }
+
+}    // namespace
+
+// amax[0] = max|x| (NaN counts as +inf). With `counter` non-null the last block also writes
+// scale = rule(amax) * prescale and scale_inv = 1/scale; `counter` is a zero-initialised word
+// of scratch that the kernel leaves at zero again.
+MSAMP_API int msamp_amax(const void* x, int64_t n, int dtype, float* amax, float* scale, float* scale_inv, float fp_max,
+                         int margin, float prescale, unsigned int* counter, void* stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  MSAMP_REQUIRE(n >= 0 && amax != nullptr, "msamp_amax: bad arguments");
+  cudaMemsetAsync(amax, 0, sizeof(float), stream);
+  int grid = msamp_grid_for((n + 7) / 8, kThreads, 4);
+  if (n == 0) grid = 1;
+  MSAMP_DISPATCH_HP(dtype, T, {
+    if (aligned16(x))
+      amax_kernel<T, true><<<grid, kThreads, 0, stream>>>((const T*)x, n, amax, scale, scale_inv, fp_max, margin, prescale, counter);
+    else
+      amax_kernel<T, false><<<grid, kThreads, 0, stream>>>((const T*)x, n, amax, scale, scale_inv, fp_max, margin, prescale, counter);
+  });
+  return msamp_check_launch("msamp_amax");
+}
+
+// out = saturate_fp8(x * scale). With `amax` non-null it receives max|x| (it is cleared first).
+MSAMP_API int msamp_cast_to_fp8(const void* x, int64_t n, int dtype, void* out, int fmt, const float* scale, float* amax,
+                                void* stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  MSAMP_REQUIRE(n >= 0 && scale != nullptr, "msamp_cast_to_fp8: bad arguments");
+  if (amax) cudaMemsetAsync(amax, 0, sizeof(float), stream);
+  if (n == 0) return MSAMP_OK;
+  int grid = msamp_grid_for((n + 7) / 8, kThreads, 4);
+  const bool vec = aligned16(x) && aligned8(out);
+  MSAMP_DISPATCH_HP(dtype, T, {
+    MSAMP_DISPATCH_FP8(fmt, F, {
+      if (vec)
+        cast_to_fp8_kernel<T, F, true><<<grid, kThreads, 0, stream>>>((const T*)x, (uint8_t*)out, n, scale, amax);
+      else
+        cast_to_fp8_kernel<T, F, false><<<grid, kThreads, 0, stream>>>((const T*)x, (uint8_t*)out, n, scale, amax);
+    });
+  });
+  return msamp_check_launch("msamp_cast_to_fp8");
+}
+
+MSAMP_API int msamp_cast_from_fp8(const void* in, int64_t n, int fmt, const float* scale_inv, void* out, int out_dtype,
+                                  void* stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  MSAMP_REQUIRE(n >= 0 && scale_inv != nullptr, "msamp_cast_from_fp8: bad arguments");
+  if (n == 0) return MSAMP_OK;
+  int grid = msamp_grid_for((n + 7) / 8, kThreads, 4);
+  const bool vec = aligned16(out) && aligned8(in);
+  MSAMP_DISPATCH_HP(out_dtype, T, {
+    MSAMP_DISPATCH_FP8(fmt, F, {
+      if (vec)
+        cast_from_fp8_kernel<T, F, true><<<grid, kThreads, 0, stream>>>((const uint8_t*)in, (T*)out, n, scale_inv);
+      else
+        cast_from_fp8_kernel<T, F, false><<<grid, kThreads, 0, stream>>>((const uint8_t*)in, (T*)out, n, scale_inv);
+    });
+  });
+  return msamp_check_launch("msamp_cast_from_fp8");
+}
+
+// x is [rows, cols] row-major. out (may be null) is the row-major FP8 copy, out_t the [cols, rows] one.
+MSAMP_API int msamp_cast_transpose_fp8(const void* x, int rows, int cols, int dtype, void* out, void* out_t, int fmt,
+                                       const float* scale, float* amax, void* stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  MSAMP_REQUIRE(rows >= 0 && cols >= 0 && out_t != nullptr && scale != nullptr, "msamp_cast_transpose_fp8: bad arguments");
+  if (amax) cudaMemsetAsync(amax, 0, sizeof(float), stream);
+  if ((int64_t)rows * cols == 0) return MSAMP_OK;
+  int64_t ntiles = (int64_t)((rows + kTile - 1) / kTile) * ((cols + kTile - 1) / kTile);
+  int cap = msamp_sm_count() * 8;
+  int grid = (int)(ntiles < cap ? ntiles : cap);
+  const bool aligned = aligned16(x) && aligned16(out_t) && (out == nullptr || aligned8(out)) && (cols % 8 == 0) && (rows % 16 == 0);
+  MSAMP_DISPATCH_HP(dtype, T, {
+    MSAMP_DISPATCH_FP8(fmt, F, {
+      if (out)
+        cast_transpose_kernel<T, F, true><<<grid, kThreads, 0, stream>>>((const T*)x, (uint8_t*)out, (uint8_t*)out_t, rows, cols, scale, amax, aligned);
+      else
+        cast_transpose_kernel<T, F, false><<<grid, kThreads, 0, stream>>>((const T*)x, nullptr, (uint8_t*)out_t, rows, cols, scale, amax, aligned);
+    });
+  });
+  return msamp_check_launch("msamp_cast_transpose_fp8");
+}
+
+MSAMP_API int msamp_transpose_fp8(const void* in, int rows, int cols, void* out, void* stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  MSAMP_REQUIRE(rows >= 0 && cols >= 0, "msamp_transpose_fp8: bad arguments");
+  if ((int64_t)rows * cols == 0) return MSAMP_OK;
+  int64_t ntiles = (int64_t)((rows + kTile - 1) / kTile) * ((cols + kTile - 1) / kTile);
+  int cap = msamp_sm_count() * 8;
+  int grid = (int)(ntiles < cap ? ntiles : cap);
+  const bool aligned = aligned16(in) && aligned16(out) && (cols % 16 == 0) && (rows % 16 == 0);
+  transpose_bytes_kernel<<<grid, kThreads, 0, stream>>>((const uint8_t*)in, (uint8_t*)out, rows, cols, aligned);
+  return msamp_check_launch("msamp_transpose_fp8");
+}
+
+// scale[i] = rule(amax[i * amax_stride]); scale_inv[i] = 1 / scale[i].
+MSAMP_API int msamp_update_scales(const float* amax, int64_t amax_stride, float* scale, float* scale_inv, int n, float fp_max,
+                                  int margin, void* stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  if (n <= 0) return MSAMP_OK;
+  update_scales_kernel<<<(n + 127) / 128, 128, 0, stream>>>(amax, amax_stride, scale, scale_inv, n, fp_max, margin);
+  return msamp_check_launch("msamp_update_scales");
+}
+
+MSAMP_API int msamp_roll_windows(float* amax, float* scale, int* counters, int n, int window, float fp_max, int margin,
+                                 void* stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  if (n <= 0) return MSAMP_OK;
+  roll_windows_kernel<<<(n + 127) / 128, 128, 0, stream>>>(amax, scale, counters, n, window, fp_max, margin);
+  return msamp_check_launch("msamp_roll_windows");
+}

@@ -1,0 +1,407 @@
+// FP8 GEMM for sm_100a:  D[M,N] = (sa_inv * sb_inv) * A[M,K] * B[N,K]^T  (+ bias[N]) (+ D)
+//
+// A and B hold e4m3 or e5m2 bytes with K contiguous ("TN" layout); the per-tensor scale_inv
+// factors are read from device memory so that no host synchronisation is needed.  The kernel is
+// persistent (one CTA per SM) and warp specialised:
+//   warp 0        TMA producer: 128-byte-swizzled A/B tiles into a ring of shared-memory stages
+//   warp 1        allocates TMEM and issues tcgen05.mma (kind::f8f6f4, 128 x BN x 32 per instruction)
+//   warps 2..5    epilogue: tcgen05.ld the fp32 accumulator, scale, add bias / previous D, convert,
+//                 store, and optionally reduce max|D| for the next quantisation
+// Two accumulator buffers in TMEM let the epilogue of tile i overlap the main loop of tile i+1.
+// Every wait on an mbarrier is bounded; when one gives up the CTA sets the device status word,
+// lets its outstanding copies land, frees its TMEM and returns.
+//
+// Replaces the cuBLASLt call behind the reference's Gemm.fp8_gemm (msamp/operators/gemm/gemm.py:121-144).
+#include <mutex>
+#include <unordered_map>
+
+#include "tcgen05.cuh"
+
+namespace {
+
+constexpr int BM = 128;
+constexpr int BK = 128;    // bytes == fp8 elements per stage along K (one 128B swizzle atom)
+constexpr int UMMA_K = 32;
+constexpr int kGemmThreads = 192;
+
+template <int BN>
+struct Cfg {
+  static constexpr int STAGES = (BN == 256) ? 4 : 6;
+  static constexpr int A_BYTES = BM * BK;
+  static constexpr int B_BYTES = BN * BK;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int TILE_BYTES = STAGES * STAGE_BYTES;
+  static constexpr int BAR_BYTES = 256;
+  static constexpr int SMEM_BYTES = TILE_BYTES + BAR_BYTES + 1024;    // +1024: manual alignment slack
+  static constexpr int TMEM_COLS = 2 * BN;                            // two accumulator buffers (512 or 256)
+};
+
+struct GemmParams {
+  void* d;
+  const void* bias;
+  const float* scale_inv_a;
+  const float* scale_inv_b;
+  float* amax_out;
+  unsigned int* status;
+  int M, N, K;
+  int64_t ldd;    // elements
+  int out_dtype;
+  int bias_dtype;
+  int accumulate;
+  int a_fmt, b_fmt;
+};
+
+template <typename OutT>
+__device__ __forceinline__ void store_chunk(OutT* dst, const float (&v)[32], bool vec_ok, int valid) {
+  if (vec_ok && valid == 32) {
+    if constexpr (sizeof(OutT) == 4) {
+#pragma unroll
+      for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(dst + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; j += 8) {
+        Bytes16 o;
+        OutT* e = reinterpret_cast<OutT*>(&o);
+#pragma unroll
+        for (int q = 0; q < 8; ++q) e[q] = from_f32<OutT>(v[j + q]);
+        *reinterpret_cast<Bytes16*>(dst + j) = o;
+      }
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (j < valid) dst[j] = from_f32<OutT>(v[j]);
+  }
+}
+
+template <typename OutT>
+__device__ __forceinline__ void load_chunk(const OutT* src, float (&v)[32], bool vec_ok, int valid) {
+  if (vec_ok && valid == 32) {
+    if constexpr (sizeof(OutT) == 4) {
+#pragma unroll
+      for (int j = 0; j < 32; j += 4) {
+        float4 t = *reinterpret_cast<const float4*>(src + j);
+        v[j] = t.x; v[j + 1] = t.y; v[j + 2] = t.z; v[j + 3] = t.w;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; j += 8) {
+        Bytes16 o = *reinterpret_cast<const Bytes16*>(src + j);
+        const OutT* e = reinterpret_cast<const OutT*>(&o);
+#pragma unroll
+        for (int q = 0; q < 8; ++q) v[j + q] = to_f32<OutT>(e[q]);
+      }
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] = (j < valid) ? to_f32<OutT>(src[j]) : 0.0f;
+  }
+}
+
+template <int BN, typename OutT>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_fp8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b, const GemmParams p) {
+  using C = Cfg<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  // 128B-swizzled tiles need 1024-byte alignment.
+  const uint32_t raw_addr = tc5::smem_u32(smem_raw);
+  const uint32_t base = (raw_addr + 1023u) & ~1023u;
+  uint8_t* smem = smem_raw + (base - raw_addr);
+
+  const uint32_t bars = base + C::TILE_BYTES;
+  auto full_bar = [&](int s) { return bars + 8u * s; };
+  auto empty_bar = [&](int s) { return bars + 8u * (C::STAGES + s); };
+  auto tfull_bar = [&](int b) { return bars + 8u * (2 * C::STAGES + b); };
+  auto tempty_bar = [&](int b) { return bars + 8u * (2 * C::STAGES + 2 + b); };
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(smem + C::TILE_BYTES + 8 * (2 * C::STAGES + 4));
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  const int num_m = (p.M + BM - 1) / BM;
+  const int num_n = (p.N + BN - 1) / BN;
+  const int num_tiles = num_m * num_n;
+  const int num_kb = (p.K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < C::STAGES; ++s) {
+      tc5::mbar_init(full_bar(s), 1);
+      tc5::mbar_init(empty_bar(s), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      tc5::mbar_init(tfull_bar(b), 1);
+      tc5::mbar_init(tempty_bar(b), 4);
+    }
+    *abort_flag = 0;
+    tc5::mbar_fence_init();
+    tc5::tma_prefetch_desc(&tma_a);
+    tc5::tma_prefetch_desc(&tma_b);
+  }
+  if (warp == 1) {
+    tc5::tmem_alloc(tc5::smem_u32(tmem_holder), C::TMEM_COLS);
+    tc5::tmem_relinquish();
+  }
+  tc5::fence_before_sync();
+  __syncthreads();
+  tc5::fence_after_sync();
+  const uint32_t tmem_base = *tmem_holder;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      uint32_t it = 0;
+      for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+        const int m0 = (tile % num_m) * BM;
+        const int n0 = (tile / num_m) * BN;
+        bool ok = true;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % C::STAGES;
+          const uint32_t ph = (it / C::STAGES) & 1;
+          if (!tc5::mbar_wait(empty_bar(s), ph ^ 1, abort_flag, p.status, 1u)) { ok = false; break; }
+          tc5::mbar_arrive_expect_tx(full_bar(s), C::STAGE_BYTES);
+          const uint32_t sa = base + s * C::STAGE_BYTES;
+          tc5::tma_load_2d(sa, &tma_a, kb * BK, m0, full_bar(s));
+          tc5::tma_load_2d(sa + C::A_BYTES, &tma_b, kb * BK, n0, full_bar(s));
+        }
+        if (!ok) break;
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc = tc5::idesc_f8(BM, BN, p.a_fmt, p.b_fmt);
+      uint32_t it = 0;
+      uint32_t lt = 0;
+      for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++lt) {
+        const int buf = lt & 1;
+        const uint32_t aph = (lt >> 1) & 1;
+        if (!tc5::mbar_wait(tempty_bar(buf), aph ^ 1, abort_flag, p.status, 1u)) break;
+        tc5::fence_after_sync();
+        const uint32_t tmem_d = tmem_base + (uint32_t)(buf * BN);
+        bool ok = true;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % C::STAGES;
+          const uint32_t ph = (it / C::STAGES) & 1;
+          if (!tc5::mbar_wait(full_bar(s), ph, abort_flag, p.status, 1u)) { ok = false; break; }
+          tc5::fence_after_sync();
+          const uint32_t sa = base + s * C::STAGE_BYTES;
+          const uint64_t da = tc5::smem_desc_k_sw128(sa);
+          const uint64_t db = tc5::smem_desc_k_sw128(sa + C::A_BYTES);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            // +2 in the start-address field == +32 bytes along K inside the swizzle atom
+            tc5::mma_f8f6f4(tmem_d, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc, (kb | k) ? 1u : 0u);
+          }
+          tc5::mma_commit(empty_bar(s));    // frees the stage once these MMAs have read it
+        }
+        if (!ok) break;
+        tc5::mma_commit(tfull_bar(buf));    // accumulator complete
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (4 warps)
+    const int q = warp & 3;    // TMEM lane quarter this warp may access
+    const float alpha = (*p.scale_inv_a) * (*p.scale_inv_b);
+    OutT* D = reinterpret_cast<OutT*>(p.d);
+    const bool vec_ok = ((reinterpret_cast<uintptr_t>(D) & 15) == 0) && ((p.ldd * sizeof(OutT)) % 16 == 0);
+    float amax = 0.0f;
+    uint32_t lt = 0;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++lt) {
+      const int m0 = (tile % num_m) * BM;
+      const int n0 = (tile / num_m) * BN;
+      const int buf = lt & 1;
+      const uint32_t aph = (lt >> 1) & 1;
+      if (!tc5::mbar_wait(tfull_bar(buf), aph, abort_flag, p.status, 1u)) break;
+      tc5::fence_after_sync();
+      const int row = m0 + q * 32 + lane;
+      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN);
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tc5::tmem_ld32(taddr + (uint32_t)(c * 32), r);
+        tc5::tmem_ld_wait();
+        const int col = n0 + c * 32;
+        int valid = p.N - col;
+        valid = valid > 32 ? 32 : valid;
+        if (row < p.M && valid > 0) {
+          float v[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * alpha;
+          if (p.bias != nullptr) {
+            if (p.bias_dtype == DT_F32) {
+              const float* b = reinterpret_cast<const float*>(p.bias) + col;
+#pragma unroll
+              for (int j = 0; j < 32; ++j) if (j < valid) v[j] += __ldg(b + j);
+            } else if (p.bias_dtype == DT_BF16) {
+              const __nv_bfloat16* b = reinterpret_cast<const __nv_bfloat16*>(p.bias) + col;
+#pragma unroll
+              for (int j = 0; j < 32; ++j) if (j < valid) v[j] += __bfloat162float(b[j]);
+            } else {
+              const __half* b = reinterpret_cast<const __half*>(p.bias) + col;
+#pragma unroll
+              for (int j = 0; j < 32; ++j) if (j < valid) v[j] += __half2float(b[j]);
+            }
+          }
+          OutT* dst = D + (int64_t)row * p.ldd + col;
+          if (p.accumulate) {
+            float old[32];
+            load_chunk<OutT>(dst, old, vec_ok, valid);
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] += old[j];
+          }
+          if (p.amax_out != nullptr) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) if (j < valid) amax = fmaxf(amax, abs_nan_to_inf(v[j]));
+          }
+          store_chunk<OutT>(dst, v, vec_ok, valid);
+        }
+      }
+      tc5::fence_before_sync();
+      __syncwarp();
+      if (lane == 0) tc5::mbar_arrive(tempty_bar(buf));
+    }
+    if (p.amax_out != nullptr) {
+      amax = warp_max(amax);
+      if (lane == 0) atomic_max_nonneg(p.amax_out, amax);
+    }
+  }
+
+  // ---------------------------------------------------------------------- tear-down
+  __syncwarp();
+  if (*abort_flag) __nanosleep(200000);    // let copies / MMAs in flight finish before smem and TMEM go away
+  tc5::fence_before_sync();
+  __syncthreads();
+  tc5::fence_after_sync();
+  if (warp == 1) tc5::tmem_dealloc(tmem_base, C::TMEM_COLS);
+}
+
+// ---- host side -----------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess) {
+      fn = reinterpret_cast<EncodeTiledFn>(sym);
+    }
+  });
+  return fn;
+}
+
+struct MapKey {
+  const void* ptr;
+  int64_t rows, cols, pitch;
+  int box_rows;
+  bool operator==(const MapKey& o) const {
+    return ptr == o.ptr && rows == o.rows && cols == o.cols && pitch == o.pitch && box_rows == o.box_rows;
+  }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey& k) const {
+    size_t h = reinterpret_cast<size_t>(k.ptr);
+    h ^= (size_t)k.rows * 0x9e3779b97f4a7c15ull + (h << 6) + (h >> 2);
+    h ^= (size_t)k.cols * 0xc2b2ae3d27d4eb4full + (h << 6) + (h >> 2);
+    h ^= (size_t)k.pitch * 0x165667b19e3779f9ull + (h << 6) + (h >> 2);
+    h ^= (size_t)k.box_rows + (h << 6) + (h >> 2);
+    return h;
+  }
+};
+
+std::unordered_map<MapKey, CUtensorMap, MapKeyHash> g_maps;
+std::mutex g_maps_mutex;
+
+// Tensor map over a [rows, cols] byte matrix with row pitch `pitch` bytes; box = [box_rows, 128].
+int make_map(const void* ptr, int64_t rows, int64_t cols, int64_t pitch, int box_rows, CUtensorMap* out) {
+  MapKey key{ptr, rows, cols, pitch, box_rows};
+  {
+    std::lock_guard<std::mutex> lk(g_maps_mutex);
+    auto it = g_maps.find(key);
+    if (it != g_maps.end()) {
+      *out = it->second;
+      return MSAMP_OK;
+    }
+  }
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) {
+    msamp_set_error("cuTensorMapEncodeTiled is not available from the driver");
+    return MSAMP_ETMAP;
+  }
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)pitch};
+  cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    msamp_set_error("cuTensorMapEncodeTiled failed with %d (ptr=%p rows=%lld cols=%lld pitch=%lld)", (int)r, ptr,
+                    (long long)rows, (long long)cols, (long long)pitch);
+    return MSAMP_ETMAP;
+  }
+  std::lock_guard<std::mutex> lk(g_maps_mutex);
+  if (g_maps.size() > 8192) g_maps.clear();
+  g_maps[key] = *out;
+  return MSAMP_OK;
+}
+
+template <int BN, typename OutT>
+int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, int max_ctas, cudaStream_t stream) {
+  using C = Cfg<BN>;
+  static bool configured[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (!configured[dev & 63]) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_fp8_kernel<BN, OutT>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
+    if (e != cudaSuccess) {
+      msamp_set_error("cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+      return MSAMP_ELAUNCH;
+    }
+    configured[dev & 63] = true;
+  }
+  const int num_tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
+  int grid = msamp_sm_count();
+  if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
+  if (num_tiles < grid) grid = num_tiles;
+  gemm_fp8_kernel<BN, OutT><<<grid, kGemmThreads, C::SMEM_BYTES, stream>>>(ma, mb, p);
+  return msamp_check_launch("gemm_fp8_kernel");
+}
+
+}    // namespace
+
+// A: [M, K] fp8 bytes with row pitch lda (bytes), B: [N, K] with pitch ldb, D: [M, N] of out_dtype
+// with row pitch ldd (elements).  K, lda, ldb must be multiples of 16 and A, B 16-byte aligned
+// (TMA rules).  bias may be null; amax_out (nullable) must be zeroed by the caller and receives
+// max|D|.  max_ctas > 0 caps the number of persistent CTAs (to leave SMs to a concurrent kernel).
+MSAMP_API int msamp_gemm_fp8(const void* A, const void* B, void* D, int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldd,
+                             int a_fmt, int b_fmt, int out_dtype, const float* scale_inv_a, const float* scale_inv_b,
+                             const void* bias, int bias_dtype, int accumulate, float* amax_out, int max_ctas, void* stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  MSAMP_REQUIRE(M > 0 && N > 0 && K > 0, "msamp_gemm_fp8: empty problem M=%d N=%d K=%d", M, N, K);
+  MSAMP_REQUIRE(K % 16 == 0 && lda % 16 == 0 && ldb % 16 == 0, "msamp_gemm_fp8: K and the row pitches must be multiples of 16");
+  MSAMP_REQUIRE((reinterpret_cast<uintptr_t>(A) & 15) == 0 && (reinterpret_cast<uintptr_t>(B) & 15) == 0,
+                "msamp_gemm_fp8: operands must be 16-byte aligned");
+  MSAMP_REQUIRE(scale_inv_a && scale_inv_b && D, "msamp_gemm_fp8: null pointer");
+  const int bn = (N > 128 && (int64_t)((M + BM - 1) / BM) * ((N + 255) / 256) >= msamp_sm_count()) ? 256 : 128;
+  CUtensorMap ma, mb;
+  int rc = make_map(A, M, K, lda, BM, &ma);
+  if (rc) return rc;
+  rc = make_map(B, N, K, ldb, bn, &mb);
+  if (rc) return rc;
+  GemmParams p;
+  p.d = D; p.bias = bias; p.scale_inv_a = scale_inv_a; p.scale_inv_b = scale_inv_b; p.amax_out = amax_out;
+  p.status = msamp_device_status_ptr();
+  p.M = M; p.N = N; p.K = K; p.ldd = ldd; p.out_dtype = out_dtype; p.bias_dtype = bias_dtype; p.accumulate = accumulate;
+  p.a_fmt = a_fmt; p.b_fmt = b_fmt;
+  MSAMP_DISPATCH_HP(out_dtype, T, {
+    if (bn == 256) return launch<256, T>(ma, mb, p, max_ctas, stream);
+    return launch<128, T>(ma, mb, p, max_ctas, stream);
+  });
+  return MSAMP_OK;
+}
