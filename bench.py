@@ -1,0 +1,231 @@
+"""Headline benchmark: GPT training throughput (tokens/s) with MS-AMP O2 on N B200 GPUs of one node.
+
+    python bench.py --gpus 1 --steps 8 --warmup 3
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \
+        bench.py --gpus N --steps K --warmup W
+
+Prints one JSON line (rank 0).  ``value`` is the whole-job tokens/s over K device-timed steps (CUDA
+events, max over ranks) with the inputs already on the device; ``e2e`` repeats the measurement
+through the public API with every step's tokens copied from pinned host memory and its loss read
+back to the host.  Data are synthetic uniform token ids, weights are random-init N(0, 0.02).
+``--impl reference`` runs the unmodified reference from ``baseline/_ref`` if it can be imported.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+# tokens/s/GPU of the reference's published MS-AMP FP8 GPT runs (32x H100, seq 2048, micro-batch 4)
+PUBLISHED_PER_GPU = {'gpt-7b': 230.5 * 2048 / 32, 'gpt-13b': 121.5 * 2048 / 32}
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument('--gpus', type=int, default=1)
+    ap.add_argument('--steps', type=int, default=6)
+    ap.add_argument('--warmup', type=int, default=3)
+    ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
+    ap.add_argument('--model', default='gpt-7b')
+    ap.add_argument('--micro-batch', type=int, default=4)
+    ap.add_argument('--seq', type=int, default=2048)
+    ap.add_argument('--opt-level', default='O2')
+    ap.add_argument('--layers', type=int, default=0, help='override the layer count (the result is then labelled as a reduced config)')
+    ap.add_argument('--no-e2e', action='store_true')
+    return ap.parse_args()
+
+
+def reference_arm(args):
+    """Run the reference through its own public API, or say in one line why that is impossible here."""
+    ref = os.path.join(ROOT, 'baseline', '_ref')
+    reason = None
+    if not os.path.isdir(os.path.join(ref, 'msamp')):
+        reason = 'baseline/_ref is empty: the reference was not installed'
+    else:
+        code = 'import sys; sys.path.insert(0, %r); import msamp' % ref
+        res = subprocess.run([sys.executable, '-c', code], capture_output=True, text=True, cwd='/tmp')
+        if res.returncode != 0:
+            last = (res.stderr.strip().splitlines() or ['import failed'])[-1]
+            reason = ('reference installed with --no-deps but not importable: %s (it needs deepspeed, transformer_engine v1.1 and '
+                      'the MSCCL shim, none of which exist on this image or have an sm_100 build)' % last)
+        else:
+            reason = 'reference imports, but ships no GPT model or benchmark script to drive'
+    if int(os.environ.get('RANK', '0')) == 0:
+        print(json.dumps({'impl': 'reference', 'unavailable': reason}))
+    return 0
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    FIELDS = ('index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,'
+              'clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap')
+
+    def __init__(self, index):
+        self.index = index
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ['nvidia-smi', '-i', str(self.index), f'--query-gpu={self.FIELDS}', '--format=csv,noheader,nounits', '-lms', '200'],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True
+            )
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {'sm_mhz': None, 'sm_max_mhz': None, 'reasons': ['nvidia-smi unavailable']}
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except Exception:
+            self.proc.kill()
+            out = ''
+        sm, mx, reasons = [], [], set()
+        names = ['hw_slowdown', 'hw_thermal_slowdown', 'sw_thermal_slowdown', 'sw_power_cap']
+        for line in out.strip().splitlines():
+            parts = [p.strip() for p in line.split(',')]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1]))
+                mx.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[5:9]):
+                if val.lower().startswith('active'):
+                    reasons.add(name)
+        return {
+            'sm_mhz': statistics.median(sm) if sm else None,
+            'sm_max_mhz': max(mx) if mx else None,
+            'samples': len(sm),
+            'reasons': sorted(reasons)
+        }
+
+
+def main():
+    args = parse()
+    if args.impl == 'reference':
+        return reference_arm(args)
+
+    import torch
+    import torch.distributed as dist
+    import msamp
+    from msamp.models import GPT, gpt_config
+    from msamp.ops import native
+    from msamp.parallel import DataParallelTrainer
+
+    world = int(os.environ.get('WORLD_SIZE', '1'))
+    rank = int(os.environ.get('RANK', '0'))
+    local = int(os.environ.get('LOCAL_RANK', '0'))
+    torch.cuda.set_device(local)
+    dev = torch.device('cuda', local)
+    if world > 1:
+        os.environ.setdefault('MASTER_ADDR', '127.0.0.1')
+        dist.init_process_group('nccl', device_id=dev)
+    if world != args.gpus and rank == 0:
+        print(f'warning: --gpus {args.gpus} but WORLD_SIZE={world}', file=sys.stderr)
+
+    over = {'max_seq': args.seq}
+    if args.layers:
+        over['n_layer'] = args.layers
+    cfg = gpt_config(args.model, **over)
+    torch.manual_seed(1234)
+    model = GPT(cfg, device=dev)
+    opt = torch.optim.AdamW(model.parameters(), lr=1e-4, betas=(0.9, 0.95), weight_decay=0.1)
+    model, opt = msamp.initialize(model, opt, args.opt_level)
+    trainer = DataParallelTrainer(model, opt, zero_stage=2 if world > 1 else 0)
+
+    B, S = args.micro_batch, args.seq
+    gen = torch.Generator().manual_seed(rank)
+    host_tok = [torch.randint(0, cfg.vocab_size, (B, S), generator=gen).pin_memory() for _ in range(4)]
+    host_lab = [torch.randint(0, cfg.vocab_size, (B, S), generator=gen).pin_memory() for _ in range(4)]
+    dev_tok = [t.to(dev) for t in host_tok]
+    dev_lab = [t.to(dev) for t in host_lab]
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(step_fn, steps):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        calls0 = native.launch_count
+        e0.record()
+        for i in range(steps):
+            step_fn(i)
+        e1.record()
+        barrier()
+        ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return ms.item(), native.launch_count - calls0
+
+    def step_device(i):
+        trainer.step(dev_tok[i % 4], dev_lab[i % 4])
+
+    last_loss = [0.0]
+
+    def step_e2e(i):
+        tok = host_tok[i % 4].to(dev, non_blocking=True)
+        lab = host_lab[i % 4].to(dev, non_blocking=True)
+        loss = trainer.step(tok, lab)
+        last_loss[0] = loss.item()    # device -> host read of the step's result
+
+    for i in range(args.warmup):
+        step_device(i)
+    sampler = ClockSampler(torch.cuda.current_device() if 'CUDA_VISIBLE_DEVICES' not in os.environ else local)
+    sampler.start()
+    ms, launches = timed(step_device, args.steps)
+    clocks = sampler.stop()
+    tokens = B * S * world * args.steps
+    value = tokens / (ms / 1e3)
+
+    e2e = None
+    if not args.no_e2e:
+        step_e2e(0)
+        ms2, _ = timed(step_e2e, args.steps)
+        e2e = {
+            'value': tokens / (ms2 / 1e3), 'unit': 'tokens/s', 'h2d_bytes_per_step': 2 * B * S * 8, 'd2h_bytes_per_step': 4,
+            'ms_per_step': ms2 / args.steps, 'last_loss': last_loss[0]
+        }
+    peak_mem = torch.cuda.max_memory_allocated() / 2**30
+    status = native.device_status()
+    if rank == 0:
+        base = PUBLISHED_PER_GPU.get(args.model)
+        reduced = bool(args.layers)
+        flops = cfg.flops_per_token(S) * value
+        out = {
+            'metric': f'tokens/sec {args.model} MS-AMP {args.opt_level} training' + (' (REDUCED layer count, not the headline config)' if reduced else ''),
+            'value': value, 'unit': 'tokens/s', 'n_gpus': world, 'steps': args.steps, 'warmup': args.warmup,
+            'ms_per_step': ms / args.steps, 'higher_is_better': True, 'scaling': 'weak',
+            'vs_baseline': (value / (base * world)) if (base and not reduced) else None,
+            'dtype': 'fp8 GEMM (e4m3/e5m2) with bf16 activations', 'data': 'synthetic uniform token ids, random-init weights N(0,0.02)',
+            'impl': 'ours',
+            'config': {
+                'model': args.model, 'layers': cfg.n_layer, 'hidden': cfg.hidden, 'heads': cfg.n_head, 'ffn': cfg.ffn_hidden,
+                'vocab': cfg.vocab_size, 'global_batch': B * world, 'micro_batch': B, 'seq_len': S,
+                'parallelism': f'dp{world}' + ('+zero2' if world > 1 else ''), 'opt_level': args.opt_level,
+                'l2': 'per-step working set (GBs of weights and activations) is far larger than the 126 MB L2, no explicit flush',
+            },
+            'model_tflops_per_gpu': flops / world / 1e12,
+            'peak_mem_gib_per_gpu': peak_mem,
+            'clocks': clocks, 'e2e': e2e, 'gpu_launches': launches, 'device_status': status,
+        }
+        print(json.dumps(out))
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == '__main__':
+    t0 = time.time()
+    sys.exit(main())

@@ -56,13 +56,12 @@ class TypeCast:
         input = input.contiguous()
         record = TypeCast._prepare_scale(input, meta, sync)
         amax_out = meta.amax[0] if record else None
+        sinv_out = meta.scale_inv if record else None
         if fuse_transpose:
             x2d = input.reshape(-1, input.shape[-1])
-            out, out_t = _k.cast_transpose_fp8(x2d, meta.qtype, meta.scale, amax_out)
+            out, out_t = _k.cast_transpose_fp8(x2d, meta.qtype, meta.scale, amax_out, scale_inv_out=sinv_out)
         else:
-            out = _k.cast_to_fp8(input, meta.qtype, meta.scale, amax_out)
-        if record:
-            torch.reciprocal(meta.scale, out=meta.scale_inv)
+            out = _k.cast_to_fp8(input, meta.qtype, meta.scale, amax_out, scale_inv_out=sinv_out)
         return (out, out_t) if fuse_transpose else out
 
     @staticmethod
@@ -78,7 +77,7 @@ class TypeCast:
             meta.reset_scaling_factor()
         torch.reciprocal(meta.scale, out=meta.scale_inv)
         dtype = Dtypes.get_dtype_from_qtype(meta.qtype)
-        return (input * meta.scale).to(dtype)
+        return (input.float() * meta.scale).to(dtype)    # fp32 math: a 0-d scale would not promote a half tensor
 
     @staticmethod
     def cast_from_fp8(input, meta, otype):
@@ -90,7 +89,7 @@ class TypeCast:
     @staticmethod
     def cast_from_fp16(input, meta, otype):
         """Undo a scaled 16/32-bit cast: ``(x * scale_inv).to(dtype)``."""
-        return (input * meta.scale_inv).to(Dtypes.get_dtype_from_qtype(otype))
+        return (input.float() * meta.scale_inv).to(Dtypes.get_dtype_from_qtype(otype))
 
     cast_from_fp32 = cast_from_fp16
 

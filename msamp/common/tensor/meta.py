@@ -14,7 +14,8 @@ from msamp.common.dtype import Dtypes, Floating
 
 
 def _default_device():
-    return torch.device('cuda', torch.cuda.current_device()) if torch.cuda.is_available() else torch.device('cpu')
+    from msamp.common.utils.device import default_device
+    return default_device()
 
 
 class ScalingMeta:

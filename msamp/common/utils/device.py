@@ -9,6 +9,21 @@ from enum import Enum
 import torch
 
 
+def default_device():
+    """Device on which converted modules and new metas are placed.
+
+    The current CUDA device when one is visible, otherwise the CPU.  ``MSAMP_DEVICE=cpu`` pins the
+    CPU emulation even on a GPU machine (used by the gloo multi-process tests).
+    """
+    import os
+    forced = os.environ.get('MSAMP_DEVICE')
+    if forced:
+        return torch.device(forced)
+    if torch.cuda.is_available():
+        return torch.device('cuda', torch.cuda.current_device())
+    return torch.device('cpu')
+
+
 class GPUType(Enum):
     """Vendor of the visible accelerator."""
     NVIDIA = 1

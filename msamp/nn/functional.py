@@ -1,0 +1,231 @@
+"""FP8 linear: autograd function and the ``torch.nn.functional.linear`` override.
+
+Data flow of one linear (shapes: x ``[T,K]``, W ``[N,K]``, y ``[T,N]``), all GEMMs in the one
+K-major layout of the tcgen05 kernel, no FP8 transposes materialised on the way:
+
+  forward   x  --cast+transpose(e4m3, meta 'input')-->  x8 [T,K], x8ᵀ [K,T] (x8ᵀ is what backward keeps)
+            W  --cast+transpose(e4m3), cached until the weight changes-->  W8 [N,K], W8ᵀ [K,N]
+            y  = x8 · W8ᵀ  (+ bias in the epilogue)
+  backward  dy --cast+transpose(e5m2, meta 'ograd')-->  dy8 [T,N], dy8ᵀ [N,T]
+            dx = dy8 · (W8ᵀ)ᵀ
+            dW = dy8ᵀ · (x8ᵀ)ᵀ  with max|dW| reduced in the epilogue
+            dW --cast(e4m3, meta 'wgrad', scale from that amax [MAX-reduced over the DP group])--> ScalingTensor
+            delivered through ``weight.backward_grad_update`` (not through autograd)
+
+Semantics follow the reference's _FP8GemmFunction and F.linear wrapper (msamp/nn/functional.py:16-194):
+formats, window sizes, gradient accumulation in high precision, FP8-DDP and FSDP special cases.
+"""
+import torch
+import torch.distributed as dist
+import torch.nn.functional as F
+
+from msamp.common.dtype import Dtypes, Floating
+from msamp.common.tensor import ScalingMeta, ScalingTensor, TypeCast
+from msamp.common.utils.dist import DistUtil
+from msamp.nn.state import model_state
+from msamp.nn.parameter import ScalingParameter
+from msamp.ops import cast as _k
+from msamp.ops import gemm as _g
+
+E4M3, E5M2 = Dtypes.kfloat8_e4m3, Dtypes.kfloat8_e5m2
+
+
+def _bump_version(t):
+    try:
+        torch.autograd.graph.increment_version(t)
+    except Exception:    # pragma: no cover - very old torch
+        pass
+
+
+def weight_fp8_pair(weight):
+    """FP8 copies ``(W8 [N,K], W8ᵀ [K,N], scale_inv)`` of a weight, cached on the parameter.
+
+    The cache key is the identity and in-place version of ``weight.value`` and of its ``scale_inv``,
+    so any optimizer step, ``copy_``, ``cast_`` or checkpoint load invalidates it.
+    """
+    val = weight.value
+    key = (val.data_ptr(), val._version, weight.meta.scale_inv._version, weight.meta.scale_inv.data_ptr())
+    cache = getattr(weight, '_fp8_cache', None)
+    if cache is not None and cache[0] == key:
+        return cache[1], cache[2], cache[3]
+    w2d = val.reshape(-1, val.shape[-1])
+    if Dtypes.is_fp8_qtype(weight.meta.qtype):
+        if weight.meta.qtype != E4M3:
+            raise TypeError('FP8 weights must be e4m3')
+        w8 = w2d
+        w8t = _k.transpose_fp8(w2d)
+        sinv = weight.meta.scale_inv
+    else:
+        # Scaled 16-bit weight: value == w * s_w. Quantise with the scale implied by the stored
+        # amax of w, expressed relative to the stored payload.
+        meta = weight.meta
+        new_scale = ScalingMeta.compute_scaling_factor(meta.amax[0], torch.ones_like(meta.scale), Floating.qfp_max[E4M3], 0)
+        factor = new_scale * meta.scale_inv
+        w8, w8t = _k.cast_transpose_fp8(w2d, E4M3, factor)
+        sinv = torch.reciprocal(new_scale)
+    weight._fp8_cache = (key, w8, w8t, sinv)
+    return w8, w8t, sinv
+
+
+class _FP8GemmFunction(torch.autograd.Function):
+    """y = x · Wᵀ (+ bias) with FP8 operands; weight gradient delivered out of band."""
+    @staticmethod
+    def forward(ctx, input, weight, metas, dtype_holder, bias=None):
+        fsdp_weight = isinstance(weight, torch.Tensor) and hasattr(weight, '_meta')
+        if fsdp_weight:
+            # Flat fp32 FSDP parameter carrying e4m3 bytes (see msamp.fsdp): reinterpret in place.
+            raw = weight.view(torch.uint8).reshape(-1)
+            if weight._padded:
+                raw = raw[:raw.numel() - weight._padded]
+            flat_param = weight
+            weight = ScalingParameter(ScalingTensor(raw.view(weight._original_shape), weight._meta))
+            weight._flat_param = flat_param
+        ctx.return_wgrad = fsdp_weight
+        model_state.check_metas_in_flat(metas)
+        out_dtype = dtype_holder.dtype
+        need_wgrad = weight.requires_grad and ctx.needs_input_grad[3]    # the holder tells whether grad mode is on
+        in_meta = metas['input']
+
+        x = input.contiguous()
+        record = TypeCast._prepare_scale(x, in_meta, sync=False)
+        amax_out = in_meta.amax[0] if record else None
+        sinv_out = in_meta.scale_inv if record else None
+        if need_wgrad:
+            x8, x8t = _k.cast_transpose_fp8(x, E4M3, in_meta.scale, amax_out, scale_inv_out=sinv_out)
+        else:
+            x8, x8t = _k.cast_to_fp8(x, E4M3, in_meta.scale, amax_out, scale_inv_out=sinv_out), None
+        x_sinv = in_meta.scale_inv.clone()    # the meta may be reused before backward runs
+
+        w8, w8t, w_sinv = weight_fp8_pair(weight)
+        out = _g.gemm_fp8(x8, E4M3, x_sinv, w8, E4M3, w_sinv, out_dtype, bias=bias)
+
+        ctx.metas = metas
+        ctx.weight = weight
+        ctx.x8t, ctx.x_sinv = x8t, x_sinv
+        ctx.w8t, ctx.w_sinv = w8t, w_sinv
+        ctx.out_dtype = out_dtype
+        ctx.input_requires_grad = input.requires_grad
+        ctx.has_bias = bias is not None
+        ctx.bias_dtype = bias.dtype if bias is not None else None
+        return out
+
+    @staticmethod
+    def backward(ctx, output_grad):
+        dy = output_grad.contiguous()
+        metas = ctx.metas
+        og_meta, wg_meta = metas['ograd'], metas['wgrad']
+        weight = ctx.weight
+        need_wgrad = weight.requires_grad and ctx.x8t is not None
+
+        record = TypeCast._prepare_scale(dy, og_meta, sync=False)
+        amax_out = og_meta.amax[0] if record else None
+        sinv_out = og_meta.scale_inv if record else None
+        if need_wgrad:
+            dy8, dy8t = _k.cast_transpose_fp8(dy, E5M2, og_meta.scale, amax_out, scale_inv_out=sinv_out)
+        else:
+            dy8, dy8t = _k.cast_to_fp8(dy, E5M2, og_meta.scale, amax_out, scale_inv_out=sinv_out), None
+        dy_sinv = og_meta.scale_inv
+
+        dx = None
+        if ctx.input_requires_grad:
+            dx = _g.gemm_fp8(dy8, E5M2, dy_sinv, ctx.w8t, E4M3, ctx.w_sinv, ctx.out_dtype)
+        dbias = None
+        if ctx.has_bias:
+            dbias = dy.sum(0, dtype=torch.float32).to(ctx.bias_dtype)
+
+        wgrad_ret = None
+        if need_wgrad:
+            amax0 = wg_meta.amax[0]
+            if weight.grad is None:
+                wgrad = _g.gemm_fp8(dy8t, E5M2, dy_sinv, ctx.x8t, E4M3, ctx.x_sinv, ctx.out_dtype, amax_out=amax0)
+            else:
+                old = weight.grad.to(ctx.out_dtype) if isinstance(weight.grad, ScalingTensor) else weight.grad.to(ctx.out_dtype)
+                wgrad = _g.gemm_fp8(
+                    dy8t, E5M2, dy_sinv, ctx.x8t, E4M3, ctx.x_sinv, ctx.out_dtype, accumulate=True, out=old, amax_out=amax0
+                )
+            wgrad = wgrad.view(weight.shape)
+            if model_state.use_fp8_ddp and not ctx.return_wgrad:
+                # The FP8 DDP reducer quantises whole buckets with a cross-rank scale.
+                wgrad.meta = wg_meta
+            else:
+                wgrad = _quantize_wgrad(wgrad, wg_meta)
+            if ctx.return_wgrad:
+                flat = wgrad.value.reshape(-1)
+                pad = weight._flat_param._padded
+                if pad:
+                    flat = F.pad(flat, (0, pad))
+                wgrad_ret = flat.view(torch.float32).view_as(weight._flat_param)
+                wgrad_ret.meta = wg_meta
+            else:
+                weight.backward_grad_update(wgrad)
+        ctx.x8t = ctx.w8t = None
+        return dx, wgrad_ret, None, None, dbias
+
+
+def _quantize_wgrad(wgrad, meta):
+    """High-precision wgrad whose amax is already in ``meta.amax[0]`` → e4m3 ScalingTensor (in-time scale, DP-synced)."""
+    amax0 = meta.amax[0]
+    if DistUtil.get_world_size(meta.group) > 1:
+        dist.all_reduce(amax0, op=dist.ReduceOp.MAX, group=meta.group)
+    value = _k.cast_to_fp8(wgrad, E4M3, meta.scale, scale_inv_out=meta.scale_inv, amax_in=amax0)
+    return ScalingTensor(value, meta)
+
+
+class FunctionalOverider:
+    """Replaces ``F.linear`` by a version that routes ScalingTensor weights to the FP8 path."""
+    EMPTY_GRAD_TENSOR = torch.nn.Parameter(torch.tensor([]))
+    _holders = {}
+    _installed = False
+
+    @classmethod
+    def override(cls):
+        if cls._installed:
+            return
+        cls._installed = True
+        F.linear = cls._get_wrapper_for_linear(F.linear)
+
+    @classmethod
+    def _holder(cls, dtype, device):
+        """A zero-size leaf that requires grad, so backward runs even when the input needs no gradient."""
+        key = (dtype, device)
+        h = cls._holders.get(key)
+        if h is None:
+            h = torch.nn.Parameter(torch.empty(0, dtype=dtype, device=device))
+            cls._holders[key] = h
+        return h
+
+    @classmethod
+    def _get_wrapper_for_linear(cls, old_fn):
+        def new_fn(input, weight, bias=None):
+            """``linear(input, weight, bias=None)``; FP8 GEMM when ``weight`` is a ScalingTensor (or an FSDP FP8 flat view)."""
+            if not isinstance(input, torch.Tensor):
+                raise TypeError(f'input should be a torch.Tensor. current type: {type(input)}')
+            if not isinstance(weight, (torch.Tensor, ScalingTensor)):
+                raise TypeError(f'weight should be a torch.Tensor or ScalingTensor. current type: {type(weight)}')
+            if bias is not None and not isinstance(bias, torch.Tensor):
+                raise TypeError(f'bias should be a torch.Tensor. current type: {type(bias)}')
+            if isinstance(weight, torch.Tensor) and not hasattr(weight, '_meta'):
+                return old_fn(input, weight, bias=bias)
+            if not hasattr(weight, '_scaling_metas'):
+                raise ValueError('weight (ScalingTensor) should have _scaling_metas attribute.')
+            model_state.ready_to_scale_tensor = True
+            shape = input.shape
+            if len(shape) != 2:
+                input = input.reshape(-1, shape[-1])
+            if torch.is_autocast_enabled(input.device.type):
+                out_dtype = torch.get_autocast_dtype(input.device.type)
+                input = input.to(out_dtype)
+            else:
+                out_dtype = input.dtype
+            if out_dtype not in (torch.float32, torch.float16, torch.bfloat16):
+                raise TypeError(f'unsupported activation dtype {out_dtype}')
+            out = _FP8GemmFunction.apply(input, weight, weight._scaling_metas, cls._holder(out_dtype, input.device), bias)
+            if len(shape) != 2:
+                out = out.view(shape[:-1] + (-1, ))
+            return out
+
+        new_fn.__wrapped__ = old_fn
+        return new_fn
+
+
+FunctionalOverider.override()

@@ -87,24 +87,34 @@ def _emulate_to_fp8(x, scale, qtype):
     return y.to(_F8[qtype]).view(torch.uint8)
 
 
-def cast_to_fp8(x, qtype, scale, amax_out=None):
-    """Quantise ``x`` (fp32/fp16/bf16) to FP8 bytes with the given scale; optionally record ``max|x|``."""
+def cast_to_fp8(x, qtype, scale, amax_out=None, scale_inv_out=None, amax_in=None, prescale=1.0):
+    """Quantise ``x`` (fp32/fp16/bf16) to FP8 bytes with the given scale.
+
+    Optionally records ``max|x|`` in ``amax_out`` and ``1/scale`` in ``scale_inv_out`` in the same pass.
+    With ``amax_in`` (a 0-d tensor already holding ``max|x|``, e.g. from a GEMM epilogue) the scale is
+    first recomputed from it by the power-of-two rule, times ``prescale``, and written to ``scale``.
+    """
     if x.is_cuda:
         x = x.contiguous()
         out = torch.empty(x.shape, dtype=torch.uint8, device=x.device)
         native.check(
             native.lib().msamp_cast_to_fp8(
                 native.ptr(x), native.i64(x.numel()), native.dt(x.dtype), native.ptr(out), native.fmt(qtype), native.ptr(scale),
-                native.ptr(amax_out), native.stream()
+                native.ptr(amax_out), native.ptr(scale_inv_out), native.ptr(amax_in), ctypes.c_float(prescale), native.stream()
             ), 'cast_to_fp8'
         )
         return out
+    if amax_in is not None:
+        scale.copy_(compute_scale(amax_in, scale, Floating.qfp_max[qtype]) * torch.where(
+            (amax_in > 0) & torch.isfinite(amax_in), prescale, 1.0))
     if amax_out is not None:
         amax(x, out=amax_out)
+    if scale_inv_out is not None:
+        torch.reciprocal(scale, out=scale_inv_out)
     return _emulate_to_fp8(x, scale, qtype)
 
 
-def cast_transpose_fp8(x, qtype, scale, amax_out=None, need_rowmajor=True):
+def cast_transpose_fp8(x, qtype, scale, amax_out=None, need_rowmajor=True, scale_inv_out=None):
     """Quantise a 2-D tensor and also produce its transpose. Returns ``(out or None, out_t)``."""
     assert x.dim() == 2
     rows, cols = x.shape
@@ -115,12 +125,14 @@ def cast_transpose_fp8(x, qtype, scale, amax_out=None, need_rowmajor=True):
         native.check(
             native.lib().msamp_cast_transpose_fp8(
                 native.ptr(x), rows, cols, native.dt(x.dtype), native.ptr(out), native.ptr(out_t), native.fmt(qtype),
-                native.ptr(scale), native.ptr(amax_out), native.stream()
+                native.ptr(scale), native.ptr(amax_out), native.ptr(scale_inv_out), native.stream()
             ), 'cast_transpose_fp8'
         )
         return out, out_t
     if amax_out is not None:
         amax(x, out=amax_out)
+    if scale_inv_out is not None:
+        torch.reciprocal(scale, out=scale_inv_out)
     out = _emulate_to_fp8(x, scale, qtype)
     return (out if need_rowmajor else None), out.t().contiguous()
 
@@ -169,19 +181,21 @@ def update_scales(amax_flat, scale, scale_inv, qtype, margin=0, amax_stride=1):
     scale_inv.copy_(torch.reciprocal(scale))
 
 
-def roll_windows(amaxs, scales, counters, qtype, margin=0):
+def roll_windows(amaxs, scales, qtype, margin=0, bad_out=None):
     """Delayed-scaling bookkeeping for all metas of one kind in a single launch.
 
-    ``amaxs`` is ``[n, window]`` fp32, ``scales`` ``[n]`` fp32, ``counters`` ``[n]`` int32 on the same device.
-    Behaviour follows LBOptimizer._update_scaling_factors of the reference (msamp/optim/optimizer.py:61-108).
+    ``amaxs`` is ``[n, window]`` fp32 and ``scales`` ``[n]`` fp32 on one device: a non-finite newest
+    amax is dropped, the scale is recomputed from the window maximum, and the window moves one slot.
+    ``bad_out`` (optional ``[n]`` int32 on the same device) is set to 1 where a non-finite amax was
+    seen.  Behaviour follows LBOptimizer._update_scaling_factors of the reference
+    (msamp/optim/optimizer.py:61-108) except that step counters stay on the host.
     """
     fp_max = Floating.qfp_max[qtype]
     n, window = amaxs.shape
     if amaxs.is_cuda:
-        assert counters.is_cuda and counters.dtype == torch.int32
         native.check(
             native.lib().msamp_roll_windows(
-                native.ptr(amaxs), native.ptr(scales), native.ptr(counters), n, window, ctypes.c_float(fp_max), int(margin),
+                native.ptr(amaxs), native.ptr(scales), native.ptr(bad_out), n, window, ctypes.c_float(fp_max), int(margin),
                 native.stream()
             ), 'roll_windows'
         )
@@ -191,5 +205,5 @@ def roll_windows(amaxs, scales, counters, qtype, margin=0):
     scales.copy_(compute_scale(amaxs.max(1).values, scales, fp_max, margin))
     amaxs.copy_(amaxs.roll(1, dims=1))
     amaxs[:, 0] = 0
-    counters += 1
-    counters[bad] = 0
+    if bad_out is not None:
+        bad_out.copy_(bad.to(torch.int32))

@@ -57,9 +57,20 @@ __global__ void __launch_bounds__(kThreads) amax_kernel(const T* __restrict__ x,
 // ---- high precision -> fp8 ------------------------------------------------------------------------
 template <typename T, int FMT, bool VEC>
 __global__ void __launch_bounds__(kThreads) cast_to_fp8_kernel(const T* __restrict__ x, uint8_t* __restrict__ out, int64_t n,
-                                                                const float* __restrict__ scale_ptr, float* amax) {
+                                                                float* scale_ptr, float* amax, float* scale_inv_out,
+                                                                const float* amax_in, float fp_max, float prescale) {
   __shared__ float red[32];
-  const float scale = *scale_ptr;
+  float scale = *scale_ptr;
+  if (amax_in != nullptr) {
+    // In-time scaling from an amax that an earlier kernel produced (e.g. a GEMM epilogue): every
+    // thread derives the same scale; one thread publishes it. When amax is unusable the old
+    // scale is kept, so the concurrent read of *scale_ptr by other blocks sees a value that the
+    // write does not change.
+    float a = *amax_in;
+    if ((a > 0.0f) && !isinf(a) && !isnan(a)) scale = msamp_compute_scale(a, scale, fp_max, 0) * prescale;
+    if (blockIdx.x == 0 && threadIdx.x == 0) *scale_ptr = scale;
+  }
+  if (scale_inv_out != nullptr && blockIdx.x == 0 && threadIdx.x == 0) *scale_inv_out = __frcp_rn(scale);
   float m = 0.0f;
   int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   int64_t stride = (int64_t)gridDim.x * blockDim.x;
@@ -140,10 +151,11 @@ template <typename T, int FMT, bool WRITE_ROWMAJOR>
 __global__ void __launch_bounds__(kThreads) cast_transpose_kernel(const T* __restrict__ x, uint8_t* __restrict__ out,
                                                                    uint8_t* __restrict__ out_t, int rows, int cols,
                                                                    const float* __restrict__ scale_ptr, float* amax,
-                                                                   bool aligned) {
+                                                                   float* scale_inv_out, bool aligned) {
   __shared__ __align__(16) uint8_t tile_t[kTile * kTStride];    // [c][r]
   __shared__ float red[32];
   const float scale = *scale_ptr;
+  if (scale_inv_out != nullptr && blockIdx.x == 0 && threadIdx.x == 0) *scale_inv_out = __frcp_rn(scale);
   const int tiles_c = (cols + kTile - 1) / kTile;
   const int tiles_r = (rows + kTile - 1) / kTile;
   const int64_t ntiles = (int64_t)tiles_c * tiles_r;
@@ -266,10 +278,11 @@ __global__ void update_scales_kernel(const float* __restrict__ amax, int64_t ama
 
 // Delayed-scaling bookkeeping for n metas that share flat buffers (one launch for all layers),
 // amax is [n, window]: a non-finite newest entry is dropped, the scale is recomputed from the
-// window maximum, the window moves by one slot with slot 0 cleared, and the step counter advances
-// (or restarts after a non-finite entry).  scale_inv is left alone: it belongs to the tensors that
-// were quantised with the old scale and is refreshed by the next cast.
-__global__ void roll_windows_kernel(float* amax, float* scale, int* counters, int n, int window, float fp_max, int margin) {
+// window maximum and the window moves by one slot with slot 0 cleared.  `bad[i]` (optional) is set
+// to 1 when meta i saw a non-finite entry, so that the host can restart its warm-up counter later
+// without synchronising now.  scale_inv is left alone: it belongs to the tensors that were
+// quantised with the old scale and is refreshed by the next cast.
+__global__ void roll_windows_kernel(float* amax, float* scale, int* bad, int n, int window, float fp_max, int margin) {
   int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
   float* a = amax + (int64_t)i * window;
@@ -280,7 +293,7 @@ __global__ void roll_windows_kernel(float* amax, float* scale, int* counters, in
   scale[i] = msamp_compute_scale(mx, scale[i], fp_max, margin);
   for (int j = window - 1; j > 0; --j) a[j] = a[j - 1];
   a[0] = 0.0f;
-  counters[i] = finite ? counters[i] + 1 : 0;
+  if (bad != nullptr) bad[i] = finite ? 0 : 1;
 }
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
@@ -307,9 +320,11 @@ MSAMP_API int msamp_amax(const void* x, int64_t n, int dtype, float* amax, float
   return msamp_check_launch("msamp_amax");
 }
 
-// out = saturate_fp8(x * scale). With `amax` non-null it receives max|x| (it is cleared first).
-MSAMP_API int msamp_cast_to_fp8(const void* x, int64_t n, int dtype, void* out, int fmt, const float* scale, float* amax,
-                                void* stream_) {
+// out = saturate_fp8(x * scale). With `amax` non-null it receives max|x| (it is cleared first);
+// with `scale_inv_out` non-null it receives 1 / scale. With `amax_in` non-null the scale is first
+// recomputed as rule(*amax_in) * prescale and stored to *scale (amax and amax_in must differ).
+MSAMP_API int msamp_cast_to_fp8(const void* x, int64_t n, int dtype, void* out, int fmt, float* scale, float* amax,
+                                float* scale_inv_out, const float* amax_in, float prescale, void* stream_) {
   cudaStream_t stream = (cudaStream_t)stream_;
   MSAMP_REQUIRE(n >= 0 && scale != nullptr, "msamp_cast_to_fp8: bad arguments");
   if (amax) cudaMemsetAsync(amax, 0, sizeof(float), stream);
@@ -319,9 +334,9 @@ MSAMP_API int msamp_cast_to_fp8(const void* x, int64_t n, int dtype, void* out, 
   MSAMP_DISPATCH_HP(dtype, T, {
     MSAMP_DISPATCH_FP8(fmt, F, {
       if (vec)
-        cast_to_fp8_kernel<T, F, true><<<grid, kThreads, 0, stream>>>((const T*)x, (uint8_t*)out, n, scale, amax);
+        cast_to_fp8_kernel<T, F, true><<<grid, kThreads, 0, stream>>>((const T*)x, (uint8_t*)out, n, scale, amax, scale_inv_out, amax_in, fp8_max(F), prescale);
       else
-        cast_to_fp8_kernel<T, F, false><<<grid, kThreads, 0, stream>>>((const T*)x, (uint8_t*)out, n, scale, amax);
+        cast_to_fp8_kernel<T, F, false><<<grid, kThreads, 0, stream>>>((const T*)x, (uint8_t*)out, n, scale, amax, scale_inv_out, amax_in, fp8_max(F), prescale);
     });
   });
   return msamp_check_launch("msamp_cast_to_fp8");
@@ -347,7 +362,7 @@ MSAMP_API int msamp_cast_from_fp8(const void* in, int64_t n, int fmt, const floa
 
 // x is [rows, cols] row-major. out (may be null) is the row-major FP8 copy, out_t the [cols, rows] one.
 MSAMP_API int msamp_cast_transpose_fp8(const void* x, int rows, int cols, int dtype, void* out, void* out_t, int fmt,
-                                       const float* scale, float* amax, void* stream_) {
+                                       const float* scale, float* amax, float* scale_inv_out, void* stream_) {
   cudaStream_t stream = (cudaStream_t)stream_;
   MSAMP_REQUIRE(rows >= 0 && cols >= 0 && out_t != nullptr && scale != nullptr, "msamp_cast_transpose_fp8: bad arguments");
   if (amax) cudaMemsetAsync(amax, 0, sizeof(float), stream);
@@ -359,9 +374,9 @@ MSAMP_API int msamp_cast_transpose_fp8(const void* x, int rows, int cols, int dt
   MSAMP_DISPATCH_HP(dtype, T, {
     MSAMP_DISPATCH_FP8(fmt, F, {
       if (out)
-        cast_transpose_kernel<T, F, true><<<grid, kThreads, 0, stream>>>((const T*)x, (uint8_t*)out, (uint8_t*)out_t, rows, cols, scale, amax, aligned);
+        cast_transpose_kernel<T, F, true><<<grid, kThreads, 0, stream>>>((const T*)x, (uint8_t*)out, (uint8_t*)out_t, rows, cols, scale, amax, scale_inv_out, aligned);
       else
-        cast_transpose_kernel<T, F, false><<<grid, kThreads, 0, stream>>>((const T*)x, nullptr, (uint8_t*)out_t, rows, cols, scale, amax, aligned);
+        cast_transpose_kernel<T, F, false><<<grid, kThreads, 0, stream>>>((const T*)x, nullptr, (uint8_t*)out_t, rows, cols, scale, amax, scale_inv_out, aligned);
     });
   });
   return msamp_check_launch("msamp_cast_transpose_fp8");
@@ -388,10 +403,10 @@ MSAMP_API int msamp_update_scales(const float* amax, int64_t amax_stride, float*
   return msamp_check_launch("msamp_update_scales");
 }
 
-MSAMP_API int msamp_roll_windows(float* amax, float* scale, int* counters, int n, int window, float fp_max, int margin,
+MSAMP_API int msamp_roll_windows(float* amax, float* scale, int* bad, int n, int window, float fp_max, int margin,
                                  void* stream_) {
   cudaStream_t stream = (cudaStream_t)stream_;
   if (n <= 0) return MSAMP_OK;
-  roll_windows_kernel<<<(n + 127) / 128, 128, 0, stream>>>(amax, scale, counters, n, window, fp_max, margin);
+  roll_windows_kernel<<<(n + 127) / 128, 128, 0, stream>>>(amax, scale, bad, n, window, fp_max, margin);
   return msamp_check_launch("msamp_roll_windows");
 }

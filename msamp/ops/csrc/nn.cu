@@ -1,0 +1,394 @@
+// Non-GEMM kernels of the transformer block: LayerNorm forward/backward, GeLU forward/backward
+// (tanh form), and fused softmax cross-entropy (loss + in-place logit gradient).  All are
+// HBM-bandwidth bound: one pass over the data with 16-byte accesses, statistics in fp32.
+#include "common.cuh"
+
+namespace {
+
+// ------------------------------------------------------------------------------------------------
+// LayerNorm.  One CTA per row; the row is held in registers between the statistics and the
+// normalisation (up to LN_VPT 16-byte vectors per thread), so x is read once.
+// ------------------------------------------------------------------------------------------------
+constexpr int LN_THREADS = 256;
+constexpr int LN_VPT = 4;    // vectors per thread -> rows up to 256 * 4 * 8 = 8192 elements of 16-bit data
+
+template <typename T>
+__device__ __forceinline__ float ld_param(const void* p, int i, int dtype) {
+  if (dtype == DT_F32) return reinterpret_cast<const float*>(p)[i];
+  if (dtype == DT_BF16) return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p)[i]);
+  return __half2float(reinterpret_cast<const __half*>(p)[i]);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(LN_THREADS) layernorm_fwd_kernel(const T* __restrict__ x, const void* __restrict__ gamma,
+                                                                    const void* __restrict__ beta, int pdtype, T* __restrict__ y,
+                                                                    float* __restrict__ mean_out, float* __restrict__ rstd_out, int rows,
+                                                                    int cols, float eps) {
+  __shared__ float red[32];
+  __shared__ float stat[2];
+  constexpr int N = 16 / sizeof(T);
+  const int nvec = cols / N;
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    const T* xr = x + (int64_t)row * cols;
+    Bytes16 v[LN_VPT];
+    float sum = 0.0f;
+#pragma unroll
+    for (int k = 0; k < LN_VPT; ++k) {
+      int i = threadIdx.x + k * LN_THREADS;
+      if (i < nvec) {
+        v[k] = reinterpret_cast<const Bytes16*>(xr)[i];
+        const T* e = reinterpret_cast<const T*>(&v[k]);
+#pragma unroll
+        for (int j = 0; j < N; ++j) sum += to_f32<T>(e[j]);
+      }
+    }
+    sum = block_sum(sum, red);
+    if (threadIdx.x == 0) stat[0] = sum / cols;
+    __syncthreads();
+    const float mean = stat[0];
+    float sq = 0.0f;
+#pragma unroll
+    for (int k = 0; k < LN_VPT; ++k) {
+      int i = threadIdx.x + k * LN_THREADS;
+      if (i < nvec) {
+        const T* e = reinterpret_cast<const T*>(&v[k]);
+#pragma unroll
+        for (int j = 0; j < N; ++j) {
+          float d = to_f32<T>(e[j]) - mean;
+          sq += d * d;
+        }
+      }
+    }
+    sq = block_sum(sq, red);
+    if (threadIdx.x == 0) stat[1] = rsqrtf(sq / cols + eps);
+    __syncthreads();
+    const float rstd = stat[1];
+    if (threadIdx.x == 0) {
+      mean_out[row] = mean;
+      rstd_out[row] = rstd;
+    }
+    T* yr = y + (int64_t)row * cols;
+#pragma unroll
+    for (int k = 0; k < LN_VPT; ++k) {
+      int i = threadIdx.x + k * LN_THREADS;
+      if (i < nvec) {
+        const T* e = reinterpret_cast<const T*>(&v[k]);
+        Bytes16 o;
+        T* oe = reinterpret_cast<T*>(&o);
+#pragma unroll
+        for (int j = 0; j < N; ++j) {
+          int c = i * N + j;
+          float g = ld_param<T>(gamma, c, pdtype);
+          float b = beta ? ld_param<T>(beta, c, pdtype) : 0.0f;
+          oe[j] = from_f32<T>((to_f32<T>(e[j]) - mean) * rstd * g + b);
+        }
+        reinterpret_cast<Bytes16*>(yr)[i] = o;
+      }
+    }
+    __syncthreads();
+  }
+}
+
+// Backward: dx per row; dgamma / dbeta partial sums per CTA (each thread owns fixed columns),
+// written to part[gridDim.x][2][cols] and reduced by a second kernel.
+template <typename T>
+__global__ void __launch_bounds__(LN_THREADS) layernorm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x,
+                                                                    const void* __restrict__ gamma, int pdtype,
+                                                                    const float* __restrict__ mean, const float* __restrict__ rstd,
+                                                                    T* __restrict__ dx, float* __restrict__ part, int rows, int cols) {
+  __shared__ float red[32];
+  __shared__ float stat[2];
+  constexpr int N = 16 / sizeof(T);
+  const int nvec = cols / N;
+  float dg[LN_VPT][N], db[LN_VPT][N];
+#pragma unroll
+  for (int k = 0; k < LN_VPT; ++k)
+#pragma unroll
+    for (int j = 0; j < N; ++j) dg[k][j] = db[k][j] = 0.0f;
+
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    const T* xr = x + (int64_t)row * cols;
+    const T* dyr = dy + (int64_t)row * cols;
+    const float mu = mean[row], rs = rstd[row];
+    Bytes16 vx[LN_VPT], vd[LN_VPT];
+    float s1 = 0.0f, s2 = 0.0f;    // sum(g*dy), sum(g*dy*xhat)
+#pragma unroll
+    for (int k = 0; k < LN_VPT; ++k) {
+      int i = threadIdx.x + k * LN_THREADS;
+      if (i < nvec) {
+        vx[k] = reinterpret_cast<const Bytes16*>(xr)[i];
+        vd[k] = reinterpret_cast<const Bytes16*>(dyr)[i];
+        const T* ex = reinterpret_cast<const T*>(&vx[k]);
+        const T* ed = reinterpret_cast<const T*>(&vd[k]);
+#pragma unroll
+        for (int j = 0; j < N; ++j) {
+          float xh = (to_f32<T>(ex[j]) - mu) * rs;
+          float d = to_f32<T>(ed[j]);
+          float gd = d * ld_param<T>(gamma, i * N + j, pdtype);
+          s1 += gd;
+          s2 += gd * xh;
+          dg[k][j] += d * xh;
+          db[k][j] += d;
+        }
+      }
+    }
+    s1 = block_sum(s1, red);
+    if (threadIdx.x == 0) stat[0] = s1 / cols;
+    s2 = block_sum(s2, red);
+    if (threadIdx.x == 0) stat[1] = s2 / cols;
+    __syncthreads();
+    const float m1 = stat[0], m2 = stat[1];
+    T* dxr = dx + (int64_t)row * cols;
+#pragma unroll
+    for (int k = 0; k < LN_VPT; ++k) {
+      int i = threadIdx.x + k * LN_THREADS;
+      if (i < nvec) {
+        const T* ex = reinterpret_cast<const T*>(&vx[k]);
+        const T* ed = reinterpret_cast<const T*>(&vd[k]);
+        Bytes16 o;
+        T* oe = reinterpret_cast<T*>(&o);
+#pragma unroll
+        for (int j = 0; j < N; ++j) {
+          float xh = (to_f32<T>(ex[j]) - mu) * rs;
+          float gd = to_f32<T>(ed[j]) * ld_param<T>(gamma, i * N + j, pdtype);
+          oe[j] = from_f32<T>(rs * (gd - m1 - xh * m2));
+        }
+        reinterpret_cast<Bytes16*>(dxr)[i] = o;
+      }
+    }
+    __syncthreads();
+  }
+  float* pg = part + (int64_t)blockIdx.x * 2 * cols;
+  float* pb = pg + cols;
+#pragma unroll
+  for (int k = 0; k < LN_VPT; ++k) {
+    int i = threadIdx.x + k * LN_THREADS;
+    if (i < nvec) {
+#pragma unroll
+      for (int j = 0; j < N; ++j) {
+        pg[i * N + j] = dg[k][j];
+        pb[i * N + j] = db[k][j];
+      }
+    }
+  }
+}
+
+__global__ void layernorm_reduce_kernel(const float* __restrict__ part, int nparts, int cols, void* dgamma, void* dbeta, int pdtype) {
+  int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= cols) return;
+  float g = 0.0f, b = 0.0f;
+  for (int i = 0; i < nparts; ++i) {
+    g += part[(int64_t)i * 2 * cols + c];
+    b += part[(int64_t)i * 2 * cols + cols + c];
+  }
+  if (pdtype == DT_F32) {
+    reinterpret_cast<float*>(dgamma)[c] = g;
+    if (dbeta) reinterpret_cast<float*>(dbeta)[c] = b;
+  } else if (pdtype == DT_BF16) {
+    reinterpret_cast<__nv_bfloat16*>(dgamma)[c] = __float2bfloat16_rn(g);
+    if (dbeta) reinterpret_cast<__nv_bfloat16*>(dbeta)[c] = __float2bfloat16_rn(b);
+  } else {
+    reinterpret_cast<__half*>(dgamma)[c] = __float2half_rn(g);
+    if (dbeta) reinterpret_cast<__half*>(dbeta)[c] = __float2half_rn(b);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// GeLU, tanh form: 0.5 x (1 + tanh(sqrt(2/pi) (x + 0.044715 x^3)))
+// ------------------------------------------------------------------------------------------------
+__device__ __forceinline__ float gelu_f(float x) {
+  const float k0 = 0.7978845608028654f, k1 = 0.044715f;
+  float u = k0 * (x + k1 * x * x * x);
+  return 0.5f * x * (1.0f + tanhf(u));
+}
+__device__ __forceinline__ float gelu_grad_f(float x) {
+  const float k0 = 0.7978845608028654f, k1 = 0.044715f;
+  float u = k0 * (x + k1 * x * x * x);
+  float th = tanhf(u);
+  return 0.5f * (1.0f + th) + 0.5f * x * (1.0f - th * th) * k0 * (1.0f + 3.0f * k1 * x * x);
+}
+
+template <typename T, bool BWD>
+__global__ void __launch_bounds__(256) gelu_kernel(const T* __restrict__ x, const T* __restrict__ dy, T* __restrict__ out, int64_t n) {
+  constexpr int N = 16 / sizeof(T);
+  int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  int64_t nv = n / N;
+  for (int64_t i = tid; i < nv; i += stride) {
+    Bytes16 vx = reinterpret_cast<const Bytes16*>(x)[i];
+    Bytes16 vd;
+    if (BWD) vd = reinterpret_cast<const Bytes16*>(dy)[i];
+    const T* ex = reinterpret_cast<const T*>(&vx);
+    const T* ed = reinterpret_cast<const T*>(&vd);
+    Bytes16 o;
+    T* oe = reinterpret_cast<T*>(&o);
+#pragma unroll
+    for (int j = 0; j < N; ++j) {
+      float xv = to_f32<T>(ex[j]);
+      oe[j] = from_f32<T>(BWD ? to_f32<T>(ed[j]) * gelu_grad_f(xv) : gelu_f(xv));
+    }
+    reinterpret_cast<Bytes16*>(out)[i] = o;
+  }
+  for (int64_t i = nv * N + tid; i < n; i += stride) {
+    float xv = to_f32<T>(x[i]);
+    out[i] = from_f32<T>(BWD ? to_f32<T>(dy[i]) * gelu_grad_f(xv) : gelu_f(xv));
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// Softmax cross-entropy over [rows, vocab] logits, one CTA per row.
+// Forward pass: loss[row] = logsumexp(logits) - logits[target]; lse saved.
+// Backward pass (in place): logits <- (softmax(logits) - onehot(target)) * gscale[0] * (target valid).
+// Rows whose target equals ignore_index contribute zero loss and zero gradient.
+// ------------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(512) xent_fwd_kernel(const T* __restrict__ logits, const int64_t* __restrict__ target,
+                                                        float* __restrict__ loss, float* __restrict__ lse_out, int vocab,
+                                                        int64_t row_stride, int64_t ignore_index) {
+  __shared__ float red[32];
+  constexpr int N = 16 / sizeof(T);
+  const int row = blockIdx.x;
+  const T* lr = logits + (int64_t)row * row_stride;
+  const int nv = vocab / N;
+  // online max / sum
+  float m = -INFINITY, s = 0.0f;
+  for (int i = threadIdx.x; i < nv; i += blockDim.x) {
+    Bytes16 v = reinterpret_cast<const Bytes16*>(lr)[i];
+    const T* e = reinterpret_cast<const T*>(&v);
+    float lm = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < N; ++j) lm = fmaxf(lm, to_f32<T>(e[j]));
+    if (lm > m) {
+      s *= __expf(m - lm);
+      m = lm;
+    }
+#pragma unroll
+    for (int j = 0; j < N; ++j) s += __expf(to_f32<T>(e[j]) - m);
+  }
+  for (int i = nv * N + threadIdx.x; i < vocab; i += blockDim.x) {
+    float v = to_f32<T>(lr[i]);
+    if (v > m) {
+      s *= __expf(m - v);
+      m = v;
+    }
+    s += __expf(v - m);
+  }
+  // combine (m, s) across the block: first the exact max, then the rescaled sums
+  float mm = m;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) mm = fmaxf(mm, __shfl_xor_sync(0xffffffffu, mm, o));
+  __shared__ float wmax[32];
+  if ((threadIdx.x & 31) == 0) wmax[threadIdx.x >> 5] = mm;
+  __syncthreads();
+  float bm = -INFINITY;
+  for (int w = 0; w < (int)(blockDim.x >> 5); ++w) bm = fmaxf(bm, wmax[w]);
+  float contrib = (m == -INFINITY) ? 0.0f : s * __expf(m - bm);
+  float total = block_sum(contrib, red);
+  if (threadIdx.x == 0) {
+    float lse = bm + logf(total);
+    lse_out[row] = lse;
+    int64_t t = target[row];
+    loss[row] = (t == ignore_index || t < 0 || t >= vocab) ? 0.0f : lse - to_f32<T>(lr[t]);
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(512) xent_bwd_kernel(T* __restrict__ logits, const int64_t* __restrict__ target,
+                                                        const float* __restrict__ lse_in, const float* __restrict__ gscale, int vocab,
+                                                        int64_t row_stride, int64_t ignore_index) {
+  constexpr int N = 16 / sizeof(T);
+  const int row = blockIdx.x;
+  T* lr = logits + (int64_t)row * row_stride;
+  const int64_t t = target[row];
+  const bool valid = !(t == ignore_index || t < 0 || t >= vocab);
+  const float gs = valid ? *gscale : 0.0f;
+  const float lse = lse_in[row];
+  const int nv = vocab / N;
+  for (int i = threadIdx.x; i < nv; i += blockDim.x) {
+    Bytes16 v = reinterpret_cast<const Bytes16*>(lr)[i];
+    T* e = reinterpret_cast<T*>(&v);
+#pragma unroll
+    for (int j = 0; j < N; ++j) {
+      int c = i * N + j;
+      float pr = __expf(to_f32<T>(e[j]) - lse);
+      e[j] = from_f32<T>((pr - ((valid && c == t) ? 1.0f : 0.0f)) * gs);
+    }
+    reinterpret_cast<Bytes16*>(lr)[i] = v;
+  }
+  for (int c = nv * N + threadIdx.x; c < vocab; c += blockDim.x) {
+    float pr = __expf(to_f32<T>(lr[c]) - lse);
+    lr[c] = from_f32<T>((pr - ((valid && c == t) ? 1.0f : 0.0f)) * gs);
+  }
+}
+
+}    // namespace
+
+MSAMP_API int msamp_layernorm_max_cols(int dtype) { return LN_THREADS * LN_VPT * (dtype == DT_F32 ? 4 : 8); }
+
+MSAMP_API int msamp_layernorm_fwd(const void* x, const void* gamma, const void* beta, int dtype, int pdtype, void* y, float* mean,
+                                  float* rstd, int rows, int cols, float eps, void* stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  MSAMP_REQUIRE(rows >= 0 && cols > 0, "layernorm: bad shape");
+  MSAMP_REQUIRE(cols <= msamp_layernorm_max_cols(dtype) && cols % (dtype == DT_F32 ? 4 : 8) == 0,
+                "layernorm: cols=%d must be a multiple of the 16-byte vector and at most %d", cols, msamp_layernorm_max_cols(dtype));
+  if (rows == 0) return MSAMP_OK;
+  int grid = rows < msamp_sm_count() * 8 ? rows : msamp_sm_count() * 8;
+  MSAMP_DISPATCH_HP(dtype, T, {
+    layernorm_fwd_kernel<T><<<grid, LN_THREADS, 0, stream>>>((const T*)x, gamma, beta, pdtype, (T*)y, mean, rstd, rows, cols, eps);
+  });
+  return msamp_check_launch("msamp_layernorm_fwd");
+}
+
+// part: scratch of msamp_layernorm_bwd_parts() * 2 * cols floats owned by the caller.
+MSAMP_API int msamp_layernorm_bwd_parts() { return msamp_sm_count() * 2; }
+
+MSAMP_API int msamp_layernorm_bwd(const void* dy, const void* x, const void* gamma, int dtype, int pdtype, const float* mean,
+                                  const float* rstd, void* dx, void* dgamma, void* dbeta, float* part, int rows, int cols,
+                                  void* stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  MSAMP_REQUIRE(rows > 0 && cols > 0, "layernorm_bwd: bad shape");
+  MSAMP_REQUIRE(cols <= msamp_layernorm_max_cols(dtype) && cols % (dtype == DT_F32 ? 4 : 8) == 0, "layernorm_bwd: unsupported cols=%d", cols);
+  int nparts = msamp_layernorm_bwd_parts();
+  int grid = rows < nparts ? rows : nparts;
+  MSAMP_DISPATCH_HP(dtype, T, {
+    layernorm_bwd_kernel<T><<<grid, LN_THREADS, 0, stream>>>((const T*)dy, (const T*)x, gamma, pdtype, mean, rstd, (T*)dx, part, rows, cols);
+  });
+  layernorm_reduce_kernel<<<(cols + 127) / 128, 128, 0, stream>>>(part, grid, cols, dgamma, dbeta, pdtype);
+  return msamp_check_launch("msamp_layernorm_bwd");
+}
+
+MSAMP_API int msamp_gelu_fwd(const void* x, void* y, int64_t n, int dtype, void* stream_) {
+  if (n <= 0) return MSAMP_OK;
+  MSAMP_REQUIRE(((uintptr_t)x & 15) == 0 && ((uintptr_t)y & 15) == 0, "gelu: pointers must be 16-byte aligned");
+  int grid = msamp_grid_for((n + 7) / 8, 256, 8);
+  MSAMP_DISPATCH_HP(dtype, T, { gelu_kernel<T, false><<<grid, 256, 0, (cudaStream_t)stream_>>>((const T*)x, nullptr, (T*)y, n); });
+  return msamp_check_launch("msamp_gelu_fwd");
+}
+
+MSAMP_API int msamp_gelu_bwd(const void* x, const void* dy, void* dx, int64_t n, int dtype, void* stream_) {
+  if (n <= 0) return MSAMP_OK;
+  MSAMP_REQUIRE(((uintptr_t)x & 15) == 0 && ((uintptr_t)dy & 15) == 0 && ((uintptr_t)dx & 15) == 0, "gelu: pointers must be 16-byte aligned");
+  int grid = msamp_grid_for((n + 7) / 8, 256, 8);
+  MSAMP_DISPATCH_HP(dtype, T, { gelu_kernel<T, true><<<grid, 256, 0, (cudaStream_t)stream_>>>((const T*)x, (const T*)dy, (T*)dx, n); });
+  return msamp_check_launch("msamp_gelu_bwd");
+}
+
+MSAMP_API int msamp_xent_fwd(const void* logits, const int64_t* target, float* loss, float* lse, int rows, int vocab, int64_t row_stride,
+                             int64_t ignore_index, int dtype, void* stream_) {
+  if (rows <= 0) return MSAMP_OK;
+  MSAMP_REQUIRE(((uintptr_t)logits & 15) == 0 && (row_stride * (dtype == DT_F32 ? 4 : 2)) % 16 == 0, "xent: rows must be 16-byte aligned");
+  MSAMP_DISPATCH_HP(dtype, T, {
+    xent_fwd_kernel<T><<<rows, 512, 0, (cudaStream_t)stream_>>>((const T*)logits, target, loss, lse, vocab, row_stride, ignore_index);
+  });
+  return msamp_check_launch("msamp_xent_fwd");
+}
+
+MSAMP_API int msamp_xent_bwd(void* logits, const int64_t* target, const float* lse, const float* gscale, int rows, int vocab,
+                             int64_t row_stride, int64_t ignore_index, int dtype, void* stream_) {
+  if (rows <= 0) return MSAMP_OK;
+  MSAMP_REQUIRE(((uintptr_t)logits & 15) == 0 && (row_stride * (dtype == DT_F32 ? 4 : 2)) % 16 == 0, "xent: rows must be 16-byte aligned");
+  MSAMP_DISPATCH_HP(dtype, T, {
+    xent_bwd_kernel<T><<<rows, 512, 0, (cudaStream_t)stream_>>>((T*)logits, target, lse, gscale, vocab, row_stride, ignore_index);
+  });
+  return msamp_check_launch("msamp_xent_bwd");
+}

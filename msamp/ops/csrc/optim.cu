@@ -1,0 +1,299 @@
+// Multi-tensor low-bit Adam / AdamW.
+//
+// One launch per stage covers every parameter of the optimizer (the reference launches two kernels
+// per parameter from a Python loop and synchronises with the host twice per step,
+// msamp/optim/adamw.py:148-199, msamp/optim/adamw.cu:30-153).
+//
+//   stage 1  reads p, g, m, v; computes the new moments and the new parameter in fp32 and reduces
+//            max|p_new|, max|m_new|, max|v_new| per tensor.
+//   stage 2  derives the new per-tensor scales from those maxima on the device, recomputes the same
+//            values and stores them in their storage formats (scaled fp16 / e4m3 / e5m2 / plain),
+//            then block 0 of each tensor publishes scale, scale_inv and amax into the metas.
+//
+// The update itself always uses the unquantised new moments, exactly like the reference kernels.
+#include "common.cuh"
+
+namespace {
+
+// storage codes: 0 f32, 1 f16, 2 bf16, 3 e4m3, 4 e5m2
+enum { ST_F32 = 0, ST_F16 = 1, ST_BF16 = 2, ST_E4M3 = 3, ST_E5M2 = 4 };
+
+struct AdamTensor {
+  void* p;
+  const void* g;
+  void* m;
+  void* v;
+  float* p_scale;    // null when the parameter is unscaled
+  float* p_scale_inv;
+  float* p_amax;
+  const float* g_scale_inv;    // null: gradient is plain high precision
+  float* m_scale;
+  float* m_scale_inv;
+  float* m_amax;
+  float* v_scale;
+  float* v_scale_inv;
+  float* v_amax;
+  int64_t n;
+  int p_st, g_st, m_st, v_st;
+  float lr_wd_factor;    // 1 - lr * wd (decoupled) or 1
+  float l2;              // wd for L2 mode, else 0
+  float beta1, beta2, eps, step_size, sqrt_bc2, gsign;
+  int tensor_scale;
+  int pad;
+  float red[4];          // stage-1 results: max|p|, max|m|, max|v|
+};
+
+constexpr int kChunk = 8192;    // elements per block
+constexpr int kAdamThreads = 256;
+
+__device__ __forceinline__ float st_max(int st) {
+  switch (st) {
+    case ST_F16: return 65504.0f;
+    case ST_E4M3: return 448.0f;
+    case ST_E5M2: return 57344.0f;
+    default: return 3.0e38f;
+  }
+}
+
+__device__ __forceinline__ void load8(const void* base, int st, int64_t i, float (&o)[8]) {
+  switch (st) {
+    case ST_F32: {
+      const float4* p = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(base) + i);
+      float4 a = p[0], b = p[1];
+      o[0] = a.x; o[1] = a.y; o[2] = a.z; o[3] = a.w; o[4] = b.x; o[5] = b.y; o[6] = b.z; o[7] = b.w;
+      break;
+    }
+    case ST_F16: {
+      Bytes16 r = *reinterpret_cast<const Bytes16*>(reinterpret_cast<const __half*>(base) + i);
+      const __half* e = reinterpret_cast<const __half*>(&r);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = __half2float(e[j]);
+      break;
+    }
+    case ST_BF16: {
+      Bytes16 r = *reinterpret_cast<const Bytes16*>(reinterpret_cast<const __nv_bfloat16*>(base) + i);
+      const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(&r);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = __bfloat162float(e[j]);
+      break;
+    }
+    case ST_E4M3: {
+      Bytes8 r = *reinterpret_cast<const Bytes8*>(reinterpret_cast<const uint8_t*>(base) + i);
+      const uint8_t* e = reinterpret_cast<const uint8_t*>(&r);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = fp8_to_f32<FMT_E4M3>(e[j]);
+      break;
+    }
+    default: {
+      Bytes8 r = *reinterpret_cast<const Bytes8*>(reinterpret_cast<const uint8_t*>(base) + i);
+      const uint8_t* e = reinterpret_cast<const uint8_t*>(&r);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = fp8_to_f32<FMT_E5M2>(e[j]);
+      break;
+    }
+  }
+}
+
+__device__ __forceinline__ float load1(const void* base, int st, int64_t i) {
+  switch (st) {
+    case ST_F32: return reinterpret_cast<const float*>(base)[i];
+    case ST_F16: return __half2float(reinterpret_cast<const __half*>(base)[i]);
+    case ST_BF16: return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(base)[i]);
+    case ST_E4M3: return fp8_to_f32<FMT_E4M3>(reinterpret_cast<const uint8_t*>(base)[i]);
+    default: return fp8_to_f32<FMT_E5M2>(reinterpret_cast<const uint8_t*>(base)[i]);
+  }
+}
+
+__device__ __forceinline__ float sat(float x, float mx) { return (x != x) ? x : fminf(fmaxf(x, -mx), mx); }
+
+__device__ __forceinline__ void store8(void* base, int st, int64_t i, const float (&o)[8]) {
+  switch (st) {
+    case ST_F32: {
+      float4* p = reinterpret_cast<float4*>(reinterpret_cast<float*>(base) + i);
+      p[0] = make_float4(o[0], o[1], o[2], o[3]);
+      p[1] = make_float4(o[4], o[5], o[6], o[7]);
+      break;
+    }
+    case ST_F16: {
+      Bytes16 r;
+      __half* e = reinterpret_cast<__half*>(&r);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) e[j] = __float2half_rn(sat(o[j], 65504.0f));
+      *reinterpret_cast<Bytes16*>(reinterpret_cast<__half*>(base) + i) = r;
+      break;
+    }
+    case ST_BF16: {
+      Bytes16 r;
+      __nv_bfloat16* e = reinterpret_cast<__nv_bfloat16*>(&r);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) e[j] = __float2bfloat16_rn(o[j]);
+      *reinterpret_cast<Bytes16*>(reinterpret_cast<__nv_bfloat16*>(base) + i) = r;
+      break;
+    }
+    case ST_E4M3: {
+      Bytes8 r;
+      uint16_t* e = reinterpret_cast<uint16_t*>(&r);
+#pragma unroll
+      for (int j = 0; j < 8; j += 2) e[j / 2] = f32x2_to_fp8x2<FMT_E4M3>(o[j], o[j + 1]);
+      *reinterpret_cast<Bytes8*>(reinterpret_cast<uint8_t*>(base) + i) = r;
+      break;
+    }
+    default: {
+      Bytes8 r;
+      uint16_t* e = reinterpret_cast<uint16_t*>(&r);
+#pragma unroll
+      for (int j = 0; j < 8; j += 2) e[j / 2] = f32x2_to_fp8x2<FMT_E5M2>(o[j], o[j + 1]);
+      *reinterpret_cast<Bytes8*>(reinterpret_cast<uint8_t*>(base) + i) = r;
+      break;
+    }
+  }
+}
+
+__device__ __forceinline__ void store1(void* base, int st, int64_t i, float x) {
+  switch (st) {
+    case ST_F32: reinterpret_cast<float*>(base)[i] = x; break;
+    case ST_F16: reinterpret_cast<__half*>(base)[i] = __float2half_rn(sat(x, 65504.0f)); break;
+    case ST_BF16: reinterpret_cast<__nv_bfloat16*>(base)[i] = __float2bfloat16_rn(x); break;
+    case ST_E4M3: reinterpret_cast<uint8_t*>(base)[i] = f32_to_fp8<FMT_E4M3>(x); break;
+    default: reinterpret_cast<uint8_t*>(base)[i] = f32_to_fp8<FMT_E5M2>(x); break;
+  }
+}
+
+struct Elem {
+  float p, m, v;
+};
+
+__device__ __forceinline__ Elem adam_elem(const AdamTensor& t, float p, float g, float m, float v, float psi, float gsi, float msi,
+                                          float vsi) {
+  p *= psi;
+  g = g * gsi * t.gsign;
+  g += t.l2 * p;
+  p *= t.lr_wd_factor;
+  Elem e;
+  e.m = t.beta1 * (m * msi) + (1.0f - t.beta1) * g;
+  e.v = t.beta2 * (v * vsi) + (1.0f - t.beta2) * (g * g);
+  float denom = sqrtf(e.v) / t.sqrt_bc2 + t.eps;
+  e.p = p - t.step_size * (e.m / denom);
+  return e;
+}
+
+// block -> (tensor, chunk) map: work[2*b] = tensor index, work[2*b+1] = chunk index
+template <int STAGE>
+__global__ void __launch_bounds__(kAdamThreads) lbadam_kernel(AdamTensor* tensors, const int* __restrict__ work) {
+  __shared__ float red[32];
+  AdamTensor& t = tensors[work[2 * blockIdx.x]];
+  const int chunk = work[2 * blockIdx.x + 1];
+  const int64_t begin = (int64_t)chunk * kChunk;
+  const int64_t end = (begin + kChunk < t.n) ? begin + kChunk : t.n;
+
+  const float psi = t.p_scale_inv ? *t.p_scale_inv : 1.0f;
+  const float gsi = t.g_scale_inv ? *t.g_scale_inv : 1.0f;
+  const float msi = t.m_scale_inv ? *t.m_scale_inv : 1.0f;
+  const float vsi = t.v_scale_inv ? *t.v_scale_inv : 1.0f;
+
+  float ps = 1.0f, ms = 1.0f, vs = 1.0f;
+  if (STAGE == 2) {
+    if (t.p_scale) ps = msamp_compute_scale(t.red[0], *t.p_scale, st_max(t.p_st), 0);
+    if (t.m_scale) ms = t.tensor_scale ? msamp_compute_scale(t.red[1], 1.0f, st_max(t.m_st), 0) : 1.0f;
+    if (t.v_scale) vs = t.tensor_scale ? msamp_compute_scale(t.red[2], 1.0f, st_max(t.v_st), 0) : 1.0f;
+  }
+
+  const bool vec = ((reinterpret_cast<uintptr_t>(t.p) | reinterpret_cast<uintptr_t>(t.g) | reinterpret_cast<uintptr_t>(t.m) |
+                     reinterpret_cast<uintptr_t>(t.v)) & 15) == 0;
+  float ap = 0.0f, am = 0.0f, av = 0.0f;
+  if (vec) {
+    for (int64_t i = begin + (int64_t)threadIdx.x * 8; i + 8 <= end; i += (int64_t)kAdamThreads * 8) {
+      float p[8], g[8], m[8], v[8];
+      load8(t.p, t.p_st, i, p);
+      load8(t.g, t.g_st, i, g);
+      load8(t.m, t.m_st, i, m);
+      load8(t.v, t.v_st, i, v);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        Elem e = adam_elem(t, p[j], g[j], m[j], v[j], psi, gsi, msi, vsi);
+        if (STAGE == 1) {
+          ap = fmaxf(ap, abs_nan_to_inf(e.p));
+          am = fmaxf(am, abs_nan_to_inf(e.m));
+          av = fmaxf(av, abs_nan_to_inf(e.v));
+        } else {
+          p[j] = e.p * ps;
+          m[j] = e.m * ms;
+          v[j] = e.v * vs;
+        }
+      }
+      if (STAGE == 2) {
+        store8(t.p, t.p_st, i, p);
+        store8(t.m, t.m_st, i, m);
+        store8(t.v, t.v_st, i, v);
+      }
+    }
+  }
+  {
+    // tail of the chunk (or the whole chunk when the pointers are not 16-byte aligned)
+    int64_t tail = vec ? begin + ((end - begin) / 8) * 8 : begin;
+    for (int64_t i = tail + threadIdx.x; i < end; i += kAdamThreads) {
+      Elem e = adam_elem(t, load1(t.p, t.p_st, i), load1(t.g, t.g_st, i), load1(t.m, t.m_st, i), load1(t.v, t.v_st, i), psi, gsi,
+                         msi, vsi);
+      if (STAGE == 1) {
+        ap = fmaxf(ap, abs_nan_to_inf(e.p));
+        am = fmaxf(am, abs_nan_to_inf(e.m));
+        av = fmaxf(av, abs_nan_to_inf(e.v));
+      } else {
+        store1(t.p, t.p_st, i, e.p * ps);
+        store1(t.m, t.m_st, i, e.m * ms);
+        store1(t.v, t.v_st, i, e.v * vs);
+      }
+    }
+  }
+  if (STAGE == 1) {
+    ap = block_max(ap, red);
+    am = block_max(am, red);
+    av = block_max(av, red);
+    if (threadIdx.x == 0) {
+      atomic_max_nonneg(&t.red[0], ap);
+      atomic_max_nonneg(&t.red[1], am);
+      atomic_max_nonneg(&t.red[2], av);
+    }
+  }
+}
+
+// After stage 2 has consumed the old inverse scales everywhere: publish the new metas.
+__global__ void lbadam_finalize_kernel(AdamTensor* tensors, int n) {
+  int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  AdamTensor& t = tensors[i];
+  if (t.p_scale) {
+    float s = msamp_compute_scale(t.red[0], *t.p_scale, st_max(t.p_st), 0);
+    *t.p_scale = s;
+    *t.p_scale_inv = __frcp_rn(s);
+    if (t.p_amax) *t.p_amax = t.red[0];
+  }
+  if (t.m_scale) {
+    float s = t.tensor_scale ? msamp_compute_scale(t.red[1], 1.0f, st_max(t.m_st), 0) : 1.0f;
+    *t.m_scale = s;
+    *t.m_scale_inv = __frcp_rn(s);
+    if (t.m_amax) *t.m_amax = t.red[1];
+  }
+  if (t.v_scale) {
+    float s = t.tensor_scale ? msamp_compute_scale(t.red[2], 1.0f, st_max(t.v_st), 0) : 1.0f;
+    *t.v_scale = s;
+    *t.v_scale_inv = __frcp_rn(s);
+    if (t.v_amax) *t.v_amax = t.red[2];
+  }
+}
+
+}    // namespace
+
+MSAMP_API int msamp_lbadam_tensor_bytes() { return (int)sizeof(AdamTensor); }
+MSAMP_API int msamp_lbadam_chunk() { return kChunk; }
+
+// `tensors`: device array of n_tensors descriptors (layout of AdamTensor; `red` must be zero on
+// entry); `work`: device array of 2 * n_blocks ints mapping each block to (tensor, chunk).
+MSAMP_API int msamp_lbadam_step(void* tensors, int n_tensors, const int* work, int n_blocks, void* stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  if (n_tensors <= 0 || n_blocks <= 0) return MSAMP_OK;
+  lbadam_kernel<1><<<n_blocks, kAdamThreads, 0, stream>>>((AdamTensor*)tensors, work);
+  lbadam_kernel<2><<<n_blocks, kAdamThreads, 0, stream>>>((AdamTensor*)tensors, work);
+  lbadam_finalize_kernel<<<(n_tensors + 127) / 128, 128, 0, stream>>>((AdamTensor*)tensors, n_tensors);
+  return msamp_check_launch("msamp_lbadam_step");
+}

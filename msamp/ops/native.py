@@ -66,8 +66,13 @@ def lib():
     return _lib
 
 
+launch_count = 0    # native entry points called so far (each launches at least one kernel)
+
+
 def check(status, what=''):
-    """Raise ``NativeError`` for a non-zero status code."""
+    """Raise ``NativeError`` for a non-zero status code; counts the call."""
+    global launch_count
+    launch_count += 1
     if status != 0:
         detail = lib().msamp_last_error().decode()
         raise NativeError(f'{what}: {_ERRORS.get(status, status)} ({detail})')

@@ -1,0 +1,67 @@
+"""A small training-step driver used by the benchmark, the examples and the tests.
+
+One call of ``step(tokens, labels)`` runs forward, backward, the gradient exchange of the chosen
+data-parallel flavour and the optimizer update, and returns the (device-resident) loss.
+"""
+import torch
+import torch.distributed as dist
+
+from msamp.common.tensor import ScalingTensor, TensorDist
+from msamp.common.utils.dist import DistUtil
+
+
+class DataParallelTrainer:
+    """Replicated data parallelism (``zero_stage=0``) or sharded optimizer states (``zero_stage=1/2``).
+
+    FP8 weight gradients already share one scale across ranks (their amax is MAX-reduced when they
+    are quantised), so they are summed as FP8 numbers and averaged by dividing ``scale_inv``;
+    high-precision gradients are averaged in flat buckets.
+    """
+    def __init__(self, model, optimizer, zero_stage=0, group=None, clip_grad=0.0, bucket_elems=64 * 1024 * 1024):
+        self.model = model
+        self.optimizer = optimizer
+        self.group = group
+        self.world = DistUtil.get_world_size(group)
+        self.clip_grad = clip_grad
+        self.bucket_elems = bucket_elems
+        self.zero = None
+        if zero_stage and self.world > 1:
+            from msamp.parallel.zero import ZeroShardedOptimizer
+            self.zero = ZeroShardedOptimizer(model, optimizer, stage=zero_stage, group=group)
+
+    def _sync_grads(self):
+        if self.world == 1:
+            return
+        fp8, hp = [], []
+        for p in self.model.parameters():
+            g = p.grad
+            if g is None:
+                continue
+            (fp8 if isinstance(g, ScalingTensor) else hp).append(g)
+        TensorDist.all_reduce_avg(fp8, bucket_size=self.bucket_elems, group=self.group)
+        by_dtype = {}
+        for g in hp:
+            by_dtype.setdefault(g.dtype, []).append(g)
+        for grads in by_dtype.values():
+            flat = torch.cat([g.reshape(-1) for g in grads])
+            dist.all_reduce(flat, group=self.group)
+            flat.div_(self.world)
+            off = 0
+            for g in grads:
+                n = g.numel()
+                g.copy_(flat[off:off + n].view_as(g))
+                off += n
+
+    def step(self, *inputs):
+        self.optimizer.zero_grad(set_to_none=True)
+        loss = self.model(*inputs)
+        loss.backward()
+        if self.zero is not None:
+            self.zero.reduce_and_step(clip_grad=self.clip_grad)
+        else:
+            self._sync_grads()
+            if self.clip_grad > 0:
+                from msamp.nn import clip_grad_norm_
+                clip_grad_norm_(self.model.parameters(), self.clip_grad)
+            self.optimizer.step()
+        return loss.detach()

@@ -1,0 +1,32 @@
+"""Test configuration: registers the ``gpu`` marker and makes the repository importable."""
+import os
+import sys
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+
+def pytest_configure(config):
+    config.addinivalue_line('markers', 'gpu: test needs a CUDA device (run with -m gpu on a B200)')
+
+
+def pytest_collection_modifyitems(config, items):
+    import torch
+    if torch.cuda.is_available():
+        return
+    skip = pytest.mark.skip(reason='no CUDA device')
+    for item in items:
+        if 'gpu' in item.keywords:
+            item.add_marker(skip)
+
+
+@pytest.fixture(autouse=True)
+def _fresh_model_state():
+    """Each test starts with an empty registry of scaling metas."""
+    from msamp.nn import model_state
+    model_state.clear()
+    yield
+    model_state.clear()

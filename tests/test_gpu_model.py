@@ -1,0 +1,124 @@
+"""GPU end-to-end: FP8Linear against fp32, O1/O2 training steps, GPT forward/backward, checkpoint round trip."""
+import copy
+
+import pytest
+import torch
+
+import msamp
+from msamp.common.tensor import ScalingTensor
+from msamp.models import GPT, gpt_config
+from msamp.nn import FP8Linear, LinearReplacer
+from msamp.ops import native
+
+pytestmark = pytest.mark.gpu
+DEV = 'cuda'
+
+
+def test_native_library_is_loaded():
+    native.lib()
+    assert native.lib().msamp_device_sm_count() >= 100
+
+
+@pytest.mark.parametrize('dt', [torch.float32, torch.bfloat16, torch.float16])
+def test_fp8linear_close_to_linear(dt):
+    torch.manual_seed(0)
+    lin = torch.nn.Linear(256, 512).to(DEV)
+    ref = copy.deepcopy(lin).float()
+    model = LinearReplacer.replace(torch.nn.Sequential(lin))
+    assert isinstance(model[0], FP8Linear)
+    x = torch.randn(64, 256, device=DEV, dtype=dt, requires_grad=True)
+    xr = x.detach().float().requires_grad_()
+    y = model(x)
+    yr = ref(xr)
+    assert y.dtype == dt
+    assert (y.float() - yr).abs().max().item() < 0.12
+    g = torch.randn_like(y)
+    y.backward(g)
+    yr.backward(g.float())
+    w = model[0].weight
+    assert isinstance(w.grad, ScalingTensor)
+    rel = (w.grad.float() - ref.weight.grad).abs().max().item() / ref.weight.grad.abs().max().item()
+    assert rel < 0.1, rel
+    assert (x.grad.float() - xr.grad).abs().max().item() < 0.1 * xr.grad.abs().max().item() + 0.05
+    assert (model[0].bias.grad - ref.bias.grad).abs().max().item() < 0.05 * ref.bias.grad.abs().max().item() + 1e-2
+    # gradient accumulation ~ doubling
+    y2 = model(x)
+    y2.backward(g)
+    rel2 = (w.grad.float() - 2 * ref.weight.grad).abs().max().item() / ref.weight.grad.abs().max().item()
+    assert rel2 < 0.2, rel2
+    assert native.device_status() == 0
+
+
+@pytest.mark.parametrize('level', ['O1', 'O2'])
+def test_training_tracks_fp32(level):
+    def mk():
+        torch.manual_seed(0)
+        return torch.nn.Sequential(torch.nn.Linear(64, 128), torch.nn.GELU(), torch.nn.Linear(128, 16)).to(DEV)
+
+    x = torch.randn(256, 64, device=DEV)
+    t = torch.randn(256, 16, device=DEV)
+    m, r = mk(), mk()
+    opt = torch.optim.AdamW(m.parameters(), lr=1e-2)
+    ropt = torch.optim.AdamW(r.parameters(), lr=1e-2)
+    m, opt = msamp.initialize(m, opt, level)
+    first = last = None
+    for i in range(30):
+        for mm, oo in ((m, opt), (r, ropt)):
+            oo.zero_grad()
+            loss = ((mm(x) - t)**2).mean()
+            loss.backward()
+            oo.step()
+            if mm is m:
+                last = loss.item()
+                first = first if first is not None else last
+            else:
+                rl = loss.item()
+    assert last < 0.6 * first
+    assert abs(last - rl) < 0.1 * rl + 0.02
+    sd = opt.state_dict()
+    opt.load_state_dict(sd)
+    msd = m.state_dict()
+    assert isinstance(msd['0.weight'], ScalingTensor)
+    m.load_state_dict(msd)
+
+
+def test_gpt_steps_and_loss_decreases():
+    torch.manual_seed(0)
+    cfg = gpt_config('gpt-tiny', n_layer=2, n_head=2, hidden=256, ffn_hidden=1024, vocab_size=1024, max_seq=128)
+    model = GPT(cfg, device=DEV)
+    opt = torch.optim.AdamW(model.parameters(), lr=2e-3)
+    model, opt = msamp.initialize(model, opt, 'O2')
+    tok = torch.randint(0, cfg.vocab_size, (4, 128), device=DEV)
+    lab = torch.randint(0, cfg.vocab_size, (4, 128), device=DEV)
+    losses = []
+    for _ in range(25):    # crosses the 16-step warm-up into delayed scaling
+        opt.zero_grad()
+        loss = model(tok, lab)
+        loss.backward()
+        opt.step()
+        losses.append(loss.item())
+    assert all(l == l for l in losses)
+    assert losses[-1] < losses[0] - 0.5, losses
+    assert native.device_status() == 0
+
+
+def test_gpt_matches_cpu_emulation_forward():
+    torch.manual_seed(0)
+    cfg = gpt_config('gpt-tiny')
+    cpu = GPT(cfg, device='cpu', act_dtype=torch.bfloat16)
+    gpu = copy.deepcopy(cpu).to(DEV)
+    import os
+    os.environ['MSAMP_DEVICE'] = 'cpu'
+    try:
+        cpu = LinearReplacer.replace(cpu)
+    finally:
+        del os.environ['MSAMP_DEVICE']
+    from msamp.nn import model_state
+    tok = torch.randint(0, cfg.vocab_size, (2, 64))
+    with torch.no_grad():
+        lc = cpu(tok).float()
+    model_state.clear()
+    gpu = LinearReplacer.replace(gpu)
+    with torch.no_grad():
+        lg = gpu(tok.to(DEV)).float().cpu()
+    assert (lc - lg).abs().max().item() < 0.15, (lc - lg).abs().max()
