@@ -87,7 +87,7 @@ class Block(nn.Module):
     def forward(self, x, batch, seq):
         # x: [batch*seq, hidden]
         qkv = self.qkv(self.ln1(x)).view(batch, seq, 3, self.n_head, self.head_dim)
-        o = K.attention(qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2], causal=True, grad_layout='packed')
+        o = K.attention_qkv(qkv, causal=True)
         x = x + self.proj(o.view(batch * seq, -1))
         x = x + self.fc2(K.gelu(self.fc1(self.ln2(x))))
         return x

@@ -59,10 +59,8 @@ def weight_fp8_pair(weight):
         # Scaled 16-bit weight: value == w * s_w. Quantise with the scale implied by the stored
         # amax of w, expressed relative to the stored payload.
         meta = weight.meta
-        new_scale = ScalingMeta.compute_scaling_factor(meta.amax[0], torch.ones_like(meta.scale), Floating.qfp_max[E4M3], 0)
-        factor = new_scale * meta.scale_inv
-        w8, w8t = _k.cast_transpose_fp8(w2d, E4M3, factor)
-        sinv = torch.reciprocal(new_scale)
+        sinv = torch.empty_like(meta.scale_inv)
+        w8, w8t = _k.cast_transpose_fp8(w2d, E4M3, meta.scale_inv, scale_inv_out=sinv, amax_in=meta.amax[0])
     weight._fp8_cache = (key, w8, w8t, sinv)
     return w8, w8t, sinv
 

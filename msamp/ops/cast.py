@@ -114,8 +114,13 @@ def cast_to_fp8(x, qtype, scale, amax_out=None, scale_inv_out=None, amax_in=None
     return _emulate_to_fp8(x, scale, qtype)
 
 
-def cast_transpose_fp8(x, qtype, scale, amax_out=None, need_rowmajor=True, scale_inv_out=None):
-    """Quantise a 2-D tensor and also produce its transpose. Returns ``(out or None, out_t)``."""
+def cast_transpose_fp8(x, qtype, scale, amax_out=None, need_rowmajor=True, scale_inv_out=None, amax_in=None):
+    """Quantise a 2-D tensor and also produce its transpose. Returns ``(out or None, out_t)``.
+
+    With ``amax_in`` the input is a *scaled* tensor ``x * s_old``: ``scale`` must hold ``1 / s_old`` and ``amax_in``
+    ``max|x|``; the kernel derives ``s_new`` from the amax, multiplies by ``s_new / s_old`` and writes ``1 / s_new`` to
+    ``scale_inv_out`` - all in the one launch.
+    """
     assert x.dim() == 2
     rows, cols = x.shape
     if x.is_cuda:
@@ -125,14 +130,19 @@ def cast_transpose_fp8(x, qtype, scale, amax_out=None, need_rowmajor=True, scale
         native.check(
             native.lib().msamp_cast_transpose_fp8(
                 native.ptr(x), rows, cols, native.dt(x.dtype), native.ptr(out), native.ptr(out_t), native.fmt(qtype),
-                native.ptr(scale), native.ptr(amax_out), native.ptr(scale_inv_out), native.stream()
+                native.ptr(scale), native.ptr(amax_out), native.ptr(scale_inv_out), native.ptr(amax_in), native.stream()
             ), 'cast_transpose_fp8'
         )
         return out, out_t
+    if amax_in is not None:
+        new_scale = compute_scale(amax_in, torch.ones_like(scale), Floating.qfp_max[qtype])
+        if scale_inv_out is not None:
+            torch.reciprocal(new_scale, out=scale_inv_out)
+        scale = new_scale * scale
+    elif scale_inv_out is not None:
+        torch.reciprocal(scale, out=scale_inv_out)
     if amax_out is not None:
         amax(x, out=amax_out)
-    if scale_inv_out is not None:
-        torch.reciprocal(scale, out=scale_inv_out)
     out = _emulate_to_fp8(x, scale, qtype)
     return (out if need_rowmajor else None), out.t().contiguous()
 

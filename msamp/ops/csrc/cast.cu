@@ -151,11 +151,20 @@ template <typename T, int FMT, bool WRITE_ROWMAJOR>
 __global__ void __launch_bounds__(kThreads) cast_transpose_kernel(const T* __restrict__ x, uint8_t* __restrict__ out,
                                                                    uint8_t* __restrict__ out_t, int rows, int cols,
                                                                    const float* __restrict__ scale_ptr, float* amax,
-                                                                   float* scale_inv_out, bool aligned) {
+                                                                   float* scale_inv_out, const float* __restrict__ amax_in,
+                                                                   float fp_max, bool aligned) {
   __shared__ __align__(16) uint8_t tile_t[kTile * kTStride];    // [c][r]
   __shared__ float red[32];
-  const float scale = *scale_ptr;
-  if (scale_inv_out != nullptr && blockIdx.x == 0 && threadIdx.x == 0) *scale_inv_out = __frcp_rn(scale);
+  float scale = *scale_ptr;
+  float logical_scale = scale;
+  if (amax_in != nullptr) {
+    // Re-quantisation of a tensor that is stored as x * s_old: *scale_ptr holds 1 / s_old and
+    // *amax_in holds max|x|.  The payload is multiplied by s_new / s_old where s_new follows the
+    // power-of-two rule; scale_inv_out receives 1 / s_new.
+    logical_scale = msamp_compute_scale(*amax_in, 1.0f, fp_max, 0);
+    scale = logical_scale * scale;
+  }
+  if (scale_inv_out != nullptr && blockIdx.x == 0 && threadIdx.x == 0) *scale_inv_out = __frcp_rn(logical_scale);
   const int tiles_c = (cols + kTile - 1) / kTile;
   const int tiles_r = (rows + kTile - 1) / kTile;
   const int64_t ntiles = (int64_t)tiles_c * tiles_r;
@@ -361,8 +370,10 @@ MSAMP_API int msamp_cast_from_fp8(const void* in, int64_t n, int fmt, const floa
 }
 
 // x is [rows, cols] row-major. out (may be null) is the row-major FP8 copy, out_t the [cols, rows] one.
+// With amax_in non-null the input is a scaled tensor (x * s_old): `scale` must then point to
+// 1 / s_old, amax_in to max|x|, and the effective factor becomes rule(amax) / s_old.
 MSAMP_API int msamp_cast_transpose_fp8(const void* x, int rows, int cols, int dtype, void* out, void* out_t, int fmt,
-                                       const float* scale, float* amax, float* scale_inv_out, void* stream_) {
+                                       const float* scale, float* amax, float* scale_inv_out, const float* amax_in, void* stream_) {
   cudaStream_t stream = (cudaStream_t)stream_;
   MSAMP_REQUIRE(rows >= 0 && cols >= 0 && out_t != nullptr && scale != nullptr, "msamp_cast_transpose_fp8: bad arguments");
   if (amax) cudaMemsetAsync(amax, 0, sizeof(float), stream);
@@ -374,9 +385,9 @@ MSAMP_API int msamp_cast_transpose_fp8(const void* x, int rows, int cols, int dt
   MSAMP_DISPATCH_HP(dtype, T, {
     MSAMP_DISPATCH_FP8(fmt, F, {
       if (out)
-        cast_transpose_kernel<T, F, true><<<grid, kThreads, 0, stream>>>((const T*)x, (uint8_t*)out, (uint8_t*)out_t, rows, cols, scale, amax, scale_inv_out, aligned);
+        cast_transpose_kernel<T, F, true><<<grid, kThreads, 0, stream>>>((const T*)x, (uint8_t*)out, (uint8_t*)out_t, rows, cols, scale, amax, scale_inv_out, amax_in, fp8_max(F), aligned);
       else
-        cast_transpose_kernel<T, F, false><<<grid, kThreads, 0, stream>>>((const T*)x, nullptr, (uint8_t*)out_t, rows, cols, scale, amax, scale_inv_out, aligned);
+        cast_transpose_kernel<T, F, false><<<grid, kThreads, 0, stream>>>((const T*)x, nullptr, (uint8_t*)out_t, rows, cols, scale, amax, scale_inv_out, amax_in, fp8_max(F), aligned);
     });
   });
   return msamp_check_launch("msamp_cast_transpose_fp8");

@@ -9,8 +9,8 @@ namespace {
 // LayerNorm.  One CTA per row; the row is held in registers between the statistics and the
 // normalisation (up to LN_VPT 16-byte vectors per thread), so x is read once.
 // ------------------------------------------------------------------------------------------------
-constexpr int LN_THREADS = 256;
-constexpr int LN_VPT = 4;    // vectors per thread -> rows up to 256 * 4 * 8 = 8192 elements of 16-bit data
+constexpr int LN_THREADS = 256;    // widest CTA; rows that fit use 128 threads so that more rows are in flight per SM
+constexpr int LN_VPT = 4;          // vectors per thread -> rows up to 256 * 4 * 8 = 8192 elements of 16-bit data
 
 template <typename T>
 __device__ __forceinline__ float ld_param(const void* p, int i, int dtype) {
@@ -19,8 +19,8 @@ __device__ __forceinline__ float ld_param(const void* p, int i, int dtype) {
   return __half2float(reinterpret_cast<const __half*>(p)[i]);
 }
 
-template <typename T>
-__global__ void __launch_bounds__(LN_THREADS) layernorm_fwd_kernel(const T* __restrict__ x, const void* __restrict__ gamma,
+template <typename T, int THREADS>
+__global__ void __launch_bounds__(THREADS) layernorm_fwd_kernel(const T* __restrict__ x, const void* __restrict__ gamma,
                                                                     const void* __restrict__ beta, int pdtype, T* __restrict__ y,
                                                                     float* __restrict__ mean_out, float* __restrict__ rstd_out, int rows,
                                                                     int cols, float eps) {
@@ -34,7 +34,7 @@ __global__ void __launch_bounds__(LN_THREADS) layernorm_fwd_kernel(const T* __re
     float sum = 0.0f;
 #pragma unroll
     for (int k = 0; k < LN_VPT; ++k) {
-      int i = threadIdx.x + k * LN_THREADS;
+      int i = threadIdx.x + k * THREADS;
       if (i < nvec) {
         v[k] = reinterpret_cast<const Bytes16*>(xr)[i];
         const T* e = reinterpret_cast<const T*>(&v[k]);
@@ -49,7 +49,7 @@ __global__ void __launch_bounds__(LN_THREADS) layernorm_fwd_kernel(const T* __re
     float sq = 0.0f;
 #pragma unroll
     for (int k = 0; k < LN_VPT; ++k) {
-      int i = threadIdx.x + k * LN_THREADS;
+      int i = threadIdx.x + k * THREADS;
       if (i < nvec) {
         const T* e = reinterpret_cast<const T*>(&v[k]);
 #pragma unroll
@@ -70,7 +70,7 @@ __global__ void __launch_bounds__(LN_THREADS) layernorm_fwd_kernel(const T* __re
     T* yr = y + (int64_t)row * cols;
 #pragma unroll
     for (int k = 0; k < LN_VPT; ++k) {
-      int i = threadIdx.x + k * LN_THREADS;
+      int i = threadIdx.x + k * THREADS;
       if (i < nvec) {
         const T* e = reinterpret_cast<const T*>(&v[k]);
         Bytes16 o;
@@ -91,8 +91,8 @@ __global__ void __launch_bounds__(LN_THREADS) layernorm_fwd_kernel(const T* __re
 
 // Backward: dx per row; dgamma / dbeta partial sums per CTA (each thread owns fixed columns),
 // written to part[gridDim.x][2][cols] and reduced by a second kernel.
-template <typename T>
-__global__ void __launch_bounds__(LN_THREADS) layernorm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x,
+template <typename T, int THREADS>
+__global__ void __launch_bounds__(THREADS) layernorm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x,
                                                                     const void* __restrict__ gamma, int pdtype,
                                                                     const float* __restrict__ mean, const float* __restrict__ rstd,
                                                                     T* __restrict__ dx, float* __restrict__ part, int rows, int cols) {
@@ -114,7 +114,7 @@ __global__ void __launch_bounds__(LN_THREADS) layernorm_bwd_kernel(const T* __re
     float s1 = 0.0f, s2 = 0.0f;    // sum(g*dy), sum(g*dy*xhat)
 #pragma unroll
     for (int k = 0; k < LN_VPT; ++k) {
-      int i = threadIdx.x + k * LN_THREADS;
+      int i = threadIdx.x + k * THREADS;
       if (i < nvec) {
         vx[k] = reinterpret_cast<const Bytes16*>(xr)[i];
         vd[k] = reinterpret_cast<const Bytes16*>(dyr)[i];
@@ -141,7 +141,7 @@ __global__ void __launch_bounds__(LN_THREADS) layernorm_bwd_kernel(const T* __re
     T* dxr = dx + (int64_t)row * cols;
 #pragma unroll
     for (int k = 0; k < LN_VPT; ++k) {
-      int i = threadIdx.x + k * LN_THREADS;
+      int i = threadIdx.x + k * THREADS;
       if (i < nvec) {
         const T* ex = reinterpret_cast<const T*>(&vx[k]);
         const T* ed = reinterpret_cast<const T*>(&vd[k]);
@@ -162,7 +162,7 @@ __global__ void __launch_bounds__(LN_THREADS) layernorm_bwd_kernel(const T* __re
   float* pb = pg + cols;
 #pragma unroll
   for (int k = 0; k < LN_VPT; ++k) {
-    int i = threadIdx.x + k * LN_THREADS;
+    int i = threadIdx.x + k * THREADS;
     if (i < nvec) {
 #pragma unroll
       for (int j = 0; j < N; ++j) {
@@ -173,23 +173,39 @@ __global__ void __launch_bounds__(LN_THREADS) layernorm_bwd_kernel(const T* __re
   }
 }
 
-__global__ void layernorm_reduce_kernel(const float* __restrict__ part, int nparts, int cols, void* dgamma, void* dbeta, int pdtype) {
-  int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= cols) return;
+// Column sums of the per-CTA partials: a block of 32 x 8 threads owns 32 columns; the 8 thread rows
+// stride over the partials (coalesced 128-byte reads) and are combined through shared memory.
+__global__ void __launch_bounds__(256) layernorm_reduce_kernel(const float* __restrict__ part, int nparts, int cols, void* dgamma,
+                                                                void* dbeta, int pdtype) {
+  __shared__ float sg[8][33], sb[8][33];
+  const int cx = threadIdx.x & 31, ry = threadIdx.x >> 5;
+  const int c = blockIdx.x * 32 + cx;
   float g = 0.0f, b = 0.0f;
-  for (int i = 0; i < nparts; ++i) {
-    g += part[(int64_t)i * 2 * cols + c];
-    b += part[(int64_t)i * 2 * cols + cols + c];
+  if (c < cols) {
+    for (int i = ry; i < nparts; i += 8) {
+      g += part[(int64_t)i * 2 * cols + c];
+      b += part[(int64_t)i * 2 * cols + cols + c];
+    }
   }
-  if (pdtype == DT_F32) {
-    reinterpret_cast<float*>(dgamma)[c] = g;
-    if (dbeta) reinterpret_cast<float*>(dbeta)[c] = b;
-  } else if (pdtype == DT_BF16) {
-    reinterpret_cast<__nv_bfloat16*>(dgamma)[c] = __float2bfloat16_rn(g);
-    if (dbeta) reinterpret_cast<__nv_bfloat16*>(dbeta)[c] = __float2bfloat16_rn(b);
-  } else {
-    reinterpret_cast<__half*>(dgamma)[c] = __float2half_rn(g);
-    if (dbeta) reinterpret_cast<__half*>(dbeta)[c] = __float2half_rn(b);
+  sg[ry][cx] = g;
+  sb[ry][cx] = b;
+  __syncthreads();
+  if (ry == 0 && c < cols) {
+#pragma unroll
+    for (int k = 1; k < 8; ++k) {
+      g += sg[k][cx];
+      b += sb[k][cx];
+    }
+    if (pdtype == DT_F32) {
+      reinterpret_cast<float*>(dgamma)[c] = g;
+      if (dbeta) reinterpret_cast<float*>(dbeta)[c] = b;
+    } else if (pdtype == DT_BF16) {
+      reinterpret_cast<__nv_bfloat16*>(dgamma)[c] = __float2bfloat16_rn(g);
+      if (dbeta) reinterpret_cast<__nv_bfloat16*>(dbeta)[c] = __float2bfloat16_rn(b);
+    } else {
+      reinterpret_cast<__half*>(dgamma)[c] = __float2half_rn(g);
+      if (dbeta) reinterpret_cast<__half*>(dbeta)[c] = __float2half_rn(b);
+    }
   }
 }
 
@@ -332,15 +348,20 @@ MSAMP_API int msamp_layernorm_fwd(const void* x, const void* gamma, const void* 
   MSAMP_REQUIRE(cols <= msamp_layernorm_max_cols(dtype) && cols % (dtype == DT_F32 ? 4 : 8) == 0,
                 "layernorm: cols=%d must be a multiple of the 16-byte vector and at most %d", cols, msamp_layernorm_max_cols(dtype));
   if (rows == 0) return MSAMP_OK;
-  int grid = rows < msamp_sm_count() * 8 ? rows : msamp_sm_count() * 8;
+  const bool narrow = cols <= 128 * LN_VPT * (dtype == DT_F32 ? 4 : 8);
+  int cap = msamp_sm_count() * (narrow ? 16 : 8);
+  int grid = rows < cap ? rows : cap;
   MSAMP_DISPATCH_HP(dtype, T, {
-    layernorm_fwd_kernel<T><<<grid, LN_THREADS, 0, stream>>>((const T*)x, gamma, beta, pdtype, (T*)y, mean, rstd, rows, cols, eps);
+    if (narrow)
+      layernorm_fwd_kernel<T, 128><<<grid, 128, 0, stream>>>((const T*)x, gamma, beta, pdtype, (T*)y, mean, rstd, rows, cols, eps);
+    else
+      layernorm_fwd_kernel<T, 256><<<grid, 256, 0, stream>>>((const T*)x, gamma, beta, pdtype, (T*)y, mean, rstd, rows, cols, eps);
   });
   return msamp_check_launch("msamp_layernorm_fwd");
 }
 
 // part: scratch of msamp_layernorm_bwd_parts() * 2 * cols floats owned by the caller.
-MSAMP_API int msamp_layernorm_bwd_parts() { return msamp_sm_count() * 2; }
+MSAMP_API int msamp_layernorm_bwd_parts() { return msamp_sm_count() * 4; }
 
 MSAMP_API int msamp_layernorm_bwd(const void* dy, const void* x, const void* gamma, int dtype, int pdtype, const float* mean,
                                   const float* rstd, void* dx, void* dgamma, void* dbeta, float* part, int rows, int cols,
@@ -350,10 +371,14 @@ MSAMP_API int msamp_layernorm_bwd(const void* dy, const void* x, const void* gam
   MSAMP_REQUIRE(cols <= msamp_layernorm_max_cols(dtype) && cols % (dtype == DT_F32 ? 4 : 8) == 0, "layernorm_bwd: unsupported cols=%d", cols);
   int nparts = msamp_layernorm_bwd_parts();
   int grid = rows < nparts ? rows : nparts;
+  const bool narrow = cols <= 128 * LN_VPT * (dtype == DT_F32 ? 4 : 8);
   MSAMP_DISPATCH_HP(dtype, T, {
-    layernorm_bwd_kernel<T><<<grid, LN_THREADS, 0, stream>>>((const T*)dy, (const T*)x, gamma, pdtype, mean, rstd, (T*)dx, part, rows, cols);
+    if (narrow)
+      layernorm_bwd_kernel<T, 128><<<grid, 128, 0, stream>>>((const T*)dy, (const T*)x, gamma, pdtype, mean, rstd, (T*)dx, part, rows, cols);
+    else
+      layernorm_bwd_kernel<T, 256><<<grid, 256, 0, stream>>>((const T*)dy, (const T*)x, gamma, pdtype, mean, rstd, (T*)dx, part, rows, cols);
   });
-  layernorm_reduce_kernel<<<(cols + 127) / 128, 128, 0, stream>>>(part, grid, cols, dgamma, dbeta, pdtype);
+  layernorm_reduce_kernel<<<(cols + 31) / 32, 256, 0, stream>>>(part, grid, cols, dgamma, dbeta, pdtype);
   return msamp_check_launch("msamp_layernorm_bwd");
 }
 

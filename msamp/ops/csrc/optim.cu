@@ -177,15 +177,13 @@ __device__ __forceinline__ Elem adam_elem(const AdamTensor& t, float p, float g,
   return e;
 }
 
-// block -> (tensor, chunk) map: work[2*b] = tensor index, work[2*b+1] = chunk index
-template <int STAGE>
-__global__ void __launch_bounds__(kAdamThreads) lbadam_kernel(AdamTensor* tensors, const int* __restrict__ work) {
-  __shared__ float red[32];
-  AdamTensor& t = tensors[work[2 * blockIdx.x]];
-  const int chunk = work[2 * blockIdx.x + 1];
-  const int64_t begin = (int64_t)chunk * kChunk;
-  const int64_t end = (begin + kChunk < t.n) ? begin + kChunk : t.n;
-
+// Work of one block on elements [begin, end) of tensor t.  The storage codes are template
+// parameters for the combinations that dominate real models (the switches in load8/store8 then
+// fold away and the four loads of an iteration are issued back to back); -1 means "read the code
+// from the descriptor at run time".
+template <int STAGE, int PS, int GS, int MS, int VS>
+__device__ __forceinline__ void adam_block(AdamTensor& t, int64_t begin, int64_t end, float* red) {
+  const int p_st = PS >= 0 ? PS : t.p_st, g_st = GS >= 0 ? GS : t.g_st, m_st = MS >= 0 ? MS : t.m_st, v_st = VS >= 0 ? VS : t.v_st;
   const float psi = t.p_scale_inv ? *t.p_scale_inv : 1.0f;
   const float gsi = t.g_scale_inv ? *t.g_scale_inv : 1.0f;
   const float msi = t.m_scale_inv ? *t.m_scale_inv : 1.0f;
@@ -193,21 +191,22 @@ __global__ void __launch_bounds__(kAdamThreads) lbadam_kernel(AdamTensor* tensor
 
   float ps = 1.0f, ms = 1.0f, vs = 1.0f;
   if (STAGE == 2) {
-    if (t.p_scale) ps = msamp_compute_scale(t.red[0], *t.p_scale, st_max(t.p_st), 0);
-    if (t.m_scale) ms = t.tensor_scale ? msamp_compute_scale(t.red[1], 1.0f, st_max(t.m_st), 0) : 1.0f;
-    if (t.v_scale) vs = t.tensor_scale ? msamp_compute_scale(t.red[2], 1.0f, st_max(t.v_st), 0) : 1.0f;
+    if (t.p_scale) ps = msamp_compute_scale(t.red[0], *t.p_scale, st_max(p_st), 0);
+    if (t.m_scale) ms = t.tensor_scale ? msamp_compute_scale(t.red[1], 1.0f, st_max(m_st), 0) : 1.0f;
+    if (t.v_scale) vs = t.tensor_scale ? msamp_compute_scale(t.red[2], 1.0f, st_max(v_st), 0) : 1.0f;
   }
 
   const bool vec = ((reinterpret_cast<uintptr_t>(t.p) | reinterpret_cast<uintptr_t>(t.g) | reinterpret_cast<uintptr_t>(t.m) |
                      reinterpret_cast<uintptr_t>(t.v)) & 15) == 0;
   float ap = 0.0f, am = 0.0f, av = 0.0f;
   if (vec) {
+#pragma unroll 2
     for (int64_t i = begin + (int64_t)threadIdx.x * 8; i + 8 <= end; i += (int64_t)kAdamThreads * 8) {
       float p[8], g[8], m[8], v[8];
-      load8(t.p, t.p_st, i, p);
-      load8(t.g, t.g_st, i, g);
-      load8(t.m, t.m_st, i, m);
-      load8(t.v, t.v_st, i, v);
+      load8(t.p, p_st, i, p);
+      load8(t.g, g_st, i, g);
+      load8(t.m, m_st, i, m);
+      load8(t.v, v_st, i, v);
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         Elem e = adam_elem(t, p[j], g[j], m[j], v[j], psi, gsi, msi, vsi);
@@ -222,9 +221,9 @@ __global__ void __launch_bounds__(kAdamThreads) lbadam_kernel(AdamTensor* tensor
         }
       }
       if (STAGE == 2) {
-        store8(t.p, t.p_st, i, p);
-        store8(t.m, t.m_st, i, m);
-        store8(t.v, t.v_st, i, v);
+        store8(t.p, p_st, i, p);
+        store8(t.m, m_st, i, m);
+        store8(t.v, v_st, i, v);
       }
     }
   }
@@ -232,16 +231,15 @@ __global__ void __launch_bounds__(kAdamThreads) lbadam_kernel(AdamTensor* tensor
     // tail of the chunk (or the whole chunk when the pointers are not 16-byte aligned)
     int64_t tail = vec ? begin + ((end - begin) / 8) * 8 : begin;
     for (int64_t i = tail + threadIdx.x; i < end; i += kAdamThreads) {
-      Elem e = adam_elem(t, load1(t.p, t.p_st, i), load1(t.g, t.g_st, i), load1(t.m, t.m_st, i), load1(t.v, t.v_st, i), psi, gsi,
-                         msi, vsi);
+      Elem e = adam_elem(t, load1(t.p, p_st, i), load1(t.g, g_st, i), load1(t.m, m_st, i), load1(t.v, v_st, i), psi, gsi, msi, vsi);
       if (STAGE == 1) {
         ap = fmaxf(ap, abs_nan_to_inf(e.p));
         am = fmaxf(am, abs_nan_to_inf(e.m));
         av = fmaxf(av, abs_nan_to_inf(e.v));
       } else {
-        store1(t.p, t.p_st, i, e.p * ps);
-        store1(t.m, t.m_st, i, e.m * ms);
-        store1(t.v, t.v_st, i, e.v * vs);
+        store1(t.p, p_st, i, e.p * ps);
+        store1(t.m, m_st, i, e.m * ms);
+        store1(t.v, v_st, i, e.v * vs);
       }
     }
   }
@@ -255,6 +253,29 @@ __global__ void __launch_bounds__(kAdamThreads) lbadam_kernel(AdamTensor* tensor
       atomic_max_nonneg(&t.red[2], av);
     }
   }
+}
+
+// block -> (tensor, chunk) map: work[2*b] = tensor index, work[2*b+1] = chunk index
+template <int STAGE>
+__global__ void __launch_bounds__(kAdamThreads) lbadam_kernel(AdamTensor* tensors, const int* __restrict__ work) {
+  __shared__ float red[32];
+  AdamTensor& t = tensors[work[2 * blockIdx.x]];
+  const int chunk = work[2 * blockIdx.x + 1];
+  const int64_t begin = (int64_t)chunk * kChunk;
+  const int64_t end = (begin + kChunk < t.n) ? begin + kChunk : t.n;
+  const int combo = (t.p_st << 9) | (t.g_st << 6) | (t.m_st << 3) | t.v_st;
+#define MSAMP_COMBO(P, G, M, V) \
+  case ((P << 9) | (G << 6) | (M << 3) | V): adam_block<STAGE, P, G, M, V>(t, begin, end, red); break;
+  switch (combo) {
+    MSAMP_COMBO(ST_F16, ST_E4M3, ST_E4M3, ST_F16)      // FP8-linear weights at O2
+    MSAMP_COMBO(ST_F32, ST_F32, ST_E4M3, ST_F16)       // biases / LayerNorm at O2
+    MSAMP_COMBO(ST_BF16, ST_BF16, ST_E4M3, ST_F16)     // bf16 embeddings at O2
+    MSAMP_COMBO(ST_F16, ST_E4M3, ST_F32, ST_F32)       // the same three at O1
+    MSAMP_COMBO(ST_F32, ST_F32, ST_F32, ST_F32)
+    MSAMP_COMBO(ST_BF16, ST_BF16, ST_F32, ST_F32)
+    default: adam_block<STAGE, -1, -1, -1, -1>(t, begin, end, red); break;
+  }
+#undef MSAMP_COMBO
 }
 
 // After stage 2 has consumed the old inverse scales everywhere: publish the new metas.

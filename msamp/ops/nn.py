@@ -149,6 +149,61 @@ class _AttentionFn(torch.autograd.Function):
         return dq, dk, dv, None, None, None
 
 
+class _AttentionPackedFn(torch.autograd.Function):
+    """Attention on a fused ``[B, S, 3, heads, d]`` QKV tensor; the gradient comes back in the same packed layout.
+
+    Taking the packed tensor as the one autograd input (instead of three ``select`` views of it) keeps
+    autograd from materialising three zero-filled full-size gradients and adding them up.
+    """
+    @staticmethod
+    def forward(ctx, qkv, causal, scale):
+        B, S, _, nh, d = qkv.shape
+        q, k, v = qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2]
+        o = torch.empty((B, S, nh, d), dtype=qkv.dtype, device=qkv.device)
+        lse = torch.empty((B, nh, S), dtype=torch.float32, device=qkv.device)
+        st = _strides(q) + _strides(k) + _strides(v) + _strides(o) + [0] * 12
+        native.check(
+            native.lib().msamp_attention_fwd(
+                native.ptr(q), native.ptr(k), native.ptr(v), native.ptr(o), native.ptr(lse), _i64x24(*st), B, nh, S, d,
+                ctypes.c_float(scale), int(causal), native.stream()
+            ), 'attention_fwd'
+        )
+        ctx.save_for_backward(qkv, o, lse)
+        ctx.causal, ctx.scale = causal, scale
+        return o
+
+    @staticmethod
+    def backward(ctx, d_o):
+        qkv, o, lse = ctx.saved_tensors
+        B, S, _, nh, d = qkv.shape
+        q, k, v = qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2]
+        if d_o.stride(3) != 1 or any(s % 8 for s in d_o.stride()[:3]):
+            d_o = d_o.contiguous()
+        dqkv = torch.empty_like(qkv)
+        dq, dk, dv = dqkv[:, :, 0], dqkv[:, :, 1], dqkv[:, :, 2]
+        delta = torch.empty((B, nh, S), dtype=torch.float32, device=qkv.device)
+        st = _strides(q) + _strides(k) + _strides(v) + _strides(o) + _strides(d_o) + _strides(dq) + _strides(dk) + _strides(dv)
+        native.check(
+            native.lib().msamp_attention_bwd(
+                native.ptr(q), native.ptr(k), native.ptr(v), native.ptr(o), native.ptr(lse), native.ptr(d_o), native.ptr(dq),
+                native.ptr(dk), native.ptr(dv), native.ptr(delta), _i64x24(*st), B, nh, S, d, ctypes.c_float(ctx.scale), int(ctx.causal),
+                native.stream()
+            ), 'attention_bwd'
+        )
+        return dqkv, None, None
+
+
+def attention_qkv(qkv, causal=True, scale=None):
+    """Self-attention on a fused ``[B, S, 3, heads, head_dim]`` projection output; returns ``[B, S, heads, head_dim]``."""
+    d = qkv.shape[-1]
+    scale = 1.0 / math.sqrt(d) if scale is None else scale
+    if _use_native(qkv):
+        if qkv.dtype != torch.bfloat16 or d not in (64, 128) or not qkv.is_contiguous() or qkv.data_ptr() % 16:
+            raise RuntimeError(f'attention_qkv: CUDA kernel needs contiguous bf16 with head_dim 64/128 (got {qkv.dtype}, {d})')
+        return _AttentionPackedFn.apply(qkv, causal, scale)
+    return attention(qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2], causal=causal, scale=scale)
+
+
 def attention(q, k, v, causal=True, scale=None, grad_layout='separate'):
     """Softmax attention on ``[B, S, heads, head_dim]`` tensors; returns ``[B, S, heads, head_dim]``.
 

@@ -274,6 +274,11 @@ def test_attention(d, S, causal):
     assert (o.float() - r).abs().max().item() <= 3e-2
     err = (qkv.grad.float() - ref_in.grad).abs().max().item()
     assert err <= 6e-2 * max(1.0, ref_in.grad.abs().max().item()), err
+    # the packed entry point gives the same numbers
+    qkv3 = qkv.detach().clone().requires_grad_()
+    o3 = K.attention_qkv(qkv3, causal=causal)
+    o3.backward(do)
+    assert torch.equal(o3, o) and torch.equal(qkv3.grad, qkv.grad)
     # separate tensors / separate gradients
     q2, k2, v2 = (t.detach().contiguous().requires_grad_() for t in (q, k, v))
     o2 = K.attention(q2, k2, v2, causal=causal)
