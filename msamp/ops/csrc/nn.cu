@@ -2,6 +2,7 @@
 // (tanh form), and fused softmax cross-entropy (loss + in-place logit gradient).  All are
 // HBM-bandwidth bound: one pass over the data with 16-byte accesses, statistics in fp32.
 #include "common.cuh"
+#include "msamp_noalloc.h"
 
 namespace {
 
@@ -380,6 +381,54 @@ MSAMP_API int msamp_layernorm_bwd(const void* dy, const void* x, const void* gam
   });
   layernorm_reduce_kernel<<<(cols + 31) / 32, 256, 0, stream>>>(part, grid, cols, dgamma, dbeta, pdtype);
   return msamp_check_launch("msamp_layernorm_bwd");
+}
+
+// ---- allocation-free LayerNorm backward ---------------------------------------------------------
+// Scratch for the per-CTA partial sums of dgamma / dbeta lives in this file-scope array instead of
+// caller-provided memory.  Every device that loads the library holds these 4 MiB until exit.
+static __device__ __align__(256) float g_ln_static_part[MSAMP_LN_STATIC_PARTS * 2 * MSAMP_LN_STATIC_MAX_COLS];
+
+MSAMP_API int msamp_layernorm_bwd_static(const void* dy, const void* x, const void* gamma, int dtype, int pdtype, const float* mean,
+                                         const float* rstd, void* dx, void* dgamma, void* dbeta, int rows, int cols, void* stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  MSAMP_REQUIRE(rows > 0 && cols > 0, "layernorm_bwd_static: bad shape");
+  if (cols > MSAMP_LN_STATIC_MAX_COLS) {
+    msamp_set_error("layernorm_bwd_static: cols=%d exceeds the static scratch capacity of %d columns; use msamp_layernorm_bwd "
+                    "with caller-provided scratch", cols, MSAMP_LN_STATIC_MAX_COLS);
+    return MSAMP_ECAPACITY;
+  }
+  MSAMP_REQUIRE(cols <= msamp_layernorm_max_cols(dtype) && cols % (dtype == DT_F32 ? 4 : 8) == 0,
+                "layernorm_bwd_static: unsupported cols=%d", cols);
+  // In host code the array's name is only a handle; the device address has to be asked for, once
+  // per device, with that device current.
+  static float* scratch_of_device[64] = {nullptr};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+    msamp_set_error("layernorm_bwd_static: cannot identify the current device");
+    return MSAMP_EINVAL;
+  }
+  if (scratch_of_device[dev] == nullptr) {
+    float* ptr = nullptr;
+    cudaError_t e = cudaGetSymbolAddress((void**)&ptr, g_ln_static_part);
+    if (e != cudaSuccess || ptr == nullptr) {
+      msamp_set_error("layernorm_bwd_static: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+      return MSAMP_ELAUNCH;
+    }
+    scratch_of_device[dev] = ptr;
+  }
+  float* part = scratch_of_device[dev];
+  const int grid = rows < MSAMP_LN_STATIC_PARTS ? rows : MSAMP_LN_STATIC_PARTS;
+  // Each of the `grid` CTAs overwrites its whole slice of the scratch and the reduction reads
+  // exactly those slices, so leftovers of an earlier call never need clearing.
+  const bool narrow = cols <= 128 * LN_VPT * (dtype == DT_F32 ? 4 : 8);
+  MSAMP_DISPATCH_HP(dtype, T, {
+    if (narrow)
+      layernorm_bwd_kernel<T, 128><<<grid, 128, 0, stream>>>((const T*)dy, (const T*)x, gamma, pdtype, mean, rstd, (T*)dx, part, rows, cols);
+    else
+      layernorm_bwd_kernel<T, 256><<<grid, 256, 0, stream>>>((const T*)dy, (const T*)x, gamma, pdtype, mean, rstd, (T*)dx, part, rows, cols);
+  });
+  layernorm_reduce_kernel<<<(cols + 31) / 32, 256, 0, stream>>>(part, grid, cols, dgamma, dbeta, pdtype);
+  return msamp_check_launch("msamp_layernorm_bwd_static");
 }
 
 MSAMP_API int msamp_gelu_fwd(const void* x, void* y, int64_t n, int dtype, void* stream_) {
