@@ -89,9 +89,15 @@ class TensorDist:
         if world == 1 or len(tensors) == 0:
             return
         if Dtypes.is_fp8_qtype(tensors[0].qtype):
-            cls.all_reduce(tensors, dist.ReduceOp.SUM, bucket_size, group=group)
-            for t in tensors:
-                t.div_(world)
+            first = tensors[0].value if isinstance(tensors[0], ScalingTensor) else tensors[0]
+            if first.is_cuda and DistUtil.backend(group) == 'nccl':
+                # NCCL sums the FP8 numbers; the division goes into scale_inv (the reference's rule).
+                cls.all_reduce(tensors, dist.ReduceOp.SUM, bucket_size, group=group)
+                for t in tensors:
+                    t.div_(world)
+            else:
+                # emulated collective: the mean is formed in fp32 and rounded once, so it cannot saturate
+                cls.all_reduce(tensors, dist.ReduceOp.AVG, bucket_size, group=group)
         else:
             op = dist.ReduceOp.AVG if DistUtil.backend(group) == 'nccl' else dist.ReduceOp.SUM
             cls.all_reduce(tensors, op, bucket_size, group=group)

@@ -146,7 +146,7 @@ class _FP8GemmFunction(torch.autograd.Function):
                 # The FP8 DDP reducer quantises whole buckets with a cross-rank scale.
                 wgrad.meta = wg_meta
             else:
-                wgrad = _quantize_wgrad(wgrad, wg_meta)
+                wgrad = _quantize_wgrad(wgrad, wg_meta, out=getattr(weight, '_grad_out', None))
             if ctx.return_wgrad:
                 flat = wgrad.value.reshape(-1)
                 pad = weight._flat_param._padded
@@ -160,13 +160,20 @@ class _FP8GemmFunction(torch.autograd.Function):
         return dx, wgrad_ret, None, None, dbias
 
 
-def _quantize_wgrad(wgrad, meta):
-    """High-precision wgrad whose amax is already in ``meta.amax[0]`` → e4m3 ScalingTensor (in-time scale, DP-synced)."""
+def _quantize_wgrad(wgrad, meta, out=None):
+    """High-precision wgrad whose amax is already in ``meta.amax[0]`` → e4m3 ScalingTensor with an in-time scale.
+
+    Without ``out`` the amax is MAX-reduced over the data-parallel group first so that all ranks share
+    one scale and the bytes can be summed directly (the reference's rule).  With ``out`` – a slice of a
+    sharded optimizer's flat symmetric gradient buffer – each rank keeps its own scale: the fused
+    reduce kernel dequantises every rank's bytes with that rank's scale, so no collective runs here.
+    """
     amax0 = meta.amax[0]
-    if DistUtil.get_world_size(meta.group) > 1:
+    if out is None and DistUtil.get_world_size(meta.group) > 1:
         dist.all_reduce(amax0, op=dist.ReduceOp.MAX, group=meta.group)
-    value = _k.cast_to_fp8(wgrad, E4M3, meta.scale, scale_inv_out=meta.scale_inv, amax_in=amax0)
-    return ScalingTensor(value, meta)
+    value = _k.cast_to_fp8(wgrad, E4M3, meta.scale, scale_inv_out=meta.scale_inv, amax_in=amax0,
+                           out=None if out is None else out.view(-1))
+    return ScalingTensor(value.view(wgrad.shape), meta)
 
 
 class FunctionalOverider:

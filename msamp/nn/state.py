@@ -90,6 +90,26 @@ class ModelState:
             m.locked = True
         return dict(qtype=qtype, scales=scales, scales_inv=scales_inv, amaxs=amaxs.view(n, window), amax_counters=counters)
 
+    def rebase(self, key, field, storage):
+        """Move the flat buffer ``field`` of meta kind ``key`` into ``storage`` (same dtype and size, e.g. symmetric
+        memory) and re-point every registered meta at it; values are preserved."""
+        flat = self._flattened_scaling_metas[key]
+        old = flat[field]
+        new = storage.view(old.shape)
+        new.copy_(old)
+        attr = {'scales': 'scale', 'scales_inv': 'scale_inv', 'amaxs': 'amax', 'amax_counters': 'amax_counter'}[field]
+        for i, metas in enumerate(self._local_scaling_metas.values()):
+            t = getattr(metas[key], attr)
+            t.data = new[i].view(t.shape)
+        flat[field] = new
+
+    def index_of(self, scaling_metas):
+        """Position of a layer's meta dict in the flat buffers (registration order), or -1."""
+        for i, metas in enumerate(self._local_scaling_metas.values()):
+            if metas is scaling_metas:
+                return i
+        return -1
+
     def check_metas_in_flat(self, scaling_metas):
         """Raise if a layer's metas no longer alias the flat buffers."""
         if self._flattened_scaling_metas is None:

@@ -87,16 +87,20 @@ def _emulate_to_fp8(x, scale, qtype):
     return y.to(_F8[qtype]).view(torch.uint8)
 
 
-def cast_to_fp8(x, qtype, scale, amax_out=None, scale_inv_out=None, amax_in=None, prescale=1.0):
+def cast_to_fp8(x, qtype, scale, amax_out=None, scale_inv_out=None, amax_in=None, prescale=1.0, out=None):
     """Quantise ``x`` (fp32/fp16/bf16) to FP8 bytes with the given scale.
 
     Optionally records ``max|x|`` in ``amax_out`` and ``1/scale`` in ``scale_inv_out`` in the same pass.
     With ``amax_in`` (a 0-d tensor already holding ``max|x|``, e.g. from a GEMM epilogue) the scale is
     first recomputed from it by the power-of-two rule, times ``prescale``, and written to ``scale``.
+    ``out`` (uint8, same number of elements, contiguous) receives the bytes when given.
     """
+    if out is not None:
+        assert out.dtype == torch.uint8 and out.numel() == x.numel() and out.is_contiguous() and out.device == x.device
     if x.is_cuda:
         x = x.contiguous()
-        out = torch.empty(x.shape, dtype=torch.uint8, device=x.device)
+        if out is None:
+            out = torch.empty(x.shape, dtype=torch.uint8, device=x.device)
         native.check(
             native.lib().msamp_cast_to_fp8(
                 native.ptr(x), native.i64(x.numel()), native.dt(x.dtype), native.ptr(out), native.fmt(qtype), native.ptr(scale),
@@ -111,7 +115,11 @@ def cast_to_fp8(x, qtype, scale, amax_out=None, scale_inv_out=None, amax_in=None
         amax(x, out=amax_out)
     if scale_inv_out is not None:
         torch.reciprocal(scale, out=scale_inv_out)
-    return _emulate_to_fp8(x, scale, qtype)
+    res = _emulate_to_fp8(x, scale, qtype)
+    if out is not None:
+        out.copy_(res.view_as(out))
+        return out
+    return res
 
 
 def cast_transpose_fp8(x, qtype, scale, amax_out=None, need_rowmajor=True, scale_inv_out=None, amax_in=None):

@@ -1,0 +1,347 @@
+"""Sharded data parallelism for FP8 models (ZeRO stages 1/2 semantics, plus a replicated stage 0).
+
+Ownership follows the reference's FP8 ZeRO optimizer (msamp/deepspeed/runtime/zero/fp8_stage_1_and_2.py:77-110):
+whole tensors are assigned greedily to the least-loaded rank; the owner keeps the scaled-fp16 master
+weight and the low-bit Adam moments; every rank keeps the e4m3 weights (flat buffer) and produces e4m3
+weight gradients (flat buffer).  What differs is how data moves:
+
+* both flat buffers live in symmetric memory, so one fused kernel per step replaces the per-parameter
+  amax all-reduce (X12) and per-parameter ``ncclReduce`` (X13): each owner pulls its tensors from all
+  peers over NVLink, dequantises with each peer's own scale, averages in fp32 and rounds once;
+* after the partitioned LBAdam step one fused kernel casts each master to e4m3 and stores it straight
+  into every peer's weight buffer with its ``scale_inv`` (replaces X14 + X15).
+
+On backends without CUDA (gloo tests) the same algorithm runs with emulated collectives.
+"""
+import ctypes
+
+import torch
+import torch.distributed as dist
+
+from msamp.common.dtype import Dtypes
+from msamp.common.tensor import ScalingMeta, ScalingTensor
+from msamp.common.utils.dist import DistUtil
+from msamp.nn import ScalingParameter, model_state
+
+E4M3 = Dtypes.kfloat8_e4m3
+
+
+def partition_tensors(sizes, world):
+    """Greedy whole-tensor partition: each tensor (in order) goes to the currently least-loaded rank.
+
+    Returns ``owners`` (list of rank per tensor). Ties go to the lowest rank, so every process computes
+    the same answer without communicating.
+    """
+    load = [0] * world
+    owners = []
+    for n in sizes:
+        r = min(range(world), key=lambda k: (load[k], k))
+        owners.append(r)
+        load[r] += n
+    return owners
+
+
+def _pad16(n):
+    return (n + 15) // 16 * 16
+
+
+class ZeroShardedOptimizer:
+    """Wraps an LB optimizer: reduce gradients to their owners, update the owned shard, publish the new weights.
+
+    Args:
+        model: model converted by ``msamp.initialize`` / ``LinearReplacer`` (FP8Linear weights are ScalingParameters).
+        optimizer: the LBAdam/LBAdamW/DSAdam built for it.
+        stage: 0 = replicated states (FP8 all-reduce), 1 or 2 = sharded master weights and moments.
+        group: data-parallel process group.
+    """
+    def __init__(self, model, optimizer, stage=2, group=None, wait_seconds=30.0):
+        self.model, self.optimizer, self.stage, self.group = model, optimizer, stage, group
+        self.world = DistUtil.get_world_size(group)
+        self.rank = DistUtil.get_rank(group)
+        self.wait_seconds = wait_seconds
+        params = [p for p in model.parameters() if isinstance(p, ScalingParameter)]
+        self.fp8_params = params
+        self.hp_params = [p for p in model.parameters() if not isinstance(p, ScalingParameter)]
+        sizes = [p.numel() for p in params]
+        self.owners = partition_tensors(sizes, self.world)
+        offs = [0]
+        for n in sizes:
+            offs.append(offs[-1] + _pad16(n))
+        self.offsets = offs
+        self.n = len(params)
+        self.device = params[0].device if params else torch.device('cpu')
+        self.native = self.device.type == 'cuda' and self.world > 1
+        self.sharded = stage >= 1 and self.world > 1
+        self._build_buffers()
+        if self.sharded:
+            self._shard_states()
+
+    # ------------------------------------------------------------------ set-up
+    def _alloc(self, nbytes):
+        if self.native:
+            from msamp.parallel.symm import SymmetricBuffer
+            return SymmetricBuffer(max(nbytes, 16), self.group)
+        return None
+
+    def _build_buffers(self):
+        total = self.offsets[-1]
+        n = self.n
+        if self.native:
+            from msamp.parallel.symm import FlagPad
+            self.g_buf = self._alloc(total)
+            self.g_meta = self._alloc(3 * n * 4)
+            self.flags = FlagPad(self.group)
+            g_flat = self.g_buf.view(torch.uint8)
+            g_meta = self.g_meta.view(torch.float32).view(3, n)
+        else:
+            g_flat = torch.zeros(max(total, 1), dtype=torch.uint8, device=self.device)
+            g_meta = torch.zeros(3, max(n, 1), dtype=torch.float32, device=self.device)
+        g_meta[0].fill_(1.0)
+        self.g_flat, self.g_meta_t = g_flat, g_meta
+        # gradient metas: re-home scale_inv / amax of every layer's 'wgrad' meta into the meta rows
+        self.meta_index = []
+        for i, p in enumerate(self.fp8_params):
+            meta = p._scaling_metas['wgrad']
+            if meta.window_size != 1:
+                raise RuntimeError('sharded FP8 gradients need a wgrad window of 1')
+            was_locked, meta.locked = meta.locked, False
+            si, am = g_meta[0, i:i + 1].view(()), g_meta[1, i:i + 1]
+            si.copy_(meta.scale_inv)
+            am.copy_(meta.amax)
+            meta.scale_inv, meta.amax = si, am
+            meta.locked = was_locked
+            p._grad_out = g_flat[self.offsets[i]:self.offsets[i] + p.numel()].view(p.shape)
+        # the metas no longer alias model_state's flat wgrad buffers; tell model_state so its aliasing check passes
+        flat = model_state.flattened_scaling_metas
+        if flat is not None and 'wgrad' in flat:
+            flat['wgrad'] = dict(flat['wgrad'], scales_inv=g_meta[0], amaxs=g_meta[1].view(-1, 1), _external=True)
+        work = []
+        chunk = 16384
+        for i, p in enumerate(self.fp8_params):
+            if self.owners[i] == self.rank:
+                nb = _pad16(p.numel())
+                work += [(i, c) for c in range((nb + chunk - 1) // chunk)]
+        self.n_work = len(work)
+        self.work_t = torch.tensor(work if work else [(0, 0)], dtype=torch.int32, device=self.device).reshape(-1)
+        self.offsets_t = torch.tensor(self.offsets, dtype=torch.int64, device=self.device)
+        self.owned = [i for i in range(n) if self.owners[i] == self.rank]
+        self.owned_t = torch.tensor(self.owned if self.owned else [0], dtype=torch.int32, device=self.device)
+        self.all_t = torch.arange(max(n, 1), dtype=torch.int32, device=self.device)
+
+    def _shard_states(self):
+        """FP8 weights in a flat (symmetric) buffer on every rank; scaled-fp16 masters and moments only on the owner."""
+        total, n = self.offsets[-1], self.n
+        if self.native:
+            self.w_buf = self._alloc(total)
+            self.w_meta = self._alloc(3 * n * 4)
+            w_flat = self.w_buf.view(torch.uint8)
+            w_meta = self.w_meta.view(torch.float32).view(3, n)
+        else:
+            w_flat = torch.zeros(max(total, 1), dtype=torch.uint8, device=self.device)
+            w_meta = torch.zeros(3, max(n, 1), dtype=torch.float32, device=self.device)
+        self.w_flat, self.w_meta_t = w_flat, w_meta
+        # masters of the owned tensors share one padded fp16 buffer so that 16-element vector reads never leave it
+        owned_total = sum(_pad16(self.fp8_params[i].numel()) for i in self.owned)
+        self.master_flat = torch.zeros(max(owned_total, 1), dtype=torch.float16, device=self.device)
+        self.masters = {}
+        replace = {}
+        moff = 0
+        for i, p in enumerate(self.fp8_params):
+            n_el = p.numel()
+            if self.owners[i] == self.rank:
+                src = p if p.qtype == Dtypes.kfloat16 else p.cast(Dtypes.kfloat16)
+                mval = self.master_flat[moff:moff + n_el].view(p.shape)
+                mval.copy_(src.value)
+                mmeta = ScalingMeta(Dtypes.kfloat16, window_size=1, device=self.device)
+                mmeta.copy_(src.meta)
+                master = ScalingParameter(ScalingTensor(mval, mmeta), requires_grad=True)
+                self.masters[i] = master
+                replace[id(p)] = master
+                moff += _pad16(n_el)
+            else:
+                replace[id(p)] = None
+            # the model-side weight becomes e4m3 in the flat buffer, its scale_inv/amax in the meta rows
+            q = p if p.qtype == E4M3 else p.cast(E4M3)
+            view = w_flat[self.offsets[i]:self.offsets[i] + n_el].view(p.shape)
+            view.copy_(q.value)
+            si, am = w_meta[0, i:i + 1].view(()), w_meta[1, i:i + 1]
+            si.copy_(q.meta.scale_inv)
+            am.copy_(q.meta.amax)
+            new_meta = ScalingMeta(E4M3, scale=torch.reciprocal(si), scale_inv=si, amax=am, window_size=1)
+            p.value = view
+            p.meta = new_meta
+            p._fp8_cache = None
+        # rebind the optimizer's groups: owned FP8 params -> masters, others dropped
+        for group in self.optimizer.param_groups:
+            new = []
+            for p in group['params']:
+                if id(p) in replace:
+                    if replace[id(p)] is not None:
+                        new.append(replace[id(p)])
+                else:
+                    new.append(p)
+            group['params'] = new
+        self.optimizer.state.clear()
+        if self.native:
+            ptrs = [0] * n
+            sinvs = [0] * n
+            amaxs = [0] * n
+            for i, m in self.masters.items():
+                ptrs[i], sinvs[i], amaxs[i] = m.value.data_ptr(), m.meta.scale_inv.data_ptr(), m.meta.amax.data_ptr()
+            self.master_ptrs = torch.tensor(ptrs, dtype=torch.int64, device=self.device)
+            self.master_sinvs = torch.tensor(sinvs, dtype=torch.int64, device=self.device)
+            self.master_amaxs = torch.tensor(amaxs, dtype=torch.int64, device=self.device)
+
+    # ------------------------------------------------------------------ step
+    def _reduce_fp8_grads(self):
+        broadcast = 0 if self.sharded else 1
+        if self.native:
+            from msamp.ops import native
+            epoch = self.flags.next_epoch()
+            native.check(
+                native.lib().msamp_symm_grad_reduce(
+                    self.g_buf.table, self.g_meta.table, self.flags.table, native.ptr(self.offsets_t), native.ptr(self.work_t), self.n_work,
+                    self.n, self.rank, self.world, ctypes.c_uint(epoch), broadcast, ctypes.c_double(self.wait_seconds), 0, native.stream()
+                ), 'symm_grad_reduce'
+            )
+            which = self.all_t if broadcast else self.owned_t
+            count = self.n if broadcast else len(self.owned)
+            native.check(
+                native.lib().msamp_symm_commit_meta(native.ptr(self.g_meta_t), self.n, native.ptr(which), count, native.stream()),
+                'symm_commit_meta'
+            )
+            return
+        if self.world == 1:
+            return
+        self._emulated_reduce(broadcast)
+
+    def _emulated_reduce(self, broadcast):
+        """Same arithmetic as the fused kernel, with gloo/NCCL collectives: gather bytes + metas, average in fp32, round once."""
+        from msamp.ops import cast as _k
+        from msamp.common.dtype import Floating
+        flats = [torch.empty_like(self.g_flat) for _ in range(self.world)]
+        metas = [torch.empty_like(self.g_meta_t) for _ in range(self.world)]
+        dist.all_gather(flats, self.g_flat, group=self.group)
+        dist.all_gather(metas, self.g_meta_t.contiguous(), group=self.group)
+        for i, p in enumerate(self.fp8_params):
+            if not broadcast and self.owners[i] != self.rank:
+                continue
+            lo, hi = self.offsets[i], self.offsets[i] + p.numel()
+            acc = torch.zeros(p.numel(), dtype=torch.float32, device=self.device)
+            amax = torch.zeros((), device=self.device)
+            for r in range(self.world):
+                acc += flats[r][lo:hi].view(torch.float8_e4m3fn).float() * (metas[r][0, i] / self.world)
+                amax = torch.maximum(amax, torch.nan_to_num(metas[r][1, i], nan=float('inf')))
+            scale = _k.compute_scale(amax, torch.ones(()), Floating.qfp_max[E4M3])
+            self.g_flat[lo:hi] = _k._emulate_to_fp8(acc, scale, E4M3)
+            self.g_meta_t[0, i] = 1.0 / scale
+
+    def _reduce_hp_grads(self):
+        if self.world == 1:
+            return
+        by_dtype = {}
+        for p in self.hp_params:
+            if p.grad is not None:
+                by_dtype.setdefault(p.grad.dtype, []).append(p.grad)
+        for grads in by_dtype.values():
+            flat = torch.cat([g.reshape(-1) for g in grads])
+            dist.all_reduce(flat, group=self.group)
+            flat.div_(self.world)
+            off = 0
+            for g in grads:
+                k = g.numel()
+                g.copy_(flat[off:off + k].view_as(g))
+                off += k
+
+    def _publish_weights(self):
+        if self.native:
+            from msamp.ops import native
+            epoch = self.flags.next_epoch()
+            native.check(
+                native.lib().msamp_symm_cast_bcast(
+                    self.w_buf.table, self.w_meta.table, self.flags.table, native.ptr(self.offsets_t), native.ptr(self.work_t), self.n_work,
+                    self.n, native.ptr(self.master_ptrs), native.ptr(self.master_sinvs), native.ptr(self.master_amaxs), self.rank, self.world,
+                    ctypes.c_uint(epoch), ctypes.c_double(self.wait_seconds), native.stream()
+                ), 'symm_cast_bcast'
+            )
+        else:
+            from msamp.ops import cast as _k
+            from msamp.common.dtype import Floating
+            for i, m in self.masters.items():
+                p = self.fp8_params[i]
+                scale = _k.compute_scale(m.meta.amax[0], torch.ones(()), Floating.qfp_max[E4M3])
+                p.value.copy_(_k._emulate_to_fp8(m.value.float() * m.meta.scale_inv, scale, E4M3).view_as(p.value))
+                self.w_meta_t[0, i] = 1.0 / scale
+                self.w_meta_t[1, i] = m.meta.amax[0]
+            if self.world > 1:
+                flats = [torch.empty_like(self.w_flat) for _ in range(self.world)]
+                metas = [torch.empty_like(self.w_meta_t) for _ in range(self.world)]
+                dist.all_gather(flats, self.w_flat, group=self.group)
+                dist.all_gather(metas, self.w_meta_t.contiguous(), group=self.group)
+                for i, p in enumerate(self.fp8_params):
+                    r = self.owners[i]
+                    if r != self.rank:
+                        lo, hi = self.offsets[i], self.offsets[i] + p.numel()
+                        self.w_flat[lo:hi] = flats[r][lo:hi]
+                        self.w_meta_t[:2, i] = metas[r][:2, i]
+        for p in self.fp8_params:
+            torch.autograd.graph.increment_version(p.value)
+
+    def reduce_and_step(self, clip_grad=0.0):
+        """Call after backward: exchange gradients, update the owned shard, publish weights, clear gradients."""
+        self._reduce_fp8_grads()
+        self._reduce_hp_grads()
+        if self.sharded:
+            for i, m in self.masters.items():
+                p = self.fp8_params[i]
+                m.grad = p.grad
+        if clip_grad > 0:
+            self._clip(clip_grad)
+        self.optimizer.step()
+        if self.sharded:
+            self._publish_weights()
+            for m in self.masters.values():
+                m.grad = None
+        for p in self.fp8_params:
+            p.grad = None
+
+    def _clip(self, max_norm):
+        from msamp.nn.clip_grad import _grad_norm
+        sq = torch.zeros((), device=self.device)
+        owned = list(self.masters.values()) if self.sharded else self.fp8_params
+        for p in owned:
+            if p.grad is not None:
+                sq += _grad_norm(p.grad, 2.0)**2
+        if self.sharded and self.world > 1:
+            dist.all_reduce(sq, group=self.group)
+        for p in self.hp_params:
+            if p.grad is not None:
+                sq += _grad_norm(p.grad, 2.0)**2
+        total = sq.sqrt()
+        coef = torch.clamp(max_norm / (total + 1e-6), max=1.0)
+        for p in owned:
+            if p.grad is not None:
+                p.grad.mul_(coef)
+        for p in self.hp_params:
+            if p.grad is not None:
+                p.grad.mul_(coef.to(p.grad.dtype))
+        return total
+
+    # ------------------------------------------------------------------ checkpoint
+    def state_dict(self):
+        """Inner optimizer state plus this rank's master weights, under the reference's key name."""
+        return {
+            'optimizer_state_dict': self.optimizer.state_dict(),
+            'single_partition_of_fp8_groups': [self.masters[i].detach() for i in sorted(getattr(self, 'masters', {}))],
+            'partition_count': self.world,
+            'zero_stage': self.stage,
+        }
+
+    def load_state_dict(self, sd):
+        if sd.get('partition_count', self.world) != self.world:
+            raise ValueError('loading a sharded optimizer state needs the same data-parallel size')
+        self.optimizer.load_state_dict(sd['optimizer_state_dict'])
+        for i, saved in zip(sorted(getattr(self, 'masters', {})), sd['single_partition_of_fp8_groups']):
+            self.masters[i].copy_(saved.to(device=self.device))
+        if self.sharded:
+            self._publish_weights()
