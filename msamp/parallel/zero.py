@@ -71,7 +71,7 @@ class ZeroShardedOptimizer:
         self.n = len(params)
         self.device = params[0].device if params else torch.device('cpu')
         self.native = self.device.type == 'cuda' and self.world > 1
-        self.sharded = stage >= 1 and self.world > 1
+        self.sharded = stage >= 1    # with one rank this is plain FP8 weights + fp16 masters (the O3 layout)
         self._build_buffers()
         if self.sharded:
             self._shard_states()
@@ -232,7 +232,7 @@ class ZeroShardedOptimizer:
             for r in range(self.world):
                 acc += flats[r][lo:hi].view(torch.float8_e4m3fn).float() * (metas[r][0, i] / self.world)
                 amax = torch.maximum(amax, torch.nan_to_num(metas[r][1, i], nan=float('inf')))
-            scale = _k.compute_scale(amax, torch.ones(()), Floating.qfp_max[E4M3])
+            scale = _k.compute_scale(amax, torch.ones((), device=self.device), Floating.qfp_max[E4M3])
             self.g_flat[lo:hi] = _k._emulate_to_fp8(acc, scale, E4M3)
             self.g_meta_t[0, i] = 1.0 / scale
 
@@ -266,12 +266,13 @@ class ZeroShardedOptimizer:
             )
         else:
             from msamp.ops import cast as _k
-            from msamp.common.dtype import Floating
             for i, m in self.masters.items():
                 p = self.fp8_params[i]
-                scale = _k.compute_scale(m.meta.amax[0], torch.ones(()), Floating.qfp_max[E4M3])
-                p.value.copy_(_k._emulate_to_fp8(m.value.float() * m.meta.scale_inv, scale, E4M3).view_as(p.value))
-                self.w_meta_t[0, i] = 1.0 / scale
+                # master value is w * s_m: one pass rescales by rule(amax) / s_m, rounds to e4m3 and stores 1 / rule(amax)
+                new_scale = _k.compute_scale(m.meta.amax[0], torch.ones((), device=self.device), 448.0)
+                factor = new_scale * m.meta.scale_inv
+                _k.cast_to_fp8(m.value, E4M3, factor, out=p.value.view(-1))
+                self.w_meta_t[0, i] = torch.reciprocal(new_scale)
                 self.w_meta_t[1, i] = m.meta.amax[0]
             if self.world > 1:
                 flats = [torch.empty_like(self.w_flat) for _ in range(self.world)]

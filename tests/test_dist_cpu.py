@@ -127,3 +127,54 @@ def _zero_matches_single(rank, world):
 
 def test_zero_tracks_fp32_training():
     run_workers(_zero_matches_single, 2)
+
+
+def _ddp_training(rank, world):
+    import torch.nn as nn
+    from msamp.nn.distributed import FP8DistributedDataParallel
+    torch.manual_seed(0)
+
+    class Net(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.conv1 = nn.Conv2d(1, 8, 3, 1)
+            self.conv2 = nn.Conv2d(8, 16, 3, 1)
+            self.fc1 = nn.Linear(2304, 64)
+            self.fc2 = nn.Linear(64, 10)
+
+        def forward(self, x):
+            x = torch.relu(self.conv1(x))
+            x = torch.max_pool2d(torch.relu(self.conv2(x)), 2)
+            return self.fc2(torch.relu(self.fc1(torch.flatten(x, 1))))
+
+    model = Net()
+    opt = torch.optim.Adam(model.parameters(), lr=1e-3)
+    model, opt = msamp.initialize(model, opt, 'O1')
+    assert torch.nn.parallel.DistributedDataParallel is FP8DistributedDataParallel
+    ddp = torch.nn.parallel.DistributedDataParallel(model)
+    g = torch.Generator().manual_seed(10 + rank)
+    x = torch.randn(16, 1, 28, 28, generator=g)
+    y = torch.randint(0, 10, (16, ), generator=g)
+    losses = []
+    for _ in range(8):
+        opt.zero_grad()
+        loss = torch.nn.functional.cross_entropy(ddp(x), y)
+        loss.backward()
+        opt.all_reduce_grads(model)    # no-op under FP8 DDP
+        opt.step()
+        losses.append(loss.item())
+    assert losses[-1] < losses[0]
+    w = model.fc1.weight
+    assert w.grad is not None and w.grad.qtype == E4M3
+    flat = torch.cat([p.float().reshape(-1) for p in model.parameters()])
+    ref = flat.clone()
+    dist.broadcast(ref, src=0)
+    assert torch.equal(flat, ref)
+    gflat = w.grad.value.clone()
+    gref = gflat.clone()
+    dist.broadcast(gref, src=0)
+    assert torch.equal(gflat, gref)
+
+
+def test_fp8_ddp_mnist_shaped_cnn_gloo():
+    run_workers(_ddp_training, 2)
