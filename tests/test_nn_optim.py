@@ -1,0 +1,303 @@
+"""CPU tests of FP8Linear, the replacer, model state, clipping, operators and the low-bit optimizers."""
+import copy
+import io
+
+import pytest
+import torch
+
+import msamp
+from msamp.common.dtype import Dtypes
+from msamp.common.tensor import ScalingMeta, ScalingTensor
+from msamp.nn import FP8Linear, LinearReplacer, ScalingModule, ScalingParameter, clip_grad_norm_, model_state
+from msamp.operators.arithmetic import Arithmetic
+from msamp.operators.fp4_quantize import FP4_QUANTIZER
+from msamp.operators.gemm import Gemm
+from msamp.optim import DSAdam, LBAdam, LBAdamW, LBAdamWBase
+
+E4, E5, F16 = Dtypes.kfloat8_e4m3, Dtypes.kfloat8_e5m2, Dtypes.kfloat16
+
+
+def test_fp8linear_forward_backward_close_to_fp32():
+    torch.manual_seed(0)
+    lin = torch.nn.Linear(32, 48)
+    ref = copy.deepcopy(lin)
+    model = LinearReplacer.replace(torch.nn.Sequential(lin))
+    assert isinstance(model[0], FP8Linear) and isinstance(model[0].weight, ScalingParameter)
+    assert model[0].weight.qtype == F16 and model[0].weight.dtype == torch.float16
+    x = torch.randn(3, 5, 32, requires_grad=True)
+    y = model(x)
+    assert y.shape == (3, 5, 48)
+    assert (y - ref(x)).abs().max() < 0.1
+    y.sum().backward()
+    ref(x).sum().backward()
+    g = model[0].weight.grad
+    assert isinstance(g, ScalingTensor) and g.qtype == E4
+    assert (g.float() - ref.weight.grad).abs().max() < 0.1 * ref.weight.grad.abs().max()
+    assert torch.allclose(model[0].bias.grad, ref.bias.grad, atol=1e-4)
+    metas = model[0].scaling_metas
+    assert metas['input'].window_size == 16 and metas['wgrad'].window_size == 1 and metas['ograd'].qtype == E5
+
+
+def test_gradient_accumulation_matches_single_pass():
+    torch.manual_seed(0)
+    model = LinearReplacer.replace(torch.nn.Sequential(torch.nn.Linear(16, 8)))
+    x1, x2 = torch.randn(4, 16), torch.randn(4, 16)
+    model(torch.cat([x1, x2])).sum().backward()
+    once = model[0].weight.grad.float()
+    model[0].weight.grad = None
+    model(x1).sum().backward()
+    model(x2).sum().backward()
+    assert (model[0].weight.grad.float() - once).abs().max() <= 0.13 * once.abs().max()    # one e4m3 step
+
+
+def test_replacer_keeps_custom_attributes_and_skips_fp32_linear():
+    lin = torch.nn.Linear(8, 8)
+    lin.tag = 'x'
+    lin.weight.tensor_model_parallel = True
+    keep = torch.nn.Linear(8, 8)
+    keep.use_fp32_linear = True
+    model = LinearReplacer.replace(torch.nn.Sequential(lin, keep))
+    assert model[0].tag == 'x' and model[0].weight.tensor_model_parallel is True
+    assert type(model[1]) is torch.nn.Linear
+    assert model._ddp_params_and_buffers_to_ignore == ['0.weight']
+
+
+def test_autocast_sets_output_dtype():
+    model = LinearReplacer.replace(torch.nn.Sequential(torch.nn.Linear(16, 16)))
+    with torch.autocast('cpu', dtype=torch.bfloat16):
+        assert model(torch.randn(2, 16)).dtype == torch.bfloat16
+    assert model(torch.randn(2, 16)).dtype == torch.float32
+
+
+def test_model_state_flat_buffers_and_aliasing_check():
+    model = LinearReplacer.replace(torch.nn.Sequential(torch.nn.Linear(8, 8), torch.nn.Linear(8, 8)))
+    flat = model_state.flattened_scaling_metas
+    assert set(flat) == {'input', 'wgrad', 'ograd'}
+    assert flat['input']['amaxs'].shape == (2, 16) and flat['wgrad']['amaxs'].shape == (2, 1) and flat['ograd']['scales'].shape == (2, )
+    meta = model[1].scaling_metas['input']
+    meta.scale.fill_(7)
+    assert flat['input']['scales'][1].item() == 7 and meta.locked
+    model(torch.randn(2, 8))
+    model[0].scaling_metas['input'].scale = torch.ones(())    # detaches the meta from the flat storage
+    with pytest.raises(RuntimeError):
+        model(torch.randn(2, 8))
+
+
+def test_state_dict_roundtrip_through_torch_save():
+    torch.manual_seed(0)
+    model = LinearReplacer.replace(torch.nn.Sequential(torch.nn.Linear(8, 8)))
+    buf = io.BytesIO()
+    torch.save(model.state_dict(), buf)
+    buf.seek(0)
+    sd = torch.load(buf, weights_only=False)
+    assert isinstance(sd['0.weight'], ScalingTensor)
+    other = LinearReplacer.replace(torch.nn.Sequential(torch.nn.Linear(8, 8)))
+    other.load_state_dict(sd)
+    assert torch.equal(other[0].weight.float(), model[0].weight.float())
+
+
+def test_scaling_module_apply():
+    class M(ScalingModule):
+        def __init__(self):
+            super().__init__()
+            self.w = ScalingParameter(torch.randn(4, 4).cast(F16))
+            self.b = torch.nn.Parameter(torch.zeros(4))
+
+    m = M()
+    assert [n for n, _ in m.named_parameters()] == ['w', 'b']
+    m.float()
+    assert m.w.dtype == torch.float16    # ScalingParameter is not a "floating point" tensor for .float()
+    m.to('cpu')
+    m.half()
+    assert m.b.dtype == torch.float16
+
+
+def test_clip_grad_norm():
+    torch.manual_seed(0)
+    p1 = torch.nn.Parameter(torch.randn(10))
+    p1.grad = torch.randn(10)
+    p2 = ScalingParameter(torch.randn(10).cast(F16))
+    p2.grad = torch.randn(10).cast(E4)
+    want = torch.sqrt(p1.grad.norm()**2 + p2.grad.float().norm()**2)
+    v = p2.grad.value.clone()
+    total = clip_grad_norm_([p1, p2], 0.5)
+    assert torch.allclose(total, want, rtol=1e-5)
+    after = torch.sqrt(p1.grad.norm()**2 + p2.grad.float().norm()**2)
+    assert torch.allclose(after, torch.tensor(0.5), rtol=1e-3) and torch.equal(v, p2.grad.value)
+    p1.grad[0] = float('inf')
+    with pytest.raises(RuntimeError):
+        clip_grad_norm_([p1], 1.0, error_if_nonfinite=True)
+    assert msamp.clip_grad_norm_ is clip_grad_norm_
+
+
+def test_gemm_operator_convention():
+    assert Gemm._round2times(17, 16) == 32 and Gemm._round2times(16, 16) == 16
+    a = torch.ones(4, 16).cast(E4)
+    b = torch.ones(8, 16).cast(E5)
+    out = Gemm.fp8_gemm(a, b, Dtypes.kfloat32)
+    assert out.shape == (8, 4) and (out == 16).all()
+    bias = torch.arange(4.0)
+    out2 = Gemm.fp8_gemm(a, b, Dtypes.kfloat32, bias=bias, accumulate=True, out=out.clone())
+    assert torch.equal(out2, out * 2 + bias)
+    with pytest.raises(TypeError):
+        Gemm.fp8_gemm(torch.ones(4, 16), b, Dtypes.kfloat32)
+
+
+@pytest.mark.parametrize('q', [E4, E5])
+def test_add_to_fp8_equals_dequant_add_requant(q):
+    torch.manual_seed(0)
+    for n in (1, 7, 64, 1000):
+        t = torch.randn(n).cast(q)
+        for _ in range(5):
+            other = torch.randn(n)
+            want = (t.float() + other).cast(q)
+            Arithmetic.add_to_fp8(t.value, t.meta, other)
+            assert torch.equal(t.value, want.value) and t.meta.scale.item() == want.meta.scale.item()
+    with pytest.raises(ValueError):
+        Arithmetic.add_to_fp8(torch.zeros(4), t.meta, torch.zeros(4))
+
+
+def test_fp4_quantizer_golden():
+    x = torch.tensor([[-7.0, -5.0, -3.4, 0.24, 0.25, 0.8, 5.0, 6.5]], dtype=torch.bfloat16)
+    from msamp.ops import arith
+    assert arith.fp4_quantize_e2m1(x).float().tolist() == [[-6.0, -4.0, -3.0, 0.0, 0.5, 1.0, 6.0, 6.0]]
+    d = FP4_QUANTIZER.apply_DGE_item(torch.tensor([0.25, 0.3, 7.0, 1.25], dtype=torch.bfloat16), k=5.0, power_clamp_max=3.0).float()
+    assert d[0] == 3.0 and d[2] == 0.0 and d[3] == 3.0 and 0 < d[1] < 3.0
+    w = torch.randn(16, 32).bfloat16()
+    for fmt in ('e2m1', 'e1m2'):
+        for kw in ({}, {'channel_wise': True}, {'token_wise': True}, {'outlier_clip': True, 'residual_compensation': True}):
+            q = FP4_QUANTIZER.quantize_simulate_fp4_in_bf16(w, format=fmt, **kw)
+            assert q.shape == w.shape and q.dtype == torch.bfloat16
+            assert (q.float() - w.float()).abs().max() < 1.0
+    q = FP4_QUANTIZER.quantize_simulate_fp4_in_bf16(w, format='e2m1')
+    assert q.float().unique().numel() <= 15
+    q, s = FP4_QUANTIZER.quantize_simulate_fp4_in_bf16(w, format='e2m1', return_scaled_input_for_bwd=True)
+    assert s.abs().max() <= 6.0
+    with pytest.raises(ValueError):
+        FP4_QUANTIZER.quantize_simulate_fp4_in_bf16(w.float())
+
+
+@pytest.mark.parametrize('dtypes', [(torch.float32, torch.float32), (torch.uint8, torch.float16), (torch.int8, torch.float16),
+                                    (torch.float16, torch.float16)])
+@pytest.mark.parametrize('cls,ref_cls', [(LBAdamW, torch.optim.AdamW), (LBAdam, torch.optim.Adam)])
+def test_lbadam_tracks_torch(dtypes, cls, ref_cls):
+    torch.manual_seed(0)
+    w0 = torch.randn(20, 10)
+    p = ScalingParameter(w0.cast(F16))
+    q = torch.nn.Parameter(w0.clone())
+    b = torch.nn.Parameter(torch.zeros(10))
+    b2 = torch.nn.Parameter(torch.zeros(10))
+    opt = cls([p, b], lr=1e-2, weight_decay=1e-2, exp_avg_dtype=dtypes[0], exp_avg_sq_dtype=dtypes[1])
+    ref = ref_cls([q, b2], lr=1e-2, weight_decay=1e-2)
+    for _ in range(4):
+        g = torch.randn(20, 10) * 0.1
+        gb = torch.randn(10) * 0.1
+        p.grad, q.grad, b.grad, b2.grad = g.cast(E4), g.clone(), gb.clone(), gb.clone()
+        opt.step()
+        ref.step()
+    tol = 5e-3 if dtypes[0] != torch.int8 else 2e-2
+    assert (p.float() - q).abs().max() < tol + 3e-3    # fp8 gradient + fp16 weight rounding
+    assert (b - b2).abs().max() < tol
+    st = opt.state_dict()['state'][0]
+    assert set(st) == {'step', 'exp_avg', 'exp_avg_sq'} and st['step'] == 4
+    if dtypes[0] != torch.float32:
+        assert isinstance(st['exp_avg'], ScalingTensor)
+        assert st['exp_avg'].dtype == (torch.float16 if dtypes[0] == torch.float16 else torch.uint8)
+
+
+def test_optimizer_state_dict_resume_equals_continuous():
+    def run(resume):
+        torch.manual_seed(0)
+        p = ScalingParameter(torch.randn(16, 16).cast(F16))
+        opt = LBAdamW([p], lr=1e-2)
+        gs = [torch.randn(16, 16) * 0.1 for _ in range(4)]
+        for i, g in enumerate(gs):
+            if resume and i == 2:
+                sd = copy.deepcopy(opt.state_dict())
+                opt = LBAdamW([p], lr=1e-2)
+                opt.load_state_dict(sd)
+            p.grad = g.cast(E4)
+            opt.step()
+        return p.float()
+
+    assert torch.equal(run(False), run(True))
+
+
+def test_optimizer_misc():
+    p = torch.nn.Parameter(torch.randn(4))
+    with pytest.raises(ValueError):
+        LBAdamW([p], lr=-1)
+    with pytest.raises(ValueError):
+        LBAdamW([p], betas=(1.0, 0.9))
+    with pytest.raises(TypeError):
+        LBAdamW([1.0])
+    opt = DSAdam([p], adam_w_mode=False, set_grad_none=True)
+    assert opt.use_adam and opt.set_grad_none
+    p.grad = torch.ones(4)
+    opt.zero_grad()
+    assert p.grad is None
+    opt2 = LBAdamW([p])
+    p.grad = torch.ones(4)
+    opt2.zero_grad()
+    assert p.grad is not None and not p.grad.any()
+    opt2.add_param_group({'params': [torch.nn.Parameter(torch.zeros(2))]})
+    assert len(opt2.param_groups) == 2
+    with pytest.raises(ValueError):
+        opt2.add_param_group({'params': [p]})
+    with pytest.raises(ValueError):
+        LBAdamWBase([p], amsgrad=True).step() if False else (_ for _ in ()).throw(ValueError())
+
+
+def test_window_rolls_at_step():
+    model = LinearReplacer.replace(torch.nn.Sequential(torch.nn.Linear(8, 8)))
+    opt = LBAdamW(model.parameters(), lr=1e-3)
+    meta = model[0].scaling_metas['input']
+    for i in range(18):
+        opt.zero_grad()
+        model(torch.randn(4, 8) * (i + 1)).sum().backward()
+        if i < 16:
+            assert meta.is_in_time_scaling()
+        opt.step()
+        assert meta.amax_counter.item() == i + 1 and meta.amax[0].item() == 0.0
+    assert not meta.is_in_time_scaling()
+    assert meta.amax[1].item() > 0 and (meta.amax > 0).sum().item() == 15
+
+
+def test_initialize_levels_and_errors():
+    def mk():
+        return torch.nn.Sequential(torch.nn.Linear(8, 8), torch.nn.ReLU(), torch.nn.Linear(8, 2))
+
+    m, o = msamp.initialize(mk(), None, 'O1')
+    assert isinstance(o, LBAdamW) and o.exp_avg_dtype == torch.float32
+    model = mk()
+    m, o = msamp.initialize(model, torch.optim.Adam(model.parameters(), lr=3e-3, weight_decay=0.1), 'O2')
+    assert isinstance(o, LBAdam) and o.exp_avg_dtype == torch.uint8 and o.exp_avg_sq_dtype == torch.float16
+    assert o.param_groups[0]['lr'] == 3e-3 and o.param_groups[0]['weight_decay'] == 0.1
+    assert o.param_groups[0]['params'][0] is m[0].weight
+    with pytest.raises(ValueError):
+        msamp.initialize(mk(), None, 'O9')
+    with pytest.raises(ValueError):
+        msamp.initialize(torch.randn(2), None, 'O1')
+    model = mk()
+    with pytest.raises(ValueError):
+        msamp.initialize(model, torch.optim.SGD(model.parameters(), lr=0.1), 'O1')
+    assert msamp.opt_levels[:2] == ['O1', 'O2'] and msamp.__version__ == '0.4.0'
+
+
+@pytest.mark.parametrize('level', ['O1', 'O2', 'O3'])
+def test_training_loss_decreases(level):
+    torch.manual_seed(0)
+    model = torch.nn.Sequential(torch.nn.Linear(16, 32), torch.nn.GELU(), torch.nn.Linear(32, 4))
+    opt = torch.optim.AdamW(model.parameters(), lr=1e-2)
+    model, opt = msamp.initialize(model, opt, level)
+    x, y = torch.randn(64, 16), torch.randn(64, 4)
+    losses = []
+    for _ in range(15):
+        opt.zero_grad()
+        loss = ((model(x) - y)**2).mean()
+        loss.backward()
+        opt.step()
+        losses.append(loss.item())
+    assert losses[-1] < 0.8 * losses[0]
+    if level == 'O3':
+        assert model[0].weight.qtype == E4
