@@ -122,3 +122,78 @@ def _zero2_training(rank, world):
 def test_zero2_training_two_gpus():
     _need(2)
     run_workers(_zero2_training, 2, backend='nccl')
+
+
+def _fused_gemms(rank, world):
+    from msamp.ops import cast, gemm, native
+    from msamp.parallel.fused import FusedGemmContext, all_gather_cols, all_gather_rows, reduce_scatter_rows
+    dev = torch.device('cuda', rank)
+    F8 = Dtypes.qtype_to_float8
+    ctx = FusedGemmContext(max_shard_bytes=8 << 20, max_out_bytes=64 << 20, n_comm=4)
+    assert ctx.native
+    sinv = torch.tensor(1 / 16.0, device=dev)
+    scale = torch.tensor(16.0, device=dev)
+
+    def q(shape, seed):
+        g = torch.Generator(device=dev).manual_seed(seed)
+        return cast.cast_to_fp8(torch.randn(*shape, device=dev, generator=g), E4M3, scale)
+
+    for (rows, K, N) in ((128, 256, 128), (256, 512, 384), (1024, 4096, 1536), (512, 1024, 1000)):
+        # --- all-gather(rows of A) + GEMM
+        a_shard = q((rows, K), 100 + rank)
+        b = q((N, K), 7)
+        view = ctx.shard_view(rows * K).view(rows, K)
+        view.copy_(a_shard)
+        bias = torch.randn(N, device=dev)
+        out = ctx.ag_rows_gemm(view, E4M3, sinv, b, E4M3, sinv, torch.bfloat16, bias=bias)
+        full = all_gather_rows(a_shard)
+        ref = gemm.gemm_fp8(full, E4M3, sinv, b, E4M3, sinv, torch.bfloat16, bias=bias)
+        torch.cuda.synchronize()
+        assert native.device_status() == 0
+        assert torch.equal(out, ref), ('ag_rows a', rows, K, N, (out.float() - ref.float()).abs().max().item())
+        assert torch.equal(ctx.gathered_rows(rows, K), full)
+        # --- all-gather(rows of B) + GEMM (parameter gather)
+        if N % 256 == 0 or N == 128:
+            pass
+        w_rows = 256
+        w_shard = q((w_rows, K), 200 + rank)
+        x = q((rows, K), 9)
+        view = ctx.shard_view(w_rows * K).view(w_rows, K)
+        view.copy_(w_shard)
+        out = ctx.ag_rows_gemm(view, E4M3, sinv, x, E4M3, sinv, torch.bfloat16, shard_is='b')
+        ref = gemm.gemm_fp8(x, E4M3, sinv, all_gather_rows(w_shard), E4M3, sinv, torch.bfloat16)
+        torch.cuda.synchronize()
+        assert native.device_status() == 0
+        assert torch.equal(out, ref), ('ag_rows b', rows, K)
+        # --- GEMM with K-gathered B (wgrad shape): D[N, K] = A[N, W*rows] . concat_K(B_r[K, rows])^T
+        a_full = q((N, rows * world), 11)
+        bt_shard = q((K, rows), 300 + rank)
+        if rows % 128 == 0:
+            view = ctx.shard_view(((K + 255) // 256 * 256) * rows)[:K * rows].view(K, rows)
+            view.copy_(bt_shard)
+            am = torch.zeros((), device=dev)
+            out = ctx.ag_k_gemm(a_full, E4M3, sinv, view, E4M3, sinv, torch.float32, amax_out=am)
+            ref = gemm.gemm_fp8(a_full, E4M3, sinv, all_gather_cols(bt_shard), E4M3, sinv, torch.float32)
+            torch.cuda.synchronize()
+            assert native.device_status() == 0
+            err = (out - ref).abs().max().item()
+            assert err <= 1e-3 * ref.abs().max().item() + 1e-4, ('ag_k', rows, K, N, err)    # summation order differs
+            assert abs(am.item() - out.abs().max().item()) <= 1e-6 * am.item() + 1e-6
+        # --- GEMM + reduce-scatter
+        M = rows * world
+        a_part = q((M, K), 400 + rank)
+        b_part = q((N, K), 500 + rank)
+        if (N * 2) % 16 == 0:
+            out = ctx.gemm_rs(a_part, E4M3, sinv, b_part, E4M3, sinv, torch.bfloat16)
+            part = gemm.gemm_fp8(a_part, E4M3, sinv, b_part, E4M3, sinv, torch.float32)
+            ref = reduce_scatter_rows(part)
+            torch.cuda.synchronize()
+            assert native.device_status() == 0
+            err = (out.float() - ref).abs().max().item()
+            assert err <= 2e-2 * ref.abs().max().item() + 1e-3, ('gemm_rs', rows, K, N, err)    # partials are rounded to bf16 before the sum
+    dist.barrier()
+
+
+def test_fused_gemm_collectives_two_gpus():
+    _need(2)
+    run_workers(_fused_gemms, 2, backend='nccl')
