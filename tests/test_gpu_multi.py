@@ -197,3 +197,45 @@ def _fused_gemms(rank, world):
 def test_fused_gemm_collectives_two_gpus():
     _need(2)
     run_workers(_fused_gemms, 2, backend='nccl')
+
+
+def _sp_block_fused(rank, world):
+    from msamp.megatron import ColumnParallelLinear, RowParallelLinear, parallel_state as mpu
+    from msamp.ops import native
+    mpu.initialize_model_parallel(tensor_model_parallel_size=world)
+    dev = torch.device('cuda', rank)
+    torch.manual_seed(0)
+    H, F, S, B = 256, 1024, 256 * world, 1
+    full_w1 = (torch.randn(F, H, device=dev) * 0.05)
+    full_w2 = (torch.randn(H, F, device=dev) * 0.05)
+    x_full = torch.randn(S, B, H, device=dev)
+    g_full = torch.randn(S, B, H, device=dev)
+    col = ColumnParallelLinear(H, F, bias=True, sequence_parallel=True, device=dev)
+    row = RowParallelLinear(F, H, bias=True, sequence_parallel=True, device=dev)
+    fs = F // world
+    with torch.no_grad():
+        col.weight.copy_(full_w1[rank * fs:(rank + 1) * fs].cast(col.weight.qtype))
+        row.weight.copy_(full_w2[:, rank * fs:(rank + 1) * fs].contiguous().cast(row.weight.qtype))
+    sl = slice(rank * (S // world), (rank + 1) * (S // world))
+    x = x_full[sl].bfloat16().clone().requires_grad_()
+    y = row(torch.nn.functional.gelu(col(x)))
+    ctx = mpu.get_fused_context()
+    assert ctx.native
+    y.backward(g_full[sl].bfloat16())
+    torch.cuda.synchronize()
+    assert native.device_status() == 0
+    w1 = full_w1.clone().requires_grad_()
+    w2 = full_w2.clone().requires_grad_()
+    ref_x = x_full.clone().requires_grad_()
+    ref = torch.nn.functional.gelu(ref_x @ w1.t()) @ w2.t()
+    ref.backward(g_full)
+    assert (y.float() - ref[sl]).abs().max().item() < 0.05 * ref.abs().max().item() + 0.02
+    assert (x.grad.float() - ref_x.grad[sl]).abs().max().item() < 0.2 * ref_x.grad.abs().max().item()
+    assert (col.weight.grad.float() - w1.grad[rank * fs:(rank + 1) * fs]).abs().max().item() < 0.12 * w1.grad.abs().max().item()
+    assert (row.weight.grad.float() - w2.grad[:, rank * fs:(rank + 1) * fs]).abs().max().item() < 0.12 * w2.grad.abs().max().item()
+    mpu.destroy_model_parallel()
+
+
+def test_sequence_parallel_block_fused_kernels():
+    _need(2)
+    run_workers(_sp_block_fused, 2, backend='nccl')

@@ -1,0 +1,104 @@
+"""Megatron-style tensor/sequence parallel linears, local FP8 DDP and the distributed optimizer on gloo ranks."""
+import os
+import tempfile
+
+import torch
+import torch.distributed as dist
+
+from tests.dist_utils import run_workers
+
+
+def _tp_block(rank, world, sequence_parallel):
+    from msamp.megatron import ColumnParallelLinear, RowParallelLinear, parallel_state as mpu
+    mpu.initialize_model_parallel(tensor_model_parallel_size=world)
+    torch.manual_seed(0)
+    H, F, S = 32, 64, 16
+    full_w1 = torch.randn(F, H) * 0.1
+    full_w2 = torch.randn(H, F) * 0.1
+    x_full = torch.randn(S, 2, H)
+    col = ColumnParallelLinear(H, F, bias=True, sequence_parallel=sequence_parallel)
+    row = RowParallelLinear(F, H, bias=True, sequence_parallel=sequence_parallel)
+    fs, hs = F // world, H
+    with torch.no_grad():
+        col.weight.copy_(full_w1[rank * fs:(rank + 1) * fs].cast(col.weight.qtype))
+        row.weight.copy_(full_w2[:, rank * fs:(rank + 1) * fs].contiguous().cast(row.weight.qtype))
+    x = x_full[rank * (S // world):(rank + 1) * (S // world)] if sequence_parallel else x_full
+    x = x.clone().requires_grad_()
+    y = row(torch.nn.functional.gelu(col(x)))
+    ref_x = x_full.clone().requires_grad_()
+    ref = torch.nn.functional.gelu(ref_x @ full_w1.t()) @ full_w2.t()
+    want = ref[rank * (S // world):(rank + 1) * (S // world)] if sequence_parallel else ref
+    assert y.shape == want.shape
+    assert (y - want).abs().max() < 0.08, (y - want).abs().max()
+    g_full = torch.randn(S, 2, H)
+    g = g_full[rank * (S // world):(rank + 1) * (S // world)] if sequence_parallel else g_full
+    y.backward(g)
+    ref.backward(g_full)
+    want_dx = ref_x.grad[rank * (S // world):(rank + 1) * (S // world)] if sequence_parallel else ref_x.grad
+    assert (x.grad - want_dx).abs().max() < 0.2 * want_dx.abs().max() + 0.05    # two chained GEMMs with e5m2 gradients
+    gw1 = col.weight.grad
+    # weight gradients against autograd of the dense reference
+    w1 = full_w1.clone().requires_grad_()
+    w2 = full_w2.clone().requires_grad_()
+    (torch.nn.functional.gelu(x_full @ w1.t()) @ w2.t()).backward(g_full)
+    got1 = gw1.float() if hasattr(gw1, 'meta') and not torch.is_tensor(gw1) else gw1
+    got2 = row.weight.grad
+    got2 = got2.float() if not torch.is_tensor(got2) else got2
+    assert (got1 - w1.grad[rank * fs:(rank + 1) * fs]).abs().max() < 0.12 * w1.grad.abs().max()
+    assert (got2 - w2.grad[:, rank * fs:(rank + 1) * fs]).abs().max() < 0.12 * w2.grad.abs().max()
+    mpu.destroy_model_parallel()
+
+
+def test_tensor_parallel_block_allreduce():
+    run_workers(_tp_block, 2, args=(False, ))
+
+
+def test_sequence_parallel_block():
+    run_workers(_tp_block, 2, args=(True, ))
+
+
+def _ddp_distopt(rank, world):
+    import msamp
+    from msamp.megatron import FP8DistributedDataParallel, FP8DistributedOptimizer, clip_grad_norm_fp32, parallel_state as mpu
+    from msamp.optim import LBAdamW
+    mpu.initialize_model_parallel(tensor_model_parallel_size=1)
+    torch.manual_seed(0)
+    model = torch.nn.Sequential(torch.nn.Linear(16, 32), torch.nn.GELU(), torch.nn.Linear(32, 32), torch.nn.GELU(), torch.nn.Linear(32, 4))
+    model = msamp.nn.LinearReplacer.replace(model)
+    ddp = FP8DistributedDataParallel(model, accumulate_allreduce_grads_in_fp32=True, use_contiguous_buffers=True)
+    assert sum(b - a for a, b in ddp.fp8_partitions) == sum(p.numel() for p in ddp.fp8_params)
+    opt = FP8DistributedOptimizer(LBAdamW(model.parameters(), lr=1e-2), clip_grad=1.0, models=[ddp])
+    x_all, y_all = torch.randn(16 * world, 16), torch.randn(16 * world, 4)
+    losses = []
+    for it in range(10):
+        opt.zero_grad()
+        for micro in range(2):    # two micro-batches accumulate into the FP8 main grads
+            lo = rank * 16 + micro * 8
+            loss = ((ddp(x_all[lo:lo + 8]) - y_all[lo:lo + 8])**2).mean() / 2
+            loss.backward()
+        opt.reduce_model_grads()
+        ok, norm, _ = opt.step()
+        assert ok and norm is not None and norm > 0
+        losses.append(loss.item())
+    assert losses[-1] < losses[0]
+    flat = torch.cat([p.float().reshape(-1) for p in model.parameters()])
+    ref = flat.clone()
+    dist.broadcast(ref, src=0)
+    assert torch.equal(flat, ref)
+    sd = opt.state_dict()
+    assert 'param_groups' in sd['optimizer'] and 'params' not in sd['optimizer']['param_groups'][0]
+    path = os.path.join(tempfile.gettempdir(), 'msamp_distrib_opt_test.pt')
+    opt.save_parameter_state(path)
+    dist.barrier()
+    before = flat.clone()
+    opt.load_parameter_state(path)
+    after = torch.cat([p.float().reshape(-1) for p in model.parameters()])
+    assert (before - after).abs().max() < 0.05 * before.abs().max()
+    st = torch.load(path, weights_only=False)
+    assert set(st[0].keys()) == {torch.uint8, torch.float32} and set(st[0][torch.uint8]) == {'param', 'exp_avg', 'exp_avg_sq'}
+    assert clip_grad_norm_fp32([torch.nn.Parameter(torch.ones(4))], [torch.ones(4) * 3], 1.0) == 6.0
+    mpu.destroy_model_parallel()
+
+
+def test_local_ddp_and_distributed_optimizer():
+    run_workers(_ddp_distopt, 2)
