@@ -229,10 +229,10 @@ def _sp_block_fused(rank, world):
     ref_x = x_full.clone().requires_grad_()
     ref = torch.nn.functional.gelu(ref_x @ w1.t()) @ w2.t()
     ref.backward(g_full)
-    assert (y.float() - ref[sl]).abs().max().item() < 0.05 * ref.abs().max().item() + 0.02
-    assert (x.grad.float() - ref_x.grad[sl]).abs().max().item() < 0.2 * ref_x.grad.abs().max().item()
-    assert (col.weight.grad.float() - w1.grad[rank * fs:(rank + 1) * fs]).abs().max().item() < 0.12 * w1.grad.abs().max().item()
-    assert (row.weight.grad.float() - w2.grad[:, rank * fs:(rank + 1) * fs]).abs().max().item() < 0.12 * w2.grad.abs().max().item()
+    assert (y.float() - ref[sl]).abs().max().item() < 0.1 * ref.abs().max().item() + 0.02    # two chained FP8 GEMMs
+    assert (x.grad.float() - ref_x.grad[sl]).abs().max().item() < 0.25 * ref_x.grad.abs().max().item()
+    assert (col.weight.grad.float() - w1.grad[rank * fs:(rank + 1) * fs]).abs().max().item() < 0.15 * w1.grad.abs().max().item()
+    assert (row.weight.grad.float() - w2.grad[:, rank * fs:(rank + 1) * fs]).abs().max().item() < 0.15 * w2.grad.abs().max().item()
     mpu.destroy_model_parallel()
 
 
