@@ -20,7 +20,7 @@ def _is_fused_adam(optimizer):
     return type(optimizer).__name__ == 'FusedAdam' and hasattr(optimizer, 'adam_w_mode')
 
 
-def initialize(model, optimizer=None, opt_level='O1', use_te=False):
+def initialize(model, optimizer=None, opt_level='O1', use_te=False, group=None, src_rank=0):
     """Convert ``model`` and ``optimizer`` for FP8 training and return ``(model, optimizer)``.
 
     ================  =====  =====  ==========  =============  ================
@@ -40,7 +40,10 @@ def initialize(model, optimizer=None, opt_level='O1', use_te=False):
         optimizer: ``torch.optim.Adam``/``AdamW`` (or DeepSpeed ``FusedAdam``); default ``AdamW(model.parameters())``.
         opt_level (str): one of ``opt_levels``.
         use_te (bool): convert Transformer Engine modules instead (needs transformer_engine).
+        group, src_rank: process group (and the global rank inside it) from which the converted weights are broadcast;
+            default: the world group and rank 0. Pipeline stages pass their own data-parallel group.
     """
+    process_group = group    # `group` is reused below as the loop variable over optimizer param groups
     if not isinstance(model, torch.nn.Module):
         raise ValueError('Model must be an instance of torch.nn.Module')
     if opt_level not in opt_levels:
@@ -64,7 +67,7 @@ def initialize(model, optimizer=None, opt_level='O1', use_te=False):
         from msamp.te import TeReplacer
         cast_model = TeReplacer.replace(model)
     else:
-        cast_model = LinearReplacer.replace(model, weight_qtype=Dtypes.kfloat16)
+        cast_model = LinearReplacer.replace(model, weight_qtype=Dtypes.kfloat16, src_rank=src_rank, group=process_group)
 
     parameters = list(cast_model.parameters())
     k = 0

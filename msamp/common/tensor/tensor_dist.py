@@ -33,8 +33,8 @@ class TensorDist:
             off += n
 
     @classmethod
-    def _dist_tensors_by_bucket(cls, tensors, dist_fn, bucket_size):
-        if DistUtil.get_world_size() == 1:
+    def _dist_tensors_by_bucket(cls, tensors, dist_fn, bucket_size, group=None):
+        if DistUtil.get_world_size(group) == 1:
             return
         if not isinstance(tensors, (list, tuple)):
             tensors = [tensors]
@@ -54,18 +54,18 @@ class TensorDist:
     @classmethod
     def broadcast(cls, tensors, src, bucket_size=BROADCAST_BUCKET_SIZE, group=None):
         """Broadcast values (and, for ScalingTensors, their ``scale_inv``) from ``src``."""
-        if DistUtil.get_world_size() == 1 or len(tensors) == 0:
+        if DistUtil.get_world_size(group) == 1 or len(tensors) == 0:
             return
 
         def dist_fn(x):
             dist.broadcast(x, src=src, group=group)
 
         if isinstance(tensors[0], ScalingTensor):
-            cls._dist_tensors_by_bucket([p.value for p in tensors], dist_fn, bucket_size)
-            cls._dist_tensors_by_bucket([p.meta.scale_inv for p in tensors], dist_fn, bucket_size)
-            cls._dist_tensors_by_bucket([p.meta.scale for p in tensors], dist_fn, bucket_size)
+            cls._dist_tensors_by_bucket([p.value for p in tensors], dist_fn, bucket_size, group)
+            cls._dist_tensors_by_bucket([p.meta.scale_inv for p in tensors], dist_fn, bucket_size, group)
+            cls._dist_tensors_by_bucket([p.meta.scale for p in tensors], dist_fn, bucket_size, group)
         else:
-            cls._dist_tensors_by_bucket(tensors, dist_fn, bucket_size)
+            cls._dist_tensors_by_bucket(tensors, dist_fn, bucket_size, group)
 
     @classmethod
     def all_reduce(cls, tensors, op, bucket_size=ALL_REDUCE_BUCKET_SIZE, group=None):
@@ -80,7 +80,7 @@ class TensorDist:
         def dist_fn(x):
             DistOp.all_reduce(x, qtype, op, group=group)
 
-        cls._dist_tensors_by_bucket(tensors, dist_fn, bucket_size)
+        cls._dist_tensors_by_bucket(tensors, dist_fn, bucket_size, group)
 
     @classmethod
     def all_reduce_avg(cls, tensors, bucket_size=ALL_REDUCE_BUCKET_SIZE, group=None):

@@ -1,0 +1,253 @@
+"""Full-shard (ZeRO-3) data parallelism for FP8 linears, built on the fused gather-GEMM kernels.
+
+Every FP8Linear weight ``W [N, K]`` is split by rows over the data-parallel group; a rank permanently holds
+only its e4m3 shard ``W_r [N/W, K]`` (and the shard's transpose), its scaled-fp16 master shard and its Adam
+moment shards.  One scale per *tensor* is kept consistent by MAX-reducing the amax over the shards before
+every re-quantisation (the reference's rule, msamp/optim/adamw.py:306-337).
+
+  forward   y  = x8 · all-gather-rows(W8_r)ᵀ           parameter all-gather fused into the GEMM
+  backward  dx = dy8 · all-gather-K(W8ᵀ_r)ᵀ            parameter all-gather (transposed shards) fused into the GEMM
+            dW_r = reduce-scatter-rows(dy8ᵀ · x8)      gradient reduce-scatter fused into the GEMM; the owner keeps its rows
+
+The reference routes FP8 bytes through torch's FSDP by patching its private flat-parameter handle and
+all-reduces full gradients before slicing (msamp/fsdp/fully_sharded_data_parallel.py:14-63); torch's
+private FSDP API has since moved, so this module owns the sharding itself.  ``FsdpReplacer`` plus
+``msamp.optim.FSDPAdamW`` remain available for use with torch FSDP (``use_orig_params=True``).
+"""
+import torch
+import torch.distributed as dist
+
+from msamp.common.dtype import Dtypes
+from msamp.common.tensor import ScalingMeta, ScalingTensor, TypeCast
+from msamp.common.utils.dist import DistUtil
+from msamp.nn.linear import FP8Linear
+from msamp.nn.module import ScalingModule
+from msamp.nn.parameter import ScalingParameter
+from msamp.nn.state import model_state
+from msamp.ops import cast as _k
+from msamp.ops import gemm as _g
+from msamp.parallel.fused import FusedGemmContext, all_gather_cols, all_gather_rows, reduce_scatter_rows
+
+E4M3, E5M2, F16 = Dtypes.kfloat8_e4m3, Dtypes.kfloat8_e5m2, Dtypes.kfloat16
+
+
+class _ShardedLinearFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, module, holder, bias):
+        fs = module._fsdp
+        in_meta = module.scaling_metas['input']
+        x2 = x.contiguous().view(-1, x.shape[-1])
+        record = TypeCast._prepare_scale(x2, in_meta, sync=False)
+        x8, x8t = _k.cast_transpose_fp8(x2, E4M3, in_meta.scale, in_meta.amax[0] if record else None,
+                                        scale_inv_out=in_meta.scale_inv if record else None)
+        x_sinv = in_meta.scale_inv.clone()
+        w8, w_sinv = module.weight_shard, module.weight_meta.scale_inv
+        rows, K = w8.shape
+        fused = fs.ctx if (fs.ctx is not None and fs.ctx.native and rows % 256 == 0) else None
+        if fused is not None:
+            view = fused.shard_view(rows * K).view(rows, K)
+            view.copy_(w8)
+            out = fused.ag_rows_gemm(view, E4M3, w_sinv, x8, E4M3, x_sinv, x.dtype, bias=bias if bias is None or bias.dtype == torch.float32 else None,
+                                     shard_is='b')
+            if bias is not None and bias.dtype != torch.float32:
+                out.add_(bias)
+        else:
+            out = _g.gemm_fp8(x8, E4M3, x_sinv, all_gather_rows(w8, fs.group), E4M3, w_sinv, x.dtype, bias=bias)
+        ctx.module, ctx.x8t, ctx.x_sinv = module, x8t, x_sinv
+        ctx.in_shape, ctx.out_dtype = x.shape, x.dtype
+        ctx.has_bias = bias is not None
+        ctx.bias_dtype = bias.dtype if bias is not None else None
+        ctx.input_requires_grad = x.requires_grad
+        return out.view(tuple(x.shape[:-1]) + (out.shape[-1], ))
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        module = ctx.module
+        fs = module._fsdp
+        og_meta, wg_meta = module.scaling_metas['ograd'], module.scaling_metas['wgrad']
+        dy = grad_output.contiguous().view(-1, grad_output.shape[-1])
+        T, N = dy.shape
+        record = TypeCast._prepare_scale(dy, og_meta, sync=False)
+        dy8, dy8t = _k.cast_transpose_fp8(dy, E5M2, og_meta.scale, og_meta.amax[0] if record else None,
+                                          scale_inv_out=og_meta.scale_inv if record else None)
+        dy_sinv = og_meta.scale_inv
+        w8t, w_sinv = module.weight_shard_t, module.weight_meta.scale_inv    # [K, N/W]
+        K, n_local = w8t.shape
+        fused_ok = fs.ctx is not None and fs.ctx.native
+        dx = None
+        if ctx.input_requires_grad:
+            if fused_ok and n_local % 128 == 0:
+                rows_pad = (K + 255) // 256 * 256
+                view = fs.ctx.shard_view(rows_pad * n_local)[:K * n_local].view(K, n_local)
+                view.copy_(w8t)
+                dx = fs.ctx.ag_k_gemm(dy8, E5M2, dy_sinv, view, E4M3, w_sinv, ctx.out_dtype)
+            else:
+                dx = _g.gemm_fp8(dy8, E5M2, dy_sinv, all_gather_cols(w8t, fs.group), E4M3, w_sinv, ctx.out_dtype)
+            dx = dx.view(ctx.in_shape)
+        # weight gradient of the local batch, reduced over ranks; this rank keeps the rows of its shard
+        if fused_ok and n_local % 128 == 0:
+            part = fs.ctx.gemm_rs(dy8t, E5M2, dy_sinv, ctx.x8t, E4M3, ctx.x_sinv, torch.float32)
+        else:
+            full = _g.gemm_fp8(dy8t, E5M2, dy_sinv, ctx.x8t, E4M3, ctx.x_sinv, torch.float32)
+            part = reduce_scatter_rows(full, fs.group)
+        part.div_(fs.world)
+        # quantise with a scale agreed over the shards of this tensor
+        amax0 = wg_meta.amax[0]
+        _k.amax(part, out=amax0)
+        if fs.world > 1:
+            dist.all_reduce(amax0, op=dist.ReduceOp.MAX, group=fs.group)
+        old = module.master.grad
+        if old is not None:
+            part.add_(old.float())
+            _k.amax(part, out=amax0)
+            if fs.world > 1:
+                dist.all_reduce(amax0, op=dist.ReduceOp.MAX, group=fs.group)
+        value = _k.cast_to_fp8(part, E4M3, wg_meta.scale, scale_inv_out=wg_meta.scale_inv, amax_in=amax0)
+        module.master.grad = ScalingTensor(value, wg_meta)
+        dbias = dy.sum(0, dtype=torch.float32).to(ctx.bias_dtype) if ctx.has_bias else None
+        ctx.x8t = None
+        return dx, None, None, dbias
+
+
+class ShardedFP8Linear(ScalingModule):
+    """A linear layer whose FP8 weight, master weight and optimizer state are split by rows over the group."""
+    def __init__(self, linear, fsdp):
+        super().__init__()
+        self._fsdp = fsdp
+        self.in_features, self.out_features = linear.in_features, linear.out_features
+        W, r = fsdp.world, fsdp.rank
+        if self.out_features % W:
+            raise ValueError(f'out_features={self.out_features} is not divisible by the shard count {W}')
+        rows = self.out_features // W
+        w = linear.weight
+        full = w.float() if isinstance(w, ScalingTensor) else w.detach().float()
+        dev = full.device
+        shard = full[r * rows:(r + 1) * rows].contiguous()
+        # one scale for the whole tensor
+        amax = full.abs().max()
+        self.master = ScalingParameter(shard.cast(F16, meta=_meta_from_amax(F16, amax, dev)))
+        self.weight_meta = _meta_from_amax(E4M3, amax, dev)
+        self.weight_shard = _k.cast_to_fp8(shard, E4M3, self.weight_meta.scale)
+        self.weight_shard_t = _k.transpose_fp8(self.weight_shard)
+        self.bias = linear.bias
+        self.scaling_metas = linear.scaling_metas if isinstance(linear, FP8Linear) else dict(
+            input=ScalingMeta(E4M3, window_size=FP8Linear.DEFAULT_WINDOW_SIZE, device=dev),
+            wgrad=ScalingMeta(E4M3, window_size=1, device=dev),
+            ograd=ScalingMeta(E5M2, window_size=FP8Linear.DEFAULT_WINDOW_SIZE, device=dev),
+        )
+        self.master._scaling_metas = self.scaling_metas
+        self._holder = torch.nn.Parameter(torch.empty(0, device=dev))
+
+    def forward(self, x):
+        model_state.ready_to_scale_tensor = True
+        return _ShardedLinearFn.apply(x, self, self._holder, self.bias)
+
+    @torch.no_grad()
+    def requantize(self):
+        """Master shard → e4m3 shard (and its transpose) with the tensor-wide scale."""
+        fs = self._fsdp
+        amax = self.weight_meta.amax[0]
+        amax.copy_(self.master.meta.amax[0])
+        if fs.world > 1:
+            dist.all_reduce(amax, op=dist.ReduceOp.MAX, group=fs.group)
+        self.weight_meta.reset_scaling_factor()
+        torch.reciprocal(self.weight_meta.scale, out=self.weight_meta.scale_inv)
+        factor = self.weight_meta.scale * self.master.meta.scale_inv
+        self.weight_shard, self.weight_shard_t = _k.cast_transpose_fp8(self.master.value, E4M3, factor)
+
+    def extra_repr(self):
+        return f'in_features={self.in_features}, out_features={self.out_features}, shards={self._fsdp.world}'
+
+
+def _meta_from_amax(qtype, amax, device):
+    meta = ScalingMeta(qtype, window_size=1, device=device)
+    meta.amax[0] = amax
+    meta.reset_scaling_factor()
+    torch.reciprocal(meta.scale, out=meta.scale_inv)
+    meta.amax_counter += 1    # keep the given scale when casting with this meta
+    return meta
+
+
+class FP8FullyShardedDataParallel(torch.nn.Module):
+    """Wrap ``module``: shard every (FP8)Linear over ``process_group``, replicate and all-reduce everything else.
+
+    Use ``optimizer = fsdp.build_optimizer(torch.optim.AdamW, lr=...)`` (low-bit Adam on the master shards and on
+    the replicated high-precision parameters) and call ``fsdp.step(optimizer)`` after ``backward``.
+    """
+    def __init__(self, module, process_group=None, min_shard_numel=0, **unused):
+        super().__init__()
+        self.group = process_group
+        self.world = DistUtil.get_world_size(process_group)
+        self.rank = DistUtil.get_rank(process_group)
+        self.ctx = None
+        self.sharded = []
+        biggest_shard, biggest_out = 0, 0
+        module = self._convert(module, min_shard_numel)
+        for m in self.sharded:
+            rows, K = m.weight_shard.shape
+            pad_k = (K + 255) // 256 * 256
+            biggest_shard = max(biggest_shard, rows * K, pad_k * rows)
+            biggest_out = max(biggest_out, m.out_features * K * 4)
+        first = self.sharded[0].weight_shard if self.sharded else None
+        if first is not None and first.is_cuda and self.world > 1:
+            self.ctx = FusedGemmContext(process_group, biggest_shard, biggest_out)
+        self.module = module
+        model_state.register_scaling_metas(module, None)
+        self.hp_params = [p for p in module.parameters() if not isinstance(p, ScalingParameter) and p.numel() > 0]
+        if self.world > 1:
+            src = dist.get_global_rank(process_group, 0) if process_group is not None else 0
+            for p in self.hp_params:
+                dist.broadcast(p.data, src=src, group=process_group)
+
+    def _convert(self, module, min_numel):
+        if isinstance(module, (torch.nn.Linear, FP8Linear)) and not getattr(module, 'use_fp32_linear', False):
+            if module.in_features * module.out_features >= min_numel and module.out_features % self.world == 0:
+                sharded = ShardedFP8Linear(module, self)
+                self.sharded.append(sharded)
+                return sharded
+            return module
+        for name, child in list(module.named_children()):
+            setattr(module, name, self._convert(child, min_numel))
+        return module
+
+    def forward(self, *args, **kwargs):
+        return self.module(*args, **kwargs)
+
+    def master_parameters(self):
+        """Parameters an optimizer should update: master shards of the sharded linears + replicated parameters."""
+        return [m.master for m in self.sharded] + self.hp_params
+
+    def build_optimizer(self, torch_cls=torch.optim.AdamW, **kwargs):
+        from msamp.optim import LBAdam, LBAdamW
+        cls = LBAdamW if torch_cls is torch.optim.AdamW else LBAdam
+        return cls(self.master_parameters(), exp_avg_dtype=torch.uint8, exp_avg_sq_dtype=torch.float16, **kwargs)
+
+    @torch.no_grad()
+    def step(self, optimizer):
+        """Average the replicated gradients, update, re-quantise the shards, clear gradients."""
+        if self.world > 1:
+            grads = [p.grad for p in self.hp_params if p.grad is not None]
+            by_dtype = {}
+            for g in grads:
+                by_dtype.setdefault(g.dtype, []).append(g)
+            for gs in by_dtype.values():
+                flat = torch.cat([g.reshape(-1) for g in gs])
+                dist.all_reduce(flat, group=self.group)
+                flat.div_(self.world)
+                off = 0
+                for g in gs:
+                    g.copy_(flat[off:off + g.numel()].view_as(g))
+                    off += g.numel()
+        optimizer.step()
+        for m in self.sharded:
+            m.requantize()
+            m.master.grad = None
+        for p in self.hp_params:
+            p.grad = None
+
+    def memory_per_rank(self):
+        """Bytes of persistent parameter/optimizer storage on this rank for the sharded layers (fp8 W, W^T, fp16 master)."""
+        return sum(m.weight_shard.numel() * 2 + m.master.numel() * 2 for m in self.sharded)
+
+
+__all__ = ['FP8FullyShardedDataParallel', 'ShardedFP8Linear']

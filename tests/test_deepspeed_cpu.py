@@ -1,0 +1,119 @@
+"""msamp.deepspeed on CPU: config parsing, engine selection, loss decrease with/without ZeRO, checkpoints, pipeline."""
+import tempfile
+
+import pytest
+import torch
+
+from msamp import deepspeed
+from msamp.deepspeed.runtime.config import MSAMPDeepSpeedConfig
+from msamp.deepspeed.runtime.fp8.fused_optimizer import FP8Optimizer
+from msamp.deepspeed.runtime.zero.fp8_stage_1_and_2 import FP8DeepSpeedZeroOptimizer
+from msamp.optim import LBAdamW
+from tests.dist_utils import run_workers
+
+
+def _cfg(level='O2', zero=0, **extra):
+    cfg = {
+        'train_batch_size': 8, 'train_micro_batch_size_per_gpu': 4,
+        'optimizer': {'type': 'AdamW', 'params': {'lr': 1e-2, 'weight_decay': 0.01}},
+        'zero_optimization': {'stage': zero},
+        'msamp': {'enabled': True, 'opt_level': level},
+        'gradient_clipping': 1.0, 'wall_clock_breakdown': True, 'steps_per_print': 1000,
+    }
+    cfg.update(extra)
+    return cfg
+
+
+def _model():
+    torch.manual_seed(0)
+    return torch.nn.Sequential(torch.nn.Linear(16, 32), torch.nn.GELU(), torch.nn.Linear(32, 4))
+
+
+def test_config_parsing_and_checks():
+    c = MSAMPDeepSpeedConfig(_cfg())
+    assert c.msamp_enabled and c.msamp_optlevel == 'O2' and c.gradient_accumulation_steps == 2 and not c.msamp_use_te
+    assert not MSAMPDeepSpeedConfig({'train_batch_size': 4}).msamp_enabled
+    with pytest.raises(AssertionError):
+        MSAMPDeepSpeedConfig(_cfg(level='O3', zero=0))
+    with pytest.raises(AssertionError):
+        MSAMPDeepSpeedConfig(_cfg(level='O7'))
+    with pytest.raises(AssertionError):
+        MSAMPDeepSpeedConfig({'train_batch_size': 8, 'train_micro_batch_size_per_gpu': 3, 'gradient_accumulation_steps': 1})
+
+
+@pytest.mark.parametrize('level,zero,cls', [('O1', 0, FP8Optimizer), ('O2', 0, FP8Optimizer), ('O2', 1, FP8DeepSpeedZeroOptimizer),
+                                            ('O3', 2, FP8DeepSpeedZeroOptimizer)])
+def test_engine_selection_and_training(level, zero, cls):
+    engine, opt, _, _ = deepspeed.initialize(model=_model(), config=_cfg(level, zero))
+    assert type(opt) is cls and isinstance(opt.optimizer, LBAdamW)
+    x, y = torch.randn(32, 16), torch.randn(32, 4)
+    losses = []
+    for epoch in range(10):
+        for i in range(0, 32, 4):
+            loss = ((engine(x[i:i + 4]) - y[i:i + 4])**2).mean()
+            engine.backward(loss)
+            engine.step()
+        losses.append(((engine(x) - y)**2).mean().item())
+    assert losses[-1] < losses[0]
+    assert engine.global_steps == 40 and engine.micro_steps == 80
+    assert 'forward' in engine.timers.summary()
+    with tempfile.TemporaryDirectory() as d:
+        engine.save_checkpoint(d, tag='t')
+        before = [p.float().clone() for p in engine.module.parameters()]
+        engine.load_checkpoint(d)
+        for a, b in zip(before, engine.module.parameters()):
+            assert torch.allclose(a, b.float(), atol=1e-2)
+    sd = opt.state_dict()
+    assert {'dynamic_loss_scale', 'cur_scale', 'optimizer_state_dict', 'fp32_groups_flat', 'fp8_master_groups', 'clip_grad'} <= set(sd)
+    if cls is FP8DeepSpeedZeroOptimizer:
+        assert 'single_partition_of_fp8_groups' in sd
+
+
+def test_dynamic_loss_scale_skips_overflow():
+    cfg = _cfg('O2', 0, fp16={'enabled': True, 'loss_scale': 0, 'initial_scale_power': 4, 'hysteresis': 1})
+    engine, opt, _, _ = deepspeed.initialize(model=_model(), config=cfg)
+    assert opt.dynamic_loss_scale and opt.cur_scale == 16
+    x = torch.randn(4, 16)
+    w0 = engine.module[0].weight.float().clone()
+    for _ in range(2):
+        engine.backward(engine(x).mean() * float('inf'))    # every gradient becomes inf/nan
+        engine.step()
+    assert engine.skipped_steps == 1 and opt.cur_scale == 8
+    assert torch.equal(w0, engine.module[0].weight.float())
+
+
+def test_plain_engine_without_msamp():
+    cfg = {'train_batch_size': 4, 'optimizer': {'type': 'Adam', 'params': {'lr': 1e-2}}}
+    engine, opt, _, _ = deepspeed.initialize(model=_model(), config=cfg)
+    assert isinstance(opt, torch.optim.Adam)
+    loss = engine(torch.randn(4, 16)).square().mean()
+    engine.backward(loss)
+    engine.step()
+    assert engine.global_steps == 1
+
+
+def _pipeline(rank, world):
+    from msamp.deepspeed import PipelineModule
+    torch.manual_seed(0)
+    layers = [torch.nn.Linear(16, 32), torch.nn.GELU(), torch.nn.Linear(32, 32), torch.nn.GELU(), torch.nn.Linear(32, 4)]
+    pipe = PipelineModule(layers, num_stages=2, loss_fn=lambda out, y: ((out - y)**2).mean())
+    cfg = {'train_batch_size': 8, 'train_micro_batch_size_per_gpu': 4, 'optimizer': {'type': 'AdamW', 'params': {'lr': 1e-2}},
+           'msamp': {'enabled': True, 'opt_level': 'O2'}}
+    engine, _, _, _ = deepspeed.initialize(model=pipe, config=cfg)
+    g = torch.Generator().manual_seed(1)
+    x, y = torch.randn(8, 16, generator=g), torch.randn(8, 4, generator=g)
+
+    def batches():
+        while True:
+            yield x[:4], y[:4]
+            yield x[4:], y[4:]
+
+    it = batches()
+    losses = [engine.train_batch(it).item() for _ in range(15)]
+    if pipe.is_last_stage:
+        assert losses[-1] < losses[0], losses
+    assert len(list(pipe.layers)) in (2, 3)
+
+
+def test_pipeline_engine_two_stages():
+    run_workers(_pipeline, 2)

@@ -178,3 +178,44 @@ def _ddp_training(rank, world):
 
 def test_fp8_ddp_mnist_shaped_cnn_gloo():
     run_workers(_ddp_training, 2)
+
+
+def _full_shard(rank, world):
+    from msamp.fsdp import FP8FullyShardedDataParallel, FsdpReplacer
+    torch.manual_seed(0)
+    model = _mk_model()
+    ref = _mk_model()
+    fsdp = FP8FullyShardedDataParallel(model)
+    assert len(fsdp.sharded) == 3 and fsdp.sharded[0].weight_shard.shape == (32 // world, 16)
+    opt = fsdp.build_optimizer(torch.optim.AdamW, lr=1e-2)
+    ropt = torch.optim.AdamW(ref.parameters(), lr=1e-2)
+    x_all, y_all = torch.randn(8 * world, 16), torch.randn(8 * world, 4)
+    for _ in range(10):
+        xb, yb = x_all[rank * 8:(rank + 1) * 8], y_all[rank * 8:(rank + 1) * 8]
+        loss = ((fsdp(xb) - yb)**2).mean()
+        loss.backward()
+        fsdp.step(opt)
+        ropt.zero_grad()
+        rl = ((ref(x_all) - y_all)**2).mean()
+        rl.backward()
+        ropt.step()
+    full = ((fsdp(x_all) - y_all)**2).mean()
+    assert abs(full.item() - ((ref(x_all) - y_all)**2).mean().item()) < 0.15 * rl.item() + 0.02
+    # one scale per tensor on every shard
+    s = fsdp.sharded[0].weight_meta.scale.clone()
+    s2 = s.clone()
+    dist.broadcast(s2, src=0)
+    assert torch.equal(s, s2)
+    # the torch-FSDP preparation path: fp32-viewed parameters carrying their meta
+    from msamp.nn import model_state
+    model_state.clear()
+    m2 = FsdpReplacer.replace(_mk_model())
+    p = m2[0].weight
+    assert p.dtype == torch.float32 and p._original_shape == (32, 16) and p._padded == 0 and p._meta.qtype == E4M3
+    out = m2(torch.randn(4, 16))
+    out.sum().backward()
+    assert p.grad is not None and p.grad.shape == p.shape
+
+
+def test_full_shard_gloo():
+    run_workers(_full_shard, 2)

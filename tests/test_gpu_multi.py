@@ -239,3 +239,35 @@ def _sp_block_fused(rank, world):
 def test_sequence_parallel_block_fused_kernels():
     _need(2)
     run_workers(_sp_block_fused, 2, backend='nccl')
+
+
+def _full_shard_fused(rank, world):
+    from msamp.fsdp import FP8FullyShardedDataParallel
+    from msamp.ops import native
+    dev = torch.device('cuda', rank)
+    torch.manual_seed(0)
+    model = torch.nn.Sequential(torch.nn.Linear(512, 1024), torch.nn.GELU(), torch.nn.Linear(1024, 512)).to(dev)
+    fsdp = FP8FullyShardedDataParallel(model)
+    assert fsdp.ctx is not None and fsdp.ctx.native and len(fsdp.sharded) == 2
+    opt = fsdp.build_optimizer(torch.optim.AdamW, lr=2e-3)
+    torch.manual_seed(5)
+    xs = torch.randn(world * 256, 512, device=dev).bfloat16()
+    ys = torch.randn(world * 256, 512, device=dev).bfloat16()
+    losses = []
+    for _ in range(15):
+        loss = (fsdp(xs[rank * 256:(rank + 1) * 256]) - ys[rank * 256:(rank + 1) * 256]).float().square().mean()
+        loss.backward()
+        fsdp.step(opt)
+        losses.append(loss.item())
+    torch.cuda.synchronize()
+    assert native.device_status() == 0
+    assert losses[-1] < 0.9 * losses[0], losses
+    s = fsdp.sharded[0].weight_meta.scale.clone()
+    ref = s.clone()
+    dist.broadcast(ref, src=0)
+    assert torch.equal(s, ref)
+
+
+def test_full_shard_fused_two_gpus():
+    _need(2)
+    run_workers(_full_shard_fused, 2, backend='nccl')
