@@ -49,7 +49,11 @@ def initialize(model, optimizer=None, opt_level='O1', use_te=False, group=None, 
     if opt_level not in opt_levels:
         raise ValueError(f'Invalid optimization level. Please choose from {opt_levels}')
     if not optimizer:
-        optimizer = torch.optim.AdamW(model.parameters())
+        # Default AdamW. The model may already contain ScalingParameters (msamp.te modules), which torch's
+        # optimizers reject, so the stand-in is built on the plain tensors only and rebound after conversion.
+        plain = [p for p in model.parameters() if torch.is_tensor(p)]
+        optimizer = torch.optim.AdamW(plain if plain else [torch.nn.Parameter(torch.zeros(1))])
+        optimizer.param_groups[0]['params'] = list(model.parameters())
     if not (isinstance(optimizer, (torch.optim.AdamW, torch.optim.Adam)) or _is_fused_adam(optimizer)):
         raise ValueError(f'Optimizer {optimizer} is not supported in optimization level {opt_level}')
 
