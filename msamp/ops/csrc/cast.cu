@@ -142,10 +142,13 @@ __global__ void __launch_bounds__(kThreads) cast_from_fp8_kernel(const uint8_t* 
 }
 
 // ---- cast + transpose -----------------------------------------------------------------------------
-// One CTA converts a 64x64 tile. The row-major copy is written straight from registers; the
-// transposed copy goes through shared memory so that both outputs are written in 64-byte runs.
-constexpr int kTile = 64;
-constexpr int kTStride = kTile + 4;    // bytes; keeps 4-byte alignment and spreads banks
+// One CTA converts a tile of 128 rows x 64 columns.  The row-major copy is written straight from
+// registers (64-byte runs); the transposed copy goes through shared memory and leaves in 128-byte
+// runs.  The shared tile is stored transposed with a row stride of 33 words, which makes the
+// word reads of the second phase conflict free.
+constexpr int kTileR = 128;
+constexpr int kTileC = 64;
+constexpr int kCtStride = 132;    // bytes per transposed row in shared memory
 
 template <typename T, int FMT, bool WRITE_ROWMAJOR>
 __global__ void __launch_bounds__(kThreads) cast_transpose_kernel(const T* __restrict__ x, uint8_t* __restrict__ out,
@@ -153,7 +156,7 @@ __global__ void __launch_bounds__(kThreads) cast_transpose_kernel(const T* __res
                                                                    const float* __restrict__ scale_ptr, float* amax,
                                                                    float* scale_inv_out, const float* __restrict__ amax_in,
                                                                    float fp_max, bool aligned) {
-  __shared__ __align__(16) uint8_t tile_t[kTile * kTStride];    // [c][r]
+  __shared__ __align__(16) uint8_t tile_t[kTileC * kCtStride];    // [c][r]
   __shared__ float red[32];
   float scale = *scale_ptr;
   float logical_scale = scale;
@@ -165,20 +168,22 @@ __global__ void __launch_bounds__(kThreads) cast_transpose_kernel(const T* __res
     scale = logical_scale * scale;
   }
   if (scale_inv_out != nullptr && blockIdx.x == 0 && threadIdx.x == 0) *scale_inv_out = __frcp_rn(logical_scale);
-  const int tiles_c = (cols + kTile - 1) / kTile;
-  const int tiles_r = (rows + kTile - 1) / kTile;
+  const int tiles_c = (cols + kTileC - 1) / kTileC;
+  const int tiles_r = (rows + kTileR - 1) / kTileR;
   const int64_t ntiles = (int64_t)tiles_c * tiles_r;
   float m = 0.0f;
   for (int64_t t = blockIdx.x; t < ntiles; t += gridDim.x) {
-    const int r0 = (int)(t / tiles_c) * kTile;
-    const int c0 = (int)(t % tiles_c) * kTile;
-    const bool full = aligned && (r0 + kTile <= rows) && (c0 + kTile <= cols);
+    const int r0 = (int)(t / tiles_c) * kTileR;
+    const int c0 = (int)(t % tiles_c) * kTileC;
+    const bool full = aligned && (r0 + kTileR <= rows) && (c0 + kTileC <= cols);
     if (full) {
-      // 8 threads cover a row of 64 elements (8 each); 32 rows per pass.
-      const int cr = threadIdx.x >> 3, cc = (threadIdx.x & 7) * 8;
+      // 8 threads cover the 64 columns (8 each); a thread converts 4 consecutive rows and transposes its
+      // 4 x 8 bytes in registers, so the shared tile is written with 32-bit stores.
+      const int rg = threadIdx.x >> 3, cc = (threadIdx.x & 7) * 8;
+      uint32_t w[4][2];
 #pragma unroll
-      for (int p = 0; p < 2; ++p) {
-        const int r = cr + p * 32;
+      for (int i = 0; i < 4; ++i) {
+        const int r = rg * 4 + i;
         const T* src = x + (int64_t)(r0 + r) * cols + c0 + cc;
         T e[8];
         if constexpr (sizeof(T) == 2) {
@@ -187,31 +192,51 @@ __global__ void __launch_bounds__(kThreads) cast_transpose_kernel(const T* __res
           *reinterpret_cast<Bytes16*>(e) = *reinterpret_cast<const Bytes16*>(src);
           *reinterpret_cast<Bytes16*>(e + 4) = *reinterpret_cast<const Bytes16*>(src + 4);
         }
-        uint8_t b[8];
+        uint16_t q[4];
 #pragma unroll
         for (int j = 0; j < 8; j += 2) {
           float a0 = to_f32<T>(e[j]), a1 = to_f32<T>(e[j + 1]);
           m = fmaxf(m, fmaxf(abs_nan_to_inf(a0), abs_nan_to_inf(a1)));
-          uint16_t q = f32x2_to_fp8x2<FMT>(a0 * scale, a1 * scale);
-          b[j] = (uint8_t)(q & 0xff);
-          b[j + 1] = (uint8_t)(q >> 8);
+          q[j / 2] = f32x2_to_fp8x2<FMT>(a0 * scale, a1 * scale);
         }
-        if (WRITE_ROWMAJOR) *reinterpret_cast<Bytes8*>(out + (int64_t)(r0 + r) * cols + c0 + cc) = *reinterpret_cast<Bytes8*>(b);
+        w[i][0] = (uint32_t)q[0] | ((uint32_t)q[1] << 16);
+        w[i][1] = (uint32_t)q[2] | ((uint32_t)q[3] << 16);
+        if (WRITE_ROWMAJOR) {
+          Bytes8 o;
+          o.w[0] = w[i][0];
+          o.w[1] = w[i][1];
+          *reinterpret_cast<Bytes8*>(out + (int64_t)(r0 + r) * cols + c0 + cc) = o;
+        }
+      }
 #pragma unroll
-        for (int j = 0; j < 8; ++j) tile_t[(cc + j) * kTStride + r] = b[j];
+      for (int h = 0; h < 2; ++h) {
+        // 4 x 4 byte transpose: column word j holds rows 4*rg .. 4*rg+3 of column cc + 4*h + j
+        const uint32_t a = __byte_perm(w[0][h], w[1][h], 0x5140), b2 = __byte_perm(w[2][h], w[3][h], 0x5140);
+        const uint32_t c = __byte_perm(w[0][h], w[1][h], 0x7362), d = __byte_perm(w[2][h], w[3][h], 0x7362);
+        uint32_t* base = reinterpret_cast<uint32_t*>(tile_t);
+        base[(cc + 4 * h + 0) * (kCtStride / 4) + rg] = __byte_perm(a, b2, 0x5410);
+        base[(cc + 4 * h + 1) * (kCtStride / 4) + rg] = __byte_perm(a, b2, 0x7632);
+        base[(cc + 4 * h + 2) * (kCtStride / 4) + rg] = __byte_perm(c, d, 0x5410);
+        base[(cc + 4 * h + 3) * (kCtStride / 4) + rg] = __byte_perm(c, d, 0x7632);
       }
       __syncthreads();
       {
-        const int c = threadIdx.x >> 2, rr = (threadIdx.x & 3) * 16;
-        Bytes16 o;
+        // 4 threads cover one transposed row of 128 bytes (32 each)
+        const int c = threadIdx.x >> 2, rr = (threadIdx.x & 3) * 32;
+        Bytes16 o0, o1;
 #pragma unroll
-        for (int j = 0; j < 4; ++j) o.w[j] = *reinterpret_cast<const uint32_t*>(&tile_t[c * kTStride + rr + 4 * j]);
-        *reinterpret_cast<Bytes16*>(out_t + (int64_t)(c0 + c) * rows + r0 + rr) = o;
+        for (int j = 0; j < 4; ++j) {
+          o0.w[j] = *reinterpret_cast<const uint32_t*>(&tile_t[c * kCtStride + rr + 4 * j]);
+          o1.w[j] = *reinterpret_cast<const uint32_t*>(&tile_t[c * kCtStride + rr + 16 + 4 * j]);
+        }
+        uint8_t* dst = out_t + (int64_t)(c0 + c) * rows + r0 + rr;
+        *reinterpret_cast<Bytes16*>(dst) = o0;
+        *reinterpret_cast<Bytes16*>(dst + 16) = o1;
       }
       __syncthreads();
     } else {
-      for (int i = threadIdx.x; i < kTile * kTile; i += blockDim.x) {
-        const int r = i / kTile, c = i % kTile;
+      for (int i = threadIdx.x; i < kTileR * kTileC; i += blockDim.x) {
+        const int r = i / kTileC, c = i % kTileC;
         uint8_t q = 0;
         if (r0 + r < rows && c0 + c < cols) {
           float a = to_f32<T>(x[(int64_t)(r0 + r) * cols + c0 + c]);
@@ -219,12 +244,12 @@ __global__ void __launch_bounds__(kThreads) cast_transpose_kernel(const T* __res
           q = f32_to_fp8<FMT>(a * scale);
           if (WRITE_ROWMAJOR) out[(int64_t)(r0 + r) * cols + c0 + c] = q;
         }
-        tile_t[c * kTStride + r] = q;
+        tile_t[c * kCtStride + r] = q;
       }
       __syncthreads();
-      for (int i = threadIdx.x; i < kTile * kTile; i += blockDim.x) {
-        const int c = i / kTile, r = i % kTile;
-        if (r0 + r < rows && c0 + c < cols) out_t[(int64_t)(c0 + c) * rows + r0 + r] = tile_t[c * kTStride + r];
+      for (int i = threadIdx.x; i < kTileR * kTileC; i += blockDim.x) {
+        const int c = i / kTileR, r = i % kTileR;
+        if (r0 + r < rows && c0 + c < cols) out_t[(int64_t)(c0 + c) * rows + r0 + r] = tile_t[c * kCtStride + r];
       }
       __syncthreads();
     }
@@ -236,6 +261,8 @@ __global__ void __launch_bounds__(kThreads) cast_transpose_kernel(const T* __res
 }
 
 // ---- byte transpose ---------------------------------------------------------------------------------
+constexpr int kTile = 64;
+constexpr int kTStride = kTile + 4;    // bytes; keeps 4-byte alignment and spreads banks
 __global__ void __launch_bounds__(kThreads) transpose_bytes_kernel(const uint8_t* __restrict__ in, uint8_t* __restrict__ out,
                                                                     int rows, int cols, bool aligned) {
   __shared__ __align__(16) uint8_t tile_t[kTile * kTStride];
@@ -378,7 +405,7 @@ MSAMP_API int msamp_cast_transpose_fp8(const void* x, int rows, int cols, int dt
   MSAMP_REQUIRE(rows >= 0 && cols >= 0 && out_t != nullptr && scale != nullptr, "msamp_cast_transpose_fp8: bad arguments");
   if (amax) cudaMemsetAsync(amax, 0, sizeof(float), stream);
   if ((int64_t)rows * cols == 0) return MSAMP_OK;
-  int64_t ntiles = (int64_t)((rows + kTile - 1) / kTile) * ((cols + kTile - 1) / kTile);
+  int64_t ntiles = (int64_t)((rows + kTileR - 1) / kTileR) * ((cols + kTileC - 1) / kTileC);
   int cap = msamp_sm_count() * 8;
   int grid = (int)(ntiles < cap ? ntiles : cap);
   const bool aligned = aligned16(x) && aligned16(out_t) && (out == nullptr || aligned8(out)) && (cols % 8 == 0) && (rows % 16 == 0);

@@ -39,6 +39,7 @@ struct GemmParams {
   int bias_dtype;
   int accumulate;
   int a_fmt, b_fmt;
+  int group_m;    // row tiles per rasterisation group (see tile_to_mn); 0 means all of them
 };
 
 template <typename OutT>

@@ -17,6 +17,21 @@
 namespace {
 using namespace gemm;
 
+// Tile index -> (m tile, n tile).  Tiles are walked in groups of group_m row tiles: inside a group the row
+// index runs fastest, so the CTAs of one wave share a few A tiles and a few B tiles that stay in L2
+// (with a plain column-major walk a wave touches every A tile once and large-K problems stream A
+// from HBM once per column of tiles).  The host picks group_m so that a group's slab of A stays well
+// inside the 126 MB L2; when all of A fits, one group covers every row tile and B is streamed exactly once.
+__device__ __forceinline__ void tile_to_mn(int tile, int num_m, int num_n, int group_m, int& mi, int& ni) {
+  const int per_group = group_m * num_n;
+  const int g = tile / per_group;
+  const int first = g * group_m;
+  const int gsize = (num_m - first) < group_m ? (num_m - first) : group_m;
+  const int r = tile - g * per_group;
+  mi = first + r % gsize;
+  ni = r / gsize;
+}
+
 template <int BN, typename OutT>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_fp8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b, const GemmParams p) {
@@ -71,8 +86,10 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
     if (lane == 0) {
       uint32_t it = 0;
       for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
-        const int m0 = (tile % num_m) * BM;
-        const int n0 = (tile / num_m) * BN;
+        int mi, ni;
+        tile_to_mn(tile, num_m, num_n, p.group_m, mi, ni);
+        const int m0 = mi * BM;
+        const int n0 = ni * BN;
         bool ok = true;
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
           const int s = it % C::STAGES;
@@ -127,8 +144,10 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
     float amax = 0.0f;
     uint32_t lt = 0;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++lt) {
-      const int m0 = (tile % num_m) * BM;
-      const int n0 = (tile / num_m) * BN;
+      int mi, ni;
+      tile_to_mn(tile, num_m, num_n, p.group_m, mi, ni);
+      const int m0 = mi * BM;
+      const int n0 = ni * BN;
       const int buf = lt & 1;
       const uint32_t aph = (lt >> 1) & 1;
       if (!tc5::mbar_wait(tfull_bar(buf), aph, abort_flag, p.status, 1u)) break;
@@ -243,6 +262,12 @@ MSAMP_API int msamp_gemm_fp8(const void* A, const void* B, void* D, int M, int N
   p.status = msamp_device_status_ptr();
   p.M = M; p.N = N; p.K = K; p.ldd = ldd; p.out_dtype = out_dtype; p.bias_dtype = bias_dtype; p.accumulate = accumulate;
   p.a_fmt = a_fmt; p.b_fmt = b_fmt;
+  {
+    const int num_m = (M + BM - 1) / BM;
+    int64_t g = (48ll << 20) / ((int64_t)BM * K);    // row tiles whose A slab is about 48 MB
+    if (g < 8) g = 8;
+    p.group_m = g >= num_m ? num_m : (int)g;
+  }
   MSAMP_DISPATCH_HP(out_dtype, T, {
     if (bn == 256) return launch<256, T>(ma, mb, p, max_ctas, stream);
     return launch<128, T>(ma, mb, p, max_ctas, stream);

@@ -528,7 +528,7 @@ MSAMP_API int msamp_gemm_fused(const MsampFusedDesc* d, void* stream_) {
   p.d = (void*)d->d; p.bias = (const void*)d->bias; p.scale_inv_a = (const float*)d->scale_inv_a; p.scale_inv_b = (const float*)d->scale_inv_b;
   p.amax_out = (float*)d->amax_out; p.status = msamp_device_status_ptr();
   p.M = d->M; p.N = d->N; p.K = d->K; p.ldd = d->ldd; p.out_dtype = d->out_dtype; p.bias_dtype = d->bias_dtype; p.accumulate = d->accumulate;
-  p.a_fmt = d->a_fmt; p.b_fmt = d->b_fmt;
+  p.a_fmt = d->a_fmt; p.b_fmt = d->b_fmt; p.group_m = 0;
   f.gather = d->gather; f.world = d->world; f.rank = d->rank; f.epoch = d->epoch; f.n_comm = d->n_comm;
   f.limit_ns = (uint64_t)(d->limit_seconds * 1e9);
   f.rs = d->rs; f.rows_per_rank = d->rows_per_rank; f.rs_out = (void*)d->rs_out; f.rs_ldo = d->rs_ldo;

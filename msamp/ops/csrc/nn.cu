@@ -13,18 +13,32 @@ namespace {
 constexpr int LN_THREADS = 256;    // widest CTA; rows that fit use 128 threads so that more rows are in flight per SM
 constexpr int LN_VPT = 4;          // vectors per thread -> rows up to 256 * 4 * 8 = 8192 elements of 16-bit data
 
-template <typename T>
-__device__ __forceinline__ float ld_param(const void* p, int i, int dtype) {
-  if (dtype == DT_F32) return reinterpret_cast<const float*>(p)[i];
-  if (dtype == DT_BF16) return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p)[i]);
-  return __half2float(reinterpret_cast<const __half*>(p)[i]);
+// N consecutive affine parameters (gamma or beta) starting at column c, as floats, with 16-byte loads.
+template <typename P, int N>
+__device__ __forceinline__ void ld_params(const void* p, int c, float (&o)[N]) {
+  const P* src = reinterpret_cast<const P*>(p) + c;
+  if constexpr (sizeof(P) == 4) {
+#pragma unroll
+    for (int j = 0; j < N; j += 4) {
+      float4 v = __ldg(reinterpret_cast<const float4*>(src + j));
+      o[j] = v.x; o[j + 1] = v.y; o[j + 2] = v.z; o[j + 3] = v.w;
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < N; j += 8) {
+      Bytes16 v = *reinterpret_cast<const Bytes16*>(src + j);
+      const P* e = reinterpret_cast<const P*>(&v);
+#pragma unroll
+      for (int q = 0; q < 8 && j + q < N; ++q) o[j + q] = to_f32<P>(e[q]);
+    }
+  }
 }
 
-template <typename T, int THREADS>
+template <typename T, typename P, int THREADS>
 __global__ void __launch_bounds__(THREADS) layernorm_fwd_kernel(const T* __restrict__ x, const void* __restrict__ gamma,
-                                                                    const void* __restrict__ beta, int pdtype, T* __restrict__ y,
-                                                                    float* __restrict__ mean_out, float* __restrict__ rstd_out, int rows,
-                                                                    int cols, float eps) {
+                                                                 const void* __restrict__ beta, T* __restrict__ y,
+                                                                 float* __restrict__ mean_out, float* __restrict__ rstd_out, int rows,
+                                                                 int cols, float eps) {
   __shared__ float red[32];
   __shared__ float stat[2];
   constexpr int N = 16 / sizeof(T);
@@ -74,15 +88,18 @@ __global__ void __launch_bounds__(THREADS) layernorm_fwd_kernel(const T* __restr
       int i = threadIdx.x + k * THREADS;
       if (i < nvec) {
         const T* e = reinterpret_cast<const T*>(&v[k]);
+        float g[N], b[N];
+        ld_params<P, N>(gamma, i * N, g);
+        if (beta) {
+          ld_params<P, N>(beta, i * N, b);
+        } else {
+#pragma unroll
+          for (int j = 0; j < N; ++j) b[j] = 0.0f;
+        }
         Bytes16 o;
         T* oe = reinterpret_cast<T*>(&o);
 #pragma unroll
-        for (int j = 0; j < N; ++j) {
-          int c = i * N + j;
-          float g = ld_param<T>(gamma, c, pdtype);
-          float b = beta ? ld_param<T>(beta, c, pdtype) : 0.0f;
-          oe[j] = from_f32<T>((to_f32<T>(e[j]) - mean) * rstd * g + b);
-        }
+        for (int j = 0; j < N; ++j) oe[j] = from_f32<T>((to_f32<T>(e[j]) - mean) * rstd * g[j] + b[j]);
         reinterpret_cast<Bytes16*>(yr)[i] = o;
       }
     }
@@ -90,22 +107,26 @@ __global__ void __launch_bounds__(THREADS) layernorm_fwd_kernel(const T* __restr
   }
 }
 
-// Backward: dx per row; dgamma / dbeta partial sums per CTA (each thread owns fixed columns),
-// written to part[gridDim.x][2][cols] and reduced by a second kernel.
-template <typename T, int THREADS>
+// Backward: dx per row; dgamma / dbeta partial sums per CTA (each thread owns fixed columns, whose
+// gamma it keeps in registers for all rows), written to part[gridDim.x][2][cols] and reduced by a
+// second kernel.
+template <typename T, typename P, int THREADS>
 __global__ void __launch_bounds__(THREADS) layernorm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x,
-                                                                    const void* __restrict__ gamma, int pdtype,
-                                                                    const float* __restrict__ mean, const float* __restrict__ rstd,
-                                                                    T* __restrict__ dx, float* __restrict__ part, int rows, int cols) {
+                                                                 const void* __restrict__ gamma, const float* __restrict__ mean,
+                                                                 const float* __restrict__ rstd, T* __restrict__ dx,
+                                                                 float* __restrict__ part, int rows, int cols) {
   __shared__ float red[32];
   __shared__ float stat[2];
   constexpr int N = 16 / sizeof(T);
   const int nvec = cols / N;
-  float dg[LN_VPT][N], db[LN_VPT][N];
+  float dg[LN_VPT][N], db[LN_VPT][N], gm[LN_VPT][N];
 #pragma unroll
-  for (int k = 0; k < LN_VPT; ++k)
+  for (int k = 0; k < LN_VPT; ++k) {
+    int i = threadIdx.x + k * THREADS;
 #pragma unroll
-    for (int j = 0; j < N; ++j) dg[k][j] = db[k][j] = 0.0f;
+    for (int j = 0; j < N; ++j) dg[k][j] = db[k][j] = gm[k][j] = 0.0f;
+    if (i < nvec) ld_params<P, N>(gamma, i * N, gm[k]);
+  }
 
   for (int row = blockIdx.x; row < rows; row += gridDim.x) {
     const T* xr = x + (int64_t)row * cols;
@@ -119,13 +140,19 @@ __global__ void __launch_bounds__(THREADS) layernorm_bwd_kernel(const T* __restr
       if (i < nvec) {
         vx[k] = reinterpret_cast<const Bytes16*>(xr)[i];
         vd[k] = reinterpret_cast<const Bytes16*>(dyr)[i];
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < LN_VPT; ++k) {
+      int i = threadIdx.x + k * THREADS;
+      if (i < nvec) {
         const T* ex = reinterpret_cast<const T*>(&vx[k]);
         const T* ed = reinterpret_cast<const T*>(&vd[k]);
 #pragma unroll
         for (int j = 0; j < N; ++j) {
           float xh = (to_f32<T>(ex[j]) - mu) * rs;
           float d = to_f32<T>(ed[j]);
-          float gd = d * ld_param<T>(gamma, i * N + j, pdtype);
+          float gd = d * gm[k][j];
           s1 += gd;
           s2 += gd * xh;
           dg[k][j] += d * xh;
@@ -151,7 +178,7 @@ __global__ void __launch_bounds__(THREADS) layernorm_bwd_kernel(const T* __restr
 #pragma unroll
         for (int j = 0; j < N; ++j) {
           float xh = (to_f32<T>(ex[j]) - mu) * rs;
-          float gd = to_f32<T>(ed[j]) * ld_param<T>(gamma, i * N + j, pdtype);
+          float gd = to_f32<T>(ed[j]) * gm[k][j];
           oe[j] = from_f32<T>(rs * (gd - m1 - xh * m2));
         }
         reinterpret_cast<Bytes16*>(dxr)[i] = o;
@@ -340,6 +367,15 @@ __global__ void __launch_bounds__(512) xent_bwd_kernel(T* __restrict__ logits, c
 
 }    // namespace
 
+// Launch `kernel<T, P, THREADS>` for the (activation dtype, parameter dtype) pair; parameters are either fp32 or of the
+// activation dtype.
+#define MSAMP_LN_DISPATCH(dtype, pdtype, T, P, ...)                                   \
+  MSAMP_DISPATCH_HP(dtype, T, {                                                       \
+    if ((pdtype) == DT_F32) { using P = float; __VA_ARGS__; }                          \
+    else if ((pdtype) == (dtype)) { using P = T; __VA_ARGS__; }                        \
+    else { msamp_set_error("layernorm: parameters must be fp32 or match the activation dtype"); return MSAMP_EDTYPE; } \
+  })
+
 MSAMP_API int msamp_layernorm_max_cols(int dtype) { return LN_THREADS * LN_VPT * (dtype == DT_F32 ? 4 : 8); }
 
 MSAMP_API int msamp_layernorm_fwd(const void* x, const void* gamma, const void* beta, int dtype, int pdtype, void* y, float* mean,
@@ -352,11 +388,11 @@ MSAMP_API int msamp_layernorm_fwd(const void* x, const void* gamma, const void* 
   const bool narrow = cols <= 128 * LN_VPT * (dtype == DT_F32 ? 4 : 8);
   int cap = msamp_sm_count() * (narrow ? 16 : 8);
   int grid = rows < cap ? rows : cap;
-  MSAMP_DISPATCH_HP(dtype, T, {
+  MSAMP_LN_DISPATCH(dtype, pdtype, T, P, {
     if (narrow)
-      layernorm_fwd_kernel<T, 128><<<grid, 128, 0, stream>>>((const T*)x, gamma, beta, pdtype, (T*)y, mean, rstd, rows, cols, eps);
+      layernorm_fwd_kernel<T, P, 128><<<grid, 128, 0, stream>>>((const T*)x, gamma, beta, (T*)y, mean, rstd, rows, cols, eps);
     else
-      layernorm_fwd_kernel<T, 256><<<grid, 256, 0, stream>>>((const T*)x, gamma, beta, pdtype, (T*)y, mean, rstd, rows, cols, eps);
+      layernorm_fwd_kernel<T, P, 256><<<grid, 256, 0, stream>>>((const T*)x, gamma, beta, (T*)y, mean, rstd, rows, cols, eps);
   });
   return msamp_check_launch("msamp_layernorm_fwd");
 }
@@ -373,11 +409,11 @@ MSAMP_API int msamp_layernorm_bwd(const void* dy, const void* x, const void* gam
   int nparts = msamp_layernorm_bwd_parts();
   int grid = rows < nparts ? rows : nparts;
   const bool narrow = cols <= 128 * LN_VPT * (dtype == DT_F32 ? 4 : 8);
-  MSAMP_DISPATCH_HP(dtype, T, {
+  MSAMP_LN_DISPATCH(dtype, pdtype, T, P, {
     if (narrow)
-      layernorm_bwd_kernel<T, 128><<<grid, 128, 0, stream>>>((const T*)dy, (const T*)x, gamma, pdtype, mean, rstd, (T*)dx, part, rows, cols);
+      layernorm_bwd_kernel<T, P, 128><<<grid, 128, 0, stream>>>((const T*)dy, (const T*)x, gamma, mean, rstd, (T*)dx, part, rows, cols);
     else
-      layernorm_bwd_kernel<T, 256><<<grid, 256, 0, stream>>>((const T*)dy, (const T*)x, gamma, pdtype, mean, rstd, (T*)dx, part, rows, cols);
+      layernorm_bwd_kernel<T, P, 256><<<grid, 256, 0, stream>>>((const T*)dy, (const T*)x, gamma, mean, rstd, (T*)dx, part, rows, cols);
   });
   layernorm_reduce_kernel<<<(cols + 31) / 32, 256, 0, stream>>>(part, grid, cols, dgamma, dbeta, pdtype);
   return msamp_check_launch("msamp_layernorm_bwd");
@@ -421,11 +457,11 @@ MSAMP_API int msamp_layernorm_bwd_static(const void* dy, const void* x, const vo
   // Each of the `grid` CTAs overwrites its whole slice of the scratch and the reduction reads
   // exactly those slices, so leftovers of an earlier call never need clearing.
   const bool narrow = cols <= 128 * LN_VPT * (dtype == DT_F32 ? 4 : 8);
-  MSAMP_DISPATCH_HP(dtype, T, {
+  MSAMP_LN_DISPATCH(dtype, pdtype, T, P, {
     if (narrow)
-      layernorm_bwd_kernel<T, 128><<<grid, 128, 0, stream>>>((const T*)dy, (const T*)x, gamma, pdtype, mean, rstd, (T*)dx, part, rows, cols);
+      layernorm_bwd_kernel<T, P, 128><<<grid, 128, 0, stream>>>((const T*)dy, (const T*)x, gamma, mean, rstd, (T*)dx, part, rows, cols);
     else
-      layernorm_bwd_kernel<T, 256><<<grid, 256, 0, stream>>>((const T*)dy, (const T*)x, gamma, pdtype, mean, rstd, (T*)dx, part, rows, cols);
+      layernorm_bwd_kernel<T, P, 256><<<grid, 256, 0, stream>>>((const T*)dy, (const T*)x, gamma, mean, rstd, (T*)dx, part, rows, cols);
   });
   layernorm_reduce_kernel<<<(cols + 31) / 32, 256, 0, stream>>>(part, grid, cols, dgamma, dbeta, pdtype);
   return msamp_check_launch("msamp_layernorm_bwd_static");

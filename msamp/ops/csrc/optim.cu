@@ -37,13 +37,13 @@ struct AdamTensor {
   int p_st, g_st, m_st, v_st;
   float lr_wd_factor;    // 1 - lr * wd (decoupled) or 1
   float l2;              // wd for L2 mode, else 0
-  float beta1, beta2, eps, step_size, sqrt_bc2, gsign;
+  float beta1, beta2, eps, step_size, inv_sqrt_bc2, gsign;
   int tensor_scale;
   int pad;
   float red[4];          // stage-1 results: max|p|, max|m|, max|v|
 };
 
-constexpr int kChunk = 8192;    // elements per block
+constexpr int kChunk = 32768;    // elements per block
 constexpr int kAdamThreads = 256;
 
 __device__ __forceinline__ float st_max(int st) {
@@ -79,16 +79,26 @@ __device__ __forceinline__ void load8(const void* base, int st, int64_t i, float
     }
     case ST_E4M3: {
       Bytes8 r = *reinterpret_cast<const Bytes8*>(reinterpret_cast<const uint8_t*>(base) + i);
-      const uint8_t* e = reinterpret_cast<const uint8_t*>(&r);
+      const uint16_t* e = reinterpret_cast<const uint16_t*>(&r);
 #pragma unroll
-      for (int j = 0; j < 8; ++j) o[j] = fp8_to_f32<FMT_E4M3>(e[j]);
+      for (int j = 0; j < 4; ++j) {    // two elements per hardware conversion
+        __half2_raw h = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)e[j], __NV_E4M3);
+        float2 f = __half22float2(__half2(h));
+        o[2 * j] = f.x;
+        o[2 * j + 1] = f.y;
+      }
       break;
     }
     default: {
       Bytes8 r = *reinterpret_cast<const Bytes8*>(reinterpret_cast<const uint8_t*>(base) + i);
-      const uint8_t* e = reinterpret_cast<const uint8_t*>(&r);
+      const uint16_t* e = reinterpret_cast<const uint16_t*>(&r);
 #pragma unroll
-      for (int j = 0; j < 8; ++j) o[j] = fp8_to_f32<FMT_E5M2>(e[j]);
+      for (int j = 0; j < 4; ++j) {
+        __half2_raw h = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)e[j], __NV_E5M2);
+        float2 f = __half22float2(__half2(h));
+        o[2 * j] = f.x;
+        o[2 * j + 1] = f.y;
+      }
       break;
     }
   }
@@ -172,8 +182,12 @@ __device__ __forceinline__ Elem adam_elem(const AdamTensor& t, float p, float g,
   Elem e;
   e.m = t.beta1 * (m * msi) + (1.0f - t.beta1) * g;
   e.v = t.beta2 * (v * vsi) + (1.0f - t.beta2) * (g * g);
-  float denom = sqrtf(e.v) / t.sqrt_bc2 + t.eps;
-  e.p = p - t.step_size * (e.m / denom);
+  // sqrt and the division use the hardware approximations (about 1 ulp): the kernel is otherwise bound by
+  // instruction issue, not by memory, and Adam is insensitive to errors of that size
+  float root;
+  asm("sqrt.approx.ftz.f32 %0, %1;" : "=f"(root) : "f"(e.v));
+  float denom = root * t.inv_sqrt_bc2 + t.eps;
+  e.p = p - t.step_size * __fdividef(e.m, denom);
   return e;
 }
 

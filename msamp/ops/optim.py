@@ -20,7 +20,7 @@ DESC = np.dtype(
         ('n', 'i8'),
         ('p_st', 'i4'), ('g_st', 'i4'), ('m_st', 'i4'), ('v_st', 'i4'),
         ('lr_wd_factor', 'f4'), ('l2', 'f4'), ('beta1', 'f4'), ('beta2', 'f4'), ('eps', 'f4'), ('step_size', 'f4'),
-        ('sqrt_bc2', 'f4'), ('gsign', 'f4'),
+        ('inv_sqrt_bc2', 'f4'), ('gsign', 'f4'),
         ('tensor_scale', 'i4'), ('pad', 'i4'),
         ('red', 'f4', (4, )),
     ],
@@ -111,7 +111,7 @@ class FusedPlan:
             r['p_st'], r['g_st'], r['m_st'], r['v_st'] = pst, gst, mst, vst
             r['lr_wd_factor'], r['l2'] = e['lr_wd_factor'], e['l2']
             r['beta1'], r['beta2'], r['eps'] = e['beta1'], e['beta2'], e['eps']
-            r['step_size'], r['sqrt_bc2'], r['gsign'] = e['step_size'], e['sqrt_bc2'], e['gsign']
+            r['step_size'], r['inv_sqrt_bc2'], r['gsign'] = e['step_size'], 1.0 / e['sqrt_bc2'], e['gsign']
             r['tensor_scale'], r['pad'] = int(e['tensor_scale']), 0
             r['red'] = 0.0
         self.dev.copy_(host, non_blocking=True)
