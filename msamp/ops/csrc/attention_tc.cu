@@ -1,0 +1,1029 @@
+// Softmax attention for bf16, head size 128, on the sm_100a tensor path (tcgen05 + TMEM + TMA).
+//
+// Three warp-specialised kernels share one structure: warp 0 streams operand tiles with TMA
+// (4-D tensor maps over the strided [batch, seq, head, 128] views, 128-byte swizzle), warp 1 issues
+// tcgen05.mma (kind::f16) into TMEM, and warps 2..9 (one thread per accumulator row) read the scores
+// back with tcgen05.ld, do the softmax arithmetic and write the bf16 probability operand into
+// swizzled shared memory for the next MMA.
+//
+//   forward   CTA = 128 query rows, key tiles of 128:  S = Q K^T  ->  P = exp2(S - m)  ->  O += P V.
+//             Two groups of softmax warps take alternating key tiles with separate S, P and O
+//             buffers, so the MMAs of one tile run under the softmax of the other; O accumulates
+//             in TMEM and is rescaled lazily.
+//   dK/dV     CTA = 128 key rows, query tiles of 64:  S^T = K Q^T, dP^T = V dO^T,
+//             dV += P^T dO, dK += dS^T Q, both accumulated in TMEM over the whole loop.
+//   dQ        CTA = 128 query rows, key tiles of 64:  S = Q K^T, dP = dO V^T, dQ += dS K in TMEM.
+//
+// V, dO, Q and K enter the second kind of product with the reduction index as rows of the tile, so
+// the same shared-memory tile is described once K-major and once MN-major; nothing is transposed.
+// The backward pass is deterministic (no atomics).  Every mbarrier wait is bounded; when one gives
+// up, bit 2 (value 4) of the device status word is set and the CTA frees its TMEM and returns.
+//
+// Same arithmetic as the mma.sync kernels in attention.cu, which remain the path for head size 64.
+#include <mutex>
+#include <unordered_map>
+
+#include "tcgen05.cuh"
+
+namespace {
+
+constexpr int kTcThreads = 320;    // warp 0: TMA, warp 1: MMA, warps 2-5 and 6-9: the two softmax groups
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
+constexpr unsigned int kStatusBit = 4u;
+
+struct TcParams {
+  __nv_bfloat16* o;
+  float* lse;             // [b, h, s] natural-log sum-exp of the scaled scores
+  const float* delta;     // [b, h, s] rowsum(dO * O)
+  __nv_bfloat16* dq;
+  __nv_bfloat16* dk;
+  __nv_bfloat16* dv;
+  int64_t o_sb, o_ss, o_sh;    // element strides: batch, sequence, head
+  int64_t dq_sb, dq_ss, dq_sh;
+  int64_t dk_sb, dk_ss, dk_sh;
+  int64_t dv_sb, dv_ss, dv_sh;
+  int batch, heads, seqlen, causal;
+  float scale;
+  unsigned int* status;
+};
+
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
+  __nv_bfloat162 t = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&t);
+}
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+// Makes this thread's ordinary shared-memory writes visible to the async proxy (the MMA reads them).
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+// Writes v[0..31] as bf16 into row `row` of a [rows][64] panel (128-byte rows, 128-byte swizzle as
+// TMA would have written it), starting at element e0 (0 or 32).
+__device__ __forceinline__ void st_panel32(uint32_t panel, int row, int e0, const float (&v)[32]) {
+  const uint32_t rbase = panel + (uint32_t)row * 128u;
+  const uint32_t x = (uint32_t)(row & 7);
+#pragma unroll
+  for (int t = 0; t < 4; ++t) {
+    const uint32_t cc = (uint32_t)((e0 >> 3) + t);
+    st_shared_v4(rbase + ((cc ^ x) << 4), pack_bf16(v[8 * t], v[8 * t + 1]), pack_bf16(v[8 * t + 2], v[8 * t + 3]),
+                 pack_bf16(v[8 * t + 4], v[8 * t + 5]), pack_bf16(v[8 * t + 6], v[8 * t + 7]));
+  }
+}
+
+// 128 fp32 values of one row -> bf16 -> 256 contiguous bytes in global memory.
+__device__ __forceinline__ void st_row32(__nv_bfloat16* dst, const float (&v)[32]) {
+  uint4* d4 = reinterpret_cast<uint4*>(dst);
+#pragma unroll
+  for (int t = 0; t < 4; ++t) {
+    uint4 u;
+    u.x = pack_bf16(v[8 * t], v[8 * t + 1]);
+    u.y = pack_bf16(v[8 * t + 2], v[8 * t + 3]);
+    u.z = pack_bf16(v[8 * t + 4], v[8 * t + 5]);
+    u.w = pack_bf16(v[8 * t + 6], v[8 * t + 7]);
+    d4[t] = u;
+  }
+}
+
+#define TC_WAIT(bar_, ph_) \
+  if (!tc5::mbar_wait((bar_), (ph_), abort_flag, p.status, kStatusBit)) break
+
+// ============================================================================================ forward
+namespace fwd {
+constexpr uint32_t PANEL = 128 * 128;    // [128 rows][64 bf16]
+constexpr uint32_t TILE = 2 * PANEL;     // [128 rows][128 bf16]
+constexpr uint32_t OFF_Q = 0, OFF_K = TILE, OFF_V = 3 * TILE, OFF_P = 5 * TILE, OFF_BAR = 7 * TILE;
+enum { B_Q = 0, B_KF = 1, B_KE = 3, B_VF = 5, B_VE = 7, B_SF = 9, B_SE = 11, B_PF = 13, B_PE = 15, B_OF = 17, B_ACC = 19, NBAR = 20 };
+constexpr int SMEM = 7 * TILE + NBAR * 8 + 16 + 1024;
+constexpr uint32_t TM_S = 0, TM_O = 256, TM_COLS = 512;
+constexpr float kRescaleStep = 8.0f;    // the reference maximum may lag the true one by 2^8
+}    // namespace fwd
+
+// The two softmax groups work on alternating key tiles and never exchange anything inside the loop:
+// group g owns score buffer g, probability buffer g and its own output accumulator O_g in TMEM with
+// its own reference maximum m_g and row sum l_g, i.e. each group computes attention over its half of
+// the key tiles and the halves are merged once at the end.  O_g stays in TMEM and is accumulated by
+// the MMA itself; it is only read back and rescaled when a row's maximum grew by more than
+// kRescaleStep since the last rescale (probabilities then stay below 2^8, far inside bf16/fp32 range).
+__global__ void __launch_bounds__(kTcThreads, 1)
+attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                   const __grid_constant__ CUtensorMap map_v, const TcParams p) {
+  using namespace fwd;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = tc5::smem_u32(smem_raw);
+  const uint32_t base = (raw_addr + 1023u) & ~1023u;
+  uint8_t* smem = smem_raw + (base - raw_addr);
+  const uint32_t bars = base + OFF_BAR;
+  auto bar = [&](int i) { return bars + 8u * (uint32_t)i; };
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(smem + OFF_BAR + NBAR * 8);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+  // Wait used by full warps that go on to warp-collective TMEM accesses: the outcome is made uniform.
+  auto wait_warp = [&](uint32_t br, uint32_t ph) {
+    return __all_sync(0xffffffffu, tc5::mbar_wait(br, ph, abort_flag, p.status, kStatusBit)) != 0;
+  };
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int qt = (int)gridDim.x - 1 - (int)blockIdx.x;    // long rows first
+  const int bh = blockIdx.y;
+  const int b = bh / p.heads;
+  const int h = bh - b * p.heads;
+  const int q0 = qt * 128;
+  const int n_all = (p.seqlen + 127) / 128;
+  const int n_kv = p.causal ? min(qt + 1, n_all) : n_all;
+
+  if (threadIdx.x == 0) {
+    tc5::mbar_init(bar(B_Q), 1);
+    for (int s = 0; s < 2; ++s) {
+      tc5::mbar_init(bar(B_KF + s), 1);
+      tc5::mbar_init(bar(B_KE + s), 1);
+      tc5::mbar_init(bar(B_VF + s), 1);
+      tc5::mbar_init(bar(B_VE + s), 1);
+      tc5::mbar_init(bar(B_SF + s), 1);
+      tc5::mbar_init(bar(B_SE + s), 4);
+      tc5::mbar_init(bar(B_PF + s), 4);
+      tc5::mbar_init(bar(B_PE + s), 1);
+      tc5::mbar_init(bar(B_OF + s), 1);
+    }
+    tc5::mbar_init(bar(B_ACC), 1);
+    *abort_flag = 0;
+    tc5::mbar_fence_init();
+    tc5::tma_prefetch_desc(&map_q);
+    tc5::tma_prefetch_desc(&map_k);
+    tc5::tma_prefetch_desc(&map_v);
+  }
+  if (warp == 1) {
+    tc5::tmem_alloc(tc5::smem_u32(tmem_holder), TM_COLS);
+    tc5::tmem_relinquish();
+  }
+  tc5::fence_before_sync();
+  __syncthreads();
+  tc5::fence_after_sync();
+  const uint32_t tmem_base = *tmem_holder;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      tc5::mbar_arrive_expect_tx(bar(B_Q), TILE);
+      tc5::tma_load_4d(base + OFF_Q, &map_q, 0, h, q0, b, bar(B_Q));
+      tc5::tma_load_4d(base + OFF_Q + PANEL, &map_q, 64, h, q0, b, bar(B_Q));
+      for (int j = 0; j < n_kv; ++j) {
+        const int s = j & 1;
+        const uint32_t ph = (uint32_t)(j >> 1) & 1u;
+        TC_WAIT(bar(B_KE + s), ph ^ 1u);
+        tc5::mbar_arrive_expect_tx(bar(B_KF + s), TILE);
+        tc5::tma_load_4d(base + OFF_K + s * TILE, &map_k, 0, h, j * 128, b, bar(B_KF + s));
+        tc5::tma_load_4d(base + OFF_K + s * TILE + PANEL, &map_k, 64, h, j * 128, b, bar(B_KF + s));
+        TC_WAIT(bar(B_VE + s), ph ^ 1u);
+        tc5::mbar_arrive_expect_tx(bar(B_VF + s), TILE);
+        tc5::tma_load_4d(base + OFF_V + s * TILE, &map_v, 0, h, j * 128, b, bar(B_VF + s));
+        tc5::tma_load_4d(base + OFF_V + s * TILE + PANEL, &map_v, 64, h, j * 128, b, bar(B_VF + s));
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc_s = tc5::idesc_bf16(128, 128, 0, 0);
+      const uint32_t idesc_o = tc5::idesc_bf16(128, 128, 0, 1);
+      // S[j&1] = Q K_j^T
+      auto issue_s = [&](int j) -> bool {
+        const int s = j & 1;
+        const uint32_t ph = (uint32_t)(j >> 1) & 1u;
+        if (!tc5::mbar_wait(bar(B_SE + s), ph ^ 1u, abort_flag, p.status, kStatusBit)) return false;
+        if (!tc5::mbar_wait(bar(B_KF + s), ph, abort_flag, p.status, kStatusBit)) return false;
+        tc5::fence_after_sync();
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint32_t off = (uint32_t)(kk >> 2) * PANEL + (uint32_t)(kk & 3) * 32u;
+          tc5::mma_f16(tmem_base + TM_S + (uint32_t)s * 128u, tc5::smem_desc_k_sw128(base + OFF_Q + off),
+                       tc5::smem_desc_k_sw128(base + OFF_K + s * TILE + off), idesc_s, kk ? 1u : 0u);
+        }
+        tc5::mma_commit(bar(B_KE + s));
+        tc5::mma_commit(bar(B_SF + s));
+        return true;
+      };
+      do {
+        TC_WAIT(bar(B_Q), 0u);
+        if (!issue_s(0)) break;
+        bool ok = true;
+        for (int j = 0; j < n_kv; ++j) {
+          if (j + 1 < n_kv && !issue_s(j + 1)) { ok = false; break; }
+          const int s = j & 1;
+          const uint32_t ph = (uint32_t)(j >> 1) & 1u;
+          if (!tc5::mbar_wait(bar(B_PF + s), ph, abort_flag, p.status, kStatusBit)) { ok = false; break; }
+          if (!tc5::mbar_wait(bar(B_VF + s), ph, abort_flag, p.status, kStatusBit)) { ok = false; break; }
+          tc5::fence_after_sync();
+          // O[j&1] (+)= P_j V_j : A = P (K-major), B = V with the key index as rows (MN-major)
+#pragma unroll
+          for (int kk = 0; kk < 8; ++kk) {
+            const uint32_t offa = (uint32_t)(kk >> 2) * PANEL + (uint32_t)(kk & 3) * 32u;
+            tc5::mma_f16(tmem_base + TM_O + (uint32_t)s * 128u, tc5::smem_desc_k_sw128(base + OFF_P + s * TILE + offa),
+                         tc5::smem_desc_mn_sw128(base + OFF_V + s * TILE + (uint32_t)kk * 2048u, PANEL), idesc_o,
+                         (j >= 2 || kk) ? 1u : 0u);
+          }
+          tc5::mma_commit(bar(B_VE + s));
+          tc5::mma_commit(bar(B_PE + s));
+          tc5::mma_commit(bar(B_OF + s));
+        }
+        if (ok) tc5::mma_commit(bar(B_ACC));
+      } while (false);
+    }
+  } else {
+    // ------------------------------------------------------------------ softmax: one thread per query row and group
+    const int qd = warp & 3;           // TMEM lane quarter this warp may access
+    const int wg = (warp - 2) >> 2;    // group 0: even key tiles, group 1: odd key tiles
+    const int row = qd * 32 + lane;
+    const int grow = q0 + row;
+    const uint32_t tlane = tmem_base + ((uint32_t)(qd * 32) << 16);
+    const uint32_t ts = tlane + TM_S + (uint32_t)wg * 128u;
+    const uint32_t to = tlane + TM_O + (uint32_t)wg * 128u;
+    const float sl = p.scale * kLog2e;
+    const int lim = p.causal ? min(grow, p.seqlen - 1) : p.seqlen - 1;    // last visible column
+    float m = -INFINITY, l = 0.0f;    // reference maximum (log2 units) and row sum of this group
+    bool ok = true;
+
+    for (int j = wg; j < n_kv; j += 2) {
+      const int k = j >> 1;
+      const uint32_t ph = (uint32_t)k & 1u;
+      if (!wait_warp(bar(B_SF + wg), ph)) { ok = false; break; }
+      tc5::fence_after_sync();
+      uint32_t r[4][32];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tc5::tmem_ld32(ts + (uint32_t)c * 32u, r[c]);
+      tc5::tmem_ld_wait();
+      tc5::fence_before_sync();
+      __syncwarp();
+      if (lane == 0) tc5::mbar_arrive(bar(B_SE + wg));    // the next S of this group may be computed already
+      const bool need_mask = (p.causal && j == qt) || (j * 128 + 128 > p.seqlen);
+      const int col0 = j * 128;
+      float mx = -INFINITY;
+      if (need_mask) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (col0 + c * 32 + i <= lim) mx = fmaxf(mx, __uint_as_float(r[c][i]));
+      } else {
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(r[c][i]));
+      }
+      mx *= sl;    // sl > 0
+      const bool grow_m = mx > m + kRescaleStep || (m == -INFINITY && mx > -INFINITY);
+      if (__any_sync(0xffffffffu, grow_m)) {
+        const float m_new = grow_m ? mx : m;
+        const float corr = (m == -INFINITY) ? 0.0f : ex2(m - m_new);
+        if (k > 0) {
+          // every earlier product of this group must have landed in O before it is rescaled
+          if (!wait_warp(bar(B_OF + wg), (uint32_t)(k - 1) & 1u)) { ok = false; break; }
+          tc5::fence_after_sync();
+#pragma unroll 1
+          for (int c = 0; c < 8; ++c) {
+            uint32_t x[16];
+            tc5::tmem_ld16(to + (uint32_t)c * 16u, x);
+            tc5::tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 16; ++i) x[i] = __float_as_uint(__uint_as_float(x[i]) * corr);
+            tc5::tmem_st16(to + (uint32_t)c * 16u, x);
+          }
+          tc5::tmem_st_wait();
+        }
+        l *= corr;
+        m = m_new;
+      }
+      if (!wait_warp(bar(B_PE + wg), ph ^ 1u)) { ok = false; break; }
+      const float m_use = (m == -INFINITY) ? 0.0f : m;
+      float rowsum = 0.0f;
+      const uint32_t prow = base + OFF_P + wg * TILE + (uint32_t)row * 128u;
+      const uint32_t swz = (uint32_t)(row & 7);
+#pragma unroll
+      for (int g = 0; g < 16; ++g) {    // 16-byte chunk g = columns 8g .. 8g+7
+        float e[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          e[i] = ex2(fmaf(__uint_as_float(r[g >> 2][(g & 3) * 8 + i]), sl, -m_use));
+          if (need_mask && col0 + g * 8 + i > lim) e[i] = 0.0f;
+          rowsum += e[i];
+        }
+        st_shared_v4(prow + (uint32_t)(g >> 3) * PANEL + ((((uint32_t)g & 7u) ^ swz) << 4), pack_bf16(e[0], e[1]),
+                     pack_bf16(e[2], e[3]), pack_bf16(e[4], e[5]), pack_bf16(e[6], e[7]));
+      }
+      l += rowsum;
+      tc5::fence_before_sync();
+      fence_async_smem();
+      __syncwarp();
+      if (lane == 0) tc5::mbar_arrive(bar(B_PF + wg));
+    }
+    ok = ok && wait_warp(bar(B_ACC), 0u);
+    tc5::fence_after_sync();
+    // merge the two groups: both halves of every row meet through shared memory (the Q tile is dead by now)
+    float* xm = reinterpret_cast<float*>(smem + OFF_Q);    // [2][128] maxima, then [2][128] sums
+    float* xl = xm + 256;
+    xm[wg * 128 + row] = m;
+    xl[wg * 128 + row] = l;
+    asm volatile("bar.sync 1, 256;" ::: "memory");    // reached by all eight softmax warps, also after a failed wait
+    if (ok) {
+      const float m0 = xm[row], m1 = xm[128 + row], l0 = xl[row], l1 = xl[128 + row];
+      const float mm = fmaxf(m0, m1);
+      const float f0 = (m0 == -INFINITY) ? 0.0f : ex2(m0 - mm);
+      const float f1 = (m1 == -INFINITY) ? 0.0f : ex2(m1 - mm);
+      const float lt = l0 * f0 + l1 * f1;
+      const float inv = lt > 0.0f ? 1.0f / lt : 0.0f;
+      const float g0 = f0 * inv, g1 = f1 * inv;
+      const bool two = n_kv > 1;    // with one key tile group 1 never wrote its accumulator
+      __nv_bfloat16* dst = p.o + (int64_t)b * p.o_sb + (int64_t)grow * p.o_ss + (int64_t)h * p.o_sh + wg * 64;
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        uint32_t a0[32], a1[32];
+        float v[32];
+        tc5::tmem_ld32(tlane + TM_O + (uint32_t)wg * 64u + (uint32_t)c * 32u, a0);
+        if (two) tc5::tmem_ld32(tlane + TM_O + 128u + (uint32_t)wg * 64u + (uint32_t)c * 32u, a1);
+        tc5::tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(a0[i]) * g0;
+        if (two) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = fmaf(__uint_as_float(a1[i]), g1, v[i]);
+        }
+        if (grow < p.seqlen) st_row32(dst + c * 32, v);
+      }
+      if (wg == 0 && grow < p.seqlen) p.lse[(int64_t)bh * p.seqlen + grow] = lt > 0.0f ? mm * kLn2 + logf(lt) : -INFINITY;
+    }
+  }
+
+  // ---------------------------------------------------------------------- tear-down
+  __syncwarp();
+  if (*abort_flag) __nanosleep(200000);    // let copies / MMAs in flight finish before smem and TMEM go away
+  tc5::fence_before_sync();
+  __syncthreads();
+  tc5::fence_after_sync();
+  if (warp == 1) tc5::tmem_dealloc(tmem_base, TM_COLS);
+}
+
+// ===================================================================================== delta = rowsum(dO * O)
+struct DeltaParams {
+  const __nv_bfloat16* o;
+  const __nv_bfloat16* d_o;
+  float* delta;
+  int64_t o_sb, o_ss, o_sh, do_sb, do_ss, do_sh;
+  int batch, heads, seqlen;
+};
+
+__global__ void attn_delta_tc_kernel(const DeltaParams p) {
+  const int64_t gw = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  const int64_t total = (int64_t)p.batch * p.heads * p.seqlen;
+  if (gw >= total) return;
+  const int s = (int)(gw % p.seqlen);
+  const int bh = (int)(gw / p.seqlen);
+  const int b = bh / p.heads;
+  const int h = bh - b * p.heads;
+  const uint2 a = *reinterpret_cast<const uint2*>(p.o + (int64_t)b * p.o_sb + (int64_t)s * p.o_ss + (int64_t)h * p.o_sh + lane * 4);
+  const uint2 g = *reinterpret_cast<const uint2*>(p.d_o + (int64_t)b * p.do_sb + (int64_t)s * p.do_ss + (int64_t)h * p.do_sh + lane * 4);
+  const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&a);
+  const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&g);
+  float acc = 0.0f;
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const float2 x = __bfloat1622float2(a2[i]);
+    const float2 y = __bfloat1622float2(g2[i]);
+    acc = fmaf(x.x, y.x, fmaf(x.y, y.y, acc));
+  }
+  acc = warp_sum(acc);
+  if (lane == 0) p.delta[gw] = acc;
+}
+
+// ============================================================================================ dK / dV
+namespace dkv {
+constexpr uint32_t PANEL_KV = 128 * 128;    // [128 key rows][64 bf16]
+constexpr uint32_t TILE_KV = 2 * PANEL_KV;
+constexpr uint32_t PANEL_Q = 64 * 128;      // [64 query rows][64 bf16]
+constexpr uint32_t TILE_Q = 2 * PANEL_Q;    // 16 KB
+constexpr uint32_t TILE_P = 128 * 128;      // [128 key rows][64 queries] bf16
+constexpr int NSQ = 3;    // ring of Q/dO stages: a stage is read by the first and by the last MMA of its tile
+constexpr uint32_t OFF_K = 0, OFF_V = TILE_KV, OFF_Q = 2 * TILE_KV, OFF_DO = OFF_Q + NSQ * TILE_Q, OFF_PT = OFF_DO + NSQ * TILE_Q,
+                   OFF_DST = OFF_PT + 2 * TILE_P, OFF_LSE = OFF_DST + 2 * TILE_P, OFF_BAR = OFF_LSE + NSQ * 2 * 64 * 4;
+enum { B_KV = 0, B_QF = 1, B_QE = B_QF + NSQ, B_SF = B_QE + NSQ, B_SE = B_SF + 2, B_PF = B_SE + 2, B_PE = B_PF + 2, B_ACC = B_PE + 2,
+       NBAR = B_ACC + 1 };
+constexpr int SMEM = OFF_BAR + NBAR * 8 + 16 + 1024;
+constexpr uint32_t TM_ST = 0, TM_DPT = 128, TM_DV = 256, TM_DK = 384, TM_COLS = 512;
+}    // namespace dkv
+
+__global__ void __launch_bounds__(kTcThreads, 1)
+attn_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                        const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do, const TcParams p) {
+  using namespace dkv;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = tc5::smem_u32(smem_raw);
+  const uint32_t base = (raw_addr + 1023u) & ~1023u;
+  uint8_t* smem = smem_raw + (base - raw_addr);
+  const uint32_t bars = base + OFF_BAR;
+  auto bar = [&](int i) { return bars + 8u * (uint32_t)i; };
+  float* s_lse = reinterpret_cast<float*>(smem + OFF_LSE);    // [NSQ][64] log2-scaled lse, then [NSQ][64] delta
+  float* s_delta = s_lse + NSQ * 64;
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(smem + OFF_BAR + NBAR * 8);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+  // Wait used by full warps that go on to warp-collective TMEM accesses: the outcome is made uniform.
+  auto wait_warp = [&](uint32_t br, uint32_t ph) {
+    return __all_sync(0xffffffffu, tc5::mbar_wait(br, ph, abort_flag, p.status, kStatusBit)) != 0;
+  };
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int kt = blockIdx.x;    // key tile 0 has the most query tiles under a causal mask and starts first
+  const int bh = blockIdx.y;
+  const int b = bh / p.heads;
+  const int h = bh - b * p.heads;
+  const int k0 = kt * 128;
+  const int nq_all = (p.seqlen + 63) / 64;
+  const int t_first = p.causal ? 2 * kt : 0;
+  const int n_q = nq_all - t_first;    // >= 1 because k0 < seqlen
+
+  if (threadIdx.x == 0) {
+    tc5::mbar_init(bar(B_KV), 1);
+    for (int s = 0; s < NSQ; ++s) {
+      tc5::mbar_init(bar(B_QF + s), 2);    // TMA bytes + the lse/delta rows written by warp 0
+      tc5::mbar_init(bar(B_QE + s), 5);    // last MMA that reads the stage + four softmax warps
+    }
+    for (int s = 0; s < 2; ++s) {
+      tc5::mbar_init(bar(B_SF + s), 1);
+      tc5::mbar_init(bar(B_SE + s), 4);
+      tc5::mbar_init(bar(B_PF + s), 4);
+      tc5::mbar_init(bar(B_PE + s), 1);
+    }
+    tc5::mbar_init(bar(B_ACC), 1);
+    *abort_flag = 0;
+    tc5::mbar_fence_init();
+    tc5::tma_prefetch_desc(&map_q);
+    tc5::tma_prefetch_desc(&map_k);
+    tc5::tma_prefetch_desc(&map_v);
+    tc5::tma_prefetch_desc(&map_do);
+  }
+  if (warp == 1) {
+    tc5::tmem_alloc(tc5::smem_u32(tmem_holder), TM_COLS);
+    tc5::tmem_relinquish();
+  }
+  tc5::fence_before_sync();
+  __syncthreads();
+  tc5::fence_after_sync();
+  const uint32_t tmem_base = *tmem_holder;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ producer (whole warp: lane 0 issues TMA)
+    if (lane == 0) {
+      tc5::mbar_arrive_expect_tx(bar(B_KV), 2 * TILE_KV);
+      tc5::tma_load_4d(base + OFF_K, &map_k, 0, h, k0, b, bar(B_KV));
+      tc5::tma_load_4d(base + OFF_K + PANEL_KV, &map_k, 64, h, k0, b, bar(B_KV));
+      tc5::tma_load_4d(base + OFF_V, &map_v, 0, h, k0, b, bar(B_KV));
+      tc5::tma_load_4d(base + OFF_V + PANEL_KV, &map_v, 64, h, k0, b, bar(B_KV));
+    }
+    const float* glse = p.lse + (int64_t)bh * p.seqlen;
+    const float* gdelta = p.delta + (int64_t)bh * p.seqlen;
+    for (int t = 0; t < n_q; ++t) {
+      const int s = t % NSQ;
+      const uint32_t ph = (uint32_t)(t / NSQ) & 1u;
+      const int qrow0 = (t_first + t) * 64;
+      TC_WAIT(bar(B_QE + s), ph ^ 1u);
+      if (lane == 0) {
+        tc5::mbar_arrive_expect_tx(bar(B_QF + s), 2 * TILE_Q);
+        tc5::tma_load_4d(base + OFF_Q + s * TILE_Q, &map_q, 0, h, qrow0, b, bar(B_QF + s));
+        tc5::tma_load_4d(base + OFF_Q + s * TILE_Q + PANEL_Q, &map_q, 64, h, qrow0, b, bar(B_QF + s));
+        tc5::tma_load_4d(base + OFF_DO + s * TILE_Q, &map_do, 0, h, qrow0, b, bar(B_QF + s));
+        tc5::tma_load_4d(base + OFF_DO + s * TILE_Q + PANEL_Q, &map_do, 64, h, qrow0, b, bar(B_QF + s));
+      }
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        const int r = lane + 32 * i;
+        const bool in = qrow0 + r < p.seqlen;
+        s_lse[s * 64 + r] = in ? glse[qrow0 + r] * kLog2e : INFINITY;    // +inf makes the probability exactly zero
+        s_delta[s * 64 + r] = in ? gdelta[qrow0 + r] : 0.0f;
+      }
+      __syncwarp();
+      if (lane == 0) tc5::mbar_arrive(bar(B_QF + s));
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc_s = tc5::idesc_bf16(128, 64, 0, 0);
+      const uint32_t idesc_acc = tc5::idesc_bf16(128, 128, 0, 1);
+      // S^T = K Q_t^T and dP^T = V dO_t^T into buffer t&1
+      auto issue_s = [&](int t) -> bool {
+        const int s = t & 1;
+        const uint32_t ph = (uint32_t)(t >> 1) & 1u;
+        const int st = t % NSQ;
+        if (!tc5::mbar_wait(bar(B_SE + s), ph ^ 1u, abort_flag, p.status, kStatusBit)) return false;
+        if (!tc5::mbar_wait(bar(B_QF + st), (uint32_t)(t / NSQ) & 1u, abort_flag, p.status, kStatusBit)) return false;
+        tc5::fence_after_sync();
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint32_t offa = (uint32_t)(kk >> 2) * PANEL_KV + (uint32_t)(kk & 3) * 32u;
+          const uint32_t offb = (uint32_t)(kk >> 2) * PANEL_Q + (uint32_t)(kk & 3) * 32u;
+          tc5::mma_f16(tmem_base + TM_ST + (uint32_t)s * 64u, tc5::smem_desc_k_sw128(base + OFF_K + offa),
+                       tc5::smem_desc_k_sw128(base + OFF_Q + st * TILE_Q + offb), idesc_s, kk ? 1u : 0u);
+        }
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint32_t offa = (uint32_t)(kk >> 2) * PANEL_KV + (uint32_t)(kk & 3) * 32u;
+          const uint32_t offb = (uint32_t)(kk >> 2) * PANEL_Q + (uint32_t)(kk & 3) * 32u;
+          tc5::mma_f16(tmem_base + TM_DPT + (uint32_t)s * 64u, tc5::smem_desc_k_sw128(base + OFF_V + offa),
+                       tc5::smem_desc_k_sw128(base + OFF_DO + st * TILE_Q + offb), idesc_s, kk ? 1u : 0u);
+        }
+        tc5::mma_commit(bar(B_SF + s));
+        return true;
+      };
+      do {
+        TC_WAIT(bar(B_KV), 0u);
+        if (!issue_s(0)) break;
+        bool ok = true;
+        for (int t = 0; t < n_q; ++t) {
+          if (t + 1 < n_q && !issue_s(t + 1)) { ok = false; break; }
+          const int s = t & 1;
+          const int st = t % NSQ;
+          const uint32_t ph = (uint32_t)(t >> 1) & 1u;
+          if (!tc5::mbar_wait(bar(B_PF + s), ph, abort_flag, p.status, kStatusBit)) { ok = false; break; }
+          tc5::fence_after_sync();
+          // dV += P^T dO_t ; dK += dS^T Q_t : A from the softmax threads (K-major), B = the TMA tile read MN-major
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk) {
+            tc5::mma_f16(tmem_base + TM_DV, tc5::smem_desc_k_sw128(base + OFF_PT + s * TILE_P + (uint32_t)kk * 32u),
+                         tc5::smem_desc_mn_sw128(base + OFF_DO + st * TILE_Q + (uint32_t)kk * 2048u, PANEL_Q), idesc_acc,
+                         (t | kk) ? 1u : 0u);
+          }
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk) {
+            tc5::mma_f16(tmem_base + TM_DK, tc5::smem_desc_k_sw128(base + OFF_DST + s * TILE_P + (uint32_t)kk * 32u),
+                         tc5::smem_desc_mn_sw128(base + OFF_Q + st * TILE_Q + (uint32_t)kk * 2048u, PANEL_Q), idesc_acc,
+                         (t | kk) ? 1u : 0u);
+          }
+          tc5::mma_commit(bar(B_PE + s));
+          tc5::mma_commit(bar(B_QE + st));
+        }
+        if (ok) tc5::mma_commit(bar(B_ACC));
+      } while (false);
+    }
+  } else {
+    // ------------------------------------------------------------------ one thread per key row
+    const int qd = warp & 3;
+    const int wg = (warp - 2) >> 2;    // group 0 takes the even query tiles (buffer 0), group 1 the odd ones
+    const int row = qd * 32 + lane;
+    const int grow = k0 + row;
+    const uint32_t tlane = tmem_base + ((uint32_t)(qd * 32) << 16);
+    const float sl = p.scale * kLog2e;
+    bool ok = true;
+    for (int t = wg; t < n_q; t += 2) {
+      const int s = t & 1;
+      const int st = t % NSQ;
+      const uint32_t ph = (uint32_t)(t >> 1) & 1u;
+      const int qrow0 = (t_first + t) * 64;
+      if (!wait_warp(bar(B_QF + st), (uint32_t)(t / NSQ) & 1u)) { ok = false; break; }
+      if (!wait_warp(bar(B_SF + s), ph)) { ok = false; break; }
+      tc5::fence_after_sync();
+      if (!wait_warp(bar(B_PE + s), ph ^ 1u)) { ok = false; break; }
+      const bool need_mask = p.causal && (qrow0 < k0 + 128);
+      const float4* lse2 = reinterpret_cast<const float4*>(s_lse + st * 64);
+      const float4* dlt = reinterpret_cast<const float4*>(s_delta + st * 64);
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        uint32_t rs[32], rd[32];
+        tc5::tmem_ld32(tlane + TM_ST + (uint32_t)s * 64u + (uint32_t)c * 32u, rs);
+        tc5::tmem_ld32(tlane + TM_DPT + (uint32_t)s * 64u + (uint32_t)c * 32u, rd);
+        tc5::tmem_ld_wait();
+        float pv[32], ds[32];
+#pragma unroll
+        for (int i4 = 0; i4 < 8; ++i4) {
+          const float4 l4 = lse2[c * 8 + i4];
+          const float4 d4 = dlt[c * 8 + i4];
+          const float la[4] = {l4.x, l4.y, l4.z, l4.w};
+          const float da[4] = {d4.x, d4.y, d4.z, d4.w};
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const int i = i4 * 4 + u;
+            float e = ex2(fmaf(__uint_as_float(rs[i]), sl, -la[u]));
+            if (need_mask && qrow0 + c * 32 + i < grow) e = 0.0f;
+            pv[i] = e;
+            ds[i] = e * (__uint_as_float(rd[i]) - da[u]);
+          }
+        }
+        st_panel32(base + OFF_PT + s * TILE_P, row, c * 32, pv);
+        st_panel32(base + OFF_DST + s * TILE_P, row, c * 32, ds);
+      }
+      tc5::fence_before_sync();
+      fence_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        tc5::mbar_arrive(bar(B_SE + s));
+        tc5::mbar_arrive(bar(B_PF + s));
+        tc5::mbar_arrive(bar(B_QE + st));
+      }
+    }
+    if (ok && wait_warp(bar(B_ACC), 0u)) {
+      tc5::fence_after_sync();
+      __nv_bfloat16* dv = p.dv + (int64_t)b * p.dv_sb + (int64_t)grow * p.dv_ss + (int64_t)h * p.dv_sh;
+      __nv_bfloat16* dk = p.dk + (int64_t)b * p.dk_sb + (int64_t)grow * p.dk_ss + (int64_t)h * p.dk_sh;
+      // group 0 stores dV, group 1 stores dK
+      __nv_bfloat16* dst = wg == 0 ? dv : dk;
+      const float f = wg == 0 ? 1.0f : p.scale;
+      const uint32_t tsrc = tlane + (wg == 0 ? TM_DV : TM_DK);
+#pragma unroll
+      for (int c = 0; c < 4; c += 2) {
+        uint32_t r0[32], r1[32];
+        float v[32];
+        tc5::tmem_ld32(tsrc + (uint32_t)c * 32u, r0);
+        tc5::tmem_ld32(tsrc + (uint32_t)c * 32u + 32u, r1);
+        tc5::tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r0[i]) * f;
+        if (grow < p.seqlen) st_row32(dst + c * 32, v);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r1[i]) * f;
+        if (grow < p.seqlen) st_row32(dst + c * 32 + 32, v);
+      }
+    }
+  }
+
+  __syncwarp();
+  if (*abort_flag) __nanosleep(200000);
+  tc5::fence_before_sync();
+  __syncthreads();
+  tc5::fence_after_sync();
+  if (warp == 1) tc5::tmem_dealloc(tmem_base, TM_COLS);
+}
+
+// ================================================================================================= dQ
+namespace dqk {
+constexpr uint32_t PANEL_Q = 128 * 128;     // [128 query rows][64 bf16]
+constexpr uint32_t TILE_Q = 2 * PANEL_Q;
+constexpr uint32_t PANEL_KV = 64 * 128;     // [64 key rows][64 bf16]
+constexpr uint32_t TILE_KV = 2 * PANEL_KV;
+constexpr uint32_t TILE_DS = 128 * 128;     // [128 query rows][64 keys] bf16
+constexpr int NSK = 4;    // ring of K/V stages: a stage is read by the first and by the last MMA of its tile
+constexpr uint32_t OFF_Q = 0, OFF_DO = TILE_Q, OFF_K = 2 * TILE_Q, OFF_V = OFF_K + NSK * TILE_KV, OFF_DS = OFF_V + NSK * TILE_KV,
+                   OFF_BAR = OFF_DS + 2 * TILE_DS;
+enum { B_Q = 0, B_KF = 1, B_KE = B_KF + NSK, B_SF = B_KE + NSK, B_SE = B_SF + 2, B_PF = B_SE + 2, B_PE = B_PF + 2, B_ACC = B_PE + 2,
+       NBAR = B_ACC + 1 };
+constexpr int SMEM = OFF_BAR + NBAR * 8 + 16 + 1024;
+constexpr uint32_t TM_S = 0, TM_DP = 128, TM_DQ = 256, TM_COLS = 512;
+}    // namespace dqk
+
+__global__ void __launch_bounds__(kTcThreads, 1)
+attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                      const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do, const TcParams p) {
+  using namespace dqk;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = tc5::smem_u32(smem_raw);
+  const uint32_t base = (raw_addr + 1023u) & ~1023u;
+  uint8_t* smem = smem_raw + (base - raw_addr);
+  const uint32_t bars = base + OFF_BAR;
+  auto bar = [&](int i) { return bars + 8u * (uint32_t)i; };
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(smem + OFF_BAR + NBAR * 8);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+  // Wait used by full warps that go on to warp-collective TMEM accesses: the outcome is made uniform.
+  auto wait_warp = [&](uint32_t br, uint32_t ph) {
+    return __all_sync(0xffffffffu, tc5::mbar_wait(br, ph, abort_flag, p.status, kStatusBit)) != 0;
+  };
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int qt = (int)gridDim.x - 1 - (int)blockIdx.x;
+  const int bh = blockIdx.y;
+  const int b = bh / p.heads;
+  const int h = bh - b * p.heads;
+  const int q0 = qt * 128;
+  const int nk_all = (p.seqlen + 63) / 64;
+  const int n_kv = p.causal ? min(2 * qt + 2, nk_all) : nk_all;
+
+  if (threadIdx.x == 0) {
+    tc5::mbar_init(bar(B_Q), 1);
+    for (int s = 0; s < NSK; ++s) {
+      tc5::mbar_init(bar(B_KF + s), 1);
+      tc5::mbar_init(bar(B_KE + s), 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      tc5::mbar_init(bar(B_SF + s), 1);
+      tc5::mbar_init(bar(B_SE + s), 4);
+      tc5::mbar_init(bar(B_PF + s), 4);
+      tc5::mbar_init(bar(B_PE + s), 1);
+    }
+    tc5::mbar_init(bar(B_ACC), 1);
+    *abort_flag = 0;
+    tc5::mbar_fence_init();
+    tc5::tma_prefetch_desc(&map_q);
+    tc5::tma_prefetch_desc(&map_k);
+    tc5::tma_prefetch_desc(&map_v);
+    tc5::tma_prefetch_desc(&map_do);
+  }
+  if (warp == 1) {
+    tc5::tmem_alloc(tc5::smem_u32(tmem_holder), TM_COLS);
+    tc5::tmem_relinquish();
+  }
+  tc5::fence_before_sync();
+  __syncthreads();
+  tc5::fence_after_sync();
+  const uint32_t tmem_base = *tmem_holder;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      tc5::mbar_arrive_expect_tx(bar(B_Q), 2 * TILE_Q);
+      tc5::tma_load_4d(base + OFF_Q, &map_q, 0, h, q0, b, bar(B_Q));
+      tc5::tma_load_4d(base + OFF_Q + PANEL_Q, &map_q, 64, h, q0, b, bar(B_Q));
+      tc5::tma_load_4d(base + OFF_DO, &map_do, 0, h, q0, b, bar(B_Q));
+      tc5::tma_load_4d(base + OFF_DO + PANEL_Q, &map_do, 64, h, q0, b, bar(B_Q));
+      for (int j = 0; j < n_kv; ++j) {
+        const int s = j % NSK;
+        const uint32_t ph = (uint32_t)(j / NSK) & 1u;
+        TC_WAIT(bar(B_KE + s), ph ^ 1u);
+        tc5::mbar_arrive_expect_tx(bar(B_KF + s), 2 * TILE_KV);
+        tc5::tma_load_4d(base + OFF_K + s * TILE_KV, &map_k, 0, h, j * 64, b, bar(B_KF + s));
+        tc5::tma_load_4d(base + OFF_K + s * TILE_KV + PANEL_KV, &map_k, 64, h, j * 64, b, bar(B_KF + s));
+        tc5::tma_load_4d(base + OFF_V + s * TILE_KV, &map_v, 0, h, j * 64, b, bar(B_KF + s));
+        tc5::tma_load_4d(base + OFF_V + s * TILE_KV + PANEL_KV, &map_v, 64, h, j * 64, b, bar(B_KF + s));
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc_s = tc5::idesc_bf16(128, 64, 0, 0);
+      const uint32_t idesc_acc = tc5::idesc_bf16(128, 128, 0, 1);
+      auto issue_s = [&](int j) -> bool {
+        const int s = j & 1;
+        const int st = j % NSK;
+        const uint32_t ph = (uint32_t)(j >> 1) & 1u;
+        if (!tc5::mbar_wait(bar(B_SE + s), ph ^ 1u, abort_flag, p.status, kStatusBit)) return false;
+        if (!tc5::mbar_wait(bar(B_KF + st), (uint32_t)(j / NSK) & 1u, abort_flag, p.status, kStatusBit)) return false;
+        tc5::fence_after_sync();
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint32_t offa = (uint32_t)(kk >> 2) * PANEL_Q + (uint32_t)(kk & 3) * 32u;
+          const uint32_t offb = (uint32_t)(kk >> 2) * PANEL_KV + (uint32_t)(kk & 3) * 32u;
+          tc5::mma_f16(tmem_base + TM_S + (uint32_t)s * 64u, tc5::smem_desc_k_sw128(base + OFF_Q + offa),
+                       tc5::smem_desc_k_sw128(base + OFF_K + st * TILE_KV + offb), idesc_s, kk ? 1u : 0u);
+        }
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint32_t offa = (uint32_t)(kk >> 2) * PANEL_Q + (uint32_t)(kk & 3) * 32u;
+          const uint32_t offb = (uint32_t)(kk >> 2) * PANEL_KV + (uint32_t)(kk & 3) * 32u;
+          tc5::mma_f16(tmem_base + TM_DP + (uint32_t)s * 64u, tc5::smem_desc_k_sw128(base + OFF_DO + offa),
+                       tc5::smem_desc_k_sw128(base + OFF_V + st * TILE_KV + offb), idesc_s, kk ? 1u : 0u);
+        }
+        tc5::mma_commit(bar(B_SF + s));
+        return true;
+      };
+      do {
+        TC_WAIT(bar(B_Q), 0u);
+        if (!issue_s(0)) break;
+        bool ok = true;
+        for (int j = 0; j < n_kv; ++j) {
+          if (j + 1 < n_kv && !issue_s(j + 1)) { ok = false; break; }
+          const int s = j & 1;
+          const int st = j % NSK;
+          const uint32_t ph = (uint32_t)(j >> 1) & 1u;
+          if (!tc5::mbar_wait(bar(B_PF + s), ph, abort_flag, p.status, kStatusBit)) { ok = false; break; }
+          tc5::fence_after_sync();
+          // dQ += dS K_j : B = the K tile with the key index as rows (MN-major)
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk) {
+            tc5::mma_f16(tmem_base + TM_DQ, tc5::smem_desc_k_sw128(base + OFF_DS + s * TILE_DS + (uint32_t)kk * 32u),
+                         tc5::smem_desc_mn_sw128(base + OFF_K + st * TILE_KV + (uint32_t)kk * 2048u, PANEL_KV), idesc_acc,
+                         (j | kk) ? 1u : 0u);
+          }
+          tc5::mma_commit(bar(B_PE + s));
+          tc5::mma_commit(bar(B_KE + st));
+        }
+        if (ok) tc5::mma_commit(bar(B_ACC));
+      } while (false);
+    }
+  } else {
+    const int qd = warp & 3;
+    const int wg = (warp - 2) >> 2;    // group 0 takes the even key tiles (buffer 0), group 1 the odd ones
+    const int row = qd * 32 + lane;
+    const int grow = q0 + row;
+    const uint32_t tlane = tmem_base + ((uint32_t)(qd * 32) << 16);
+    const float sl = p.scale * kLog2e;
+    const bool in = grow < p.seqlen;
+    const float lse2 = in ? p.lse[(int64_t)bh * p.seqlen + grow] * kLog2e : INFINITY;
+    const float dlt = in ? p.delta[(int64_t)bh * p.seqlen + grow] : 0.0f;
+    const int lim = p.causal ? min(grow, p.seqlen - 1) : p.seqlen - 1;
+    bool ok = true;
+    for (int j = wg; j < n_kv; j += 2) {
+      const int s = j & 1;
+      const uint32_t ph = (uint32_t)(j >> 1) & 1u;
+      const int col0 = j * 64;
+      if (!wait_warp(bar(B_SF + s), ph)) { ok = false; break; }
+      tc5::fence_after_sync();
+      if (!wait_warp(bar(B_PE + s), ph ^ 1u)) { ok = false; break; }
+      const bool need_mask = (p.causal && col0 + 63 > q0) || (col0 + 64 > p.seqlen);
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        uint32_t rs[32], rd[32];
+        tc5::tmem_ld32(tlane + TM_S + (uint32_t)s * 64u + (uint32_t)c * 32u, rs);
+        tc5::tmem_ld32(tlane + TM_DP + (uint32_t)s * 64u + (uint32_t)c * 32u, rd);
+        tc5::tmem_ld_wait();
+        float ds[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          float e = ex2(fmaf(__uint_as_float(rs[i]), sl, -lse2));
+          if (need_mask && col0 + c * 32 + i > lim) e = 0.0f;
+          ds[i] = e * (__uint_as_float(rd[i]) - dlt);
+        }
+        st_panel32(base + OFF_DS + s * TILE_DS, row, c * 32, ds);
+      }
+      tc5::fence_before_sync();
+      fence_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        tc5::mbar_arrive(bar(B_SE + s));
+        tc5::mbar_arrive(bar(B_PF + s));
+      }
+    }
+    if (ok && wait_warp(bar(B_ACC), 0u)) {
+      tc5::fence_after_sync();
+      __nv_bfloat16* dq = p.dq + (int64_t)b * p.dq_sb + (int64_t)grow * p.dq_ss + (int64_t)h * p.dq_sh;
+      // each group stores one half of the row
+      uint32_t r0[32], r1[32];
+      float v[32];
+      tc5::tmem_ld32(tlane + TM_DQ + (uint32_t)wg * 64u, r0);
+      tc5::tmem_ld32(tlane + TM_DQ + (uint32_t)wg * 64u + 32u, r1);
+      tc5::tmem_ld_wait();
+#pragma unroll
+      for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r0[i]) * p.scale;
+      if (in) st_row32(dq + wg * 64, v);
+#pragma unroll
+      for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r1[i]) * p.scale;
+      if (in) st_row32(dq + wg * 64 + 32, v);
+    }
+  }
+
+  __syncwarp();
+  if (*abort_flag) __nanosleep(200000);
+  tc5::fence_before_sync();
+  __syncthreads();
+  tc5::fence_after_sync();
+  if (warp == 1) tc5::tmem_dealloc(tmem_base, TM_COLS);
+}
+
+// ---- host side -----------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess) {
+      fn = reinterpret_cast<EncodeTiledFn>(sym);
+    }
+  });
+  return fn;
+}
+
+struct Map4Key {
+  const void* ptr;
+  int64_t sb, ss, sh;
+  int batch, heads, seqlen, box_rows;
+  bool operator==(const Map4Key& o) const {
+    return ptr == o.ptr && sb == o.sb && ss == o.ss && sh == o.sh && batch == o.batch && heads == o.heads && seqlen == o.seqlen &&
+           box_rows == o.box_rows;
+  }
+};
+struct Map4Hash {
+  size_t operator()(const Map4Key& k) const {
+    size_t hsh = reinterpret_cast<size_t>(k.ptr);
+    auto mix = [&](size_t v) { hsh ^= v * 0x9e3779b97f4a7c15ull + (hsh << 6) + (hsh >> 2); };
+    mix((size_t)k.sb); mix((size_t)k.ss); mix((size_t)k.sh); mix((size_t)k.batch); mix((size_t)k.heads); mix((size_t)k.seqlen);
+    mix((size_t)k.box_rows);
+    return hsh;
+  }
+};
+
+// Tensor map over a bf16 [batch, seq, head, 128] view given by element strides; the box is
+// [box_rows sequence positions][64 elements] of one head (one 128-byte-swizzled panel).
+int make_map4(const void* ptr, int batch, int heads, int seqlen, int64_t sb, int64_t ss, int64_t sh, int box_rows, CUtensorMap* out) {
+  static std::unordered_map<Map4Key, CUtensorMap, Map4Hash> cache;
+  static std::mutex mu;
+  Map4Key key{ptr, sb, ss, sh, batch, heads, seqlen, box_rows};
+  {
+    std::lock_guard<std::mutex> lk(mu);
+    auto it = cache.find(key);
+    if (it != cache.end()) {
+      *out = it->second;
+      return MSAMP_OK;
+    }
+  }
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) {
+    msamp_set_error("cuTensorMapEncodeTiled is not available from the driver");
+    return MSAMP_ETMAP;
+  }
+  // A dimension of extent 1 still needs a valid (16-byte multiple) stride.
+  cuuint64_t dims[4] = {128, (cuuint64_t)heads, (cuuint64_t)seqlen, (cuuint64_t)batch};
+  cuuint64_t strides[3] = {(cuuint64_t)sh * 2, (cuuint64_t)ss * 2, (cuuint64_t)sb * 2};
+  for (int i = 0; i < 3; ++i)
+    if (strides[i] == 0) strides[i] = 256;
+  cuuint32_t box[4] = {64, 1, (cuuint32_t)box_rows, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(ptr), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    msamp_set_error("cuTensorMapEncodeTiled (attention) failed with %d (ptr=%p b=%d h=%d s=%d strides=%lld,%lld,%lld)", (int)r, ptr,
+                    batch, heads, seqlen, (long long)sb, (long long)ss, (long long)sh);
+    return MSAMP_ETMAP;
+  }
+  std::lock_guard<std::mutex> lk(mu);
+  if (cache.size() > 4096) cache.clear();
+  cache[key] = *out;
+  return MSAMP_OK;
+}
+
+template <typename K>
+int set_smem(K kernel, int bytes) {
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (e != cudaSuccess) {
+    msamp_set_error("cudaFuncSetAttribute(%d bytes): %s", bytes, cudaGetErrorString(e));
+    return MSAMP_ELAUNCH;
+  }
+  return MSAMP_OK;
+}
+
+}    // namespace
+
+// Same contract as msamp_attention_fwd (attention.cu) for head_dim 128: strides are the (batch, seq, head)
+// element strides of q, k, v, o; every pointer 16-byte aligned, every stride a multiple of 8 elements.
+MSAMP_API int msamp_attention_tc_fwd(const void* q, const void* k, const void* v, void* o, float* lse, const int64_t* strides, int batch,
+                                     int heads, int seqlen, int head_dim, float scale, int causal, void* stream_) {
+  MSAMP_REQUIRE(head_dim == 128, "attention (tcgen05): head_dim must be 128 (got %d)", head_dim);
+  MSAMP_REQUIRE(batch > 0 && heads > 0 && seqlen > 0, "attention: empty problem");
+  for (int i = 0; i < 12; ++i) MSAMP_REQUIRE(strides[i] % 8 == 0, "attention: stride %d is not a multiple of 8 elements", i);
+  CUtensorMap mq, mk, mv;
+  int rc;
+  if ((rc = make_map4(q, batch, heads, seqlen, strides[0], strides[1], strides[2], 128, &mq))) return rc;
+  if ((rc = make_map4(k, batch, heads, seqlen, strides[3], strides[4], strides[5], 128, &mk))) return rc;
+  if ((rc = make_map4(v, batch, heads, seqlen, strides[6], strides[7], strides[8], 128, &mv))) return rc;
+  TcParams p = {};
+  p.o = (__nv_bfloat16*)o; p.lse = lse;
+  p.o_sb = strides[9]; p.o_ss = strides[10]; p.o_sh = strides[11];
+  p.batch = batch; p.heads = heads; p.seqlen = seqlen; p.causal = causal; p.scale = scale;
+  p.status = msamp_device_status_ptr();
+  if ((rc = set_smem(attn_fwd_tc_kernel, fwd::SMEM))) return rc;
+  dim3 grid((seqlen + 127) / 128, batch * heads);
+  attn_fwd_tc_kernel<<<grid, kTcThreads, fwd::SMEM, (cudaStream_t)stream_>>>(mq, mk, mv, p);
+  return msamp_check_launch("attn_fwd_tc_kernel");
+}
+
+// Same contract as msamp_attention_bwd (attention.cu) for head_dim 128.
+MSAMP_API int msamp_attention_tc_bwd(const void* q, const void* k, const void* v, const void* o, const float* lse, const void* d_o,
+                                     void* dq, void* dk, void* dv, float* delta, const int64_t* strides, int batch, int heads,
+                                     int seqlen, int head_dim, float scale, int causal, void* stream_) {
+  MSAMP_REQUIRE(head_dim == 128, "attention (tcgen05): head_dim must be 128 (got %d)", head_dim);
+  MSAMP_REQUIRE(batch > 0 && heads > 0 && seqlen > 0, "attention: empty problem");
+  for (int i = 0; i < 24; ++i) MSAMP_REQUIRE(strides[i] % 8 == 0, "attention: stride %d is not a multiple of 8 elements", i);
+  cudaStream_t stream = (cudaStream_t)stream_;
+  {
+    DeltaParams d = {};
+    d.o = (const __nv_bfloat16*)o; d.d_o = (const __nv_bfloat16*)d_o; d.delta = delta;
+    d.o_sb = strides[9]; d.o_ss = strides[10]; d.o_sh = strides[11];
+    d.do_sb = strides[12]; d.do_ss = strides[13]; d.do_sh = strides[14];
+    d.batch = batch; d.heads = heads; d.seqlen = seqlen;
+    const int64_t warps = (int64_t)batch * heads * seqlen;
+    attn_delta_tc_kernel<<<(unsigned)((warps * 32 + 255) / 256), 256, 0, stream>>>(d);
+  }
+  TcParams p = {};
+  p.lse = const_cast<float*>(lse); p.delta = delta;
+  p.dq = (__nv_bfloat16*)dq; p.dk = (__nv_bfloat16*)dk; p.dv = (__nv_bfloat16*)dv;
+  p.dq_sb = strides[15]; p.dq_ss = strides[16]; p.dq_sh = strides[17];
+  p.dk_sb = strides[18]; p.dk_ss = strides[19]; p.dk_sh = strides[20];
+  p.dv_sb = strides[21]; p.dv_ss = strides[22]; p.dv_sh = strides[23];
+  p.batch = batch; p.heads = heads; p.seqlen = seqlen; p.causal = causal; p.scale = scale;
+  p.status = msamp_device_status_ptr();
+  int rc;
+  {
+    CUtensorMap mq, mk, mv, mdo;
+    if ((rc = make_map4(q, batch, heads, seqlen, strides[0], strides[1], strides[2], 64, &mq))) return rc;
+    if ((rc = make_map4(k, batch, heads, seqlen, strides[3], strides[4], strides[5], 128, &mk))) return rc;
+    if ((rc = make_map4(v, batch, heads, seqlen, strides[6], strides[7], strides[8], 128, &mv))) return rc;
+    if ((rc = make_map4(d_o, batch, heads, seqlen, strides[12], strides[13], strides[14], 64, &mdo))) return rc;
+    if ((rc = set_smem(attn_bwd_dkdv_tc_kernel, dkv::SMEM))) return rc;
+    dim3 grid((seqlen + 127) / 128, batch * heads);
+    attn_bwd_dkdv_tc_kernel<<<grid, kTcThreads, dkv::SMEM, stream>>>(mq, mk, mv, mdo, p);
+  }
+  {
+    CUtensorMap mq, mk, mv, mdo;
+    if ((rc = make_map4(q, batch, heads, seqlen, strides[0], strides[1], strides[2], 128, &mq))) return rc;
+    if ((rc = make_map4(k, batch, heads, seqlen, strides[3], strides[4], strides[5], 64, &mk))) return rc;
+    if ((rc = make_map4(v, batch, heads, seqlen, strides[6], strides[7], strides[8], 64, &mv))) return rc;
+    if ((rc = make_map4(d_o, batch, heads, seqlen, strides[12], strides[13], strides[14], 128, &mdo))) return rc;
+    if ((rc = set_smem(attn_bwd_dq_tc_kernel, dqk::SMEM))) return rc;
+    dim3 grid((seqlen + 127) / 128, batch * heads);
+    attn_bwd_dq_tc_kernel<<<grid, kTcThreads, dqk::SMEM, stream>>>(mq, mk, mv, mdo, p);
+  }
+  return msamp_check_launch("attn_bwd_tc kernels");
+}

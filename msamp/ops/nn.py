@@ -5,6 +5,7 @@ torch math (the oracle the GPU tests compare against).
 """
 import ctypes
 import math
+import os
 
 import torch
 import torch.nn.functional as F
@@ -101,6 +102,13 @@ def gelu(x):
 
 
 # ---------------------------------------------------------------------------------------- attention
+def _attn_entry(d, which):
+    """Native entry point for head size ``d``: the tcgen05 kernels for 128 (``MSAMP_ATTN_IMPL=mma`` keeps the
+    mma.sync kernels, which always serve head size 64)."""
+    tc = d == 128 and os.environ.get('MSAMP_ATTN_IMPL', 'tc') != 'mma'
+    return getattr(native.lib(), f'msamp_attention_{"tc_" if tc else ""}{which}')
+
+
 def _strides(t):
     # t is a [B, S, nh, d] view; kernel wants element strides (batch, seq, head)
     assert t.stride(3) == 1
@@ -116,7 +124,7 @@ class _AttentionFn(torch.autograd.Function):
         lse = torch.empty((B, nh, S), dtype=torch.float32, device=q.device)
         st = _strides(q) + _strides(k) + _strides(v) + _strides(o) + [0] * 12
         native.check(
-            native.lib().msamp_attention_fwd(
+            _attn_entry(d, 'fwd')(
                 native.ptr(q), native.ptr(k), native.ptr(v), native.ptr(o), native.ptr(lse), _i64x24(*st), B, nh, S, d,
                 ctypes.c_float(scale), int(causal), native.stream()
             ), 'attention_fwd'
@@ -140,7 +148,7 @@ class _AttentionFn(torch.autograd.Function):
         delta = torch.empty((B, nh, S), dtype=torch.float32, device=q.device)
         st = _strides(q) + _strides(k) + _strides(v) + _strides(o) + _strides(d_o) + _strides(dq) + _strides(dk) + _strides(dv)
         native.check(
-            native.lib().msamp_attention_bwd(
+            _attn_entry(d, 'bwd')(
                 native.ptr(q), native.ptr(k), native.ptr(v), native.ptr(o), native.ptr(lse), native.ptr(d_o), native.ptr(dq),
                 native.ptr(dk), native.ptr(dv), native.ptr(delta), _i64x24(*st), B, nh, S, d, ctypes.c_float(ctx.scale), int(ctx.causal),
                 native.stream()
@@ -163,7 +171,7 @@ class _AttentionPackedFn(torch.autograd.Function):
         lse = torch.empty((B, nh, S), dtype=torch.float32, device=qkv.device)
         st = _strides(q) + _strides(k) + _strides(v) + _strides(o) + [0] * 12
         native.check(
-            native.lib().msamp_attention_fwd(
+            _attn_entry(d, 'fwd')(
                 native.ptr(q), native.ptr(k), native.ptr(v), native.ptr(o), native.ptr(lse), _i64x24(*st), B, nh, S, d,
                 ctypes.c_float(scale), int(causal), native.stream()
             ), 'attention_fwd'
@@ -184,7 +192,7 @@ class _AttentionPackedFn(torch.autograd.Function):
         delta = torch.empty((B, nh, S), dtype=torch.float32, device=qkv.device)
         st = _strides(q) + _strides(k) + _strides(v) + _strides(o) + _strides(d_o) + _strides(dq) + _strides(dk) + _strides(dv)
         native.check(
-            native.lib().msamp_attention_bwd(
+            _attn_entry(d, 'bwd')(
                 native.ptr(q), native.ptr(k), native.ptr(v), native.ptr(o), native.ptr(lse), native.ptr(d_o), native.ptr(dq),
                 native.ptr(dk), native.ptr(dv), native.ptr(delta), _i64x24(*st), B, nh, S, d, ctypes.c_float(ctx.scale), int(ctx.causal),
                 native.stream()

@@ -287,6 +287,29 @@ def test_attention(d, S, causal):
     assert (q2.grad.float() - ref_in.grad[:, :, 0]).abs().max().item() <= 6e-2 * max(1.0, ref_in.grad.abs().max().item())
 
 
+@pytest.mark.parametrize('impl', ['tc', 'mma'])
+def test_attention_long_rows_growing_maximum(impl, monkeypatch):
+    """Head size 128 through both kernel families; the scores grow along the key axis so that the
+    running maximum keeps rising (the tcgen05 forward rescales its TMEM accumulator on the way)."""
+    monkeypatch.setenv('MSAMP_ATTN_IMPL', impl)
+    torch.manual_seed(1)
+    B, S, H, d = 1, 1280, 2, 128
+    qkv = torch.randn(B, S, 3, H, d, device=DEV)
+    qkv[:, :, 1] *= torch.linspace(0.2, 6.0, S, device=DEV).view(1, S, 1, 1)    # later keys score higher
+    qkv = qkv.bfloat16().requires_grad_()
+    o = K.attention_qkv(qkv, causal=True)
+    do = torch.randn_like(o)
+    o.backward(do)
+    assert native.device_status() == 0
+    ref_in = qkv.detach().float().requires_grad_()
+    r = _attn_ref(ref_in[:, :, 0], ref_in[:, :, 1], ref_in[:, :, 2], True)
+    r.backward(do.float())
+    assert (o.float() - r).abs().max().item() <= 4e-2
+    for i in range(3):
+        g, gr = qkv.grad[:, :, i].float(), ref_in.grad[:, :, i]
+        assert (g - gr).abs().max().item() <= 3e-2 * max(1.0, gr.abs().max().item())
+
+
 def test_cross_entropy():
     torch.manual_seed(0)
     rows, vocab = 300, 50304
