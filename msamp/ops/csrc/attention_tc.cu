@@ -6,10 +6,10 @@
 // back with tcgen05.ld, do the softmax arithmetic and write the bf16 probability operand into
 // swizzled shared memory for the next MMA.
 //
-//   forward   CTA = 128 query rows, key tiles of 128:  S = Q K^T  ->  P = exp2(S - m)  ->  O += P V.
-//             Two groups of softmax warps take alternating key tiles with separate S, P and O
-//             buffers, so the MMAs of one tile run under the softmax of the other; O accumulates
-//             in TMEM and is rescaled lazily.
+//   forward   CTA = 128 query rows, key tiles of 64:  S = Q K^T  ->  P = exp2(S - m)  ->  O += P V.
+//             Two groups of softmax warps take alternating key tiles; K, V, S and P live in rings
+//             four tiles deep, so scores are ready ahead of the group that needs them; O
+//             accumulates in TMEM (one accumulator per group) and is rescaled lazily.
 //   dK/dV     CTA = 128 key rows, query tiles of 64:  S^T = K Q^T, dP^T = V dO^T,
 //             dV += P^T dO, dK += dS^T Q, both accumulated in TMEM over the whole loop.
 //   dQ        CTA = 128 query rows, key tiles of 64:  S = Q K^T, dP = dO V^T, dQ += dS K in TMEM.
@@ -63,19 +63,6 @@ __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t
 // Makes this thread's ordinary shared-memory writes visible to the async proxy (the MMA reads them).
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
-// Writes v[0..31] as bf16 into row `row` of a [rows][64] panel (128-byte rows, 128-byte swizzle as
-// TMA would have written it), starting at element e0 (0 or 32).
-__device__ __forceinline__ void st_panel32(uint32_t panel, int row, int e0, const float (&v)[32]) {
-  const uint32_t rbase = panel + (uint32_t)row * 128u;
-  const uint32_t x = (uint32_t)(row & 7);
-#pragma unroll
-  for (int t = 0; t < 4; ++t) {
-    const uint32_t cc = (uint32_t)((e0 >> 3) + t);
-    st_shared_v4(rbase + ((cc ^ x) << 4), pack_bf16(v[8 * t], v[8 * t + 1]), pack_bf16(v[8 * t + 2], v[8 * t + 3]),
-                 pack_bf16(v[8 * t + 4], v[8 * t + 5]), pack_bf16(v[8 * t + 6], v[8 * t + 7]));
-  }
-}
-
 // 128 fp32 values of one row -> bf16 -> 256 contiguous bytes in global memory.
 __device__ __forceinline__ void st_row32(__nv_bfloat16* dst, const float (&v)[32]) {
   uint4* d4 = reinterpret_cast<uint4*>(dst);
@@ -95,21 +82,28 @@ __device__ __forceinline__ void st_row32(__nv_bfloat16* dst, const float (&v)[32
 
 // ============================================================================================ forward
 namespace fwd {
-constexpr uint32_t PANEL = 128 * 128;    // [128 rows][64 bf16]
-constexpr uint32_t TILE = 2 * PANEL;     // [128 rows][128 bf16]
-constexpr uint32_t OFF_Q = 0, OFF_K = TILE, OFF_V = 3 * TILE, OFF_P = 5 * TILE, OFF_BAR = 7 * TILE;
-enum { B_Q = 0, B_KF = 1, B_KE = 3, B_VF = 5, B_VE = 7, B_SF = 9, B_SE = 11, B_PF = 13, B_PE = 15, B_OF = 17, B_ACC = 19, NBAR = 20 };
-constexpr int SMEM = 7 * TILE + NBAR * 8 + 16 + 1024;
-constexpr uint32_t TM_S = 0, TM_O = 256, TM_COLS = 512;
+constexpr int NB = 4;                         // ring depth of the K, V, S and P buffers (key tile j uses slot j & 3)
+constexpr uint32_t PANEL_Q = 128 * 128;       // [128 query rows][64 bf16]
+constexpr uint32_t TILE_Q = 2 * PANEL_Q;
+constexpr uint32_t PANEL_KV = 64 * 128;       // [64 key rows][64 bf16]
+constexpr uint32_t TILE_KV = 2 * PANEL_KV;    // 16 KB
+constexpr uint32_t TILE_P = 128 * 128;        // [128 query rows][64 keys] bf16
+constexpr uint32_t OFF_Q = 0, OFF_K = TILE_Q, OFF_V = OFF_K + NB * TILE_KV, OFF_P = OFF_V + NB * TILE_KV, OFF_BAR = OFF_P + NB * TILE_P;
+enum { B_Q = 0, B_KF = 1, B_KE = B_KF + NB, B_VF = B_KE + NB, B_VE = B_VF + NB, B_SF = B_VE + NB, B_SE = B_SF + NB, B_PF = B_SE + NB,
+       B_PE = B_PF + NB, B_OF = B_PE + NB, B_ACC = B_OF + 2, NBAR = B_ACC + 1 };
+constexpr int SMEM = OFF_BAR + NBAR * 8 + 16 + 1024;
+constexpr uint32_t TM_S = 0, TM_O = 256, TM_COLS = 512;    // four 64-column score buffers, two 128-column outputs
 constexpr float kRescaleStep = 8.0f;    // the reference maximum may lag the true one by 2^8
 }    // namespace fwd
 
-// The two softmax groups work on alternating key tiles and never exchange anything inside the loop:
-// group g owns score buffer g, probability buffer g and its own output accumulator O_g in TMEM with
-// its own reference maximum m_g and row sum l_g, i.e. each group computes attention over its half of
-// the key tiles and the halves are merged once at the end.  O_g stays in TMEM and is accumulated by
-// the MMA itself; it is only read back and rescaled when a row's maximum grew by more than
-// kRescaleStep since the last rescale (probabilities then stay below 2^8, far inside bf16/fp32 range).
+// The two softmax groups work on alternating key tiles (64 keys each) and never exchange anything
+// inside the loop: group g owns the score and probability slots of its tiles and its own output
+// accumulator O_g in TMEM with its own reference maximum m_g and row sum l_g, i.e. each group computes
+// attention over its half of the key tiles and the halves are merged once at the end.  Scores are
+// computed up to four tiles ahead, so a group finds its next S ready when it has finished a tile.
+// O_g stays in TMEM and is accumulated by the MMA itself; it is only read back and rescaled when a
+// row's maximum grew by more than kRescaleStep since the last rescale (probabilities then stay
+// below 2^8, far inside bf16/fp32 range).
 __global__ void __launch_bounds__(kTcThreads, 1)
 attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                    const __grid_constant__ CUtensorMap map_v, const TcParams p) {
@@ -134,12 +128,12 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
   const int b = bh / p.heads;
   const int h = bh - b * p.heads;
   const int q0 = qt * 128;
-  const int n_all = (p.seqlen + 127) / 128;
-  const int n_kv = p.causal ? min(qt + 1, n_all) : n_all;
+  const int n_all = (p.seqlen + 63) / 64;
+  const int n_kv = p.causal ? min(2 * qt + 2, n_all) : n_all;
 
   if (threadIdx.x == 0) {
     tc5::mbar_init(bar(B_Q), 1);
-    for (int s = 0; s < 2; ++s) {
+    for (int s = 0; s < NB; ++s) {
       tc5::mbar_init(bar(B_KF + s), 1);
       tc5::mbar_init(bar(B_KE + s), 1);
       tc5::mbar_init(bar(B_VF + s), 1);
@@ -148,8 +142,9 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       tc5::mbar_init(bar(B_SE + s), 4);
       tc5::mbar_init(bar(B_PF + s), 4);
       tc5::mbar_init(bar(B_PE + s), 1);
-      tc5::mbar_init(bar(B_OF + s), 1);
     }
+    tc5::mbar_init(bar(B_OF + 0), 1);
+    tc5::mbar_init(bar(B_OF + 1), 1);
     tc5::mbar_init(bar(B_ACC), 1);
     *abort_flag = 0;
     tc5::mbar_fence_init();
@@ -169,39 +164,40 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
-      tc5::mbar_arrive_expect_tx(bar(B_Q), TILE);
+      tc5::mbar_arrive_expect_tx(bar(B_Q), TILE_Q);
       tc5::tma_load_4d(base + OFF_Q, &map_q, 0, h, q0, b, bar(B_Q));
-      tc5::tma_load_4d(base + OFF_Q + PANEL, &map_q, 64, h, q0, b, bar(B_Q));
+      tc5::tma_load_4d(base + OFF_Q + PANEL_Q, &map_q, 64, h, q0, b, bar(B_Q));
       for (int j = 0; j < n_kv; ++j) {
-        const int s = j & 1;
-        const uint32_t ph = (uint32_t)(j >> 1) & 1u;
+        const int s = j & (NB - 1);
+        const uint32_t ph = (uint32_t)(j / NB) & 1u;
         TC_WAIT(bar(B_KE + s), ph ^ 1u);
-        tc5::mbar_arrive_expect_tx(bar(B_KF + s), TILE);
-        tc5::tma_load_4d(base + OFF_K + s * TILE, &map_k, 0, h, j * 128, b, bar(B_KF + s));
-        tc5::tma_load_4d(base + OFF_K + s * TILE + PANEL, &map_k, 64, h, j * 128, b, bar(B_KF + s));
+        tc5::mbar_arrive_expect_tx(bar(B_KF + s), TILE_KV);
+        tc5::tma_load_4d(base + OFF_K + s * TILE_KV, &map_k, 0, h, j * 64, b, bar(B_KF + s));
+        tc5::tma_load_4d(base + OFF_K + s * TILE_KV + PANEL_KV, &map_k, 64, h, j * 64, b, bar(B_KF + s));
         TC_WAIT(bar(B_VE + s), ph ^ 1u);
-        tc5::mbar_arrive_expect_tx(bar(B_VF + s), TILE);
-        tc5::tma_load_4d(base + OFF_V + s * TILE, &map_v, 0, h, j * 128, b, bar(B_VF + s));
-        tc5::tma_load_4d(base + OFF_V + s * TILE + PANEL, &map_v, 64, h, j * 128, b, bar(B_VF + s));
+        tc5::mbar_arrive_expect_tx(bar(B_VF + s), TILE_KV);
+        tc5::tma_load_4d(base + OFF_V + s * TILE_KV, &map_v, 0, h, j * 64, b, bar(B_VF + s));
+        tc5::tma_load_4d(base + OFF_V + s * TILE_KV + PANEL_KV, &map_v, 64, h, j * 64, b, bar(B_VF + s));
       }
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      const uint32_t idesc_s = tc5::idesc_bf16(128, 128, 0, 0);
+      const uint32_t idesc_s = tc5::idesc_bf16(128, 64, 0, 0);
       const uint32_t idesc_o = tc5::idesc_bf16(128, 128, 0, 1);
-      // S[j&1] = Q K_j^T
+      // S[j&3] = Q K_j^T
       auto issue_s = [&](int j) -> bool {
-        const int s = j & 1;
-        const uint32_t ph = (uint32_t)(j >> 1) & 1u;
+        const int s = j & (NB - 1);
+        const uint32_t ph = (uint32_t)(j / NB) & 1u;
         if (!tc5::mbar_wait(bar(B_SE + s), ph ^ 1u, abort_flag, p.status, kStatusBit)) return false;
         if (!tc5::mbar_wait(bar(B_KF + s), ph, abort_flag, p.status, kStatusBit)) return false;
         tc5::fence_after_sync();
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
-          const uint32_t off = (uint32_t)(kk >> 2) * PANEL + (uint32_t)(kk & 3) * 32u;
-          tc5::mma_f16(tmem_base + TM_S + (uint32_t)s * 128u, tc5::smem_desc_k_sw128(base + OFF_Q + off),
-                       tc5::smem_desc_k_sw128(base + OFF_K + s * TILE + off), idesc_s, kk ? 1u : 0u);
+          const uint32_t offa = (uint32_t)(kk >> 2) * PANEL_Q + (uint32_t)(kk & 3) * 32u;
+          const uint32_t offb = (uint32_t)(kk >> 2) * PANEL_KV + (uint32_t)(kk & 3) * 32u;
+          tc5::mma_f16(tmem_base + TM_S + (uint32_t)s * 64u, tc5::smem_desc_k_sw128(base + OFF_Q + offa),
+                       tc5::smem_desc_k_sw128(base + OFF_K + s * TILE_KV + offb), idesc_s, kk ? 1u : 0u);
         }
         tc5::mma_commit(bar(B_KE + s));
         tc5::mma_commit(bar(B_SF + s));
@@ -209,26 +205,27 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       };
       do {
         TC_WAIT(bar(B_Q), 0u);
-        if (!issue_s(0)) break;
         bool ok = true;
+        for (int j = 0; j < NB && j < n_kv; ++j)
+          if (!issue_s(j)) { ok = false; break; }
+        if (!ok) break;
         for (int j = 0; j < n_kv; ++j) {
-          if (j + 1 < n_kv && !issue_s(j + 1)) { ok = false; break; }
-          const int s = j & 1;
-          const uint32_t ph = (uint32_t)(j >> 1) & 1u;
+          const int s = j & (NB - 1);
+          const uint32_t ph = (uint32_t)(j / NB) & 1u;
           if (!tc5::mbar_wait(bar(B_PF + s), ph, abort_flag, p.status, kStatusBit)) { ok = false; break; }
           if (!tc5::mbar_wait(bar(B_VF + s), ph, abort_flag, p.status, kStatusBit)) { ok = false; break; }
           tc5::fence_after_sync();
           // O[j&1] (+)= P_j V_j : A = P (K-major), B = V with the key index as rows (MN-major)
 #pragma unroll
-          for (int kk = 0; kk < 8; ++kk) {
-            const uint32_t offa = (uint32_t)(kk >> 2) * PANEL + (uint32_t)(kk & 3) * 32u;
-            tc5::mma_f16(tmem_base + TM_O + (uint32_t)s * 128u, tc5::smem_desc_k_sw128(base + OFF_P + s * TILE + offa),
-                         tc5::smem_desc_mn_sw128(base + OFF_V + s * TILE + (uint32_t)kk * 2048u, PANEL), idesc_o,
+          for (int kk = 0; kk < 4; ++kk) {
+            tc5::mma_f16(tmem_base + TM_O + (uint32_t)(j & 1) * 128u, tc5::smem_desc_k_sw128(base + OFF_P + s * TILE_P + (uint32_t)kk * 32u),
+                         tc5::smem_desc_mn_sw128(base + OFF_V + s * TILE_KV + (uint32_t)kk * 2048u, PANEL_KV), idesc_o,
                          (j >= 2 || kk) ? 1u : 0u);
           }
           tc5::mma_commit(bar(B_VE + s));
           tc5::mma_commit(bar(B_PE + s));
-          tc5::mma_commit(bar(B_OF + s));
+          tc5::mma_commit(bar(B_OF + (j & 1)));
+          if (j + NB < n_kv && !issue_s(j + NB)) { ok = false; break; }
         }
         if (ok) tc5::mma_commit(bar(B_ACC));
       } while (false);
@@ -240,41 +237,38 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     const int row = qd * 32 + lane;
     const int grow = q0 + row;
     const uint32_t tlane = tmem_base + ((uint32_t)(qd * 32) << 16);
-    const uint32_t ts = tlane + TM_S + (uint32_t)wg * 128u;
     const uint32_t to = tlane + TM_O + (uint32_t)wg * 128u;
     const float sl = p.scale * kLog2e;
     const int lim = p.causal ? min(grow, p.seqlen - 1) : p.seqlen - 1;    // last visible column
+    const uint32_t swz = (uint32_t)(row & 7);
     float m = -INFINITY, l = 0.0f;    // reference maximum (log2 units) and row sum of this group
     bool ok = true;
 
     for (int j = wg; j < n_kv; j += 2) {
-      const int k = j >> 1;
-      const uint32_t ph = (uint32_t)k & 1u;
-      if (!wait_warp(bar(B_SF + wg), ph)) { ok = false; break; }
+      const int s = j & (NB - 1);
+      const uint32_t ph = (uint32_t)(j / NB) & 1u;
+      const int k = j >> 1;    // index of this tile within the group
+      if (!wait_warp(bar(B_SF + s), ph)) { ok = false; break; }
       tc5::fence_after_sync();
-      uint32_t r[4][32];
-#pragma unroll
-      for (int c = 0; c < 4; ++c) tc5::tmem_ld32(ts + (uint32_t)c * 32u, r[c]);
+      uint32_t r[2][32];
+      tc5::tmem_ld32(tlane + TM_S + (uint32_t)s * 64u, r[0]);
+      tc5::tmem_ld32(tlane + TM_S + (uint32_t)s * 64u + 32u, r[1]);
       tc5::tmem_ld_wait();
       tc5::fence_before_sync();
       __syncwarp();
-      if (lane == 0) tc5::mbar_arrive(bar(B_SE + wg));    // the next S of this group may be computed already
-      const bool need_mask = (p.causal && j == qt) || (j * 128 + 128 > p.seqlen);
-      const int col0 = j * 128;
-      float mx = -INFINITY;
+      if (lane == 0) tc5::mbar_arrive(bar(B_SE + s));    // the slot may take the scores of tile j + 4
+      const int col0 = j * 64;
+      const bool need_mask = (p.causal && col0 + 63 > q0) || (col0 + 64 > p.seqlen);
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
       if (need_mask) {
 #pragma unroll
-        for (int c = 0; c < 4; ++c)
-#pragma unroll
-          for (int i = 0; i < 32; ++i)
-            if (col0 + c * 32 + i <= lim) mx = fmaxf(mx, __uint_as_float(r[c][i]));
+        for (int i = 0; i < 64; ++i)
+          if (col0 + i <= lim) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(r[i >> 5][i & 31]));
       } else {
 #pragma unroll
-        for (int c = 0; c < 4; ++c)
-#pragma unroll
-          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(r[c][i]));
+        for (int i = 0; i < 64; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(r[i >> 5][i & 31]));
       }
-      mx *= sl;    // sl > 0
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * sl;    // sl > 0
       const bool grow_m = mx > m + kRescaleStep || (m == -INFINITY && mx > -INFINITY);
       if (__any_sync(0xffffffffu, grow_m)) {
         const float m_new = grow_m ? mx : m;
@@ -284,41 +278,40 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
           if (!wait_warp(bar(B_OF + wg), (uint32_t)(k - 1) & 1u)) { ok = false; break; }
           tc5::fence_after_sync();
 #pragma unroll 1
-          for (int c = 0; c < 8; ++c) {
-            uint32_t x[16];
-            tc5::tmem_ld16(to + (uint32_t)c * 16u, x);
+          for (int c = 0; c < 4; ++c) {
+            uint32_t x[32];
+            tc5::tmem_ld32(to + (uint32_t)c * 32u, x);
             tc5::tmem_ld_wait();
 #pragma unroll
-            for (int i = 0; i < 16; ++i) x[i] = __float_as_uint(__uint_as_float(x[i]) * corr);
-            tc5::tmem_st16(to + (uint32_t)c * 16u, x);
+            for (int i = 0; i < 32; ++i) x[i] = __float_as_uint(__uint_as_float(x[i]) * corr);
+            tc5::tmem_st32(to + (uint32_t)c * 32u, x);
           }
           tc5::tmem_st_wait();
         }
         l *= corr;
         m = m_new;
       }
-      if (!wait_warp(bar(B_PE + wg), ph ^ 1u)) { ok = false; break; }
+      if (!wait_warp(bar(B_PE + s), ph ^ 1u)) { ok = false; break; }
       const float m_use = (m == -INFINITY) ? 0.0f : m;
-      float rowsum = 0.0f;
-      const uint32_t prow = base + OFF_P + wg * TILE + (uint32_t)row * 128u;
-      const uint32_t swz = (uint32_t)(row & 7);
+      float sum4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+      const uint32_t prow = base + OFF_P + s * TILE_P + (uint32_t)row * 128u;
 #pragma unroll
-      for (int g = 0; g < 16; ++g) {    // 16-byte chunk g = columns 8g .. 8g+7
+      for (int g = 0; g < 8; ++g) {    // 16-byte chunk g = columns 8g .. 8g+7
         float e[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
           e[i] = ex2(fmaf(__uint_as_float(r[g >> 2][(g & 3) * 8 + i]), sl, -m_use));
           if (need_mask && col0 + g * 8 + i > lim) e[i] = 0.0f;
-          rowsum += e[i];
+          sum4[i & 3] += e[i];
         }
-        st_shared_v4(prow + (uint32_t)(g >> 3) * PANEL + ((((uint32_t)g & 7u) ^ swz) << 4), pack_bf16(e[0], e[1]),
-                     pack_bf16(e[2], e[3]), pack_bf16(e[4], e[5]), pack_bf16(e[6], e[7]));
+        st_shared_v4(prow + ((((uint32_t)g) ^ swz) << 4), pack_bf16(e[0], e[1]), pack_bf16(e[2], e[3]), pack_bf16(e[4], e[5]),
+                     pack_bf16(e[6], e[7]));
       }
-      l += rowsum;
+      l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
       tc5::fence_before_sync();
       fence_async_smem();
       __syncwarp();
-      if (lane == 0) tc5::mbar_arrive(bar(B_PF + wg));
+      if (lane == 0) tc5::mbar_arrive(bar(B_PF + s));
     }
     ok = ok && wait_warp(bar(B_ACC), 0u);
     tc5::fence_after_sync();
@@ -540,9 +533,11 @@ attn_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       do {
         TC_WAIT(bar(B_KV), 0u);
         if (!issue_s(0)) break;
+        if (n_q > 1 && !issue_s(1)) break;
         bool ok = true;
         for (int t = 0; t < n_q; ++t) {
-          if (t + 1 < n_q && !issue_s(t + 1)) { ok = false; break; }
+          // the scores two tiles ahead go first: their buffer was released as soon as tile t had been read
+          if (t + 2 < n_q && !issue_s(t + 2)) { ok = false; break; }
           const int s = t & 1;
           const int st = t % NSQ;
           const uint32_t ph = (uint32_t)(t >> 1) & 1u;
@@ -584,40 +579,49 @@ attn_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       if (!wait_warp(bar(B_QF + st), (uint32_t)(t / NSQ) & 1u)) { ok = false; break; }
       if (!wait_warp(bar(B_SF + s), ph)) { ok = false; break; }
       tc5::fence_after_sync();
-      if (!wait_warp(bar(B_PE + s), ph ^ 1u)) { ok = false; break; }
       const bool need_mask = p.causal && (qrow0 < k0 + 128);
       const float4* lse2 = reinterpret_cast<const float4*>(s_lse + st * 64);
       const float4* dlt = reinterpret_cast<const float4*>(s_delta + st * 64);
+      uint32_t rs[2][32], rd[2][32];
+      tc5::tmem_ld32(tlane + TM_ST + (uint32_t)s * 64u, rs[0]);
+      tc5::tmem_ld32(tlane + TM_ST + (uint32_t)s * 64u + 32u, rs[1]);
+      tc5::tmem_ld32(tlane + TM_DPT + (uint32_t)s * 64u, rd[0]);
+      tc5::tmem_ld32(tlane + TM_DPT + (uint32_t)s * 64u + 32u, rd[1]);
+      tc5::tmem_ld_wait();
+      tc5::fence_before_sync();
+      __syncwarp();
+      if (lane == 0) tc5::mbar_arrive(bar(B_SE + s));    // the buffer may take tile t + 2
+      if (!wait_warp(bar(B_PE + s), ph ^ 1u)) { ok = false; break; }
+      const uint32_t prow = base + OFF_PT + s * TILE_P + (uint32_t)row * 128u;
+      const uint32_t drow = base + OFF_DST + s * TILE_P + (uint32_t)row * 128u;
+      const uint32_t swz = (uint32_t)(row & 7);
 #pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        uint32_t rs[32], rd[32];
-        tc5::tmem_ld32(tlane + TM_ST + (uint32_t)s * 64u + (uint32_t)c * 32u, rs);
-        tc5::tmem_ld32(tlane + TM_DPT + (uint32_t)s * 64u + (uint32_t)c * 32u, rd);
-        tc5::tmem_ld_wait();
-        float pv[32], ds[32];
+      for (int g = 0; g < 8; ++g) {    // 16-byte chunk g = queries 8g .. 8g+7 of the tile
+        float e[8], ds[8];
 #pragma unroll
-        for (int i4 = 0; i4 < 8; ++i4) {
-          const float4 l4 = lse2[c * 8 + i4];
-          const float4 d4 = dlt[c * 8 + i4];
+        for (int hh = 0; hh < 2; ++hh) {
+          const float4 l4 = lse2[g * 2 + hh];
+          const float4 d4 = dlt[g * 2 + hh];
           const float la[4] = {l4.x, l4.y, l4.z, l4.w};
           const float da[4] = {d4.x, d4.y, d4.z, d4.w};
 #pragma unroll
           for (int u = 0; u < 4; ++u) {
-            const int i = i4 * 4 + u;
-            float e = ex2(fmaf(__uint_as_float(rs[i]), sl, -la[u]));
-            if (need_mask && qrow0 + c * 32 + i < grow) e = 0.0f;
-            pv[i] = e;
-            ds[i] = e * (__uint_as_float(rd[i]) - da[u]);
+            const int i = hh * 4 + u;
+            const int ql = g * 8 + i;
+            float ev = ex2(fmaf(__uint_as_float(rs[ql >> 5][ql & 31]), sl, -la[u]));
+            if (need_mask && qrow0 + ql < grow) ev = 0.0f;
+            e[i] = ev;
+            ds[i] = ev * (__uint_as_float(rd[ql >> 5][ql & 31]) - da[u]);
           }
         }
-        st_panel32(base + OFF_PT + s * TILE_P, row, c * 32, pv);
-        st_panel32(base + OFF_DST + s * TILE_P, row, c * 32, ds);
+        const uint32_t off = (((uint32_t)g) ^ swz) << 4;
+        st_shared_v4(prow + off, pack_bf16(e[0], e[1]), pack_bf16(e[2], e[3]), pack_bf16(e[4], e[5]), pack_bf16(e[6], e[7]));
+        st_shared_v4(drow + off, pack_bf16(ds[0], ds[1]), pack_bf16(ds[2], ds[3]), pack_bf16(ds[4], ds[5]), pack_bf16(ds[6], ds[7]));
       }
       tc5::fence_before_sync();
       fence_async_smem();
       __syncwarp();
       if (lane == 0) {
-        tc5::mbar_arrive(bar(B_SE + s));
         tc5::mbar_arrive(bar(B_PF + s));
         tc5::mbar_arrive(bar(B_QE + st));
       }
@@ -776,9 +780,11 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
       do {
         TC_WAIT(bar(B_Q), 0u);
         if (!issue_s(0)) break;
+        if (n_kv > 1 && !issue_s(1)) break;
         bool ok = true;
         for (int j = 0; j < n_kv; ++j) {
-          if (j + 1 < n_kv && !issue_s(j + 1)) { ok = false; break; }
+          // the scores two tiles ahead go first: their buffer was released as soon as tile j had been read
+          if (j + 2 < n_kv && !issue_s(j + 2)) { ok = false; break; }
           const int s = j & 1;
           const int st = j % NSK;
           const uint32_t ph = (uint32_t)(j >> 1) & 1u;
@@ -815,30 +821,36 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
       const int col0 = j * 64;
       if (!wait_warp(bar(B_SF + s), ph)) { ok = false; break; }
       tc5::fence_after_sync();
-      if (!wait_warp(bar(B_PE + s), ph ^ 1u)) { ok = false; break; }
       const bool need_mask = (p.causal && col0 + 63 > q0) || (col0 + 64 > p.seqlen);
+      uint32_t rs[2][32], rd[2][32];
+      tc5::tmem_ld32(tlane + TM_S + (uint32_t)s * 64u, rs[0]);
+      tc5::tmem_ld32(tlane + TM_S + (uint32_t)s * 64u + 32u, rs[1]);
+      tc5::tmem_ld32(tlane + TM_DP + (uint32_t)s * 64u, rd[0]);
+      tc5::tmem_ld32(tlane + TM_DP + (uint32_t)s * 64u + 32u, rd[1]);
+      tc5::tmem_ld_wait();
+      tc5::fence_before_sync();
+      __syncwarp();
+      if (lane == 0) tc5::mbar_arrive(bar(B_SE + s));    // the buffer may take tile j + 2
+      if (!wait_warp(bar(B_PE + s), ph ^ 1u)) { ok = false; break; }
+      const uint32_t drow = base + OFF_DS + s * TILE_DS + (uint32_t)row * 128u;
+      const uint32_t swz = (uint32_t)(row & 7);
 #pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        uint32_t rs[32], rd[32];
-        tc5::tmem_ld32(tlane + TM_S + (uint32_t)s * 64u + (uint32_t)c * 32u, rs);
-        tc5::tmem_ld32(tlane + TM_DP + (uint32_t)s * 64u + (uint32_t)c * 32u, rd);
-        tc5::tmem_ld_wait();
-        float ds[32];
+      for (int g = 0; g < 8; ++g) {    // 16-byte chunk g = keys 8g .. 8g+7 of the tile
+        float ds[8];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float e = ex2(fmaf(__uint_as_float(rs[i]), sl, -lse2));
-          if (need_mask && col0 + c * 32 + i > lim) e = 0.0f;
-          ds[i] = e * (__uint_as_float(rd[i]) - dlt);
+        for (int i = 0; i < 8; ++i) {
+          const int c = g * 8 + i;
+          float e = ex2(fmaf(__uint_as_float(rs[c >> 5][c & 31]), sl, -lse2));
+          if (need_mask && col0 + c > lim) e = 0.0f;
+          ds[i] = e * (__uint_as_float(rd[c >> 5][c & 31]) - dlt);
         }
-        st_panel32(base + OFF_DS + s * TILE_DS, row, c * 32, ds);
+        st_shared_v4(drow + ((((uint32_t)g) ^ swz) << 4), pack_bf16(ds[0], ds[1]), pack_bf16(ds[2], ds[3]), pack_bf16(ds[4], ds[5]),
+                     pack_bf16(ds[6], ds[7]));
       }
       tc5::fence_before_sync();
       fence_async_smem();
       __syncwarp();
-      if (lane == 0) {
-        tc5::mbar_arrive(bar(B_SE + s));
-        tc5::mbar_arrive(bar(B_PF + s));
-      }
+      if (lane == 0) tc5::mbar_arrive(bar(B_PF + s));
     }
     if (ok && wait_warp(bar(B_ACC), 0u)) {
       tc5::fence_after_sync();
@@ -966,8 +978,8 @@ MSAMP_API int msamp_attention_tc_fwd(const void* q, const void* k, const void* v
   CUtensorMap mq, mk, mv;
   int rc;
   if ((rc = make_map4(q, batch, heads, seqlen, strides[0], strides[1], strides[2], 128, &mq))) return rc;
-  if ((rc = make_map4(k, batch, heads, seqlen, strides[3], strides[4], strides[5], 128, &mk))) return rc;
-  if ((rc = make_map4(v, batch, heads, seqlen, strides[6], strides[7], strides[8], 128, &mv))) return rc;
+  if ((rc = make_map4(k, batch, heads, seqlen, strides[3], strides[4], strides[5], 64, &mk))) return rc;
+  if ((rc = make_map4(v, batch, heads, seqlen, strides[6], strides[7], strides[8], 64, &mv))) return rc;
   TcParams p = {};
   p.o = (__nv_bfloat16*)o; p.lse = lse;
   p.o_sb = strides[9]; p.o_ss = strides[10]; p.o_sh = strides[11];
