@@ -1,6 +1,9 @@
 """Single-GPU kernel benchmark: achieved throughput of each hot kernel and its fraction of the measured roofline.
 
-    python benchmarks/bench_kernels.py [--out results.jsonl]
+    python benchmarks/bench_kernels.py [--out results.jsonl] [--profile]
+
+``--profile`` launches every kernel once, without warm-up and on a 2 x 64 Mi-parameter optimizer case, so that the
+script can be wrapped by ``ncu`` with a kernel filter (see the command lines recorded in profiles/).
 
 Timing: CUDA events around 10 launches after 3 warm-ups; tensors are larger than the 126 MB L2 unless noted.
 Denominators come from MEASURED_PEAKS.json in the repository root when present (HBM copy GB/s, cuBLAS bf16
@@ -30,7 +33,12 @@ def peaks():
     return 6650.0, 1590.0, 'fallback'
 
 
+PROFILE = False
+
+
 def timeit(fn, iters=10, warm=3):
+    if PROFILE:
+        iters, warm = 1, 0
     for _ in range(warm):
         fn()
     torch.cuda.synchronize()
@@ -46,7 +54,10 @@ def timeit(fn, iters=10, warm=3):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument('--out', default=None)
+    ap.add_argument('--profile', action='store_true')
     args = ap.parse_args()
+    global PROFILE
+    PROFILE = args.profile
     dev = 'cuda'
     hbm, bf16, src = peaks()
     rows = []
@@ -67,7 +78,7 @@ def main():
         ms = timeit(lambda: gemm.gemm_fp8(a, E4, sa, b, E4, sb, torch.bfloat16, out=out))
         a8, b8 = a.view(torch.float8_e4m3fn), b.view(torch.float8_e4m3fn)
         try:
-            ms_ref = timeit(lambda: torch._scaled_mm(a8, b8.t(), scale_a=sa, scale_b=sb, out_dtype=torch.bfloat16))
+            ms_ref = None if PROFILE else timeit(lambda: torch._scaled_mm(a8, b8.t(), scale_a=sa, scale_b=sb, out_dtype=torch.bfloat16))
         except Exception:
             ms_ref = None
         tf = 2 * m * n * k / ms / 1e9
@@ -118,10 +129,11 @@ def main():
     # ---- fused LBAdam over 1 Gi parameters (O2 layout: fp16 scaled weight, e4m3 grad, e4m3 m, fp16 v)
     from msamp.nn import ScalingParameter
     from msamp.optim import LBAdamW
-    ps = [ScalingParameter((torch.randn(16384, 8192, device=dev) * 0.02).cast(Dtypes.kfloat16)) for _ in range(8)]
+    ps = [ScalingParameter((torch.randn(16384, 8192 if not PROFILE else 4096, device=dev) * 0.02).cast(Dtypes.kfloat16))
+          for _ in range(8 if not PROFILE else 2)]
     opt = LBAdamW(ps, lr=1e-4)
     for p in ps:
-        p.grad = (torch.randn(16384, 8192, device=dev) * 1e-3).cast(E4)
+        p.grad = (torch.randn(*p.shape, device=dev) * 1e-3).cast(E4)
     opt.step()
     ms = timeit(lambda: opt.lb_step(), iters=5, warm=2)
     npar = sum(p.numel() for p in ps)

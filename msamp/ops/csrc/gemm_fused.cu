@@ -23,6 +23,7 @@ using namespace gemm;
 
 constexpr int kMaxRanks = 8;
 constexpr int kPiece = 32768;    // bytes moved per bulk copy by a copy warp
+constexpr int kRsStageBytes = 4 * 8192;    // reduce-scatter epilogue: 32 rows x 256 bytes per epilogue warp
 
 enum GatherMode { G_NONE = 0, G_A_ROWS = 1, G_B_ROWS = 2, G_B_K = 3, G_A_K = 4 };
 
@@ -359,14 +360,55 @@ gemm_fused_kernel(const __grid_constant__ FusedMaps maps, const GemmParams p, co
       tc5::fence_after_sync();
       const int row = m0 + q * 32 + lane;
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN);
-      OutT* row_ptr;
+      OutT* row_ptr = D + (int64_t)row * p.ldd;
       if (f.rs) {
-        // this row belongs to rank `owner`; it lands in the slot reserved for this rank in the owner's staging buffer
-        const int owner = row / f.rows_per_rank;
-        row_ptr = reinterpret_cast<OutT*>(f.stage[owner < f.world ? owner : 0]) +
-                  ((int64_t)f.rank * f.rows_per_rank + (row % f.rows_per_rank)) * (int64_t)p.N;
-      } else {
-        row_ptr = D + (int64_t)row * p.ldd;
+        // The 128 rows of a tile belong to one rank (`owner`); they land in the slot reserved for this rank in
+        // the owner's staging buffer.  A thread holds one row of the accumulator, so direct stores would hit the
+        // peer with scattered 64-byte pieces; instead each warp turns 32 rows x 256 bytes around in shared memory
+        // (16-byte chunks XOR-swizzled by the row) and writes whole 256-byte row segments, two rows per store.
+        const int owner = m0 / f.rows_per_rank;
+        OutT* tile_ptr = reinterpret_cast<OutT*>(f.stage[owner < f.world ? owner : 0]) +
+                         ((int64_t)f.rank * f.rows_per_rank + (m0 % f.rows_per_rank) + q * 32) * (int64_t)p.N;
+        constexpr int kColsPerPass = 256 / (int)sizeof(OutT);    // columns in 256 bytes
+        constexpr int kChunksPerPass = kColsPerPass / 32;        // tcgen05.ld pieces per pass
+        const uint32_t wbase = base + C::TILE_BYTES + C::BAR_BYTES + (uint32_t)q * 8192u;
+#pragma unroll 1
+        for (int pass = 0; pass < BN / kColsPerPass; ++pass) {
+#pragma unroll
+          for (int cc = 0; cc < kChunksPerPass; ++cc) {
+            uint32_t r[32];
+            tc5::tmem_ld32(taddr + (uint32_t)(pass * kColsPerPass + cc * 32), r);
+            tc5::tmem_ld_wait();
+            alignas(16) OutT o[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) o[j] = from_f32<OutT>(__uint_as_float(r[j]) * alpha);
+            const Bytes16* o16 = reinterpret_cast<const Bytes16*>(o);
+            constexpr int kPieces = 32 * (int)sizeof(OutT) / 16;    // 16-byte pieces of this 32-column chunk
+#pragma unroll
+            for (int j = 0; j < kPieces; ++j) {
+              const uint32_t ch = (uint32_t)(cc * kPieces + j);
+              const uint32_t addr = wbase + (uint32_t)lane * 256u + ((ch ^ ((uint32_t)lane & 15u)) << 4);
+              asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(o16[j].w[0]), "r"(o16[j].w[1]), "r"(o16[j].w[2]), "r"(o16[j].w[3])
+                           : "memory");
+            }
+          }
+          __syncwarp();
+          const int col_b = (n0 + pass * kColsPerPass) * (int)sizeof(OutT) + (lane & 15) * 16;    // byte offset inside the row
+#pragma unroll 4
+          for (int i = 0; i < 16; ++i) {
+            const int rr = 2 * i + (lane >> 4);
+            const uint32_t addr = wbase + (uint32_t)rr * 256u + ((((uint32_t)lane & 15u) ^ ((uint32_t)rr & 15u)) << 4);
+            uint4 v;
+            asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr) : "memory");
+            if (m0 + q * 32 + rr < p.M && col_b < p.N * (int)sizeof(OutT))
+              *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(tile_ptr + (int64_t)rr * p.N) + col_b) = v;
+          }
+          __syncwarp();
+        }
+        tc5::fence_before_sync();
+        __syncwarp();
+        if (lane == 0) tc5::mbar_arrive(tempty_bar(buf));
+        continue;
       }
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
@@ -471,7 +513,7 @@ int launch_fused(const FusedMaps& maps, const GemmParams& p, const FusedArgs& f,
   int dev = 0;
   cudaGetDevice(&dev);
   if (!configured[dev & 63]) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_fused_kernel<BN, OutT>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
+    cudaError_t e = cudaFuncSetAttribute(gemm_fused_kernel<BN, OutT>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES + kRsStageBytes);
     if (e != cudaSuccess) {
       msamp_set_error("cudaFuncSetAttribute(fused): %s", cudaGetErrorString(e));
       return MSAMP_ELAUNCH;
@@ -480,7 +522,7 @@ int launch_fused(const FusedMaps& maps, const GemmParams& p, const FusedArgs& f,
   }
   // All CTAs take part in flag waits, so the grid must be co-resident: one CTA per SM at most.
   int grid = msamp_sm_count();
-  gemm_fused_kernel<BN, OutT><<<grid, kGemmThreads, C::SMEM_BYTES, stream>>>(maps, p, f);
+  gemm_fused_kernel<BN, OutT><<<grid, kGemmThreads, C::SMEM_BYTES + kRsStageBytes, stream>>>(maps, p, f);
   return msamp_check_launch("gemm_fused_kernel");
 }
 
