@@ -14,6 +14,7 @@ Each has an unfused reference composition (NCCL / gloo collective + plain GEMM) 
 size 1, and as the oracle in the tests.
 """
 import ctypes
+import os
 
 import torch
 import torch.distributed as dist
@@ -66,7 +67,11 @@ class FusedGemmContext:
         self.rank = DistUtil.get_rank(group)
         self.n_comm = n_comm
         self.wait_seconds = wait_seconds
-        self.native = torch.cuda.is_available() and self.world > 1 and DistUtil.backend(group) == 'nccl'
+        # A world of one rank runs the plain GEMM unless MSAMP_FUSED_SINGLE_RANK=1 asks for the fused kernel
+        # (its copy CTAs then have nothing to fetch); that is how the kernel is profiled on one GPU.
+        single_ok = os.environ.get('MSAMP_FUSED_SINGLE_RANK', '0') == '1'
+        self.native = (torch.cuda.is_available() and (self.world > 1 or single_ok) and dist.is_initialized()
+                       and DistUtil.backend(group) == 'nccl')
         self.max_shard_bytes = (int(max_shard_bytes) + 1023) // 1024 * 1024
         self.max_out_bytes = int(max_out_bytes)
         if not self.native:
