@@ -38,6 +38,8 @@ def parse():
     ap.add_argument('--opt-level', default='O2')
     ap.add_argument('--layers', type=int, default=0, help='override the layer count (the result is then labelled as a reduced config)')
     ap.add_argument('--no-e2e', action='store_true')
+    ap.add_argument('--tp', type=int, default=0,
+                    help='tensor-parallel size with sequence parallelism (0 = 4 for gpt-13b when the world allows it, else 1)')
     return ap.parse_args()
 
 
@@ -137,14 +139,31 @@ def main():
     if args.layers:
         over['n_layer'] = args.layers
     cfg = gpt_config(args.model, **over)
+    tp = args.tp or (min(4, world) if args.model == 'gpt-13b' else 1)
+    dp = world // tp
     torch.manual_seed(1234)
-    model = GPT(cfg, device=dev)
-    opt = torch.optim.AdamW(model.parameters(), lr=1e-4, betas=(0.9, 0.95), weight_decay=0.1)
-    model, opt = msamp.initialize(model, opt, args.opt_level)
-    trainer = DataParallelTrainer(model, opt, zero_stage=2 if world > 1 else 0)
+    if tp > 1:
+        # Megatron-style tensor + sequence parallelism inside groups of `tp` adjacent ranks, sharded optimizer over the rest
+        from msamp.megatron import parallel_state as mpu
+        from msamp.models import ParallelGPT
+        mpu.initialize_model_parallel(tensor_model_parallel_size=tp)
+        model = ParallelGPT(cfg, device=dev)    # its projections are FP8 modules already
+        if args.opt_level != 'O2':
+            raise SystemExit('the tensor-parallel configuration is built for --opt-level O2')
+        from msamp.optim import LBAdamW
+        opt = LBAdamW(model.parameters(), lr=1e-4, betas=(0.9, 0.95), weight_decay=0.1)    # O2: e4m3 first, fp16 second moment
+        trainer = DataParallelTrainer(model, opt, zero_stage=2 if dp > 1 else 0, group=mpu.get_data_parallel_group(),
+                                      after_backward=model.allreduce_sequence_parallel_grads)
+        data_rank = mpu.get_data_parallel_rank()
+    else:
+        model = GPT(cfg, device=dev)
+        opt = torch.optim.AdamW(model.parameters(), lr=1e-4, betas=(0.9, 0.95), weight_decay=0.1)
+        model, opt = msamp.initialize(model, opt, args.opt_level)
+        trainer = DataParallelTrainer(model, opt, zero_stage=2 if world > 1 else 0)
+        data_rank = rank
 
     B, S = args.micro_batch, args.seq
-    gen = torch.Generator().manual_seed(rank)
+    gen = torch.Generator().manual_seed(data_rank)    # ranks of one tensor-parallel group see the same batch
     host_tok = [torch.randint(0, cfg.vocab_size, (B, S), generator=gen).pin_memory() for _ in range(4)]
     host_lab = [torch.randint(0, cfg.vocab_size, (B, S), generator=gen).pin_memory() for _ in range(4)]
     dev_tok = [t.to(dev) for t in host_tok]
@@ -186,7 +205,7 @@ def main():
     sampler.start()
     ms, launches = timed(step_device, args.steps)
     clocks = sampler.stop()
-    tokens = B * S * world * args.steps
+    tokens = B * S * dp * args.steps
     value = tokens / (ms / 1e3)
 
     e2e = None
@@ -212,8 +231,8 @@ def main():
             'impl': 'ours',
             'config': {
                 'model': args.model, 'layers': cfg.n_layer, 'hidden': cfg.hidden, 'heads': cfg.n_head, 'ffn': cfg.ffn_hidden,
-                'vocab': cfg.vocab_size, 'global_batch': B * world, 'micro_batch': B, 'seq_len': S,
-                'parallelism': f'dp{world}' + ('+zero2' if world > 1 else ''), 'opt_level': args.opt_level,
+                'vocab': cfg.vocab_size, 'global_batch': B * dp, 'micro_batch': B, 'seq_len': S,
+                'parallelism': (f'tp{tp}+sp x ' if tp > 1 else '') + f'dp{dp}' + ('+zero2' if dp > 1 else ''), 'opt_level': args.opt_level,
                 'l2': 'per-step working set (GBs of weights and activations) is far larger than the 126 MB L2, no explicit flush',
             },
             'model_tflops_per_gpu': flops / world / 1e12,

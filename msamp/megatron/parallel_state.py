@@ -95,6 +95,15 @@ def get_tensor_model_parallel_rank():
     return dist.get_rank(g) if g is not None else 0
 
 
+def get_tensor_model_parallel_src_rank():
+    """Global rank of the first member of this rank's tensor-parallel group."""
+    c = _core()
+    if c:
+        return c.get_tensor_model_parallel_src_rank()
+    rank = dist.get_rank() if dist.is_initialized() else 0
+    return rank - get_tensor_model_parallel_rank()
+
+
 def get_data_parallel_world_size():
     c = _core()
     return c.get_data_parallel_world_size() if c else _STATE['dp_size']

@@ -17,8 +17,10 @@ class DataParallelTrainer:
     are quantised), so they are summed as FP8 numbers and averaged by dividing ``scale_inv``;
     high-precision gradients are averaged in flat buckets.
     """
-    def __init__(self, model, optimizer, zero_stage=0, group=None, clip_grad=0.0, bucket_elems=64 * 1024 * 1024):
+    def __init__(self, model, optimizer, zero_stage=0, group=None, clip_grad=0.0, bucket_elems=64 * 1024 * 1024, after_backward=None):
         self.model = model
+        # called after backward and before any gradient is reduced (e.g. ParallelGPT.allreduce_sequence_parallel_grads)
+        self.after_backward = after_backward
         self.optimizer = optimizer
         self.group = group
         self.world = DistUtil.get_world_size(group)
@@ -56,6 +58,8 @@ class DataParallelTrainer:
         self.optimizer.zero_grad(set_to_none=True)
         loss = self.model(*inputs)
         loss.backward()
+        if self.after_backward is not None:
+            self.after_backward()
         if self.zero is not None:
             self.zero.reduce_and_step(clip_grad=self.clip_grad)
         else:

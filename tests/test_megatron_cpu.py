@@ -1,4 +1,5 @@
 """Megatron-style tensor/sequence parallel linears, local FP8 DDP and the distributed optimizer on gloo ranks."""
+import math
 import os
 import tempfile
 
@@ -102,3 +103,66 @@ def _ddp_distopt(rank, world):
 
 def test_local_ddp_and_distributed_optimizer():
     run_workers(_ddp_distopt, 2)
+
+
+def _parallel_gpt(rank, world, tp):
+    import msamp
+    from msamp.megatron import parallel_state as mpu
+    from msamp.models import GPT, ParallelGPT, gpt_config
+    from msamp.optim import LBAdamW
+    from msamp.parallel import DataParallelTrainer
+    mpu.initialize_model_parallel(tensor_model_parallel_size=tp)
+    dp_rank = mpu.get_data_parallel_rank()
+    cfg = gpt_config('gpt-tiny', n_layer=2, n_head=4, hidden=64, ffn_hidden=256, vocab_size=128, max_seq=32)
+    torch.manual_seed(0)
+    model = ParallelGPT(cfg, act_dtype=torch.float32)
+    assert model.sequence_parallel == (tp > 1)
+    opt = LBAdamW(model.parameters(), lr=3e-3)
+    trainer = DataParallelTrainer(model, opt, zero_stage=0, group=mpu.get_data_parallel_group(),
+                                  after_backward=model.allreduce_sequence_parallel_grads)
+    torch.manual_seed(100 + dp_rank)    # same data inside a tensor-parallel group
+    tok = torch.randint(0, cfg.vocab_size, (2, 16))
+    losses = [trainer.step(tok, tok).item() for _ in range(12)]
+    assert losses[-1] < losses[0] - 0.2, losses
+    assert abs(losses[0] - math.log(cfg.vocab_size)) < 0.5
+    # the loss is a property of the tensor-parallel group, replicated parameters stay replicas
+    t = torch.tensor(losses)
+    ref = t.clone()
+    dist.broadcast(ref, src=mpu.get_tensor_model_parallel_src_rank(), group=mpu.get_tensor_model_parallel_group())
+    assert torch.allclose(t, ref, atol=1e-5)
+    flat = torch.cat([p.detach().float().reshape(-1) for p in model.replicated_parameters()])
+    ref = flat.clone()
+    dist.broadcast(ref, src=0)
+    assert torch.allclose(flat, ref, atol=1e-6)
+    mpu.destroy_model_parallel()
+
+
+def test_parallel_gpt_tp2_sequence_parallel():
+    run_workers(_parallel_gpt, world=2, backend='gloo', args=(2, ))
+
+
+def test_parallel_gpt_tp2_dp2():
+    run_workers(_parallel_gpt, world=4, backend='gloo', args=(2, ))
+
+
+def _vocab_parallel_xent(rank, world):
+    from msamp.megatron import parallel_state as mpu
+    from msamp.models import vocab_parallel_cross_entropy
+    mpu.initialize_model_parallel(tensor_model_parallel_size=world)
+    torch.manual_seed(3)
+    full = torch.randn(24, 40)
+    labels = torch.randint(0, 40, (24, ))
+    ref_in = full.clone().requires_grad_()
+    ref = torch.nn.functional.cross_entropy(ref_in, labels)
+    ref.backward()
+    v = 40 // world
+    mine = full[:, rank * v:(rank + 1) * v].clone().requires_grad_()
+    loss = vocab_parallel_cross_entropy(mine, labels, rank * v)
+    loss.backward()
+    assert torch.allclose(loss, ref, atol=1e-5)
+    assert torch.allclose(mine.grad, ref_in.grad[:, rank * v:(rank + 1) * v], atol=1e-6)
+    mpu.destroy_model_parallel()
+
+
+def test_vocab_parallel_cross_entropy_matches_torch():
+    run_workers(_vocab_parallel_xent, world=2, backend='gloo')
