@@ -118,8 +118,13 @@ class _FP8GemmFunction(torch.autograd.Function):
         record = TypeCast._prepare_scale(dy, og_meta, sync=False)
         amax_out = og_meta.amax[0] if record else None
         sinv_out = og_meta.scale_inv if record else None
+        dbias = None
         if need_wgrad:
-            dy8, dy8t = _k.cast_transpose_fp8(dy, E5M2, og_meta.scale, amax_out, scale_inv_out=sinv_out)
+            # the bias gradient (column sums of dy) comes out of the same pass over dy
+            colsum = torch.zeros(dy.shape[1], dtype=torch.float32, device=dy.device) if (ctx.has_bias and dy.dim() == 2) else None
+            dy8, dy8t = _k.cast_transpose_fp8(dy, E5M2, og_meta.scale, amax_out, scale_inv_out=sinv_out, colsum_out=colsum)
+            if colsum is not None:
+                dbias = colsum.to(ctx.bias_dtype)
         else:
             dy8, dy8t = _k.cast_to_fp8(dy, E5M2, og_meta.scale, amax_out, scale_inv_out=sinv_out), None
         dy_sinv = og_meta.scale_inv
@@ -127,8 +132,7 @@ class _FP8GemmFunction(torch.autograd.Function):
         dx = None
         if ctx.input_requires_grad:
             dx = _g.gemm_fp8(dy8, E5M2, dy_sinv, ctx.w8t, E4M3, ctx.w_sinv, ctx.out_dtype)
-        dbias = None
-        if ctx.has_bias:
+        if ctx.has_bias and dbias is None:
             dbias = dy.sum(0, dtype=torch.float32).to(ctx.bias_dtype)
 
         wgrad_ret = None

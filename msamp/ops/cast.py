@@ -122,8 +122,11 @@ def cast_to_fp8(x, qtype, scale, amax_out=None, scale_inv_out=None, amax_in=None
     return res
 
 
-def cast_transpose_fp8(x, qtype, scale, amax_out=None, need_rowmajor=True, scale_inv_out=None, amax_in=None):
+def cast_transpose_fp8(x, qtype, scale, amax_out=None, need_rowmajor=True, scale_inv_out=None, amax_in=None, colsum_out=None):
     """Quantise a 2-D tensor and also produce its transpose. Returns ``(out or None, out_t)``.
+
+    ``colsum_out`` (fp32 ``[cols]``, zero on entry) receives the column sums of ``x`` from the same pass - the bias
+    gradient when ``x`` is the output gradient of a linear layer.
 
     With ``amax_in`` the input is a *scaled* tensor ``x * s_old``: ``scale`` must hold ``1 / s_old`` and ``amax_in``
     ``max|x|``; the kernel derives ``s_new`` from the amax, multiplies by ``s_new / s_old`` and writes ``1 / s_new`` to
@@ -135,12 +138,22 @@ def cast_transpose_fp8(x, qtype, scale, amax_out=None, need_rowmajor=True, scale
         x = x.contiguous()
         out = torch.empty((rows, cols), dtype=torch.uint8, device=x.device) if need_rowmajor else None
         out_t = torch.empty((cols, rows), dtype=torch.uint8, device=x.device)
-        native.check(
-            native.lib().msamp_cast_transpose_fp8(
-                native.ptr(x), rows, cols, native.dt(x.dtype), native.ptr(out), native.ptr(out_t), native.fmt(qtype),
-                native.ptr(scale), native.ptr(amax_out), native.ptr(scale_inv_out), native.ptr(amax_in), native.stream()
-            ), 'cast_transpose_fp8'
-        )
+        if colsum_out is None:
+            native.check(
+                native.lib().msamp_cast_transpose_fp8(
+                    native.ptr(x), rows, cols, native.dt(x.dtype), native.ptr(out), native.ptr(out_t), native.fmt(qtype),
+                    native.ptr(scale), native.ptr(amax_out), native.ptr(scale_inv_out), native.ptr(amax_in), native.stream()
+                ), 'cast_transpose_fp8'
+            )
+        else:
+            assert colsum_out.dtype == torch.float32 and colsum_out.numel() == cols and colsum_out.is_contiguous()
+            native.check(
+                native.lib().msamp_cast_transpose_fp8_colsum(
+                    native.ptr(x), rows, cols, native.dt(x.dtype), native.ptr(out), native.ptr(out_t), native.fmt(qtype),
+                    native.ptr(scale), native.ptr(amax_out), native.ptr(scale_inv_out), native.ptr(amax_in), native.ptr(colsum_out),
+                    native.stream()
+                ), 'cast_transpose_fp8_colsum'
+            )
         return out, out_t
     if amax_in is not None:
         new_scale = compute_scale(amax_in, torch.ones_like(scale), Floating.qfp_max[qtype])
@@ -151,6 +164,8 @@ def cast_transpose_fp8(x, qtype, scale, amax_out=None, need_rowmajor=True, scale
         torch.reciprocal(scale, out=scale_inv_out)
     if amax_out is not None:
         amax(x, out=amax_out)
+    if colsum_out is not None:
+        colsum_out.add_(x.sum(0, dtype=torch.float32))
     out = _emulate_to_fp8(x, scale, qtype)
     return (out if need_rowmajor else None), out.t().contiguous()
 

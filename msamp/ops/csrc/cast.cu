@@ -155,9 +155,10 @@ __global__ void __launch_bounds__(kThreads) cast_transpose_kernel(const T* __res
                                                                    uint8_t* __restrict__ out_t, int rows, int cols,
                                                                    const float* __restrict__ scale_ptr, float* amax,
                                                                    float* scale_inv_out, const float* __restrict__ amax_in,
-                                                                   float fp_max, bool aligned) {
+                                                                   float fp_max, bool aligned, float* __restrict__ colsum) {
   __shared__ __align__(16) uint8_t tile_t[kTileC * kCtStride];    // [c][r]
   __shared__ float red[32];
+  __shared__ float colred[kThreads / 32][kTileC];    // per-warp column sums of the tile (only with colsum)
   float scale = *scale_ptr;
   float logical_scale = scale;
   if (amax_in != nullptr) {
@@ -181,6 +182,7 @@ __global__ void __launch_bounds__(kThreads) cast_transpose_kernel(const T* __res
       // 4 x 8 bytes in registers, so the shared tile is written with 32-bit stores.
       const int rg = threadIdx.x >> 3, cc = (threadIdx.x & 7) * 8;
       uint32_t w[4][2];
+      float cs[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         const int r = rg * 4 + i;
@@ -197,6 +199,8 @@ __global__ void __launch_bounds__(kThreads) cast_transpose_kernel(const T* __res
         for (int j = 0; j < 8; j += 2) {
           float a0 = to_f32<T>(e[j]), a1 = to_f32<T>(e[j + 1]);
           m = fmaxf(m, fmaxf(abs_nan_to_inf(a0), abs_nan_to_inf(a1)));
+          cs[j] += a0;
+          cs[j + 1] += a1;
           q[j / 2] = f32x2_to_fp8x2<FMT>(a0 * scale, a1 * scale);
         }
         w[i][0] = (uint32_t)q[0] | ((uint32_t)q[1] << 16);
@@ -219,7 +223,25 @@ __global__ void __launch_bounds__(kThreads) cast_transpose_kernel(const T* __res
         base[(cc + 4 * h + 2) * (kCtStride / 4) + rg] = __byte_perm(c, d, 0x5410);
         base[(cc + 4 * h + 3) * (kCtStride / 4) + rg] = __byte_perm(c, d, 0x7632);
       }
+      if (colsum != nullptr) {
+        // lanes l, l+8, l+16, l+24 hold the same eight columns for different rows
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          cs[j] += __shfl_xor_sync(0xffffffffu, cs[j], 8);
+          cs[j] += __shfl_xor_sync(0xffffffffu, cs[j], 16);
+        }
+        if ((threadIdx.x & 31) < 8) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) colred[threadIdx.x >> 5][cc + j] = cs[j];
+        }
+      }
       __syncthreads();
+      if (colsum != nullptr && threadIdx.x < kTileC) {
+        float acc = 0.0f;
+#pragma unroll
+        for (int wv = 0; wv < kThreads / 32; ++wv) acc += colred[wv][threadIdx.x];
+        atomicAdd(colsum + c0 + threadIdx.x, acc);
+      }
       {
         // 4 threads cover one transposed row of 128 bytes (32 each)
         const int c = threadIdx.x >> 2, rr = (threadIdx.x & 3) * 32;
@@ -241,6 +263,7 @@ __global__ void __launch_bounds__(kThreads) cast_transpose_kernel(const T* __res
         if (r0 + r < rows && c0 + c < cols) {
           float a = to_f32<T>(x[(int64_t)(r0 + r) * cols + c0 + c]);
           m = fmaxf(m, abs_nan_to_inf(a));
+          if (colsum != nullptr) atomicAdd(colsum + c0 + c, a);
           q = f32_to_fp8<FMT>(a * scale);
           if (WRITE_ROWMAJOR) out[(int64_t)(r0 + r) * cols + c0 + c] = q;
         }
@@ -399,9 +422,10 @@ MSAMP_API int msamp_cast_from_fp8(const void* in, int64_t n, int fmt, const floa
 // x is [rows, cols] row-major. out (may be null) is the row-major FP8 copy, out_t the [cols, rows] one.
 // With amax_in non-null the input is a scaled tensor (x * s_old): `scale` must then point to
 // 1 / s_old, amax_in to max|x|, and the effective factor becomes rule(amax) / s_old.
-MSAMP_API int msamp_cast_transpose_fp8(const void* x, int rows, int cols, int dtype, void* out, void* out_t, int fmt,
-                                       const float* scale, float* amax, float* scale_inv_out, const float* amax_in, void* stream_) {
-  cudaStream_t stream = (cudaStream_t)stream_;
+// colsum (may be null): fp32 [cols]; the column sums of x are ADDED to it (the bias gradient of a
+// linear layer when x is the output gradient), so the caller zeroes it first.
+static int cast_transpose_impl(const void* x, int rows, int cols, int dtype, void* out, void* out_t, int fmt, const float* scale,
+                               float* amax, float* scale_inv_out, const float* amax_in, float* colsum, cudaStream_t stream) {
   MSAMP_REQUIRE(rows >= 0 && cols >= 0 && out_t != nullptr && scale != nullptr, "msamp_cast_transpose_fp8: bad arguments");
   if (amax) cudaMemsetAsync(amax, 0, sizeof(float), stream);
   if ((int64_t)rows * cols == 0) return MSAMP_OK;
@@ -412,12 +436,23 @@ MSAMP_API int msamp_cast_transpose_fp8(const void* x, int rows, int cols, int dt
   MSAMP_DISPATCH_HP(dtype, T, {
     MSAMP_DISPATCH_FP8(fmt, F, {
       if (out)
-        cast_transpose_kernel<T, F, true><<<grid, kThreads, 0, stream>>>((const T*)x, (uint8_t*)out, (uint8_t*)out_t, rows, cols, scale, amax, scale_inv_out, amax_in, fp8_max(F), aligned);
+        cast_transpose_kernel<T, F, true><<<grid, kThreads, 0, stream>>>((const T*)x, (uint8_t*)out, (uint8_t*)out_t, rows, cols, scale, amax, scale_inv_out, amax_in, fp8_max(F), aligned, colsum);
       else
-        cast_transpose_kernel<T, F, false><<<grid, kThreads, 0, stream>>>((const T*)x, nullptr, (uint8_t*)out_t, rows, cols, scale, amax, scale_inv_out, amax_in, fp8_max(F), aligned);
+        cast_transpose_kernel<T, F, false><<<grid, kThreads, 0, stream>>>((const T*)x, nullptr, (uint8_t*)out_t, rows, cols, scale, amax, scale_inv_out, amax_in, fp8_max(F), aligned, colsum);
     });
   });
   return msamp_check_launch("msamp_cast_transpose_fp8");
+}
+
+MSAMP_API int msamp_cast_transpose_fp8(const void* x, int rows, int cols, int dtype, void* out, void* out_t, int fmt,
+                                       const float* scale, float* amax, float* scale_inv_out, const float* amax_in, void* stream_) {
+  return cast_transpose_impl(x, rows, cols, dtype, out, out_t, fmt, scale, amax, scale_inv_out, amax_in, nullptr, (cudaStream_t)stream_);
+}
+
+MSAMP_API int msamp_cast_transpose_fp8_colsum(const void* x, int rows, int cols, int dtype, void* out, void* out_t, int fmt,
+                                              const float* scale, float* amax, float* scale_inv_out, const float* amax_in,
+                                              float* colsum, void* stream_) {
+  return cast_transpose_impl(x, rows, cols, dtype, out, out_t, fmt, scale, amax, scale_inv_out, amax_in, colsum, (cudaStream_t)stream_);
 }
 
 MSAMP_API int msamp_transpose_fp8(const void* in, int rows, int cols, void* out, void* stream_) {

@@ -78,8 +78,14 @@ def check(status, what=''):
         raise NativeError(f'{what}: {_ERRORS.get(status, status)} ({detail})')
 
 
+_raw_stream = getattr(torch._C, '_cuda_getCurrentRawStream', None)
+_raw_device = getattr(torch._C, '_cuda_getDevice', None)
+
+
 def stream():
-    """Raw handle of torch's current CUDA stream."""
+    """Raw handle of torch's current CUDA stream (called once per launch, so it avoids the Python stream objects)."""
+    if _raw_stream is not None and _raw_device is not None:
+        return ctypes.c_void_p(_raw_stream(_raw_device()))
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 

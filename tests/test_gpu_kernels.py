@@ -62,6 +62,12 @@ def test_cast_transpose(shape):
         assert am.item() == x.float().abs().max().item()
         _, ot2 = cast.cast_transpose_fp8(x, E5, s, need_rowmajor=False)
         assert torch.equal(ot2.cpu(), cast.cast_to_fp8(x.cpu(), E5, s.cpu()).t().contiguous())
+        # column sums from the same pass (added to the buffer)
+        cs = torch.ones(shape[1], device=DEV)
+        o3, ot3 = cast.cast_transpose_fp8(x, E4, s, am, colsum_out=cs)
+        assert torch.equal(o3, o) and torch.equal(ot3, ot)
+        want = 1.0 + x.double().sum(0)
+        assert (cs.double() - want).abs().max().item() <= 1e-4 * max(1.0, x.float().abs().sum(0).max().item())
 
 
 def test_in_time_scale_and_windows():
