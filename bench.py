@@ -40,6 +40,7 @@ def parse():
     ap.add_argument('--no-e2e', action='store_true')
     ap.add_argument('--fill-history', action='store_true',
                     help='run untimed steps until the 16-step amax histories are full, so that the timed steps use delayed scaling')
+    ap.add_argument('--full-shard', action='store_true', help='ZeRO-3 / FSDP full shard (default for gpt-30b on more than one GPU)')
     ap.add_argument('--tp', type=int, default=0,
                     help='tensor-parallel size with sequence parallelism (0 = 4 for gpt-13b when the world allows it, else 1)')
     return ap.parse_args()
@@ -142,6 +143,7 @@ def main():
         over['n_layer'] = args.layers
     cfg = gpt_config(args.model, **over)
     tp = args.tp or (min(4, world) if args.model == 'gpt-13b' else 1)
+    full_shard = False
     dp = world // tp
     torch.manual_seed(1234)
     if tp > 1:
@@ -157,6 +159,27 @@ def main():
         trainer = DataParallelTrainer(model, opt, zero_stage=2 if dp > 1 else 0, group=mpu.get_data_parallel_group(),
                                       after_backward=model.allreduce_sequence_parallel_grads)
         data_rank = mpu.get_data_parallel_rank()
+    elif args.full_shard or (args.model == 'gpt-30b' and world > 1):
+        # ZeRO-3 / FSDP full shard: FP8 weight shards, scaled-fp16 master shards and low-bit Adam states are split over
+        # all ranks; the forward parameter all-gather runs inside the consuming FP8 GEMM (O3-style storage).
+        from msamp.fsdp import FP8FullyShardedDataParallel
+        full_shard = True
+        torch.set_default_dtype(torch.bfloat16)    # the unsharded model exists only during conversion: keep it at 2 bytes
+        model = GPT(cfg, device=dev)
+        torch.set_default_dtype(torch.float32)
+        fsdp = FP8FullyShardedDataParallel(model)
+        opt = fsdp.build_optimizer(torch.optim.AdamW, lr=1e-4, betas=(0.9, 0.95), weight_decay=0.1)
+        torch.cuda.empty_cache()
+
+        class _FullShardTrainer:
+            def step(self, tok, lab):
+                loss = fsdp(tok, lab)
+                loss.backward()
+                fsdp.step(opt)
+                return loss.detach()
+
+        trainer = _FullShardTrainer()
+        data_rank = rank
     else:
         model = GPT(cfg, device=dev)
         opt = torch.optim.AdamW(model.parameters(), lr=1e-4, betas=(0.9, 0.95), weight_decay=0.1)
@@ -237,7 +260,7 @@ def main():
         reduced = bool(args.layers)
         flops = cfg.flops_per_token(S) * value
         out = {
-            'metric': f'tokens/sec {args.model} MS-AMP {args.opt_level} training' + (' (REDUCED layer count, not the headline config)' if reduced else ''),
+            'metric': f'tokens/sec {args.model} MS-AMP {"O3" if full_shard else args.opt_level} training' + (' (REDUCED layer count, not the headline config)' if reduced else ''),
             'value': value, 'unit': 'tokens/s', 'n_gpus': world, 'steps': args.steps, 'warmup': args.warmup,
             'ms_per_step': ms / args.steps, 'higher_is_better': True, 'scaling': 'weak',
             'vs_baseline': (value / (base * world)) if (base and not reduced) else None,
@@ -246,7 +269,8 @@ def main():
             'config': {
                 'model': args.model, 'layers': cfg.n_layer, 'hidden': cfg.hidden, 'heads': cfg.n_head, 'ffn': cfg.ffn_hidden,
                 'vocab': cfg.vocab_size, 'global_batch': B * dp, 'micro_batch': B, 'seq_len': S,
-                'parallelism': (f'tp{tp}+sp x ' if tp > 1 else '') + f'dp{dp}' + ('+zero2' if dp > 1 else ''), 'opt_level': args.opt_level,
+                'parallelism': (f'tp{tp}+sp x ' if tp > 1 else '') + f'dp{dp}' + (('+zero3 full shard' if full_shard else '+zero2') if dp > 1 else ''),
+                'opt_level': 'O3 (FP8 weight shards, fp16 master shards, FP8/fp16 Adam states)' if full_shard else args.opt_level,
                 'untimed_steps_before_warmup': fill, 'scaling_regime': 'delayed (amax history full)' if fill + args.warmup >= 16 else 'in-time (first 16 steps of a run)',
                 'l2': 'per-step working set (GBs of weights and activations) is far larger than the 126 MB L2, no explicit flush',
             },

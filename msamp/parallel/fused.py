@@ -134,7 +134,7 @@ class FusedGemmContext:
             M, N = other.shape[0], rows * W
         if out is None:
             out = torch.empty((M, N), dtype=out_dtype, device=shard.device)
-        tile = 128 if shard_is == 'a' else (256 if N >= 256 else 128)
+        tile = 128 if shard_is == 'a' else (256 if (N >= 256 and rows % 256 == 0) else 128)
         if not self.native or rows % tile or K % 16:
             full = all_gather_rows(shard, self.group)
             if shard_is == 'a':
