@@ -43,7 +43,7 @@ class _ShardedLinearFn(torch.autograd.Function):
         x_sinv = in_meta.scale_inv.clone()
         w8, w_sinv = module.weight_shard, module.weight_meta.scale_inv
         rows, K = w8.shape
-        fused = fs.ctx if (fs.ctx is not None and fs.ctx.native and rows % 128 == 0) else None
+        fused = fs.ctx if (fs.ctx is not None and fs.ctx.native and rows % 256 == 0) else None
         if fused is not None:
             view = fused.shard_view(rows * K).view(rows, K)
             view.copy_(w8)

@@ -69,6 +69,12 @@ MSAMP_API unsigned int msamp_read_device_status() {
   return v;
 }
 
+// Same word without clearing it: a plain host read of mapped memory, cheap enough to call before every launch.
+MSAMP_API unsigned int msamp_peek_device_status() {
+  unsigned int* p = msamp_device_status_ptr();
+  return p ? *(volatile unsigned int*)p : 0u;
+}
+
 MSAMP_API int msamp_device_sm_count() { return msamp_sm_count(); }
 
 MSAMP_API int msamp_version() { return 100; }

@@ -98,6 +98,12 @@ def i64(v):
     return ctypes.c_int64(int(v))
 
 
+def peek_device_status():
+    """The device-side error word without clearing it (no synchronisation: the word lives in mapped host memory)."""
+    fn = getattr(lib(), 'msamp_peek_device_status', None)
+    return int(fn()) if fn is not None else 0
+
+
 def device_status():
     """Read and clear the device-side error word (non-zero after a bounded wait gave up)."""
     return lib().msamp_read_device_status()

@@ -116,6 +116,12 @@ class FusedGemmContext:
         return d
 
     def _launch(self, d, what):
+        # A wait that gave up in an earlier kernel (a peer is late or gone) would make every later kernel of the
+        # step wait for its full limit as well: stop at the first one instead.
+        bits = native.peek_device_status()
+        if bits:
+            raise native.NativeError(f'{what}: an earlier device-side wait gave up (status bits {bits:#x}); '
+                                     'read native.device_status() to clear the word after handling the failure')
         native.check(native.lib().msamp_gemm_fused(ctypes.byref(d), native.stream()), what)
 
     # ------------------------------------------------------------------ all-gather(rows) + GEMM
@@ -134,7 +140,7 @@ class FusedGemmContext:
             M, N = other.shape[0], rows * W
         if out is None:
             out = torch.empty((M, N), dtype=out_dtype, device=shard.device)
-        tile = 128 if shard_is == 'a' else (256 if (N >= 256 and rows % 256 == 0) else 128)
+        tile = 128 if shard_is == 'a' else (256 if N >= 256 else 128)
         if not self.native or rows % tile or K % 16:
             full = all_gather_rows(shard, self.group)
             if shard_is == 'a':
