@@ -30,24 +30,32 @@ def main():
     ap.add_argument('--lr', type=float, default=3e-4)
     ap.add_argument('--clip', type=float, default=1.0)
     ap.add_argument('--metrics', default=None, help='JSONL file for per-step metrics')
+    ap.add_argument('--cpu', action='store_true', help='run the bit-exact CPU emulation (gloo for more than one rank)')
     args = ap.parse_args()
     world = int(os.environ.get('WORLD_SIZE', '1'))
     local = int(os.environ.get('LOCAL_RANK', '0'))
-    torch.cuda.set_device(local)
-    dev = torch.device('cuda', local)
+    if args.cpu:
+        dev = torch.device('cpu')
+    else:
+        torch.cuda.set_device(local)
+        dev = torch.device('cuda', local)
     if world > 1:
         os.environ.setdefault('MASTER_ADDR', '127.0.0.1')
-        dist.init_process_group('nccl', device_id=dev)
+        if args.cpu:
+            dist.init_process_group('gloo')
+        else:
+            dist.init_process_group('nccl', device_id=dev)
     rank = dist.get_rank() if world > 1 else 0
     cfg = gpt_config(args.model, max_seq=args.seq)
-    model = GPT(cfg, device=dev)
+    model = GPT(cfg, device=dev, act_dtype=torch.float32 if args.cpu else torch.bfloat16)
     opt = torch.optim.AdamW(model.parameters(), lr=args.lr, betas=(0.9, 0.95), weight_decay=0.1)
     model, opt = msamp.initialize(model, opt, args.opt_level)
     trainer = DataParallelTrainer(model, opt, zero_stage=args.zero_stage if world > 1 else 0, clip_grad=args.clip)
     metrics = StepMetrics(args.metrics, rank)
     g = torch.Generator().manual_seed(rank)
     for step in range(args.steps):
-        tok = torch.randint(0, cfg.vocab_size, (args.micro_batch, args.seq), generator=g).pin_memory().to(dev, non_blocking=True)
+        tok = torch.randint(0, cfg.vocab_size, (args.micro_batch, args.seq), generator=g)
+        tok = tok if args.cpu else tok.pin_memory().to(dev, non_blocking=True)
         loss = trainer.step(tok, tok.roll(-1, 1))
         if step % 5 == 0:
             rec = metrics.log(step, tokens=args.micro_batch * args.seq * world * 5, loss=loss.item())
