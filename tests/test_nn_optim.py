@@ -301,3 +301,26 @@ def test_training_loss_decreases(level):
     assert losses[-1] < 0.8 * losses[0]
     if level == 'O3':
         assert model[0].weight.qtype == E4
+
+
+def test_vit_trains_under_o2_on_cpu():
+    import msamp
+    from msamp.models import ViT, vit_config
+    from msamp.nn import FP8Linear
+    torch.manual_seed(0)
+    cfg = vit_config('vit-tiny-test')
+    model = ViT(cfg, act_dtype=torch.float32)
+    opt = torch.optim.AdamW(model.parameters(), lr=2e-3)
+    model, opt = msamp.initialize(model, opt, 'O2')
+    assert isinstance(model.patch_embed, FP8Linear) and isinstance(model.blocks[0].qkv, FP8Linear)
+    images = torch.randn(16, 3, 32, 32)
+    labels = torch.randint(0, 10, (16, ))
+    assert model(images).shape == (16, 10)
+    losses = []
+    for _ in range(25):
+        opt.zero_grad()
+        loss = model(images, labels)
+        loss.backward()
+        opt.step()
+        losses.append(loss.item())
+    assert losses[-1] < 0.6 * losses[0], losses
