@@ -47,6 +47,8 @@ def initialize(args=None, model=None, optimizer=None, model_parameters=None, tra
         os.environ.setdefault('MASTER_ADDR', '127.0.0.1')
         os.environ.setdefault('MASTER_PORT', '29500')
         torch.distributed.init_process_group('nccl' if torch.cuda.is_available() else 'gloo')
+    if mpu is None and isinstance(model, PipelineModule):
+        mpu = model    # batch arithmetic counts data-parallel replicas, not pipeline stages
     cfg = MSAMPDeepSpeedConfig(config, mpu)
     cls = MSAMPPipelineEngine if isinstance(model, PipelineModule) else MSAMPDeepSpeedEngine
     engine = cls(args=args, model=model, optimizer=optimizer, model_parameters=model_parameters, training_data=training_data,

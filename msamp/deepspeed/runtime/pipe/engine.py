@@ -1,4 +1,4 @@
-"""Pipeline parallelism: stage partitioning and a GPipe-style schedule over NCCL/gloo point-to-point.
+"""Pipeline parallelism: stage partitioning and the 1F1B schedule over NCCL/gloo point-to-point.
 
 Activations and their gradients travel between adjacent stages in high precision with
 ``torch.distributed`` send/recv (the reference inherits exactly this from DeepSpeed and adds only the
@@ -65,59 +65,126 @@ class PipelineModule(torch.nn.Module):
 
 
 class MSAMPPipelineEngine(MSAMPDeepSpeedEngine):
-    """``train_batch(data_iter)`` runs all micro-batches forward, then backward in reverse order, then one optimizer step."""
+    """``train_batch(data_iter)`` runs the micro-batches of one step through the stages with the 1F1B schedule
+    (warm-up forwards, then one forward and one backward alternately, then the remaining backwards), so a stage
+    holds at most ``num_stages - stage_id`` activations, and ends with one optimizer step.
+
+    Transfers between neighbours are posted as batched ``isend`` / ``irecv`` pairs (a send and a receive in
+    opposite directions are always in one batch, which is what NCCL needs to make progress).  The shape of the
+    activation is announced once, with the first tensor a stage sends; gradients have the shape of what was sent.
+    """
     def __init__(self, *args, model=None, **kwargs):
         kwargs['mpu'] = kwargs.get('mpu') or model
         super().__init__(*args, model=model, **kwargs)
         self.__dict__['pipe'] = model    # the PipelineModule (also reachable as self.module); kept out of the submodule registry
+        self._in_shape = None       # shape of the activation received from the previous stage
+        self._meta_sent = False
 
-    def _send(self, t, dst):
-        meta = torch.tensor([t.dim()] + list(t.shape) + [0] * (7 - t.dim()), dtype=torch.int64, device=t.device if t.is_cuda else 'cpu')
-        dist.send(meta, dst)
-        dist.send(t.contiguous(), dst)
+    # ------------------------------------------------------------------ point-to-point helpers
+    def _announce(self, t, dst):
+        if not self._meta_sent:
+            meta = torch.tensor([t.dim()] + list(t.shape) + [0] * (7 - t.dim()), dtype=torch.int64, device=t.device if t.is_cuda else 'cpu')
+            dist.send(meta, dst)
+            self._meta_sent = True
 
-    def _recv(self, src, dtype, device):
-        meta = torch.zeros(8, dtype=torch.int64, device=device if device.type == 'cuda' else 'cpu')
-        dist.recv(meta, src)
-        shape = [int(v) for v in meta[1:1 + int(meta[0])]]
-        t = torch.empty(shape, dtype=dtype, device=device)
-        dist.recv(t, src)
-        return t
+    def _learn_shape(self, src, device):
+        if self._in_shape is None:
+            meta = torch.zeros(8, dtype=torch.int64, device=device if device.type == 'cuda' else 'cpu')
+            dist.recv(meta, src)
+            self._in_shape = [int(v) for v in meta[1:1 + int(meta[0])]]
+
+    @staticmethod
+    def _exchange(send=None, dst=None, recv=None, src=None):
+        """Post the given send and / or receive together and wait for both."""
+        ops = []
+        if send is not None:
+            ops.append(dist.P2POp(dist.isend, send.contiguous(), dst))
+        if recv is not None:
+            ops.append(dist.P2POp(dist.irecv, recv, src))
+        if ops:
+            for req in dist.batch_isend_irecv(ops):
+                req.wait()
+        return recv
 
     def train_batch(self, data_iter=None):
         pipe = self.pipe if isinstance(self.pipe, PipelineModule) else self.module
         ga = self.gradient_accumulation_steps()
         device = next(p for p in self.module.parameters() if torch.is_tensor(p)).device
         act_dtype = getattr(self, 'activation_dtype', torch.float32)
-        inputs, outputs, losses = [], [], []
-        for _ in range(ga):
-            batch = next(data_iter) if (pipe.is_first_stage or pipe.is_last_stage) and data_iter is not None else None
-            if pipe.is_first_stage:
-                x = batch[0].to(device)
-            else:
-                x = self._recv(pipe.prev_rank, act_dtype, device).requires_grad_()
+        first, last = pipe.is_first_stage, pipe.is_last_stage
+        warmup = min(pipe.num_stages - pipe.stage_id - 1, ga)
+        steady = ga - warmup
+        pending = []    # (input, output) of micro-batches whose backward has not run yet, oldest first
+        losses = []
+
+        def next_input(batch):
+            if first:
+                return batch[0].to(device)
+            self._learn_shape(pipe.prev_rank, device)
+            return torch.empty(self._in_shape, dtype=act_dtype, device=device)
+
+        def forward(x, batch):
+            if not first:
+                x.requires_grad_()
             y = self.module(x)
-            inputs.append(x)
-            if pipe.is_last_stage:
-                loss = pipe.loss_fn(y, batch[1].to(device)) / ga
-                losses.append(loss)
-                outputs.append(loss)
-            else:
-                self._send(y.detach(), pipe.next_rank)
-                outputs.append(y)
-        for i in reversed(range(ga)):
-            if pipe.is_last_stage:
+            if last:
+                y = pipe.loss_fn(y, batch[1].to(device)) / ga
+                losses.append(y.detach())
+            pending.append((x, y))
+            return y
+
+        def backward(grad):
+            x, y = pending.pop(0)
+            if last:
                 scale = self.optimizer.cur_scale if hasattr(self.optimizer, 'cur_scale') else 1.0
-                (outputs[i].float() * scale).backward()
+                (y.float() * scale).backward()
             else:
-                g = self._recv(pipe.next_rank, outputs[i].dtype, device)
-                outputs[i].backward(g)
-            if not pipe.is_first_stage:
-                self._send(inputs[i].grad, pipe.prev_rank)
+                y.backward(grad)
+            return None if first else x.grad
+
+        def fetch():
+            return next(data_iter) if (first or last) and data_iter is not None else None
+
+        # warm-up: forwards only
+        for _ in range(warmup):
+            batch = fetch()
+            x = next_input(batch)
+            if not first:
+                self._exchange(recv=x, src=pipe.prev_rank)
+            y = forward(x, batch)
+            if not last:
+                self._announce(y, pipe.next_rank)
+                self._exchange(send=y.detach(), dst=pipe.next_rank)
+        # steady state: one forward, one backward
+        batch = x = None
+        if steady > 0:
+            batch = fetch()
+            x = next_input(batch)
+            if not first:
+                self._exchange(recv=x, src=pipe.prev_rank)
+        for i in range(steady):
+            y = forward(x, batch)
+            grad = None
+            if not last:
+                self._announce(y, pipe.next_rank)
+                grad = torch.empty_like(y)
+                self._exchange(send=y.detach(), dst=pipe.next_rank, recv=grad, src=pipe.next_rank)
+            dx = backward(grad)
+            more = i + 1 < steady
+            if more:
+                batch = fetch()
+                x = next_input(batch)
+            if not first:
+                self._exchange(send=dx, dst=pipe.prev_rank, recv=x if more else None, src=pipe.prev_rank)
+        # cool-down: the remaining backwards
+        for _ in range(warmup):
+            grad = None
+            if not last:
+                grad = torch.empty_like(pending[0][1])
+                self._exchange(recv=grad, src=pipe.next_rank)
+            dx = backward(grad)
+            if not first:
+                self._exchange(send=dx, dst=pipe.prev_rank)
         self.micro_steps += ga - 1
         self.step()
-        total = torch.stack([l.detach().float() for l in losses]).sum() if losses else torch.zeros((), device=device)
-        if dist.is_initialized() and dist.get_world_size() > 1:
-            last = (pipe.num_stages - 1) * pipe.dp_size
-            dist.broadcast(total, src=last + (dist.get_rank() % pipe.dp_size) if pipe.dp_size > 1 else last) if pipe.dp_size == 1 else None
-        return total
+        return torch.stack([l.float() for l in losses]).sum() if losses else torch.zeros((), device=device)

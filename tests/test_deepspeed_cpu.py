@@ -117,3 +117,53 @@ def _pipeline(rank, world):
 
 def test_pipeline_engine_two_stages():
     run_workers(_pipeline, 2)
+
+
+def _pipeline_1f1b(rank, world, enabled):
+    """Four stages, six micro-batches: warm-up, steady and cool-down phases all occur; the result matches one process."""
+    from msamp.deepspeed import PipelineModule
+    torch.manual_seed(0)
+    dims = [16, 32, 32, 32, 32, 32, 32, 32, 4]
+    layers = []
+    for i in range(8):
+        layers.append(torch.nn.Sequential(torch.nn.Linear(dims[i], dims[i + 1]), torch.nn.Tanh()) if i < 7 else torch.nn.Linear(dims[i], dims[i + 1]))
+    ref = torch.nn.Sequential(*[__import__('copy').deepcopy(l) for l in layers])
+    loss_fn = lambda out, y: ((out - y)**2).mean()    # noqa: E731
+    pipe = PipelineModule(layers, num_stages=4, loss_fn=loss_fn)
+    cfg = {'train_batch_size': 24, 'train_micro_batch_size_per_gpu': 4, 'optimizer': {'type': 'AdamW', 'params': {'lr': 1e-2}},
+           'msamp': {'enabled': enabled, 'opt_level': 'O2'}}
+    engine, _, _, _ = deepspeed.initialize(model=pipe, config=cfg)
+    assert engine.gradient_accumulation_steps() == 6
+    g = torch.Generator().manual_seed(1)
+    x, y = torch.randn(24, 16, generator=g), torch.randn(24, 4, generator=g)
+
+    def batches():
+        while True:
+            for i in range(6):
+                yield x[4 * i:4 * i + 4], y[4 * i:4 * i + 4]
+
+    it = batches()
+    losses = [engine.train_batch(it).item() for _ in range(8)]
+    if pipe.is_last_stage:
+        assert losses[-1] < losses[0], losses
+        if not enabled:
+            opt = torch.optim.AdamW(ref.parameters(), lr=1e-2)
+            want = []
+            for _ in range(8):
+                opt.zero_grad()
+                total = 0.0
+                for i in range(6):
+                    lo = loss_fn(ref(x[4 * i:4 * i + 4]), y[4 * i:4 * i + 4]) / 6
+                    lo.backward()
+                    total += lo.item()
+                opt.step()
+                want.append(total)
+            assert max(abs(a - b) for a, b in zip(losses, want)) < 1e-4, (losses, want)
+
+
+def test_pipeline_1f1b_four_stages_fp8():
+    run_workers(_pipeline_1f1b, 4, args=(True, ))
+
+
+def test_pipeline_1f1b_matches_single_process():
+    run_workers(_pipeline_1f1b, 4, args=(False, ))
