@@ -17,8 +17,12 @@ class DataParallelTrainer:
     are quantised), so they are summed as FP8 numbers and averaged by dividing ``scale_inv``;
     high-precision gradients are averaged in flat buckets.
     """
-    def __init__(self, model, optimizer, zero_stage=0, group=None, clip_grad=0.0, bucket_elems=64 * 1024 * 1024, after_backward=None):
+    def __init__(self, model, optimizer, zero_stage=0, group=None, clip_grad=0.0, bucket_elems=64 * 1024 * 1024, after_backward=None,
+                 heartbeat=None):
         self.model = model
+        # msamp.utils.Heartbeat (optional): checked before every step, so a rank that went silent between steps raises
+        # RankFailure on the others before they enter a collective or a fused kernel that would wait for it
+        self.heartbeat = heartbeat
         # called after backward and before any gradient is reduced (e.g. ParallelGPT.allreduce_sequence_parallel_grads)
         self.after_backward = after_backward
         self.optimizer = optimizer
@@ -55,6 +59,8 @@ class DataParallelTrainer:
                 off += n
 
     def step(self, *inputs):
+        if self.heartbeat is not None:
+            self.heartbeat.check()
         self.optimizer.zero_grad(set_to_none=True)
         loss = self.model(*inputs)
         loss.backward()

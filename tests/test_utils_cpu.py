@@ -103,3 +103,42 @@ def _leaving_rank(rank, world):
 
 def test_rank_leaving_between_steps_is_seen_on_the_host():
     run_workers(_leaving_rank, world=2, backend='gloo')
+
+
+def _trainer_stops_before_collective(rank, world):
+    """Rank 1 stops after three steps; rank 0's trainer raises RankFailure instead of entering the next all-reduce."""
+    import msamp
+    from msamp.parallel import DataParallelTrainer
+    store = dist.distributed_c10d._get_default_store()
+    hb = Heartbeat(store, rank, world, interval=0.05, timeout=0.4).start()
+    torch.manual_seed(0)
+    model = torch.nn.Sequential(torch.nn.Linear(16, 16), torch.nn.GELU(), torch.nn.Linear(16, 16))
+    model, opt = msamp.initialize(model, torch.optim.AdamW(model.parameters(), lr=1e-3), 'O2')
+
+    class _Loss(torch.nn.Module):
+        def __init__(self, m):
+            super().__init__()
+            self.m = m
+
+        def forward(self, x, y):
+            return ((self.m(x) - y)**2).mean()
+
+    trainer = DataParallelTrainer(_Loss(model), opt, heartbeat=hb)
+    x, y = torch.randn(8, 16), torch.randn(8, 16)
+    for _ in range(3):
+        trainer.step(x, y)
+    if rank == 1:
+        hb.stop()
+        time.sleep(2.5)
+        return
+    deadline = time.time() + 5.0    # staleness counts from the last change this rank observed
+    while time.time() < deadline and not hb.stale_ranks():
+        time.sleep(0.05)
+    assert hb.stale_ranks() == [1]
+    with pytest.raises(RankFailure):
+        trainer.step(x, y)
+    hb.stop()
+
+
+def test_trainer_checks_heartbeat_before_each_step():
+    run_workers(_trainer_stops_before_collective, world=2, backend='gloo')
