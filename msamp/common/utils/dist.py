@@ -1,5 +1,4 @@
 """Helpers that behave sensibly with and without an initialised process group."""
-import torch
 import torch.distributed as dist
 
 

@@ -24,7 +24,7 @@ import torch
 import torch.distributed as dist
 
 from msamp.common.dtype import Dtypes
-from msamp.common.tensor import ScalingMeta, ScalingTensor, TypeCast
+from msamp.common.tensor import ScalingMeta, TypeCast
 from msamp.megatron import parallel_state as mpu
 from msamp.nn.functional import weight_fp8_pair
 from msamp.nn.module import ScalingModule

@@ -19,8 +19,8 @@ import torch
 import torch.distributed as dist
 import torch.nn.functional as F
 
-from msamp.common.dtype import Dtypes, Floating
-from msamp.common.tensor import ScalingMeta, ScalingTensor, TypeCast
+from msamp.common.dtype import Dtypes
+from msamp.common.tensor import ScalingTensor, TypeCast
 from msamp.common.utils.dist import DistUtil
 from msamp.nn.state import model_state
 from msamp.nn.parameter import ScalingParameter
