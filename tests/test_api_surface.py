@@ -125,3 +125,17 @@ def test_integrations_are_importable():
     from msamp.common.utils import DistUtil, TransformerEngineWrapper, logger    # noqa: F401
     from msamp.models import GPT, ParallelGPT, gpt_config    # noqa: F401
     assert gpt_config('gpt-7b').n_layer == 32 and gpt_config('gpt-13b').hidden == 5120 and gpt_config('gpt-30b').n_head == 56
+
+
+def test_bench_reference_arm_prints_one_json_line():
+    import json
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    res = subprocess.run([sys.executable, os.path.join(root, 'bench.py'), '--impl', 'reference'], capture_output=True, text=True, timeout=300)
+    assert res.returncode == 0, res.stderr[-2000:]
+    lines = [ln for ln in res.stdout.splitlines() if ln.strip()]
+    assert len(lines) == 1
+    out = json.loads(lines[0])
+    assert out['impl'] == 'reference' and ('unavailable' in out or 'value' in out)
