@@ -34,4 +34,8 @@ class FsdpReplacer:
                 new_param._grad_meta = param._scaling_metas['wgrad']
                 sub._parameters.pop(name, None)
                 sub.register_parameter(name, new_param)
+                # torch FSDP (use_orig_params) puts a plain view of its flat parameter in place of the parameter
+                # while forward and backward run; the module re-attaches these attributes to that view
+                stash = sub.__dict__.setdefault('_fp8_param_attrs', {})
+                stash[name] = {k: getattr(new_param, k) for k in ('_original_shape', '_padded', '_meta', '_scaling_metas', '_grad_meta')}
         return model

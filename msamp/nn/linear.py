@@ -53,7 +53,13 @@ class FP8Linear(ScalingModule):
         return self
 
     def forward(self, input):
-        return F.linear(input, self.weight, bias=self.bias)
+        weight = self.weight
+        attrs = self.__dict__.get('_fp8_param_attrs')
+        if attrs is not None and isinstance(weight, torch.Tensor) and not hasattr(weight, '_meta'):
+            # a view of an FSDP flat parameter standing in for the fp32-viewed FP8 weight (msamp.fsdp.FsdpReplacer)
+            for key, value in attrs['weight'].items():
+                setattr(weight, key, value)
+        return F.linear(input, weight, bias=self.bias)
 
     def extra_repr(self):
         return f'in_features={self.in_features}, out_features={self.out_features}, bias={self.bias is not None}'

@@ -219,3 +219,39 @@ def _full_shard(rank, world):
 
 def test_full_shard_gloo():
     run_workers(_full_shard, 2)
+
+
+def _torch_fsdp_fp8(rank, world):
+    """FP8 weights inside torch's own FSDP (public hooks only): bytes are sharded, gradients reduced as FP8."""
+    from msamp.fsdp.torch_fsdp import wrap_with_torch_fsdp
+    from msamp.nn import model_state
+    from msamp.optim import FSDPAdamW
+    model_state.clear()
+    torch.manual_seed(0)
+    model = _mk_model()
+    fsdp = wrap_with_torch_fsdp(model, device_id=torch.device('cpu'))
+    params = list(fsdp.parameters())
+    assert sum(hasattr(p, '_meta') for p in params) == 3    # the three linear weights carry FP8 bytes
+    opt = FSDPAdamW(params, lr=1e-2, weight_decay=0.0)
+    torch.manual_seed(5)
+    x_all, y_all = torch.randn(8 * world, 16), torch.randn(8 * world, 4)
+    losses = []
+    for _ in range(12):
+        xb, yb = x_all[rank * 8:(rank + 1) * 8], y_all[rank * 8:(rank + 1) * 8]
+        loss = ((fsdp(xb) - yb)**2).mean()
+        loss.backward()
+        opt.step()
+        opt.zero_grad(set_to_none=True)
+        losses.append(loss.item())
+    assert losses[-1] < 0.9 * losses[0], losses
+    # all shards of one weight share a scale
+    for p in params:
+        if hasattr(p, '_meta'):
+            s = p._meta.scale.clone()
+            ref = s.clone()
+            dist.broadcast(ref, src=0)
+            assert torch.equal(s, ref)
+
+
+def test_torch_fsdp_with_fp8_weights_gloo():
+    run_workers(_torch_fsdp_fp8, 2)
