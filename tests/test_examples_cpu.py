@@ -38,3 +38,8 @@ def test_gpt_pretrain_tiny():
 def test_mnist_two_ranks(script):
     out = _run([script, '--cpu', '--batches', '6'], nproc=2)
     assert 'loss' in out
+
+
+def test_mnist_torch_fsdp_two_ranks():
+    out = _run(['examples/mnist_fsdp.py', '--cpu', '--torch-fsdp', '--batches', '6'], nproc=2)
+    assert 'loss' in out
