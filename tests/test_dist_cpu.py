@@ -32,6 +32,20 @@ def _fp8_collectives(rank, world):
     DistOp.reduce(t, E4M3, dst=1)
     want = torch.tensor([2.0, 4.0, -1.0, 0.0]) if rank == 1 else torch.tensor([1.0, 2.0, -0.5, 0.0])
     assert torch.equal(t.view(torch.float8_e4m3fn).float(), want)
+    # hand-computed e4m3 bit patterns (the golden vectors of the reference's tests/operators/test_dist.py:112-136, 150-185)
+    pats = [torch.tensor([0b01001010, 0b01011000], dtype=torch.uint8), torch.tensor([0b01010000, 0b01011100], dtype=torch.uint8)]
+    t = pats[rank].clone()
+    DistOp.all_reduce(t, E4M3, dist.ReduceOp.SUM)
+    assert t.tolist() == [0b01010101, 0b01100010]
+    t = pats[rank].clone()
+    DistOp.all_reduce(t, E4M3, dist.ReduceOp.MAX)
+    assert t.tolist() == [0b01010000, 0b01011100]
+    t = pats[rank].clone()
+    DistOp.all_reduce(t, E4M3, dist.ReduceOp.MIN)
+    assert t.tolist() == [0b01001010, 0b01011000]
+    t = pats[rank].clone()
+    DistOp.reduce(t, E4M3, dst=1, op=dist.ReduceOp.SUM)
+    assert t.tolist() == ([0b01010101, 0b01100010] if rank == 1 else pats[rank].tolist())
     # saturation instead of overflow
     big = torch.full((4, ), 448.0).to(torch.float8_e4m3fn).view(torch.uint8)
     DistOp.all_reduce(big, E4M3, dist.ReduceOp.SUM)
