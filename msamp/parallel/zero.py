@@ -346,3 +346,55 @@ class ZeroShardedOptimizer:
             self.masters[i].copy_(saved.to(device=self.device))
         if self.sharded:
             self._publish_weights()
+
+    # ------------------------------------------------------------------ elastic checkpoint (any data-parallel degree)
+    def elastic_state_dict(self):
+        """State of this rank keyed by *global* tensor index, for resuming at another data-parallel degree.
+
+        ``{'fp8': {i: {'master', 'state'}}, 'hp': {k: state}, 'param_groups': [...]}``: ``i`` indexes the model's FP8
+        parameters in ``model.parameters()`` order, ``k`` the remaining parameters (their states are replicated, so
+        any one rank's copy serves).  ``consolidate_elastic_state`` merges the dictionaries of all ranks.
+        The reference cannot change the degree on resume (msamp/deepspeed/runtime/zero/fp8_stage_1_and_2.py:1007-1017).
+        """
+        fp8 = {}
+        for i, master in getattr(self, 'masters', {}).items():
+            fp8[i] = {'master': master.detach(), 'state': dict(self.optimizer.state.get(master, {}))}
+        hp = {k: dict(self.optimizer.state.get(p, {})) for k, p in enumerate(self.hp_params) if p in self.optimizer.state}
+        groups = [{k: v for k, v in g.items() if k != 'params'} for g in self.optimizer.param_groups]
+        return {'fp8': fp8, 'hp': hp, 'param_groups': groups, 'num_fp8': self.n, 'partition_count': self.world}
+
+    @staticmethod
+    def consolidate_elastic_state(states):
+        """Merge the ``elastic_state_dict`` of every rank of the saving job into one dictionary."""
+        out = {'fp8': {}, 'hp': {}, 'param_groups': states[0]['param_groups'], 'num_fp8': states[0]['num_fp8'], 'partition_count': 0}
+        for sd in states:
+            out['fp8'].update(sd['fp8'])
+            for k, st in sd['hp'].items():
+                out['hp'].setdefault(k, st)
+        missing = [i for i in range(out['num_fp8']) if i not in out['fp8']]
+        if missing:
+            raise ValueError(f'elastic state is incomplete: no owner state for FP8 tensors {missing}')
+        return out
+
+    def load_elastic_state_dict(self, full):
+        """Take from a consolidated elastic state what this rank owns under the *current* partition."""
+        if not self.sharded:
+            raise RuntimeError('elastic states belong to sharded optimizers (stage >= 1)')
+        if full['num_fp8'] != self.n:
+            raise ValueError(f"the state holds {full['num_fp8']} FP8 tensors, the model has {self.n}")
+
+        def to_dev(v):
+            return v.to(self.device) if hasattr(v, 'to') else v
+
+        for i, master in self.masters.items():
+            entry = full['fp8'][i]
+            master.copy_(to_dev(entry['master']))
+            if entry['state']:
+                self.optimizer.state[master] = {k: to_dev(v) for k, v in entry['state'].items()}
+        for k, p in enumerate(self.hp_params):
+            if k in full['hp'] and full['hp'][k]:
+                self.optimizer.state[p] = {key: to_dev(v) for key, v in full['hp'][k].items()}
+        for g, saved in zip(self.optimizer.param_groups, full['param_groups']):
+            g.update(saved)
+        self._publish_weights()
+

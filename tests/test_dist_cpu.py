@@ -269,3 +269,60 @@ def _torch_fsdp_fp8(rank, world):
 
 def test_torch_fsdp_with_fp8_weights_gloo():
     run_workers(_torch_fsdp_fp8, 2)
+
+
+def _elastic_save(rank, world, path):
+    torch.manual_seed(0)
+    x_all, y_all = torch.randn(8 * world, 16), torch.randn(8 * world, 4)
+    model = _mk_model()
+    opt = torch.optim.AdamW(model.parameters(), lr=1e-2)
+    model, opt = msamp.initialize(model, opt, 'O2')
+    zero = ZeroShardedOptimizer(model, opt, stage=2)
+    for _ in range(5):
+        loss = ((model(x_all[rank * 8:(rank + 1) * 8]) - y_all[rank * 8:(rank + 1) * 8])**2).mean()
+        loss.backward()
+        zero.reduce_and_step()
+        for p in zero.hp_params:
+            p.grad = None
+    states = [None] * world
+    dist.all_gather_object(states, zero.elastic_state_dict())
+    if rank == 0:
+        full = ZeroShardedOptimizer.consolidate_elastic_state(states)
+        weights = [p.float() for p in zero.fp8_params]
+        hp = [p.detach().clone() for p in zero.hp_params]
+        torch.save({'opt': full, 'weights': weights, 'hp': hp}, path)
+
+
+def _elastic_load(rank, world, path):
+    ck = torch.load(path, weights_only=False)
+    torch.manual_seed(123)    # a differently initialised model: everything must come from the checkpoint
+    model = torch.nn.Sequential(torch.nn.Linear(16, 32), torch.nn.GELU(), torch.nn.Linear(32, 32), torch.nn.GELU(), torch.nn.Linear(32, 4))
+    opt = torch.optim.AdamW(model.parameters(), lr=1e-2)
+    model, opt = msamp.initialize(model, opt, 'O2')
+    zero = ZeroShardedOptimizer(model, opt, stage=2)
+    with torch.no_grad():
+        for p, saved in zip(zero.hp_params, ck['hp']):
+            p.copy_(saved)
+    zero.load_elastic_state_dict(ck['opt'])
+    for p, want in zip(zero.fp8_params, ck['weights']):
+        assert (p.float() - want).abs().max().item() <= 1e-6 + 0.07 * want.abs().max().item() / 8    # same e4m3 numbers
+    for i, master in zero.masters.items():
+        st = zero.optimizer.state[master]
+        assert st['step'] == 5 and torch.equal(st['exp_avg'].value, ck['opt']['fp8'][i]['state']['exp_avg'].value)
+    owned = sum(1 for o in zero.owners if o == rank)
+    assert len(zero.masters) == owned
+    # training goes on
+    torch.manual_seed(0)
+    x, y = torch.randn(8, 16), torch.randn(8, 4)
+    loss = ((model(x) - y)**2).mean()
+    loss.backward()
+    zero.reduce_and_step()
+    assert torch.isfinite(loss)
+    assert all(zero.optimizer.state[m]['step'] == 6 for m in zero.masters.values())
+
+
+def test_elastic_resume_at_another_degree(tmp_path):
+    path = str(tmp_path / 'elastic.pt')
+    run_workers(_elastic_save, 2, args=(path, ))
+    run_workers(_elastic_load, 3, args=(path, ))
+    run_workers(_elastic_load, 1, args=(path, ))
