@@ -40,6 +40,7 @@ def parse():
     ap.add_argument('--no-e2e', action='store_true')
     ap.add_argument('--fill-history', action='store_true',
                     help='run untimed steps until the 16-step amax histories are full, so that the timed steps use delayed scaling')
+    ap.add_argument('--accum', type=int, default=1, help='micro-batches per optimizer step (gradient accumulation); global batch = micro-batch x accum x DP')
     ap.add_argument('--full-shard', action='store_true', help='ZeRO-3 / FSDP full shard (default for gpt-30b on more than one GPU)')
     ap.add_argument('--tp', type=int, default=0,
                     help='tensor-parallel size with sequence parallelism (0 = 4 for gpt-13b when the world allows it, else 1)')
@@ -217,15 +218,26 @@ def main():
             dist.all_reduce(ms, op=dist.ReduceOp.MAX)
         return ms.item(), native.launch_count - calls0
 
+    accum = max(1, args.accum)
+    if accum > 1 and not hasattr(trainer, 'step_micro_batches'):
+        raise SystemExit('--accum is not available for this configuration')
+
     def step_device(i):
-        trainer.step(dev_tok[i % 4], dev_lab[i % 4])
+        if accum == 1:
+            trainer.step(dev_tok[i % 4], dev_lab[i % 4])
+        else:
+            trainer.step_micro_batches([(dev_tok[(i + k) % 4], dev_lab[(i + k) % 4]) for k in range(accum)])
 
     last_loss = [0.0]
 
     def step_e2e(i):
-        tok = host_tok[i % 4].to(dev, non_blocking=True)
-        lab = host_lab[i % 4].to(dev, non_blocking=True)
-        loss = trainer.step(tok, lab)
+        if accum == 1:
+            tok = host_tok[i % 4].to(dev, non_blocking=True)
+            lab = host_lab[i % 4].to(dev, non_blocking=True)
+            loss = trainer.step(tok, lab)
+        else:
+            mbs = [(host_tok[(i + k) % 4].to(dev, non_blocking=True), host_lab[(i + k) % 4].to(dev, non_blocking=True)) for k in range(accum)]
+            loss = trainer.step_micro_batches(mbs)
         last_loss[0] = loss.item()    # device -> host read of the step's result
 
     # The FP8 casts of activations and output gradients derive their scale from the tensor itself ("in-time", one
@@ -241,7 +253,7 @@ def main():
     sampler.start()
     ms, launches = timed(step_device, args.steps)
     clocks = sampler.stop()
-    tokens = B * S * dp * args.steps
+    tokens = B * S * dp * accum * args.steps
     host_enqueue_ms = host_ms[0]
     value = tokens / (ms / 1e3)
 
@@ -250,7 +262,7 @@ def main():
         step_e2e(0)
         ms2, _ = timed(step_e2e, args.steps)
         e2e = {
-            'value': tokens / (ms2 / 1e3), 'unit': 'tokens/s', 'h2d_bytes_per_step': 2 * B * S * 8, 'd2h_bytes_per_step': 4,
+            'value': tokens / (ms2 / 1e3), 'unit': 'tokens/s', 'h2d_bytes_per_step': 2 * B * S * 8 * accum, 'd2h_bytes_per_step': 4,
             'ms_per_step': ms2 / args.steps, 'last_loss': last_loss[0]
         }
     peak_mem = torch.cuda.max_memory_allocated() / 2**30
@@ -268,7 +280,7 @@ def main():
             'impl': 'ours',
             'config': {
                 'model': args.model, 'layers': cfg.n_layer, 'hidden': cfg.hidden, 'heads': cfg.n_head, 'ffn': cfg.ffn_hidden,
-                'vocab': cfg.vocab_size, 'global_batch': B * dp, 'micro_batch': B, 'seq_len': S,
+                'vocab': cfg.vocab_size, 'global_batch': B * dp * accum, 'micro_batch': B, 'grad_accum': accum, 'seq_len': S,
                 'parallelism': (f'tp{tp}+sp x ' if tp > 1 else '') + f'dp{dp}' + (('+zero3 full shard' if full_shard else '+zero2') if dp > 1 else ''),
                 'opt_level': 'O3 (FP8 weight shards, fp16 master shards, FP8/fp16 Adam states)' if full_shard else args.opt_level,
                 'untimed_steps_before_warmup': fill, 'scaling_regime': 'delayed (amax history full)' if fill + args.warmup >= 16 else 'in-time (first 16 steps of a run)',

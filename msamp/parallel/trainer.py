@@ -59,11 +59,24 @@ class DataParallelTrainer:
                 off += n
 
     def step(self, *inputs):
+        return self.step_micro_batches([inputs])
+
+    def step_micro_batches(self, micro_batches):
+        """One optimizer step over several micro-batches (gradient accumulation): every micro-batch runs forward and
+        backward with its loss divided by their number, FP8 weight gradients accumulate in FP8 with a fresh scale per
+        addition, and the gradient exchange happens once.  Returns the mean loss."""
         if self.heartbeat is not None:
             self.heartbeat.check()
         self.optimizer.zero_grad(set_to_none=True)
-        loss = self.model(*inputs)
-        loss.backward()
+        k = len(micro_batches)
+        total = None
+        for inputs in micro_batches:
+            loss = self.model(*inputs)
+            if k > 1:
+                loss = loss / k
+            loss.backward()
+            total = loss.detach() if total is None else total + loss.detach()
+        loss = total
         if self.after_backward is not None:
             self.after_backward()
         if self.zero is not None:
@@ -74,4 +87,4 @@ class DataParallelTrainer:
                 from msamp.nn import clip_grad_norm_
                 clip_grad_norm_(self.model.parameters(), self.clip_grad)
             self.optimizer.step()
-        return loss.detach()
+        return loss

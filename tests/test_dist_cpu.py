@@ -326,3 +326,39 @@ def test_elastic_resume_at_another_degree(tmp_path):
     run_workers(_elastic_save, 2, args=(path, ))
     run_workers(_elastic_load, 3, args=(path, ))
     run_workers(_elastic_load, 1, args=(path, ))
+
+
+def _accumulation(rank, world, stage):
+    """Two micro-batches in one step track one step on the concatenated batch."""
+    from msamp.parallel import DataParallelTrainer
+
+    class _Loss(torch.nn.Module):
+        def __init__(self, m):
+            super().__init__()
+            self.m = m
+
+        def forward(self, x, y):
+            return ((self.m(x) - y)**2).mean()
+
+    def make():
+        model = _mk_model()
+        opt = torch.optim.AdamW(model.parameters(), lr=1e-2)
+        model, opt = msamp.initialize(model, opt, 'O2')
+        return model, DataParallelTrainer(_Loss(model), opt, zero_stage=stage)
+
+    torch.manual_seed(7)
+    x_all, y_all = torch.randn(16 * world, 16), torch.randn(16 * world, 4)
+    xs, ys = x_all[rank * 16:(rank + 1) * 16], y_all[rank * 16:(rank + 1) * 16]
+    m1, t1 = make()
+    from msamp.nn import model_state
+    l1 = [t1.step(xs, ys).item() for _ in range(6)]
+    model_state.clear()
+    m2, t2 = make()
+    l2 = [t2.step_micro_batches([(xs[:8], ys[:8]), (xs[8:], ys[8:])]).item() for _ in range(6)]
+    assert l2[-1] < l2[0]
+    assert max(abs(a - b) for a, b in zip(l1, l2)) < 0.05 * l1[0], (l1, l2)
+
+
+def test_gradient_accumulation_trainer_ddp_and_zero2():
+    run_workers(_accumulation, 2, args=(0, ))
+    run_workers(_accumulation, 2, args=(2, ))
