@@ -40,6 +40,7 @@ def parse():
     ap.add_argument('--no-e2e', action='store_true')
     ap.add_argument('--fill-history', action='store_true',
                     help='run untimed steps until the 16-step amax histories are full, so that the timed steps use delayed scaling')
+    ap.add_argument('--recompute', action='store_true', help='activation recomputation in the GPT blocks (data-parallel model only)')
     ap.add_argument('--accum', type=int, default=1, help='micro-batches per optimizer step (gradient accumulation); global batch = micro-batch x accum x DP')
     ap.add_argument('--full-shard', action='store_true', help='ZeRO-3 / FSDP full shard (default for gpt-30b on more than one GPU)')
     ap.add_argument('--tp', type=int, default=0,
@@ -142,6 +143,8 @@ def main():
     over = {'max_seq': args.seq}
     if args.layers:
         over['n_layer'] = args.layers
+    if args.recompute:
+        over['recompute'] = True
     cfg = gpt_config(args.model, **over)
     tp = args.tp or (min(4, world) if args.model == 'gpt-13b' else 1)
     full_shard = False
@@ -280,7 +283,7 @@ def main():
             'impl': 'ours',
             'config': {
                 'model': args.model, 'layers': cfg.n_layer, 'hidden': cfg.hidden, 'heads': cfg.n_head, 'ffn': cfg.ffn_hidden,
-                'vocab': cfg.vocab_size, 'global_batch': B * dp * accum, 'micro_batch': B, 'grad_accum': accum, 'seq_len': S,
+                'vocab': cfg.vocab_size, 'global_batch': B * dp * accum, 'micro_batch': B, 'grad_accum': accum, 'recompute': bool(args.recompute), 'seq_len': S,
                 'parallelism': (f'tp{tp}+sp x ' if tp > 1 else '') + f'dp{dp}' + (('+zero3 full shard' if full_shard else '+zero2') if dp > 1 else ''),
                 'opt_level': 'O3 (FP8 weight shards, fp16 master shards, FP8/fp16 Adam states)' if full_shard else args.opt_level,
                 'untimed_steps_before_warmup': fill, 'scaling_regime': 'delayed (amax history full)' if fill + args.warmup >= 16 else 'in-time (first 16 steps of a run)',

@@ -29,6 +29,7 @@ def main():
     ap.add_argument('--lr', type=float, default=3e-4)
     ap.add_argument('--clip', type=float, default=1.0)
     ap.add_argument('--metrics', default=None, help='JSONL file for per-step metrics')
+    ap.add_argument('--recompute', action='store_true', help='re-run block forwards in backward instead of storing activations')
     ap.add_argument('--cpu', action='store_true', help='run the bit-exact CPU emulation (gloo for more than one rank)')
     args = ap.parse_args()
     world = int(os.environ.get('WORLD_SIZE', '1'))
@@ -45,7 +46,7 @@ def main():
         else:
             dist.init_process_group('nccl', device_id=dev)
     rank = dist.get_rank() if world > 1 else 0
-    cfg = gpt_config(args.model, max_seq=args.seq)
+    cfg = gpt_config(args.model, max_seq=args.seq, recompute=args.recompute)
     model = GPT(cfg, device=dev, act_dtype=torch.float32 if args.cpu else torch.bfloat16)
     opt = torch.optim.AdamW(model.parameters(), lr=args.lr, betas=(0.9, 0.95), weight_decay=0.1)
     model, opt = msamp.initialize(model, opt, args.opt_level)

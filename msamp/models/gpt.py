@@ -10,6 +10,7 @@ from dataclasses import dataclass
 
 import torch
 import torch.nn as nn
+import torch.utils.checkpoint
 
 from msamp.ops import nn as K
 
@@ -25,6 +26,7 @@ class GPTConfig:
     eps: float = 1e-5
     init_std: float = 0.02
     tie_embeddings: bool = False
+    recompute: bool = False    # re-run every block's forward during backward instead of keeping its activations
 
     @property
     def head_dim(self):
@@ -124,7 +126,11 @@ class GPT(nn.Module):
         pos = torch.arange(seq, device=tokens.device)
         x = (self.wte(tokens) + self.wpe(pos)).view(batch * seq, -1)
         for blk in self.blocks:
-            x = blk(x, batch, seq)
+            if self.cfg.recompute and torch.is_grad_enabled():
+                # the FP8 casts of the re-run see the same tensors and the same metas, so they repeat bit for bit
+                x = torch.utils.checkpoint.checkpoint(blk, x, batch, seq, use_reentrant=False)
+            else:
+                x = blk(x, batch, seq)
         logits = self.lm_head(self.ln_f(x))
         if labels is None:
             return logits.view(batch, seq, -1)

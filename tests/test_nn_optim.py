@@ -324,3 +324,32 @@ def test_vit_trains_under_o2_on_cpu():
         opt.step()
         losses.append(loss.item())
     assert losses[-1] < 0.6 * losses[0], losses
+
+
+def test_gpt_recompute_matches_stored_activations():
+    import msamp
+    from msamp.models import GPT, gpt_config
+    from msamp.nn import model_state
+
+    def run(recompute):
+        model_state.clear()
+        torch.manual_seed(0)
+        cfg = gpt_config('gpt-tiny', n_layer=2, n_head=2, hidden=64, ffn_hidden=128, vocab_size=128, max_seq=32, recompute=recompute)
+        model = GPT(cfg, act_dtype=torch.float32)
+        opt = torch.optim.AdamW(model.parameters(), lr=1e-3)
+        model, opt = msamp.initialize(model, opt, 'O2')
+        torch.manual_seed(1)
+        tok = torch.randint(0, 128, (2, 32))
+        losses = []
+        for _ in range(3):
+            opt.zero_grad()
+            loss = model(tok, tok)
+            loss.backward()
+            opt.step()
+            losses.append(loss.item())
+        return losses, torch.cat([p.float().reshape(-1) for p in model.parameters()])
+
+    l0, w0 = run(False)
+    l1, w1 = run(True)
+    assert l0 == l1
+    assert torch.equal(w0, w1)
