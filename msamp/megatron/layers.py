@@ -218,6 +218,8 @@ class ColumnParallelLinear(_ParallelLinearBase):
         self.weight = _new_fp8_weight(out_features // tp, in_features, dev, init_std)
         self.weight.tensor_model_parallel = True
         self.bias = torch.nn.Parameter(torch.zeros(out_features // tp, device=dev)) if bias else None
+        if self.bias is not None:
+            self.bias.tensor_model_parallel = True    # a shard, not a replica: counts on every rank in gradient norms
         self._make_metas(dev)
 
     def forward(self, x):

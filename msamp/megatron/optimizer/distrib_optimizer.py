@@ -116,10 +116,11 @@ class FP8DistributedOptimizer:
                 is_tp = getattr(p, 'tensor_model_parallel', False)
                 if dp_rank == 0 and (is_tp or tp_rank == 0):    # replicated params count once
                     grads_for_norm.append(p.grad)
-            group = None
-            if dist.is_initialized() and dist.get_world_size() > 1:
-                group = dist.group.WORLD if mpu.get_model_parallel_group() is None else None
-            grad_norm = clip_grad_norm_fp32(params, grads_for_norm, self.clip_grad, 2, model_parallel_group=group or mpu.get_model_parallel_group())
+            # Every gradient is counted on exactly one rank of the whole job (FP8 gradients on their owner inside the
+            # data-parallel group, replicated ones on data-parallel rank 0 / tensor-parallel rank 0), so the norm is
+            # summed over all ranks: data-parallel replicas must agree on the clip coefficient.
+            group = dist.group.WORLD if dist.is_initialized() and dist.get_world_size() > 1 else None
+            grad_norm = clip_grad_norm_fp32(params, grads_for_norm, self.clip_grad, 2, model_parallel_group=group)
         self.optimizer.step()
         self.gather_model_params(args, timers)
         for m in self.zero.masters.values():

@@ -138,7 +138,10 @@ class ParallelGPT(nn.Module):
         """Sum the partial gradients of the replicated parameters over the tensor-parallel group."""
         if not self.sequence_parallel:
             return
-        grads = [p.grad for p in self.replicated_parameters() if p.grad is not None]
+        # Megatron-style local DDP accumulates into ``main_grad`` and leaves ``grad`` empty
+        grads = [getattr(p, 'main_grad', None) if getattr(p, 'main_grad', None) is not None else p.grad
+                 for p in self.replicated_parameters()]
+        grads = [g for g in grads if g is not None]
         if not grads:
             return
         group = mpu.get_tensor_model_parallel_group()

@@ -18,11 +18,13 @@ class DataParallelTrainer:
     high-precision gradients are averaged in flat buckets.
     """
     def __init__(self, model, optimizer, zero_stage=0, group=None, clip_grad=0.0, bucket_elems=64 * 1024 * 1024, after_backward=None,
-                 heartbeat=None):
+                 heartbeat=None, model_parallel_group=None):
         self.model = model
         # msamp.utils.Heartbeat (optional): checked before every step, so a rank that went silent between steps raises
         # RankFailure on the others before they enter a collective or a fused kernel that would wait for it
         self.heartbeat = heartbeat
+        # tensor / pipeline parallel ranks hold different shards: gradient clipping needs the norm over them too
+        self.model_parallel_group = model_parallel_group
         # called after backward and before any gradient is reduced (e.g. ParallelGPT.allreduce_sequence_parallel_grads)
         self.after_backward = after_backward
         self.optimizer = optimizer
@@ -33,7 +35,7 @@ class DataParallelTrainer:
         self.zero = None
         if zero_stage and self.world > 1:
             from msamp.parallel.zero import ZeroShardedOptimizer
-            self.zero = ZeroShardedOptimizer(model, optimizer, stage=zero_stage, group=group)
+            self.zero = ZeroShardedOptimizer(model, optimizer, stage=zero_stage, group=group, model_parallel_group=model_parallel_group)
 
     def _sync_grads(self):
         if self.world == 1:
@@ -83,7 +85,13 @@ class DataParallelTrainer:
             self.zero.reduce_and_step(clip_grad=self.clip_grad)
         else:
             self._sync_grads()
-            if self.clip_grad > 0:
+            if self.clip_grad > 0 and self.model_parallel_group is not None:
+                from msamp.megatron.optimizer.clip_grads import clip_grad_norm_fp32
+                first = dist.get_rank(self.model_parallel_group) == 0
+                params = [p for p in self.model.parameters() if p.grad is not None]
+                counted = [p.grad for p in params if first or getattr(p, 'tensor_model_parallel', False)]
+                clip_grad_norm_fp32(params, counted, self.clip_grad, 2, model_parallel_group=self.model_parallel_group)
+            elif self.clip_grad > 0:
                 from msamp.nn import clip_grad_norm_
                 clip_grad_norm_(self.model.parameters(), self.clip_grad)
             self.optimizer.step()

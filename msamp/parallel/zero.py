@@ -54,11 +54,12 @@ class ZeroShardedOptimizer:
         stage: 0 = replicated states (FP8 all-reduce), 1 or 2 = sharded master weights and moments.
         group: data-parallel process group.
     """
-    def __init__(self, model, optimizer, stage=2, group=None, wait_seconds=30.0):
+    def __init__(self, model, optimizer, stage=2, group=None, wait_seconds=30.0, model_parallel_group=None):
         self.model, self.optimizer, self.stage, self.group = model, optimizer, stage, group
         self.world = DistUtil.get_world_size(group)
         self.rank = DistUtil.get_rank(group)
         self.wait_seconds = wait_seconds
+        self.model_parallel_group = model_parallel_group    # gradient-norm clipping sums over it as well
         params = [p for p in model.parameters() if isinstance(p, ScalingParameter)]
         self.fp8_params = params
         self.hp_params = [p for p in model.parameters() if not isinstance(p, ScalingParameter)]
@@ -315,9 +316,17 @@ class ZeroShardedOptimizer:
                 sq += _grad_norm(p.grad, 2.0)**2
         if self.sharded and self.world > 1:
             dist.all_reduce(sq, group=self.group)
+        mp_group = getattr(self, 'model_parallel_group', None)
+        mp_rank = dist.get_rank(mp_group) if mp_group is not None else 0
         for p in self.hp_params:
-            if p.grad is not None:
-                sq += _grad_norm(p.grad, 2.0)**2
+            if p.grad is None:
+                continue
+            if mp_group is not None and mp_rank != 0 and not getattr(p, 'tensor_model_parallel', False):
+                continue    # replicated over the model-parallel group: counted on its first rank only
+            sq += _grad_norm(p.grad, 2.0)**2
+        if mp_group is not None and dist.get_world_size(mp_group) > 1:
+            # the model-parallel ranks hold different shards of the model: one norm, one clip coefficient for all
+            dist.all_reduce(sq, group=mp_group)
         total = sq.sqrt()
         coef = torch.clamp(max_norm / (total + 1e-6), max=1.0)
         for p in owned:

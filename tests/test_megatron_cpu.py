@@ -118,8 +118,9 @@ def _parallel_gpt(rank, world, tp):
     model = ParallelGPT(cfg, act_dtype=torch.float32)
     assert model.sequence_parallel == (tp > 1)
     opt = LBAdamW(model.parameters(), lr=3e-3)
-    trainer = DataParallelTrainer(model, opt, zero_stage=0, group=mpu.get_data_parallel_group(),
-                                  after_backward=model.allreduce_sequence_parallel_grads)
+    trainer = DataParallelTrainer(model, opt, zero_stage=2 if world > tp else 0, group=mpu.get_data_parallel_group(),
+                                  after_backward=model.allreduce_sequence_parallel_grads, clip_grad=0.5,
+                                  model_parallel_group=mpu.get_model_parallel_group())
     torch.manual_seed(100 + dp_rank)    # same data inside a tensor-parallel group
     tok = torch.randint(0, cfg.vocab_size, (2, 16))
     losses = [trainer.step(tok, tok).item() for _ in range(12)]
@@ -166,3 +167,38 @@ def _vocab_parallel_xent(rank, world):
 
 def test_vocab_parallel_cross_entropy_matches_torch():
     run_workers(_vocab_parallel_xent, world=2, backend='gloo')
+
+
+def _parallel_gpt_distopt(rank, world, tp):
+    """ParallelGPT under the Megatron-style FP8 DDP buffers + distributed optimizer (TP x DP)."""
+    from msamp.megatron import FP8DistributedDataParallel, FP8DistributedOptimizer, parallel_state as mpu
+    from msamp.models import ParallelGPT, gpt_config
+    from msamp.optim import LBAdamW
+    mpu.initialize_model_parallel(tensor_model_parallel_size=tp)
+    cfg = gpt_config('gpt-tiny', n_layer=2, n_head=4, hidden=64, ffn_hidden=256, vocab_size=128, max_seq=32)
+    torch.manual_seed(0)
+    model = ParallelGPT(cfg, act_dtype=torch.float32)
+    ddp = FP8DistributedDataParallel(model, accumulate_allreduce_grads_in_fp32=True, use_contiguous_buffers=True)
+    opt = FP8DistributedOptimizer(LBAdamW(model.parameters(), lr=3e-3), clip_grad=1.0, models=[ddp])
+    torch.manual_seed(100 + mpu.get_data_parallel_rank())
+    tok = torch.randint(0, cfg.vocab_size, (2, 16))
+    losses = []
+    for _ in range(12):
+        opt.zero_grad()
+        loss = ddp(tok, tok)
+        loss.backward()
+        model.allreduce_sequence_parallel_grads()
+        opt.reduce_model_grads()
+        ok, norm, _ = opt.step()
+        assert ok
+        losses.append(loss.item())
+    assert losses[-1] < losses[0] - 0.2, losses
+    flat = torch.cat([p.detach().float().reshape(-1) for p in model.replicated_parameters()])
+    ref = flat.clone()
+    dist.broadcast(ref, src=0)
+    assert torch.allclose(flat, ref, atol=1e-6)
+    mpu.destroy_model_parallel()
+
+
+def test_parallel_gpt_under_distributed_optimizer_tp2_dp2():
+    run_workers(_parallel_gpt_distopt, world=4, backend='gloo', args=(2, ))
