@@ -71,14 +71,33 @@ class FP8Optimizer:
         """Scale the loss and back-propagate."""
         (loss.float() * self.cur_scale).backward(retain_graph=retain_graph)
 
-    def _unscale_and_clip(self, params):
-        grads = [p.grad for p in params if p.grad is not None]
+    def _unscale_and_clip(self, params, sharded=()):
+        """Unscale and clip the gradients of ``params`` (held by every rank) and of ``sharded`` (each held by one rank
+        of the data-parallel group only: their squared norms are summed over the group so that all ranks clip alike)."""
+        sharded = list(sharded)
+        grads = [p.grad for p in list(params) + sharded if p.grad is not None]
         with self.timers.phase(COMPUTE_NORM):
             from msamp.nn.clip_grad import _grad_norm
-            sq = None
-            for g in grads:
-                n = _grad_norm(g, 2.0)**2
-                sq = n if sq is None else sq + n.to(sq.device)
+
+            def sumsq(ps):
+                acc = None
+                for p in ps:
+                    if p.grad is not None:
+                        n = _grad_norm(p.grad, 2.0)**2
+                        acc = n if acc is None else acc + n.to(acc.device)
+                return acc
+
+            sq = sumsq(params)
+            if self.zero is not None and self.zero.sharded and self.zero.world > 1:
+                part = sumsq(sharded)
+                part = part if part is not None else torch.zeros((), device=self.zero.device)
+                part = part.float().reshape(1).clone()
+                torch.distributed.all_reduce(part, group=self.zero.group)
+                sq = part[0] if sq is None else sq + part[0].to(sq.device)
+            else:
+                part = sumsq(sharded)
+                if part is not None:
+                    sq = part if sq is None else sq + part.to(sq.device)
             total = (sq.sqrt() / self.cur_scale) if sq is not None else torch.zeros(())
         with self.timers.phase(UNSCALE_AND_CLIP):
             combined = self.cur_scale
@@ -114,10 +133,9 @@ class FP8Optimizer:
             if self.zero.sharded:
                 for i, m in self.zero.masters.items():
                     m.grad = self.zero.fp8_params[i].grad
-                upd = list(self.zero.masters.values()) + self.zero.hp_params
+                self._unscale_and_clip(self.zero.hp_params, sharded=list(self.zero.masters.values()))
             else:
-                upd = params
-            self._unscale_and_clip(upd)
+                self._unscale_and_clip(params)
             with self.timers.phase(BASIC_STEP):
                 self.optimizer.step()
             with self.timers.phase(UPDATE_FP16):

@@ -3,6 +3,7 @@ import tempfile
 
 import pytest
 import torch
+import torch.distributed as dist
 
 from msamp import deepspeed
 from msamp.deepspeed.runtime.config import MSAMPDeepSpeedConfig
@@ -167,3 +168,34 @@ def test_pipeline_1f1b_four_stages_fp8():
 
 def test_pipeline_1f1b_matches_single_process():
     run_workers(_pipeline_1f1b, 4, args=(False, ))
+
+
+def _engine_two_ranks(rank, world, level, zero, fp16):
+    """The engine on two ranks: replicas stay identical under clipping (and dynamic loss scaling), loss falls."""
+    extra = {'train_batch_size': 16}
+    if fp16:
+        extra['fp16'] = {'enabled': True, 'initial_scale_power': 8}
+    engine, opt, _, _ = deepspeed.initialize(model=_model(), config=_cfg(level, zero, **extra))
+    assert engine.gradient_accumulation_steps() == 2
+    torch.manual_seed(3)
+    x, y = torch.randn(64, 16), torch.randn(64, 4) * 3    # large targets: clipping at 1.0 is active
+    lo = rank * 32
+    first = last = None
+    for epoch in range(6):
+        for i in range(0, 32, 4):
+            loss = ((engine(x[lo + i:lo + i + 4]) - y[lo + i:lo + i + 4])**2).mean()
+            engine.backward(loss)
+            engine.step()
+        full = ((engine(x) - y)**2).mean().item()
+        first = full if first is None else first
+        last = full
+    assert last < first
+    flat = torch.cat([p.float().reshape(-1) for p in engine.module.parameters()])
+    ref = flat.clone()
+    dist.broadcast(ref, src=0)
+    assert torch.equal(flat, ref), (flat - ref).abs().max()
+
+
+@pytest.mark.parametrize('level,zero,fp16', [('O2', 0, False), ('O2', 1, False), ('O3', 2, False), ('O2', 2, True)])
+def test_engine_two_ranks_replicas_agree(level, zero, fp16):
+    run_workers(_engine_two_ranks, 2, args=(level, zero, fp16))
