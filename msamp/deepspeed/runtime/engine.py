@@ -186,7 +186,7 @@ class MSAMPDeepSpeedEngine(torch.nn.Module):
                 if self._plain:
                     self.allreduce_gradients()
                     if self.config.gradient_clipping > 0:
-                        torch.nn.utils.clip_grad_norm_(self.module.parameters(), self.config.gradient_clipping)
+                        self._clip_plain(self.config.gradient_clipping)
                     self.optimizer.step()
                     self.optimizer.zero_grad(set_to_none=True)
                     skipped = False
@@ -203,6 +203,19 @@ class MSAMPDeepSpeedEngine(torch.nn.Module):
             if self.config.wall_clock_breakdown and self.global_steps % self.config.steps_per_print == 0 and self.global_rank == 0:
                 logger.info(f'step {self.global_steps}: ' + self.timers.log(reset=True))
         self.micro_steps += 1
+
+    def _clip_plain(self, max_norm):
+        """Global-norm clipping without FP8 gradients; the norm is summed over the model-parallel group if there is one."""
+        grads = [p.grad for p in self.module.parameters() if p.grad is not None]
+        if not grads:
+            return
+        sq = torch.stack([g.detach().float().pow(2).sum() for g in grads]).sum().reshape(1)
+        mp_group = self.mpu.get_model_parallel_group() if (self.mpu is not None and hasattr(self.mpu, 'get_model_parallel_group')) else None
+        if mp_group is not None and dist.is_initialized() and dist.get_world_size(mp_group) > 1:
+            dist.all_reduce(sq, group=mp_group)
+        coef = torch.clamp(max_norm / (sq.sqrt()[0] + 1e-6), max=1.0)
+        for g in grads:
+            g.mul_(coef.to(g.dtype))
 
     def train_batch(self, data_iter):
         """Convenience: one full batch (all accumulation steps) from an iterator of ``(inputs, labels)``-like tuples."""

@@ -24,6 +24,7 @@ class FP8Optimizer:
     def __init__(self, model, init_optimizer, static_loss_scale=1.0, dynamic_loss_scale=False, initial_dynamic_scale=2**32,
                  dynamic_loss_args=None, clip_grad=0.0, fp8_master=True, zero_stage=0, group=None, mpu=None, timers=None):
         self.model, self.optimizer, self.clip_grad = model, init_optimizer, clip_grad
+        self.mpu = mpu
         self.timers = timers or PhaseTimers(enabled=False)
         if dynamic_loss_scale:
             args = dict(dynamic_loss_args or {})
@@ -98,6 +99,12 @@ class FP8Optimizer:
                 part = sumsq(sharded)
                 if part is not None:
                     sq = part if sq is None else sq + part.to(sq.device)
+            mp_group = self.mpu.get_model_parallel_group() if (self.mpu is not None and hasattr(self.mpu, 'get_model_parallel_group')) else None
+            if mp_group is not None and torch.distributed.get_world_size(mp_group) > 1:
+                # pipeline stages / tensor-parallel ranks hold different parameters of one model: one global norm
+                part = (sq if sq is not None else torch.zeros(())).float().reshape(1).clone()
+                torch.distributed.all_reduce(part, group=mp_group)
+                sq = part[0]
             total = (sq.sqrt() / self.cur_scale) if sq is not None else torch.zeros(())
         with self.timers.phase(UNSCALE_AND_CLIP):
             combined = self.cur_scale

@@ -37,18 +37,31 @@ class PipelineModule(torch.nn.Module):
         self.prev_rank = rank - self.dp_size if self.stage_id > 0 else None
         self.next_rank = rank + self.dp_size if self.stage_id < num_stages - 1 else None
         self._dp_group = None
+        self._mp_group = None
         if dist.is_initialized() and world > 1:
             for s in range(num_stages):
                 ranks = list(range(s * self.dp_size, (s + 1) * self.dp_size))
                 g = dist.new_group(ranks)
                 if rank in ranks:
                     self._dp_group = g
+            for d in range(self.dp_size):
+                ranks = [s * self.dp_size + d for s in range(num_stages)]    # one replica of the whole model
+                g = dist.new_group(ranks)
+                if rank in ranks:
+                    self._mp_group = g
 
     def get_data_parallel_group(self):
         return self._dp_group
 
     def get_data_parallel_world_size(self):
         return self.dp_size
+
+    def get_model_parallel_group(self):
+        """The stages of this rank's model replica (gradient norms and overflow flags are combined over it)."""
+        return self._mp_group
+
+    def get_pipe_parallel_group(self):
+        return self._mp_group
 
     def forward(self, x):
         for layer in self.layers:

@@ -132,7 +132,7 @@ def _pipeline_1f1b(rank, world, enabled):
     loss_fn = lambda out, y: ((out - y)**2).mean()    # noqa: E731
     pipe = PipelineModule(layers, num_stages=4, loss_fn=loss_fn)
     cfg = {'train_batch_size': 24, 'train_micro_batch_size_per_gpu': 4, 'optimizer': {'type': 'AdamW', 'params': {'lr': 1e-2}},
-           'msamp': {'enabled': enabled, 'opt_level': 'O2'}}
+           'gradient_clipping': 0.3, 'msamp': {'enabled': enabled, 'opt_level': 'O2'}}
     engine, _, _, _ = deepspeed.initialize(model=pipe, config=cfg)
     assert engine.gradient_accumulation_steps() == 6
     g = torch.Generator().manual_seed(1)
@@ -157,6 +157,7 @@ def _pipeline_1f1b(rank, world, enabled):
                     lo = loss_fn(ref(x[4 * i:4 * i + 4]), y[4 * i:4 * i + 4]) / 6
                     lo.backward()
                     total += lo.item()
+                torch.nn.utils.clip_grad_norm_(ref.parameters(), 0.3)    # one norm over the whole model, as the stages must compute it
                 opt.step()
                 want.append(total)
             assert max(abs(a - b) for a, b in zip(losses, want)) < 1e-4, (losses, want)
@@ -199,3 +200,38 @@ def _engine_two_ranks(rank, world, level, zero, fp16):
 @pytest.mark.parametrize('level,zero,fp16', [('O2', 0, False), ('O2', 1, False), ('O3', 2, False), ('O2', 2, True)])
 def test_engine_two_ranks_replicas_agree(level, zero, fp16):
     run_workers(_engine_two_ranks, 2, args=(level, zero, fp16))
+
+
+def _pipeline_with_dp(rank, world):
+    """Two stages x two data-parallel replicas: replicas of a stage stay identical, loss falls."""
+    from msamp.deepspeed import PipelineModule
+    torch.manual_seed(0)
+    layers = [torch.nn.Linear(16, 32), torch.nn.GELU(), torch.nn.Linear(32, 32), torch.nn.GELU(), torch.nn.Linear(32, 4)]
+    pipe = PipelineModule(layers, num_stages=2, loss_fn=lambda out, y: ((out - y)**2).mean())
+    assert pipe.dp_size == 2 and pipe.stage_id == rank // 2
+    cfg = {'train_batch_size': 16, 'train_micro_batch_size_per_gpu': 4, 'optimizer': {'type': 'AdamW', 'params': {'lr': 1e-2}},
+           'gradient_clipping': 1.0, 'msamp': {'enabled': True, 'opt_level': 'O2'}}
+    engine, _, _, _ = deepspeed.initialize(model=pipe, config=cfg)
+    assert engine.gradient_accumulation_steps() == 2
+    g = torch.Generator().manual_seed(1)
+    x, y = torch.randn(16, 16, generator=g), torch.randn(16, 4, generator=g) * 3
+    dp_rank = rank % 2
+
+    def batches():
+        while True:
+            for i in range(2):
+                lo = dp_rank * 8 + 4 * i
+                yield x[lo:lo + 4], y[lo:lo + 4]
+
+    it = batches()
+    losses = [engine.train_batch(it).item() for _ in range(10)]
+    if pipe.is_last_stage:
+        assert losses[-1] < losses[0], losses
+    flat = torch.cat([p.float().reshape(-1) for p in engine.module.parameters()])
+    ref = flat.clone()
+    dist.broadcast(ref, src=dist.get_global_rank(pipe.get_data_parallel_group(), 0), group=pipe.get_data_parallel_group())
+    assert torch.equal(flat, ref), (flat - ref).abs().max()
+
+
+def test_pipeline_two_stages_two_replicas():
+    run_workers(_pipeline_with_dp, 4)
