@@ -220,6 +220,11 @@ def _full_shard(rank, world):
     s2 = s.clone()
     dist.broadcast(s2, src=0)
     assert torch.equal(s, s2)
+    # replicated (high-precision) parameters stay replicas
+    hp = torch.cat([p.detach().float().reshape(-1) for p in fsdp.hp_params])
+    hp2 = hp.clone()
+    dist.broadcast(hp2, src=0)
+    assert torch.equal(hp, hp2)
     # the torch-FSDP preparation path: fp32-viewed parameters carrying their meta
     from msamp.nn import model_state
     model_state.clear()
@@ -362,3 +367,34 @@ def _accumulation(rank, world, stage):
 def test_gradient_accumulation_trainer_ddp_and_zero2():
     run_workers(_accumulation, 2, args=(0, ))
     run_workers(_accumulation, 2, args=(2, ))
+
+
+def _te_layer_zero2(rank, world):
+    """Transformer-Engine-shaped layer under the sharded optimizer: two ranks end with identical weights."""
+    from msamp.parallel import DataParallelTrainer
+    from msamp.te import MSAMPTransformerLayer
+
+    class _Loss(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.layer = MSAMPTransformerLayer(64, 128, 4)
+
+        def forward(self, x, y):
+            return ((self.layer(x) - y)**2).mean()
+
+    torch.manual_seed(0)
+    net = _Loss()
+    net, opt = msamp.initialize(net, None, 'O2', use_te=True)
+    trainer = DataParallelTrainer(net, opt, zero_stage=2, clip_grad=1.0)
+    torch.manual_seed(20 + rank)
+    x, y = torch.randn(8, 4, 64), torch.randn(8, 4, 64)
+    losses = [trainer.step(x, y).item() for _ in range(8)]
+    assert losses[-1] < losses[0]
+    flat = torch.cat([p.float().reshape(-1) for p in net.parameters()])
+    ref = flat.clone()
+    dist.broadcast(ref, src=0)
+    assert torch.equal(flat, ref), (flat - ref).abs().max()
+
+
+def test_te_transformer_layer_under_zero2():
+    run_workers(_te_layer_zero2, 2)

@@ -202,3 +202,46 @@ def _parallel_gpt_distopt(rank, world, tp):
 
 def test_parallel_gpt_under_distributed_optimizer_tp2_dp2():
     run_workers(_parallel_gpt_distopt, world=4, backend='gloo', args=(2, ))
+
+
+def _local_ddp_allreduce(rank, world):
+    """Megatron-style local DDP with the replicated optimizer: allreduce_gradients + clip + LBAdamW keeps replicas equal."""
+    import msamp
+    from msamp.megatron import FP8DistributedDataParallel, clip_grad_norm_fp32, parallel_state as mpu
+    from msamp.optim import LBAdamW
+    mpu.initialize_model_parallel(tensor_model_parallel_size=1)
+    torch.manual_seed(0)
+    model = torch.nn.Sequential(torch.nn.Linear(16, 32), torch.nn.GELU(), torch.nn.Linear(32, 4))
+    model = msamp.nn.LinearReplacer.replace(model)
+    ddp = FP8DistributedDataParallel(model, accumulate_allreduce_grads_in_fp32=True, use_contiguous_buffers=True)
+    opt = LBAdamW(model.parameters(), lr=1e-2)
+    torch.manual_seed(10)
+    x_all, y_all = torch.randn(16 * world, 16), torch.randn(16 * world, 4) * 3
+    first = last = None
+    for it in range(12):
+        ddp.zero_grad_buffer()
+        for micro in range(2):
+            lo = rank * 16 + micro * 8
+            loss = ((ddp(x_all[lo:lo + 8]) - y_all[lo:lo + 8])**2).mean() / 2
+            loss.backward()
+        ddp.allreduce_gradients()
+        params = list(model.parameters())
+        for p in params:
+            p.grad = p.main_grad
+        clip_grad_norm_fp32(params, [p.grad for p in params], 1.0)
+        opt.step()
+        for p in params:
+            p.grad = None
+        full = ((ddp(x_all) - y_all)**2).mean().item()
+        first = full if first is None else first
+        last = full
+    assert last < first
+    flat = torch.cat([p.float().reshape(-1) for p in model.parameters()])
+    ref = flat.clone()
+    dist.broadcast(ref, src=0)
+    assert torch.equal(flat, ref), (flat - ref).abs().max()
+    mpu.destroy_model_parallel()
+
+
+def test_local_ddp_allreduce_keeps_replicas_equal():
+    run_workers(_local_ddp_allreduce, world=2, backend='gloo')
