@@ -235,3 +235,40 @@ def _pipeline_with_dp(rank, world):
 
 def test_pipeline_two_stages_two_replicas():
     run_workers(_pipeline_with_dp, 4)
+
+
+def _resume_two_ranks(rank, world, path, zero):
+    """Save after 3 steps, go on for 2; a fresh engine that loads the checkpoint and does the same 2 steps ends up equal."""
+    from msamp.nn import model_state
+    torch.manual_seed(3)
+    x, y = torch.randn(64, 16), torch.randn(64, 4)
+    lo = rank * 32
+
+    def steps(engine, first, n):
+        for s in range(first, first + n):
+            for i in (0, 4):    # two micro-batches per step
+                j = lo + (8 * s + i) % 32
+                loss = ((engine(x[j:j + 4]) - y[j:j + 4])**2).mean()
+                engine.backward(loss)
+                engine.step()
+
+    cfg = _cfg('O2', zero, train_batch_size=16)
+    engine, _, _, _ = deepspeed.initialize(model=_model(), config=cfg)
+    steps(engine, 0, 3)
+    engine.save_checkpoint(path, tag='s3')
+    steps(engine, 3, 2)
+    want = torch.cat([p.float().reshape(-1) for p in engine.module.parameters()])
+    model_state.clear()
+    torch.manual_seed(99)
+    fresh = torch.nn.Sequential(torch.nn.Linear(16, 32), torch.nn.GELU(), torch.nn.Linear(32, 4))    # other initial values
+    engine2, _, _, _ = deepspeed.initialize(model=fresh, config=cfg)
+    engine2.load_checkpoint(path)
+    assert engine2.global_steps == 3
+    steps(engine2, 3, 2)
+    got = torch.cat([p.float().reshape(-1) for p in engine2.module.parameters()])
+    assert (got - want).abs().max().item() <= 2e-2 * want.abs().max().item(), (got - want).abs().max()
+
+
+@pytest.mark.parametrize('zero', [0, 2])
+def test_engine_resume_two_ranks(tmp_path, zero):
+    run_workers(_resume_two_ranks, 2, args=(str(tmp_path), zero))
