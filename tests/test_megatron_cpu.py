@@ -105,7 +105,7 @@ def test_local_ddp_and_distributed_optimizer():
     run_workers(_ddp_distopt, 2)
 
 
-def _parallel_gpt(rank, world, tp):
+def _parallel_gpt(rank, world, tp, sp=True):
     import msamp
     from msamp.megatron import parallel_state as mpu
     from msamp.models import GPT, ParallelGPT, gpt_config
@@ -115,8 +115,8 @@ def _parallel_gpt(rank, world, tp):
     dp_rank = mpu.get_data_parallel_rank()
     cfg = gpt_config('gpt-tiny', n_layer=2, n_head=4, hidden=64, ffn_hidden=256, vocab_size=128, max_seq=32)
     torch.manual_seed(0)
-    model = ParallelGPT(cfg, act_dtype=torch.float32)
-    assert model.sequence_parallel == (tp > 1)
+    model = ParallelGPT(cfg, act_dtype=torch.float32, sequence_parallel=sp)
+    assert model.sequence_parallel == (sp and tp > 1)
     opt = LBAdamW(model.parameters(), lr=3e-3)
     trainer = DataParallelTrainer(model, opt, zero_stage=2 if world > tp else 0, group=mpu.get_data_parallel_group(),
                                   after_backward=model.allreduce_sequence_parallel_grads, clip_grad=0.5,
@@ -245,3 +245,70 @@ def _local_ddp_allreduce(rank, world):
 
 def test_local_ddp_allreduce_keeps_replicas_equal():
     run_workers(_local_ddp_allreduce, world=2, backend='gloo')
+
+
+def test_parallel_gpt_tp4():
+    run_workers(_parallel_gpt, world=4, backend='gloo', args=(4, ))
+
+
+def test_parallel_gpt_tp2_without_sequence_parallel():
+    run_workers(_parallel_gpt, world=2, backend='gloo', args=(2, False))
+
+
+def _tp_matches_unsharded(rank, world):
+    """The loss and an input-embedding gradient of ParallelGPT at tp=2 (sequence parallel) equal those of the same weights unsharded."""
+    from msamp.common.dtype import Dtypes
+    from msamp.megatron import parallel_state as mpu
+    from msamp.models import ParallelGPT, gpt_config
+    from msamp.nn import model_state
+    cfg = gpt_config('gpt-tiny', n_layer=2, n_head=4, hidden=64, ffn_hidden=256, vocab_size=128, max_seq=32)
+    mpu.initialize_model_parallel(tensor_model_parallel_size=2)
+    tp_group = mpu.get_tensor_model_parallel_group()
+    torch.manual_seed(0)
+    sharded = ParallelGPT(cfg, act_dtype=torch.float32)
+    torch.manual_seed(7)
+    tok = torch.randint(0, cfg.vocab_size, (2, 16))
+    loss_tp = sharded(tok, tok)
+    loss_tp.backward()
+    sharded.allreduce_sequence_parallel_grads()
+    g_tp = sharded.wpe.weight.grad.clone()
+
+    def gather(t, dim):
+        parts = [torch.empty_like(t) for _ in range(2)]
+        dist.all_gather(parts, t.contiguous(), group=tp_group)
+        return parts if dim is None else torch.cat(parts, dim)
+
+    full = {}
+    for name, p in sharded.named_parameters():
+        v = p.float() if hasattr(p, 'meta') else p.detach()
+        if name.endswith('qkv.weight') or name.endswith('qkv.bias'):
+            parts = gather(v, None)    # each [3 * hl * d, ...] laid out (3, hl, d)
+            hl, d = cfg.n_head // 2, cfg.head_dim
+            stacked = torch.stack([q.reshape(3, hl, d, *q.shape[1:]) for q in parts], dim=1)    # [3, tp, hl, d, ...]
+            full[name] = stacked.reshape(3 * cfg.n_head * d, *v.shape[1:])
+        elif any(name.endswith(k) for k in ('fc1.weight', 'fc1.bias', 'lm_head.weight')):
+            full[name] = gather(v, 0)
+        elif any(name.endswith(k) for k in ('proj.weight', 'fc2.weight')):
+            full[name] = gather(v, 1)
+        else:
+            full[name] = v.clone()
+    mpu.destroy_model_parallel()
+    model_state.clear()
+    mpu.initialize_model_parallel(tensor_model_parallel_size=1)
+    whole = ParallelGPT(cfg, act_dtype=torch.float32)
+    with torch.no_grad():
+        for name, p in whole.named_parameters():
+            if hasattr(p, 'meta'):
+                p.copy_(full[name].cast(Dtypes.kfloat16))
+            else:
+                p.copy_(full[name])
+    loss_1 = whole(tok, tok)
+    loss_1.backward()
+    assert abs(loss_tp.item() - loss_1.item()) < 2e-3 * abs(loss_1.item()), (loss_tp.item(), loss_1.item())
+    g_1 = whole.wpe.weight.grad
+    assert (g_tp - g_1).abs().max().item() < 0.05 * g_1.abs().max().item() + 1e-5
+    mpu.destroy_model_parallel()
+
+
+def test_tensor_parallel_gpt_matches_unsharded_weights():
+    run_workers(_tp_matches_unsharded, world=2, backend='gloo')
