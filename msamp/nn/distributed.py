@@ -42,6 +42,7 @@ class _ScalingTensorReducer:
         self.param_to_id = {id(p): i for i, p in enumerate(parameters)}
         self.buffer = None
         self.dist_handles = []
+        self.sync = True    # False while the owning DDP module is inside no_sync()
         self.bucket_unreduced_param_ids = {}
         self.reduction_stream = torch.cuda.Stream(device=self.device) if self.device.type == 'cuda' else None
         self._build_buckets()
@@ -87,7 +88,10 @@ class _ScalingTensorReducer:
                 raise RuntimeError('gradient is already reduced')
             pending.remove(pid)
             if not pending:
-                self._reduce_bucket(bucket)
+                if self.sync:
+                    self._reduce_bucket(bucket)
+                # inside DDP.no_sync() the high-precision gradients stay as they are and keep accumulating; the
+                # backward pass that synchronises quantises and reduces their sum (the reference reduces every time)
                 self.bucket_unreduced_param_ids.pop(bucket)
 
         return hook
@@ -169,6 +173,7 @@ class FP8DistributedDataParallel(_TorchDDP):
 
     def forward(self, *inputs, **kwargs):
         if self.scaling_tensor_reducer is not None and torch.is_grad_enabled():
+            self.scaling_tensor_reducer.sync = bool(getattr(self, 'require_backward_grad_sync', True))
             tensors = [(i, t) for i, t in enumerate(inputs) if torch.is_tensor(t)]
             anchor = self._anchor
             outs = _DDPSink.apply(self.scaling_tensor_reducer, anchor, anchor, *[t for _, t in tensors])
