@@ -24,8 +24,9 @@ def test_mnist_single():
     assert 'loss' in out
 
 
-def test_cifar10_deepspeed_config():
-    out = _run(['examples/cifar10_deepspeed.py', '--steps', '4'])
+@pytest.mark.parametrize('config', ['ds_config_msamp.json', 'ds_config_zero_te_msamp.json'])
+def test_cifar10_deepspeed_config(config):
+    out = _run(['examples/cifar10_deepspeed.py', '--steps', '4', '--deepspeed_config', os.path.join('examples', config)])
     assert 'loss' in out
 
 
