@@ -223,8 +223,33 @@ class FP8FullyShardedDataParallel(torch.nn.Module):
         return cls(self.master_parameters(), exp_avg_dtype=torch.uint8, exp_avg_sq_dtype=torch.float16, **kwargs)
 
     @torch.no_grad()
-    def step(self, optimizer):
-        """Average the replicated gradients, update, re-quantise the shards, clear gradients."""
+    def clip_grad_norm_(self, max_norm):
+        """Global-norm clipping: shard gradients count once over the group, replicated ones once per rank. Call after the
+        replicated gradients were averaged (``step`` does both in the right order when given ``clip_grad``)."""
+        from msamp.nn.clip_grad import _grad_norm
+        dev = self.sharded[0].master.device if self.sharded else self.hp_params[0].device
+        sq = torch.zeros(1, dtype=torch.float32, device=dev)
+        for m in self.sharded:
+            if m.master.grad is not None:
+                sq += _grad_norm(m.master.grad, 2.0)**2
+        if self.world > 1:
+            dist.all_reduce(sq, group=self.group)
+        for p in self.hp_params:
+            if p.grad is not None:
+                sq += _grad_norm(p.grad, 2.0)**2
+        total = sq.sqrt()[0]
+        coef = torch.clamp(max_norm / (total + 1e-6), max=1.0)
+        for m in self.sharded:
+            if m.master.grad is not None:
+                m.master.grad.mul_(coef)
+        for p in self.hp_params:
+            if p.grad is not None:
+                p.grad.mul_(coef.to(p.grad.dtype))
+        return total
+
+    @torch.no_grad()
+    def step(self, optimizer, clip_grad=0.0):
+        """Average the replicated gradients, (clip,) update, re-quantise the shards, clear gradients."""
         if self.world > 1:
             grads = [p.grad for p in self.hp_params if p.grad is not None]
             by_dtype = {}
@@ -238,6 +263,8 @@ class FP8FullyShardedDataParallel(torch.nn.Module):
                 for g in gs:
                     g.copy_(flat[off:off + g.numel()].view_as(g))
                     off += g.numel()
+        if clip_grad > 0:
+            self.clip_grad_norm_(clip_grad)
         optimizer.step()
         for m in self.sharded:
             m.requantize()

@@ -208,7 +208,7 @@ def _full_shard(rank, world):
         xb, yb = x_all[rank * 8:(rank + 1) * 8], y_all[rank * 8:(rank + 1) * 8]
         loss = ((fsdp(xb) - yb)**2).mean()
         loss.backward()
-        fsdp.step(opt)
+        fsdp.step(opt, clip_grad=100.0)    # far above the norm: exercises the code without changing the comparison
         ropt.zero_grad()
         rl = ((ref(x_all) - y_all)**2).mean()
         rl.backward()
