@@ -312,3 +312,25 @@ def _tp_matches_unsharded(rank, world):
 
 def test_tensor_parallel_gpt_matches_unsharded_weights():
     run_workers(_tp_matches_unsharded, world=2, backend='gloo')
+
+
+def test_parallel_gpt_state_dict_roundtrip(tmp_path):
+    """ScalingParameters of the parallel linears survive torch.save / load_state_dict (single rank, tp = 1)."""
+    from msamp.megatron import parallel_state as mpu
+    from msamp.models import ParallelGPT, gpt_config
+    from msamp.nn import model_state
+    mpu.initialize_model_parallel(tensor_model_parallel_size=1)
+    cfg = gpt_config('gpt-tiny', n_layer=1, n_head=2, hidden=32, ffn_hidden=64, vocab_size=64, max_seq=16)
+    torch.manual_seed(0)
+    a = ParallelGPT(cfg, act_dtype=torch.float32)
+    tok = torch.randint(0, 64, (2, 16))
+    want = a(tok, tok).item()
+    path = str(tmp_path / 'pgpt.pt')
+    torch.save(a.state_dict(), path)
+    model_state.clear()
+    torch.manual_seed(5)
+    b = ParallelGPT(cfg, act_dtype=torch.float32)
+    assert abs(b(tok, tok).item() - want) > 1e-4
+    b.load_state_dict(torch.load(path, weights_only=False))
+    assert abs(b(tok, tok).item() - want) < 1e-6
+    mpu.destroy_model_parallel()
