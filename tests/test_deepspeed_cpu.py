@@ -272,3 +272,29 @@ def _resume_two_ranks(rank, world, path, zero):
 @pytest.mark.parametrize('zero', [0, 2])
 def test_engine_resume_two_ranks(tmp_path, zero):
     run_workers(_resume_two_ranks, 2, args=(str(tmp_path), zero))
+
+
+def test_scheduler_dataloader_and_train_batch():
+    data = torch.utils.data.TensorDataset(torch.randn(32, 16), torch.randn(32, 4))
+
+    class WithLoss(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.net = _model()
+
+        def forward(self, x, y):
+            return ((self.net(x) - y)**2).mean()
+
+    cfg = _cfg('O2', 0, scheduler={'type': 'WarmupLR', 'params': {'warmup_min_lr': 0.0, 'warmup_max_lr': 1e-2, 'warmup_num_steps': 4}})
+    engine, opt, loader, sched = deepspeed.initialize(model=WithLoss(), config=cfg, training_data=data)
+    assert loader is not None and loader.batch_size == 4 and sched is not None
+    assert engine.get_lr()[0] == 0.0
+    it = iter(loader)
+    losses = [engine.train_batch(it) for _ in range(4)]    # two micro-batches each
+    assert engine.global_steps == 4 and engine.micro_steps == 8
+    assert abs(engine.get_lr()[0] - 1e-2) < 1e-12 and all(l == l for l in losses)
+    sd = sched.state_dict()
+    sched.load_state_dict(sd)
+    assert sched.get_lr()[0] == engine.get_lr()[0]
+    with pytest.raises(ValueError):
+        deepspeed.initialize(model=WithLoss(), config=_cfg('O2', 0, scheduler={'type': 'OneCycle', 'params': {}}))
