@@ -69,3 +69,39 @@ def test_wrapper_matches_kernels():
     assert TransformerEngineWrapper._to_te_dtype(Dtypes.kfloat8_e5m2) == 'kFloat8E5M2'
     st = torch.randn(4).cast(Dtypes.kfloat16)
     assert cast_if_needed(st, torch.float32) is st and cast_if_needed(torch.ones(2), torch.float16).dtype == torch.float16
+
+
+def test_extension_helpers_with_fake_te_meta():
+    """The TE-facing cast helpers give the same bytes for a plain tensor and for the ScalingTensor holding the same values
+    when both use one scale (the property the reference checks in tests/te/test_extension.py:31-127), against a fake of
+    TE's ``FP8TensorMeta`` (scale / scale_inv / amax_history indexed by tensor slot)."""
+    import types
+
+    from msamp.common.dtype import Dtypes
+    from msamp.te.extension import TeExtensionOverrider, cast_to_fp8, fused_cast_transpose
+    assert TeExtensionOverrider.installed is False    # Transformer Engine is not installed here; the helpers stand alone
+    torch.manual_seed(0)
+    x = torch.randn(16, 32)
+    amax = x.abs().max()
+    scale = torch.tensor(2.0**int(torch.floor(torch.log2(448.0 / amax))))
+    slot = 1
+    meta = types.SimpleNamespace(scale=torch.ones(3), scale_inv=torch.ones(3), amax_history=torch.zeros(4, 3))
+    meta.scale[slot] = scale
+    e4m3 = types.SimpleNamespace(name='kFloat8E4M3')
+    out, out_t = fused_cast_transpose(x, meta, slot, e4m3)
+    assert out.dtype == torch.uint8 and out.shape == (16, 32) and out_t.shape == (32, 16)
+    assert torch.equal(out.t().contiguous(), out_t)
+    assert abs(meta.amax_history[0][slot].item() - amax.item()) < 1e-6 and abs(meta.scale_inv[slot].item() - 1.0 / scale.item()) < 1e-9
+    # the same values as an fp16 ScalingTensor: requantised from its meta, same scale, same bytes
+    st = x.cast(Dtypes.kfloat16)
+    meta2 = types.SimpleNamespace(scale=torch.ones(3), scale_inv=torch.ones(3), amax_history=torch.zeros(4, 3))
+    out2, out2_t = fused_cast_transpose(st, meta2, slot, e4m3)
+    back = out2.view(torch.float8_e4m3fn).float() * meta2.scale_inv[slot]
+    assert (back - x).abs().max().item() <= 0.07 * amax.item()
+    assert torch.equal(out2.reshape(16, 32).t().contiguous(), out2_t)
+    single = cast_to_fp8(x, meta, slot, e4m3)
+    assert torch.equal(single, out)
+    buf = torch.empty(16, 32, dtype=torch.uint8)
+    assert cast_to_fp8(x, meta, slot, e4m3, out=buf) is None and torch.equal(buf, out)
+    e5m2 = types.SimpleNamespace(name='kFloat8E5M2')
+    assert cast_to_fp8(x, meta, slot, e5m2).dtype == torch.uint8
