@@ -1,14 +1,15 @@
 """FP8 linear: autograd function and the ``torch.nn.functional.linear`` override.
 
-Data flow of one linear (shapes: x ``[T,K]``, W ``[N,K]``, y ``[T,N]``), all GEMMs in the one
-K-major layout of the tcgen05 kernel, no FP8 transposes materialised on the way:
+Data flow of one linear (shapes: x ``[T,K]``, W ``[N,K]``, y ``[T,N]``).  The tcgen05 GEMM reads an operand either
+K-major or MN-major, so x, W and dy are quantised once, in the layout they already have, and no FP8
+transpose is ever written:
 
-  forward   x  --cast+transpose(e4m3, meta 'input')-->  x8 [T,K], x8ᵀ [K,T] (x8ᵀ is what backward keeps)
-            W  --cast+transpose(e4m3), cached until the weight changes-->  W8 [N,K], W8ᵀ [K,N]
-            y  = x8 · W8ᵀ  (+ bias in the epilogue)
-  backward  dy --cast+transpose(e5m2, meta 'ograd')-->  dy8 [T,N], dy8ᵀ [N,T]
-            dx = dy8 · (W8ᵀ)ᵀ
-            dW = dy8ᵀ · (x8ᵀ)ᵀ  with max|dW| reduced in the epilogue
+  forward   x  --cast(e4m3, meta 'input')-->  x8 [T,K]   (kept for backward)
+            W  --cast(e4m3), cached until the weight changes-->  W8 [N,K]
+            y  = x8 · W8ᵀ  (+ bias, + residual in the epilogue)
+  backward  dy --cast(e5m2, meta 'ograd'; the bias gradient = column sums of dy falls out of the same pass)--> dy8 [T,N]
+            dx = dy8 · W8           (W8 read as the MN-major B operand)
+            dW = dy8ᵀ · x8          (both read MN-major) with max|dW| reduced in the epilogue
             dW --cast(e4m3, meta 'wgrad', scale from that amax [MAX-reduced over the DP group])--> ScalingTensor
             delivered through ``weight.backward_grad_update`` (not through autograd)
 
@@ -65,6 +66,51 @@ def weight_fp8_pair(weight):
     return w8, w8t, sinv
 
 
+def weight_fp8(weight):
+    """FP8 copy ``(W8 [N,K], scale_inv)`` of a weight in its own layout, cached on the parameter.
+
+    An e4m3 weight is used as it is; a scaled 16-bit weight (``value == w * s_w``) is quantised with the
+    scale implied by the stored amax of ``w``.  The cache key is the identity and in-place version of
+    ``weight.value`` and of its ``scale_inv``, so any optimizer step, ``copy_``, ``cast_`` or checkpoint
+    load invalidates it.
+    """
+    val = weight.value
+    w2d = val.reshape(-1, val.shape[-1])
+    if Dtypes.is_fp8_qtype(weight.meta.qtype):
+        if weight.meta.qtype != E4M3:
+            raise TypeError('FP8 weights must be e4m3')
+        return w2d, weight.meta.scale_inv
+    key = (val.data_ptr(), val._version, weight.meta.scale_inv._version, weight.meta.scale_inv.data_ptr())
+    cache = getattr(weight, '_fp8_cache1', None)
+    if cache is not None and cache[0] == key:
+        return cache[1], cache[2]
+    meta = weight.meta
+    sinv = torch.empty_like(meta.scale_inv)
+    w8 = _k.cast_to_fp8(w2d, E4M3, meta.scale_inv, scale_inv_out=sinv, amax_in=meta.amax[0], rescale=True)
+    weight._fp8_cache1 = (key, w8, sinv)
+    return w8, sinv
+
+
+def _tma_ok(t):
+    """A 2-D byte matrix the GEMM can read MN-major: contiguous rows whose pitch and base are multiples of 16 bytes."""
+    return t.stride(1) == 1 and t.stride(0) % 16 == 0 and t.data_ptr() % 16 == 0
+
+
+def gemm_dgrad(dy8, dy_sinv, w8, w_sinv, out_dtype, **kw):
+    """``dx[T,K] = dy8[T,N] · W8[N,K]``: the weight is read as stored (MN-major B).  Shapes the TMA cannot
+    address that way (pitch not a multiple of 16 bytes) fall back to a transposed copy of the weight."""
+    if _tma_ok(w8) and dy8.shape[1] % 16 == 0:
+        return _g.gemm_fp8(dy8, E5M2, dy_sinv, w8, E4M3, w_sinv, out_dtype, b_mn=True, **kw)
+    return _g.gemm_fp8(dy8, E5M2, dy_sinv, _k.transpose_fp8(w8), E4M3, w_sinv, out_dtype, **kw)
+
+
+def gemm_wgrad(dy8, dy_sinv, x8, x_sinv, out_dtype, **kw):
+    """``dW[N,K] = dy8[T,N]ᵀ · x8[T,K]``: both operands are read as stored (MN-major A and B)."""
+    if _tma_ok(dy8) and _tma_ok(x8):
+        return _g.gemm_fp8(dy8, E5M2, dy_sinv, x8, E4M3, x_sinv, out_dtype, a_mn=True, b_mn=True, **kw)
+    return _g.gemm_fp8(_k.transpose_fp8(dy8), E5M2, dy_sinv, _k.transpose_fp8(x8), E4M3, x_sinv, out_dtype, **kw)
+
+
 class _FP8GemmFunction(torch.autograd.Function):
     """y = x · Wᵀ (+ bias) with FP8 operands; weight gradient delivered out of band."""
     @staticmethod
@@ -88,19 +134,16 @@ class _FP8GemmFunction(torch.autograd.Function):
         record = TypeCast._prepare_scale(x, in_meta, sync=False)
         amax_out = in_meta.amax[0] if record else None
         sinv_out = in_meta.scale_inv if record else None
-        if need_wgrad:
-            x8, x8t = _k.cast_transpose_fp8(x, E4M3, in_meta.scale, amax_out, scale_inv_out=sinv_out)
-        else:
-            x8, x8t = _k.cast_to_fp8(x, E4M3, in_meta.scale, amax_out, scale_inv_out=sinv_out), None
+        x8 = _k.cast_to_fp8(x, E4M3, in_meta.scale, amax_out, scale_inv_out=sinv_out)
         x_sinv = in_meta.scale_inv.clone()    # the meta may be reused before backward runs
 
-        w8, w8t, w_sinv = weight_fp8_pair(weight)
+        w8, w_sinv = weight_fp8(weight)
         out = _g.gemm_fp8(x8, E4M3, x_sinv, w8, E4M3, w_sinv, out_dtype, bias=bias)
 
         ctx.metas = metas
         ctx.weight = weight
-        ctx.x8t, ctx.x_sinv = x8t, x_sinv
-        ctx.w8t, ctx.w_sinv = w8t, w_sinv
+        ctx.x8, ctx.x_sinv = (x8 if need_wgrad else None), x_sinv
+        ctx.w8, ctx.w_sinv = w8, w_sinv
         ctx.out_dtype = out_dtype
         ctx.input_requires_grad = input.requires_grad
         ctx.has_bias = bias is not None
@@ -113,25 +156,22 @@ class _FP8GemmFunction(torch.autograd.Function):
         metas = ctx.metas
         og_meta, wg_meta = metas['ograd'], metas['wgrad']
         weight = ctx.weight
-        need_wgrad = weight.requires_grad and ctx.x8t is not None
+        need_wgrad = weight.requires_grad and ctx.x8 is not None
 
         record = TypeCast._prepare_scale(dy, og_meta, sync=False)
         amax_out = og_meta.amax[0] if record else None
         sinv_out = og_meta.scale_inv if record else None
         dbias = None
-        if need_wgrad:
-            # the bias gradient (column sums of dy) comes out of the same pass over dy
-            colsum = torch.zeros(dy.shape[1], dtype=torch.float32, device=dy.device) if (ctx.has_bias and dy.dim() == 2) else None
-            dy8, dy8t = _k.cast_transpose_fp8(dy, E5M2, og_meta.scale, amax_out, scale_inv_out=sinv_out, colsum_out=colsum)
-            if colsum is not None:
-                dbias = colsum.to(ctx.bias_dtype)
-        else:
-            dy8, dy8t = _k.cast_to_fp8(dy, E5M2, og_meta.scale, amax_out, scale_inv_out=sinv_out), None
+        # the bias gradient (column sums of dy) comes out of the same pass over dy
+        colsum = torch.zeros(dy.shape[1], dtype=torch.float32, device=dy.device) if (ctx.has_bias and dy.dim() == 2) else None
+        dy8 = _k.cast_to_fp8(dy, E5M2, og_meta.scale, amax_out, scale_inv_out=sinv_out, colsum_out=colsum)
+        if colsum is not None:
+            dbias = colsum.to(ctx.bias_dtype)
         dy_sinv = og_meta.scale_inv
 
         dx = None
         if ctx.input_requires_grad:
-            dx = _g.gemm_fp8(dy8, E5M2, dy_sinv, ctx.w8t, E4M3, ctx.w_sinv, ctx.out_dtype)
+            dx = gemm_dgrad(dy8, dy_sinv, ctx.w8, ctx.w_sinv, ctx.out_dtype)
         if ctx.has_bias and dbias is None:
             dbias = dy.sum(0, dtype=torch.float32).to(ctx.bias_dtype)
 
@@ -139,12 +179,10 @@ class _FP8GemmFunction(torch.autograd.Function):
         if need_wgrad:
             amax0 = wg_meta.amax[0]
             if weight.grad is None:
-                wgrad = _g.gemm_fp8(dy8t, E5M2, dy_sinv, ctx.x8t, E4M3, ctx.x_sinv, ctx.out_dtype, amax_out=amax0)
+                wgrad = gemm_wgrad(dy8, dy_sinv, ctx.x8, ctx.x_sinv, ctx.out_dtype, amax_out=amax0)
             else:
-                old = weight.grad.to(ctx.out_dtype) if isinstance(weight.grad, ScalingTensor) else weight.grad.to(ctx.out_dtype)
-                wgrad = _g.gemm_fp8(
-                    dy8t, E5M2, dy_sinv, ctx.x8t, E4M3, ctx.x_sinv, ctx.out_dtype, accumulate=True, out=old, amax_out=amax0
-                )
+                old = weight.grad.to(ctx.out_dtype)
+                wgrad = gemm_wgrad(dy8, dy_sinv, ctx.x8, ctx.x_sinv, ctx.out_dtype, accumulate=True, out=old, amax_out=amax0)
             wgrad = wgrad.view(weight.shape)
             if model_state.use_fp8_ddp and not ctx.return_wgrad:
                 # The FP8 DDP reducer quantises whole buckets with a cross-rank scale.
@@ -160,7 +198,7 @@ class _FP8GemmFunction(torch.autograd.Function):
                 wgrad_ret.meta = wg_meta
             else:
                 weight.backward_grad_update(wgrad)
-        ctx.x8t = ctx.w8t = None
+        ctx.x8 = ctx.w8 = None
         return dx, wgrad_ret, None, None, dbias
 
 

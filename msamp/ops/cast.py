@@ -87,34 +87,67 @@ def _emulate_to_fp8(x, scale, qtype):
     return y.to(_F8[qtype]).view(torch.uint8)
 
 
-def cast_to_fp8(x, qtype, scale, amax_out=None, scale_inv_out=None, amax_in=None, prescale=1.0, out=None):
+def cast_to_fp8(x, qtype, scale, amax_out=None, scale_inv_out=None, amax_in=None, prescale=1.0, out=None, rescale=False, act=None,
+                colsum_out=None):
     """Quantise ``x`` (fp32/fp16/bf16) to FP8 bytes with the given scale.
 
     Optionally records ``max|x|`` in ``amax_out`` and ``1/scale`` in ``scale_inv_out`` in the same pass.
     With ``amax_in`` (a 0-d tensor already holding ``max|x|``, e.g. from a GEMM epilogue) the scale is
     first recomputed from it by the power-of-two rule, times ``prescale``, and written to ``scale``.
+    With ``rescale`` as well, ``x`` is a *scaled* tensor ``x0 * s_old``: ``scale`` must hold ``1 / s_old`` and
+    ``amax_in`` ``max|x0|``; the bytes are ``x0 * s_new`` with ``s_new`` from the rule, ``scale_inv_out`` receives
+    ``1 / s_new`` and ``scale`` is left alone (the cast of a scaled 16-bit master weight).
+    ``act='gelu'`` quantises ``gelu(x)`` (tanh form, rounded to the dtype of ``x`` first) instead of ``x``.
+    ``colsum_out`` (fp32 ``[cols]``, zero on entry) receives the column sums of a 2-D ``x`` from the same pass - the
+    bias gradient when ``x`` is the output gradient of a linear layer.
     ``out`` (uint8, same number of elements, contiguous) receives the bytes when given.
     """
     if out is not None:
         assert out.dtype == torch.uint8 and out.numel() == x.numel() and out.is_contiguous() and out.device == x.device
+    if rescale:
+        assert amax_in is not None
+    if colsum_out is not None:
+        assert x.dim() == 2 and act is None and amax_in is None
+        assert colsum_out.dtype == torch.float32 and colsum_out.numel() == x.shape[1] and colsum_out.is_contiguous()
     if x.is_cuda:
         x = x.contiguous()
         if out is None:
             out = torch.empty(x.shape, dtype=torch.uint8, device=x.device)
+        if colsum_out is not None and (x.shape[1] * x.element_size()) % 16 == 0 and x.data_ptr() % 16 == 0 and out.data_ptr() % 8 == 0:
+            native.check(
+                native.lib().msamp_cast_to_fp8_colsum(
+                    native.ptr(x), x.shape[0], x.shape[1], native.dt(x.dtype), native.ptr(out), native.fmt(qtype), native.ptr(scale),
+                    native.ptr(amax_out), native.ptr(scale_inv_out), native.ptr(colsum_out), native.stream()
+                ), 'cast_to_fp8_colsum'
+            )
+            return out
         native.check(
-            native.lib().msamp_cast_to_fp8(
+            native.lib().msamp_cast_to_fp8_ex(
                 native.ptr(x), native.i64(x.numel()), native.dt(x.dtype), native.ptr(out), native.fmt(qtype), native.ptr(scale),
-                native.ptr(amax_out), native.ptr(scale_inv_out), native.ptr(amax_in), ctypes.c_float(prescale), native.stream()
+                native.ptr(amax_out), native.ptr(scale_inv_out), native.ptr(amax_in), ctypes.c_float(prescale), int(bool(rescale)),
+                1 if act == 'gelu' else 0, native.stream()
             ), 'cast_to_fp8'
         )
+        if colsum_out is not None:
+            colsum_out.add_(x.sum(0, dtype=torch.float32))
         return out
-    if amax_in is not None:
-        scale.copy_(compute_scale(amax_in, scale, Floating.qfp_max[qtype]) * torch.where(
-            (amax_in > 0) & torch.isfinite(amax_in), prescale, 1.0))
+    if act == 'gelu':
+        x = torch.nn.functional.gelu(x.float(), approximate='tanh').to(x.dtype)
+    if rescale:
+        new_scale = compute_scale(amax_in, torch.ones_like(scale), Floating.qfp_max[qtype])
+        if scale_inv_out is not None:
+            torch.reciprocal(new_scale, out=scale_inv_out)
+        scale = new_scale * scale
+    else:
+        if amax_in is not None:
+            scale.copy_(compute_scale(amax_in, scale, Floating.qfp_max[qtype]) * torch.where(
+                (amax_in > 0) & torch.isfinite(amax_in), prescale, 1.0))
+        if scale_inv_out is not None:
+            torch.reciprocal(scale, out=scale_inv_out)
     if amax_out is not None:
         amax(x, out=amax_out)
-    if scale_inv_out is not None:
-        torch.reciprocal(scale, out=scale_inv_out)
+    if colsum_out is not None:
+        colsum_out.add_(x.sum(0, dtype=torch.float32))
     res = _emulate_to_fp8(x, scale, qtype)
     if out is not None:
         out.copy_(res.view_as(out))

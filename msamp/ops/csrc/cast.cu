@@ -25,11 +25,20 @@ __global__ void __launch_bounds__(kThreads) amax_kernel(const T* __restrict__ x,
     constexpr int N = VecOf<T>::N;
     int64_t nv = n / N;
     const Bytes16* xv = reinterpret_cast<const Bytes16*>(x);
-    for (int64_t i = tid; i < nv; i += stride) {
-      Bytes16 v = xv[i];
-      const T* e = reinterpret_cast<const T*>(&v);
+    // four independent 16-byte loads per thread and iteration keep enough bytes in flight for HBM3e
+    for (int64_t i = tid; i < nv; i += 4 * stride) {
+      Bytes16 v[4];
 #pragma unroll
-      for (int j = 0; j < N; ++j) m = fmaxf(m, abs_nan_to_inf(to_f32<T>(e[j])));
+      for (int u = 0; u < 4; ++u)
+        if (i + u * stride < nv) v[u] = xv[i + u * stride];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        if (i + u * stride < nv) {
+          const T* e = reinterpret_cast<const T*>(&v[u]);
+#pragma unroll
+          for (int j = 0; j < N; ++j) m = fmaxf(m, abs_nan_to_inf(to_f32<T>(e[j])));
+        }
+      }
     }
     for (int64_t i = nv * N + tid; i < n; i += stride) m = fmaxf(m, abs_nan_to_inf(to_f32<T>(x[i])));
   } else {
@@ -55,22 +64,39 @@ __global__ void __launch_bounds__(kThreads) amax_kernel(const T* __restrict__ x,
 }
 
 // ---- high precision -> fp8 ------------------------------------------------------------------------
-template <typename T, int FMT, bool VEC>
+// ACT == 1 quantises gelu(x) (rounded to T first, i.e. the bits a separate GeLU kernel would have stored)
+// instead of x; amax then refers to gelu(x) as well.
+template <typename T, int ACT>
+__device__ __forceinline__ float cast_pre(T e) {
+  float a = to_f32<T>(e);
+  if (ACT == 1) a = to_f32<T>(from_f32<T>(gelu_f(a)));
+  return a;
+}
+
+template <typename T, int FMT, bool VEC, int ACT>
 __global__ void __launch_bounds__(kThreads) cast_to_fp8_kernel(const T* __restrict__ x, uint8_t* __restrict__ out, int64_t n,
                                                                 float* scale_ptr, float* amax, float* scale_inv_out,
-                                                                const float* amax_in, float fp_max, float prescale) {
+                                                                const float* amax_in, float fp_max, float prescale, int rescale) {
   __shared__ float red[32];
   float scale = *scale_ptr;
-  if (amax_in != nullptr) {
+  float logical_scale = scale;
+  if (amax_in != nullptr && rescale) {
+    // Re-quantisation of a tensor that is stored as x * s_old: *scale_ptr holds 1 / s_old and *amax_in
+    // holds max|x|.  The payload is multiplied by s_new / s_old where s_new follows the power-of-two
+    // rule; scale_inv_out receives 1 / s_new and *scale_ptr is left alone.
+    logical_scale = msamp_compute_scale(*amax_in, 1.0f, fp_max, 0);
+    scale = logical_scale * scale;
+  } else if (amax_in != nullptr) {
     // In-time scaling from an amax that an earlier kernel produced (e.g. a GEMM epilogue): every
     // thread derives the same scale; one thread publishes it. When amax is unusable the old
     // scale is kept, so the concurrent read of *scale_ptr by other blocks sees a value that the
     // write does not change.
     float a = *amax_in;
     if ((a > 0.0f) && !isinf(a) && !isnan(a)) scale = msamp_compute_scale(a, scale, fp_max, 0) * prescale;
+    logical_scale = scale;
     if (blockIdx.x == 0 && threadIdx.x == 0) *scale_ptr = scale;
   }
-  if (scale_inv_out != nullptr && blockIdx.x == 0 && threadIdx.x == 0) *scale_inv_out = __frcp_rn(scale);
+  if (scale_inv_out != nullptr && blockIdx.x == 0 && threadIdx.x == 0) *scale_inv_out = __frcp_rn(logical_scale);
   float m = 0.0f;
   int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   int64_t stride = (int64_t)gridDim.x * blockDim.x;
@@ -78,33 +104,98 @@ __global__ void __launch_bounds__(kThreads) cast_to_fp8_kernel(const T* __restri
     constexpr int N = VecOf<T>::N;    // 8 (16-bit) or 4 (fp32) inputs -> N bytes out
     int64_t nv = n / N;
     const Bytes16* xv = reinterpret_cast<const Bytes16*>(x);
-    for (int64_t i = tid; i < nv; i += stride) {
-      Bytes16 v = xv[i];
-      const T* e = reinterpret_cast<const T*>(&v);
-      uint16_t o[N / 2];
+    for (int64_t i = tid; i < nv; i += 4 * stride) {
+      Bytes16 v[4];
 #pragma unroll
-      for (int j = 0; j < N; j += 2) {
-        float a = to_f32<T>(e[j]), b = to_f32<T>(e[j + 1]);
-        m = fmaxf(m, fmaxf(abs_nan_to_inf(a), abs_nan_to_inf(b)));
-        o[j / 2] = f32x2_to_fp8x2<FMT>(a * scale, b * scale);
-      }
-      if (N == 8) {
-        reinterpret_cast<Bytes8*>(out)[i] = *reinterpret_cast<Bytes8*>(o);
-      } else {
-        reinterpret_cast<uint32_t*>(out)[i] = *reinterpret_cast<uint32_t*>(o);
+      for (int u = 0; u < 4; ++u)
+        if (i + u * stride < nv) v[u] = xv[i + u * stride];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        if (i + u * stride < nv) {
+          const T* e = reinterpret_cast<const T*>(&v[u]);
+          uint16_t o[N / 2];
+#pragma unroll
+          for (int j = 0; j < N; j += 2) {
+            float a = cast_pre<T, ACT>(e[j]), b = cast_pre<T, ACT>(e[j + 1]);
+            m = fmaxf(m, fmaxf(abs_nan_to_inf(a), abs_nan_to_inf(b)));
+            o[j / 2] = f32x2_to_fp8x2<FMT>(a * scale, b * scale);
+          }
+          if (N == 8) {
+            reinterpret_cast<Bytes8*>(out)[i + u * stride] = *reinterpret_cast<Bytes8*>(o);
+          } else {
+            reinterpret_cast<uint32_t*>(out)[i + u * stride] = *reinterpret_cast<uint32_t*>(o);
+          }
+        }
       }
     }
     for (int64_t i = nv * N + tid; i < n; i += stride) {
-      float a = to_f32<T>(x[i]);
+      float a = cast_pre<T, ACT>(x[i]);
       m = fmaxf(m, abs_nan_to_inf(a));
       out[i] = f32_to_fp8<FMT>(a * scale);
     }
   } else {
     for (int64_t i = tid; i < n; i += stride) {
-      float a = to_f32<T>(x[i]);
+      float a = cast_pre<T, ACT>(x[i]);
       m = fmaxf(m, abs_nan_to_inf(a));
       out[i] = f32_to_fp8<FMT>(a * scale);
     }
+  }
+  if (amax != nullptr) {
+    m = block_max(m, red);
+    if (threadIdx.x == 0) atomic_max_nonneg(amax, m);
+  }
+}
+
+// ---- high precision [rows, cols] -> fp8 with the column sums of the input -------------------------
+// Used for the output gradient of a linear layer: the bias gradient falls out of the pass that
+// quantises dy.  A CTA owns a slab of 256 16-byte column vectors and walks down the rows, four rows in
+// flight per thread; every thread keeps the partial sums of its own columns in registers and adds
+// them to colsum (fp32, zeroed by the caller) once at the end.  cols must be a multiple of 16 bytes.
+template <typename T, int FMT>
+__global__ void __launch_bounds__(kThreads) cast_rows_colsum_kernel(const T* __restrict__ x, uint8_t* __restrict__ out, int rows, int cols,
+                                                                     const float* __restrict__ scale_ptr, float* amax,
+                                                                     float* scale_inv_out, float* __restrict__ colsum) {
+  __shared__ float red[32];
+  constexpr int N = VecOf<T>::N;
+  const float scale = *scale_ptr;
+  if (scale_inv_out != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) *scale_inv_out = __frcp_rn(scale);
+  const int cv = cols / N;                                   // vectors per row
+  const int vec = blockIdx.y * kThreads + threadIdx.x;       // this thread's column vector
+  float m = 0.0f;
+  float cs[N];
+#pragma unroll
+  for (int j = 0; j < N; ++j) cs[j] = 0.0f;
+  if (vec < cv) {
+    const Bytes16* xv = reinterpret_cast<const Bytes16*>(x);
+    for (int r = blockIdx.x; r < rows; r += 4 * gridDim.x) {
+      Bytes16 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        if (r + u * (int)gridDim.x < rows) v[u] = xv[(int64_t)(r + u * (int)gridDim.x) * cv + vec];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int rr = r + u * (int)gridDim.x;
+        if (rr < rows) {
+          const T* e = reinterpret_cast<const T*>(&v[u]);
+          uint16_t o[N / 2];
+#pragma unroll
+          for (int j = 0; j < N; j += 2) {
+            float a = to_f32<T>(e[j]), b = to_f32<T>(e[j + 1]);
+            m = fmaxf(m, fmaxf(abs_nan_to_inf(a), abs_nan_to_inf(b)));
+            cs[j] += a;
+            cs[j + 1] += b;
+            o[j / 2] = f32x2_to_fp8x2<FMT>(a * scale, b * scale);
+          }
+          if (N == 8) {
+            reinterpret_cast<Bytes8*>(out)[(int64_t)rr * cv + vec] = *reinterpret_cast<Bytes8*>(o);
+          } else {
+            reinterpret_cast<uint32_t*>(out)[(int64_t)rr * cv + vec] = *reinterpret_cast<uint32_t*>(o);
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < N; ++j) atomicAdd(colsum + (int64_t)vec * N + j, cs[j]);
   }
   if (amax != nullptr) {
     m = block_max(m, red);
@@ -368,7 +459,7 @@ MSAMP_API int msamp_amax(const void* x, int64_t n, int dtype, float* amax, float
   cudaStream_t stream = (cudaStream_t)stream_;
   MSAMP_REQUIRE(n >= 0 && amax != nullptr, "msamp_amax: bad arguments");
   cudaMemsetAsync(amax, 0, sizeof(float), stream);
-  int grid = msamp_grid_for((n + 7) / 8, kThreads, 4);
+  int grid = msamp_grid_for((n + 31) / 32, kThreads, 6);
   if (n == 0) grid = 1;
   MSAMP_DISPATCH_HP(dtype, T, {
     if (aligned16(x))
@@ -379,26 +470,65 @@ MSAMP_API int msamp_amax(const void* x, int64_t n, int dtype, float* amax, float
   return msamp_check_launch("msamp_amax");
 }
 
-// out = saturate_fp8(x * scale). With `amax` non-null it receives max|x| (it is cleared first);
-// with `scale_inv_out` non-null it receives 1 / scale. With `amax_in` non-null the scale is first
-// recomputed as rule(*amax_in) * prescale and stored to *scale (amax and amax_in must differ).
-MSAMP_API int msamp_cast_to_fp8(const void* x, int64_t n, int dtype, void* out, int fmt, float* scale, float* amax,
-                                float* scale_inv_out, const float* amax_in, float prescale, void* stream_) {
+// out = saturate_fp8(act(x) * scale). With `amax` non-null it receives max|act(x)| (it is cleared first);
+// with `scale_inv_out` non-null it receives 1 / scale. With `amax_in` non-null (amax and amax_in must
+// differ) the scale is first derived from it:
+//   rescale == 0: scale = rule(*amax_in) * prescale, stored to *scale (in-time scaling from a producer's amax);
+//   rescale == 1: x is a scaled tensor (x0 * s_old), *scale holds 1 / s_old and *amax_in max|x0|; the
+//                 effective factor is rule(amax) / s_old, scale_inv_out receives 1 / rule(amax), *scale is not written.
+// act: 0 = identity, 1 = GeLU (tanh form), applied and rounded to the input type before quantising.
+MSAMP_API int msamp_cast_to_fp8_ex(const void* x, int64_t n, int dtype, void* out, int fmt, float* scale, float* amax,
+                                   float* scale_inv_out, const float* amax_in, float prescale, int rescale, int act, void* stream_) {
   cudaStream_t stream = (cudaStream_t)stream_;
   MSAMP_REQUIRE(n >= 0 && scale != nullptr, "msamp_cast_to_fp8: bad arguments");
+  MSAMP_REQUIRE(act == 0 || act == 1, "msamp_cast_to_fp8: unknown activation %d", act);
   if (amax) cudaMemsetAsync(amax, 0, sizeof(float), stream);
   if (n == 0) return MSAMP_OK;
-  int grid = msamp_grid_for((n + 7) / 8, kThreads, 4);
+  int grid = msamp_grid_for((n + 31) / 32, kThreads, 6);
   const bool vec = aligned16(x) && aligned8(out);
+#define MSAMP_CAST_LAUNCH(V, A) \
+  cast_to_fp8_kernel<T, F, V, A><<<grid, kThreads, 0, stream>>>((const T*)x, (uint8_t*)out, n, scale, amax, scale_inv_out, amax_in, fp8_max(F), prescale, rescale)
   MSAMP_DISPATCH_HP(dtype, T, {
     MSAMP_DISPATCH_FP8(fmt, F, {
-      if (vec)
-        cast_to_fp8_kernel<T, F, true><<<grid, kThreads, 0, stream>>>((const T*)x, (uint8_t*)out, n, scale, amax, scale_inv_out, amax_in, fp8_max(F), prescale);
-      else
-        cast_to_fp8_kernel<T, F, false><<<grid, kThreads, 0, stream>>>((const T*)x, (uint8_t*)out, n, scale, amax, scale_inv_out, amax_in, fp8_max(F), prescale);
+      if (vec && act == 0) MSAMP_CAST_LAUNCH(true, 0);
+      else if (vec) MSAMP_CAST_LAUNCH(true, 1);
+      else if (act == 0) MSAMP_CAST_LAUNCH(false, 0);
+      else MSAMP_CAST_LAUNCH(false, 1);
     });
   });
+#undef MSAMP_CAST_LAUNCH
   return msamp_check_launch("msamp_cast_to_fp8");
+}
+
+MSAMP_API int msamp_cast_to_fp8(const void* x, int64_t n, int dtype, void* out, int fmt, float* scale, float* amax,
+                                float* scale_inv_out, const float* amax_in, float prescale, void* stream_) {
+  return msamp_cast_to_fp8_ex(x, n, dtype, out, fmt, scale, amax, scale_inv_out, amax_in, prescale, 0, 0, stream_);
+}
+
+// x is [rows, cols] row-major, out its FP8 copy; the column sums of x are ADDED to colsum (fp32 [cols],
+// zeroed by the caller).  cols * sizeof(element) must be a multiple of 16 and x, out 16- / 8-byte aligned.
+MSAMP_API int msamp_cast_to_fp8_colsum(const void* x, int rows, int cols, int dtype, void* out, int fmt, const float* scale,
+                                       float* amax, float* scale_inv_out, float* colsum, void* stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  MSAMP_REQUIRE(rows >= 0 && cols >= 0 && scale != nullptr && colsum != nullptr && out != nullptr, "msamp_cast_to_fp8_colsum: bad arguments");
+  const int esize = dtype == DT_F32 ? 4 : 2;
+  MSAMP_REQUIRE(((int64_t)cols * esize) % 16 == 0 && aligned16(x) && aligned8(out), "msamp_cast_to_fp8_colsum: rows must be 16-byte multiples and aligned");
+  if (amax) cudaMemsetAsync(amax, 0, sizeof(float), stream);
+  if ((int64_t)rows * cols == 0) return MSAMP_OK;
+  const int cv = cols * esize / 16;
+  const int slabs = (cv + kThreads - 1) / kThreads;
+  int per_slab = msamp_sm_count() * 6 / slabs;
+  if (per_slab < 1) per_slab = 1;
+  int gx = (rows + 3) / 4;
+  if (gx > per_slab) gx = per_slab;
+  if (gx < 1) gx = 1;
+  dim3 grid((unsigned)gx, (unsigned)slabs, 1);
+  MSAMP_DISPATCH_HP(dtype, T, {
+    MSAMP_DISPATCH_FP8(fmt, F, {
+      cast_rows_colsum_kernel<T, F><<<grid, kThreads, 0, stream>>>((const T*)x, (uint8_t*)out, rows, cols, scale, amax, scale_inv_out, colsum);
+    });
+  });
+  return msamp_check_launch("msamp_cast_to_fp8_colsum");
 }
 
 MSAMP_API int msamp_cast_from_fp8(const void* in, int64_t n, int fmt, const float* scale_inv, void* out, int out_dtype,

@@ -114,6 +114,20 @@ __device__ __forceinline__ float abs_nan_to_inf(float v) {
   return (a != a) ? __int_as_float(0x7f800000) : a;
 }
 
+// GeLU, tanh form, and its derivative.  One definition for the elementwise kernels and the GEMM epilogues,
+// so that a fused path produces the bits of the separate kernels.
+__device__ __forceinline__ float gelu_f(float x) {
+  const float k0 = 0.7978845608028654f, k1 = 0.044715f;
+  float u = k0 * (x + k1 * x * x * x);
+  return 0.5f * x * (1.0f + tanhf(u));
+}
+__device__ __forceinline__ float gelu_grad_f(float x) {
+  const float k0 = 0.7978845608028654f, k1 = 0.044715f;
+  float u = k0 * (x + k1 * x * x * x);
+  float th = tanhf(u);
+  return 0.5f * (1.0f + th) + 0.5f * x * (1.0f - th * th) * k0 * (1.0f + 3.0f * k1 * x * x);
+}
+
 __device__ __forceinline__ float warp_max(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));

@@ -240,18 +240,6 @@ __global__ void __launch_bounds__(256) layernorm_reduce_kernel(const float* __re
 // ------------------------------------------------------------------------------------------------
 // GeLU, tanh form: 0.5 x (1 + tanh(sqrt(2/pi) (x + 0.044715 x^3)))
 // ------------------------------------------------------------------------------------------------
-__device__ __forceinline__ float gelu_f(float x) {
-  const float k0 = 0.7978845608028654f, k1 = 0.044715f;
-  float u = k0 * (x + k1 * x * x * x);
-  return 0.5f * x * (1.0f + tanhf(u));
-}
-__device__ __forceinline__ float gelu_grad_f(float x) {
-  const float k0 = 0.7978845608028654f, k1 = 0.044715f;
-  float u = k0 * (x + k1 * x * x * x);
-  float th = tanhf(u);
-  return 0.5f * (1.0f + th) + 0.5f * x * (1.0f - th * th) * k0 * (1.0f + 3.0f * k1 * x * x);
-}
-
 template <typename T, bool BWD>
 __global__ void __launch_bounds__(256) gelu_kernel(const T* __restrict__ x, const T* __restrict__ dy, T* __restrict__ out, int64_t n) {
   constexpr int N = 16 / sizeof(T);

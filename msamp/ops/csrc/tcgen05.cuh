@@ -131,6 +131,79 @@ __device__ __forceinline__ void mma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
 
+// ---- thread-block clusters and CTA pairs (cta_group::2) -----------------------------------------
+// A CTA pair is a cluster of two CTAs on the two SMs of one TPC.  One thread of the even CTA issues
+// tcgen05.mma.cta_group::2: the instruction multiplies a 256-row A tile (128 rows from each CTA's
+// shared memory) by an N-column B tile (N/2 rows from each CTA) and writes 128 accumulator lanes in
+// each CTA's TMEM.  Every CTA loads its own halves with its own TMA (no multicast).
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t cluster_id_x() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%clusterid.x;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t cluster_count_x() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%nclusterid.x;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// shared::cluster address of the location `saddr` (a shared::cta address of this CTA) in CTA `rank` of the cluster.
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t saddr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(saddr), "r"(rank));
+  return r;
+}
+// Arrival on an mbarrier that may live in the other CTA of the cluster (`bar` is a shared::cluster address).
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+// 2-D tile load into this CTA's shared memory whose completion bytes are counted on an mbarrier
+// that may belong to the other CTA of the pair (`bar` is a shared::cluster address).  Not a multicast:
+// the data lands in the executing CTA only.
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, int c_inner, int c_outer, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      :
+      : "r"(dst), "l"((uint64_t)map), "r"(c_inner), "r"(c_outer), "r"(bar)
+      : "memory");
+}
+// TMEM management for a CTA pair: the same warp index of both CTAs executes each of these.
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t smem_holder, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_holder), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+// D[tmem of both CTAs] (+)= A * B over the pair; issued by one thread of the even CTA.
+__device__ __forceinline__ void mma_f8f6f4_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, {%5, %6, %7, %8, %9, %10, %11, %12}, p;\n\t"
+      "}\n"
+      :
+      : "r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0), "r"(0), "r"(0), "r"(0), "r"(0), "r"(0), "r"(0),
+        "r"(0)
+      : "memory");
+}
+// One arrival on `bar` (a shared::cluster address, this CTA's or the partner's) once every MMA issued
+// so far by this thread for the pair has finished.
+__device__ __forceinline__ void mma_commit_pair(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
 // D[tmem] (+)= A[smem] * B[smem] for 16-bit inputs (bf16 / fp16); issued by one thread.
 __device__ __forceinline__ void mma_f16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
   asm volatile(
@@ -243,13 +316,15 @@ __host__ __device__ __forceinline__ uint32_t idesc_bf16(int m, int n, int a_mn, 
   return d;
 }
 
-// Instruction descriptor for kind::f8f6f4 with fp32 accumulation, both operands K-major.
+// Instruction descriptor for kind::f8f6f4 with fp32 accumulation; operands K-major unless a_mn / b_mn is set.
 // a_fmt / b_fmt: 0 = e4m3, 1 = e5m2.
-__host__ __device__ __forceinline__ uint32_t idesc_f8(int m, int n, int a_fmt, int b_fmt) {
+__host__ __device__ __forceinline__ uint32_t idesc_f8(int m, int n, int a_fmt, int b_fmt, int a_mn = 0, int b_mn = 0) {
   uint32_t d = 0;
   d |= 1u << 4;                      // accumulator format f32
   d |= (uint32_t)a_fmt << 7;
   d |= (uint32_t)b_fmt << 10;
+  d |= (uint32_t)a_mn << 15;         // 1: the M index of A is contiguous in shared memory
+  d |= (uint32_t)b_mn << 16;         // 1: the N index of B is contiguous
   d |= (uint32_t)(n >> 3) << 17;
   d |= (uint32_t)(m >> 4) << 24;
   return d;

@@ -144,6 +144,89 @@ def test_gemm_strided_and_capped():
     _status_ok()
 
 
+@pytest.mark.parametrize('shape', [(256, 512), (1000, 264), (8192, 4096), (3, 8)])
+def test_cast_colsum_gelu_rescale(shape):
+    """Options of the plain cast: column sums of the input, GeLU before quantising, re-quantising a scaled tensor."""
+    x = (torch.randn(*shape, device=DEV) * 3).bfloat16()
+    s = torch.tensor(4.0, device=DEV)
+    am, si = torch.zeros((), device=DEV), torch.zeros((), device=DEV)
+    cs = torch.zeros(shape[1], device=DEV)
+    out = cast.cast_to_fp8(x, E5, s, am, scale_inv_out=si, colsum_out=cs)
+    assert torch.equal(out.cpu(), cast.cast_to_fp8(x.cpu(), E5, s.cpu()))
+    assert am.item() == x.float().abs().max().item() and si.item() == 0.25
+    ref = x.float().sum(0)
+    assert (cs - ref).abs().max().item() <= 1e-3 * (ref.abs().max().item() + shape[0] ** 0.5)
+    # GeLU folded into the cast == GeLU kernel followed by the cast
+    am2 = torch.zeros((), device=DEV)
+    fused = cast.cast_to_fp8(x, E4, s, am2, act='gelu')
+    g = K.gelu(x)
+    assert torch.equal(fused, cast.cast_to_fp8(g, E4, s)) and am2.item() == g.float().abs().max().item()
+    # scaled 16-bit tensor (x0 * s_old) -> e4m3 with the scale implied by amax(x0)
+    s_old = 8.0
+    x0 = torch.randn(*shape, device=DEV)
+    xs = (x0 * s_old).half()
+    amax0 = (xs.float() / s_old).abs().max()
+    sinv_old, sinv_new = torch.tensor(1 / s_old, device=DEV), torch.zeros((), device=DEV)
+    got = cast.cast_to_fp8(xs, E4, sinv_old, scale_inv_out=sinv_new, amax_in=amax0, rescale=True)
+    sinv_cpu = torch.zeros(())
+    want = cast.cast_to_fp8(xs.cpu(), E4, sinv_old.cpu(), scale_inv_out=sinv_cpu, amax_in=amax0.cpu(), rescale=True)
+    assert torch.equal(got.cpu(), want) and sinv_new.item() == sinv_cpu.item() and sinv_old.item() == 1 / s_old
+    _status_ok()
+
+
+@pytest.mark.parametrize('tile', [1, 2])
+@pytest.mark.parametrize('layout', [(False, False), (True, False), (False, True), (True, True)])
+@pytest.mark.parametrize('mnk', [(256, 256, 128), (512, 768, 1024), (1024, 512, 384), (400, 272, 200), (4096, 4096, 2048), (128, 16, 48)])
+def test_gemm_layouts_and_tiles(mnk, layout, tile):
+    """Every operand layout (K-major / MN-major) on the single-CTA and the CTA-pair kernel against fp32 math."""
+    m, n, k = mnk
+    a_mn, b_mn = layout
+    if (a_mn != b_mn) and k % 16:
+        k = (k + 15) // 16 * 16
+    if (a_mn and m % 16) or (b_mn and n % 16):
+        pytest.skip('the contiguous dimension must be a multiple of 16 bytes')
+    a, sia = _mk(m, k, E5)
+    b, sib = _mk(n, k, E4)
+    ref = (a.view(F8[E5]).float() @ b.view(F8[E4]).float().t()) * (sia * sib)
+    sc = ref.abs().max().item() + 1e-6
+    aa = a.t().contiguous() if a_mn else a
+    bb = b.t().contiguous() if b_mn else b
+    d = gemm.gemm_fp8(aa, E5, sia, bb, E4, sib, torch.float32, a_mn=a_mn, b_mn=b_mn, tile=tile)
+    assert (d - ref).abs().max().item() <= 1e-4 * sc + 1e-4
+    _status_ok()
+
+
+@pytest.mark.parametrize('tile', [1, 2])
+def test_gemm_epilogue_options(tile):
+    """Residual add, GeLU-derivative multiply, amax of the stored values, and the quantised copy of gelu(D)."""
+    m, n, k = 512, 768, 512
+    a, sia = _mk(m, k, E4)
+    b, sib = _mk(n, k, E4)
+    bias = torch.randn(n, device=DEV)
+    ref = (a.view(F8[E4]).float() @ b.view(F8[E4]).float().t()) * (sia * sib)
+    res = torch.randn(m, n, device=DEV).bfloat16()
+    d = gemm.gemm_fp8(a, E4, sia, b, E4, sib, torch.bfloat16, bias=bias, residual=res, tile=tile)
+    want = (ref + bias + res.float()).bfloat16()
+    assert (d.float() - want.float()).abs().max().item() <= 0.02 * want.float().abs().max().item()
+    # dgelu: product times gelu'(h)
+    h = torch.randn(m, n, device=DEV).bfloat16()
+    am = torch.zeros((), device=DEV)
+    d = gemm.gemm_fp8(a, E4, sia, b, E4, sib, torch.bfloat16, gelu_src=h, amax_out=am, tile=tile)
+    want = ref * gemm._gelu_tanh_grad(h.float())
+    assert (d.float() - want).abs().max().item() <= 0.02 * want.abs().max().item()
+    assert am.item() == d.float().abs().max().item()
+    # forward of fc1: h = x W^T + b stored in bf16, amax and FP8 copy of gelu(h) from the same launch
+    am = torch.zeros((), device=DEV)
+    q_scale = torch.tensor(16.0, device=DEV)
+    out8 = torch.empty(m, n, dtype=torch.uint8, device=DEV)
+    d = gemm.gemm_fp8(a, E4, sia, b, E4, sib, torch.bfloat16, bias=bias, amax_out=am, act='gelu', out8=out8, out8_qtype=E4,
+                      out8_scale=q_scale, tile=tile)
+    g = K.gelu(d)    # the stand-alone kernel on the stored values
+    assert am.item() == g.float().abs().max().item()
+    assert torch.equal(out8, cast.cast_to_fp8(g, E4, q_scale))
+    _status_ok()
+
+
 def test_add_to_fp8_bit_exact():
     for q in (E4, E5):
         for dt in (torch.float32, torch.float16, torch.bfloat16):
