@@ -12,6 +12,7 @@ import torch
 import torch.nn as nn
 import torch.utils.checkpoint
 
+from msamp.nn import fused_layers as FL
 from msamp.ops import nn as K
 
 
@@ -88,6 +89,10 @@ class Block(nn.Module):
 
     def forward(self, x, batch, seq):
         # x: [batch*seq, hidden]
+        if FL.fusable(self.qkv, self.proj, self.fc1, self.fc2):
+            # FP8 linears: each half of the block is one fused autograd function (msamp.nn.fused_layers)
+            x = FL.attention_sublayer(x, self.ln1, self.qkv, self.proj, batch, seq, self.n_head, causal=True)
+            return FL.mlp_sublayer(x, self.ln2, self.fc1, self.fc2)
         qkv = self.qkv(self.ln1(x)).view(batch, seq, 3, self.n_head, self.head_dim)
         o = K.attention_qkv(qkv, causal=True)
         x = x + self.proj(o.view(batch * seq, -1))
@@ -131,7 +136,7 @@ class GPT(nn.Module):
                 x = torch.utils.checkpoint.checkpoint(blk, x, batch, seq, use_reentrant=False)
             else:
                 x = blk(x, batch, seq)
-        logits = self.lm_head(self.ln_f(x))
+        logits = FL.ln_linear(x, self.ln_f, self.lm_head) if FL.fusable(self.lm_head) else self.lm_head(self.ln_f(x))
         if labels is None:
             return logits.view(batch, seq, -1)
         return K.cross_entropy(logits, labels.reshape(-1))

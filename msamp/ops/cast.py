@@ -107,7 +107,7 @@ def cast_to_fp8(x, qtype, scale, amax_out=None, scale_inv_out=None, amax_in=None
     if rescale:
         assert amax_in is not None
     if colsum_out is not None:
-        assert x.dim() == 2 and act is None and amax_in is None
+        assert x.dim() == 2 and act is None and not rescale
         assert colsum_out.dtype == torch.float32 and colsum_out.numel() == x.shape[1] and colsum_out.is_contiguous()
     if x.is_cuda:
         x = x.contiguous()
@@ -117,7 +117,7 @@ def cast_to_fp8(x, qtype, scale, amax_out=None, scale_inv_out=None, amax_in=None
             native.check(
                 native.lib().msamp_cast_to_fp8_colsum(
                     native.ptr(x), x.shape[0], x.shape[1], native.dt(x.dtype), native.ptr(out), native.fmt(qtype), native.ptr(scale),
-                    native.ptr(amax_out), native.ptr(scale_inv_out), native.ptr(colsum_out), native.stream()
+                    native.ptr(amax_out), native.ptr(scale_inv_out), native.ptr(colsum_out), native.ptr(amax_in), native.stream()
                 ), 'cast_to_fp8_colsum'
             )
             return out

@@ -151,30 +151,38 @@ __global__ void __launch_bounds__(kThreads) cast_to_fp8_kernel(const T* __restri
 // quantises dy.  A CTA owns a slab of 256 16-byte column vectors and walks down the rows, four rows in
 // flight per thread; every thread keeps the partial sums of its own columns in registers and adds
 // them to colsum (fp32, zeroed by the caller) once at the end.  cols must be a multiple of 16 bytes.
+constexpr int kColsumRows = 6;    // rows in flight per thread
 template <typename T, int FMT>
-__global__ void __launch_bounds__(kThreads) cast_rows_colsum_kernel(const T* __restrict__ x, uint8_t* __restrict__ out, int rows, int cols,
-                                                                     const float* __restrict__ scale_ptr, float* amax,
-                                                                     float* scale_inv_out, float* __restrict__ colsum) {
+__global__ void __launch_bounds__(kThreads, 4) cast_rows_colsum_kernel(const T* __restrict__ x, uint8_t* __restrict__ out, int rows, int cols,
+                                                                        float* scale_ptr, float* amax, float* scale_inv_out,
+                                                                        float* __restrict__ colsum, const float* amax_in, float fp_max) {
   __shared__ float red[32];
   constexpr int N = VecOf<T>::N;
-  const float scale = *scale_ptr;
+  constexpr int U = kColsumRows;
+  float scale = *scale_ptr;
+  if (amax_in != nullptr) {    // in-time scaling from an amax that the producer of x already reduced
+    const float a = *amax_in;
+    if ((a > 0.0f) && !isinf(a) && !isnan(a)) scale = msamp_compute_scale(a, scale, fp_max, 0);
+    if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) *scale_ptr = scale;
+  }
   if (scale_inv_out != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) *scale_inv_out = __frcp_rn(scale);
   const int cv = cols / N;                                   // vectors per row
   const int vec = blockIdx.y * kThreads + threadIdx.x;       // this thread's column vector
+  const int gx = (int)gridDim.x;
   float m = 0.0f;
   float cs[N];
 #pragma unroll
   for (int j = 0; j < N; ++j) cs[j] = 0.0f;
   if (vec < cv) {
     const Bytes16* xv = reinterpret_cast<const Bytes16*>(x);
-    for (int r = blockIdx.x; r < rows; r += 4 * gridDim.x) {
-      Bytes16 v[4];
+    for (int r = blockIdx.x; r < rows; r += U * gx) {
+      Bytes16 v[U];
 #pragma unroll
-      for (int u = 0; u < 4; ++u)
-        if (r + u * (int)gridDim.x < rows) v[u] = xv[(int64_t)(r + u * (int)gridDim.x) * cv + vec];
+      for (int u = 0; u < U; ++u)
+        if (r + u * gx < rows) v[u] = xv[(int64_t)(r + u * gx) * cv + vec];
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const int rr = r + u * (int)gridDim.x;
+      for (int u = 0; u < U; ++u) {
+        const int rr = r + u * gx;
         if (rr < rows) {
           const T* e = reinterpret_cast<const T*>(&v[u]);
           uint16_t o[N / 2];
@@ -507,8 +515,9 @@ MSAMP_API int msamp_cast_to_fp8(const void* x, int64_t n, int dtype, void* out, 
 
 // x is [rows, cols] row-major, out its FP8 copy; the column sums of x are ADDED to colsum (fp32 [cols],
 // zeroed by the caller).  cols * sizeof(element) must be a multiple of 16 and x, out 16- / 8-byte aligned.
-MSAMP_API int msamp_cast_to_fp8_colsum(const void* x, int rows, int cols, int dtype, void* out, int fmt, const float* scale,
-                                       float* amax, float* scale_inv_out, float* colsum, void* stream_) {
+// With amax_in non-null (it must differ from amax) the scale is first derived from it by the power-of-two rule and stored to *scale.
+MSAMP_API int msamp_cast_to_fp8_colsum(const void* x, int rows, int cols, int dtype, void* out, int fmt, float* scale,
+                                       float* amax, float* scale_inv_out, float* colsum, const float* amax_in, void* stream_) {
   cudaStream_t stream = (cudaStream_t)stream_;
   MSAMP_REQUIRE(rows >= 0 && cols >= 0 && scale != nullptr && colsum != nullptr && out != nullptr, "msamp_cast_to_fp8_colsum: bad arguments");
   const int esize = dtype == DT_F32 ? 4 : 2;
@@ -517,15 +526,15 @@ MSAMP_API int msamp_cast_to_fp8_colsum(const void* x, int rows, int cols, int dt
   if ((int64_t)rows * cols == 0) return MSAMP_OK;
   const int cv = cols * esize / 16;
   const int slabs = (cv + kThreads - 1) / kThreads;
-  int per_slab = msamp_sm_count() * 6 / slabs;
+  int per_slab = msamp_sm_count() * 4 / slabs;    // four CTAs are resident per SM (64 registers per thread)
   if (per_slab < 1) per_slab = 1;
-  int gx = (rows + 3) / 4;
+  int gx = (rows + kColsumRows - 1) / kColsumRows;
   if (gx > per_slab) gx = per_slab;
   if (gx < 1) gx = 1;
   dim3 grid((unsigned)gx, (unsigned)slabs, 1);
   MSAMP_DISPATCH_HP(dtype, T, {
     MSAMP_DISPATCH_FP8(fmt, F, {
-      cast_rows_colsum_kernel<T, F><<<grid, kThreads, 0, stream>>>((const T*)x, (uint8_t*)out, rows, cols, scale, amax, scale_inv_out, colsum);
+      cast_rows_colsum_kernel<T, F><<<grid, kThreads, 0, stream>>>((const T*)x, (uint8_t*)out, rows, cols, scale, amax, scale_inv_out, colsum, amax_in, fp8_max(F));
     });
   });
   return msamp_check_launch("msamp_cast_to_fp8_colsum");

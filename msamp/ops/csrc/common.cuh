@@ -114,18 +114,20 @@ __device__ __forceinline__ float abs_nan_to_inf(float v) {
   return (a != a) ? __int_as_float(0x7f800000) : a;
 }
 
-// GeLU, tanh form, and its derivative.  One definition for the elementwise kernels and the GEMM epilogues,
-// so that a fused path produces the bits of the separate kernels.
-__device__ __forceinline__ float gelu_f(float x) {
+// GeLU, tanh form, and its derivative, written with the logistic function: 0.5 (1 + tanh(u)) == 1 / (1 + exp(-2u)).
+// One exponential and one approximate division per element keep it cheap enough for a GEMM epilogue.  One definition
+// for the elementwise kernels and the GEMM epilogues, so that a fused path produces the bits of the separate kernels.
+__device__ __forceinline__ float gelu_sigmoid_2u(float x) {
   const float k0 = 0.7978845608028654f, k1 = 0.044715f;
-  float u = k0 * (x + k1 * x * x * x);
-  return 0.5f * x * (1.0f + tanhf(u));
+  const float u = k0 * (x + k1 * x * x * x);
+  return __fdividef(1.0f, 1.0f + __expf(-2.0f * u));
 }
+__device__ __forceinline__ float gelu_f(float x) { return x * gelu_sigmoid_2u(x); }
 __device__ __forceinline__ float gelu_grad_f(float x) {
   const float k0 = 0.7978845608028654f, k1 = 0.044715f;
-  float u = k0 * (x + k1 * x * x * x);
-  float th = tanhf(u);
-  return 0.5f * (1.0f + th) + 0.5f * x * (1.0f - th * th) * k0 * (1.0f + 3.0f * k1 * x * x);
+  const float s = gelu_sigmoid_2u(x);
+  // d/dx [x s(2u)] = s + x * 2 s (1 - s) * du/dx
+  return s + 2.0f * x * s * (1.0f - s) * k0 * (1.0f + 3.0f * k1 * x * x);
 }
 
 __device__ __forceinline__ float warp_max(float v) {

@@ -26,6 +26,12 @@
 namespace {
 using namespace gemm;
 
+// warp 0: TMA producer, warp 1: MMA issuer, warps 2..9: epilogue.  Two epilogue warps share each TMEM lane quarter
+// (a warp may only touch the lanes 32 * (warp % 4) ...) and split the columns of the tile between them: with GeLU,
+// its derivative, the skip connection or the quantised copy in the epilogue, four warps alone need longer for a tile
+// than the tensor core needs for the next one.
+constexpr int kThreadsEpi8 = 320;
+
 struct GemmArgs {
   void* d;                    // [M,N] out_dtype, row pitch ldd elements
   const void* bias;           // [N] or null
@@ -36,6 +42,7 @@ struct GemmArgs {
   float* amax_out;            // max|D| (or max|gelu(D)| with act == 1); zeroed by the caller
   uint8_t* d8;                // optional FP8 copy of act(D) * (*d8_scale), row pitch ld8 bytes
   const float* d8_scale;
+  float* d8_scale_inv_out;    // optional: receives 1 / *d8_scale
   unsigned int* status;
   unsigned long long* stats;  // optional [4 * gridDim.x] cycle counters for tuning: producer wait, MMA wait for data, MMA wait for TMEM, total
   int64_t ldd, ldr, ldg, ld8;
@@ -95,7 +102,7 @@ __device__ __forceinline__ void store_fp8_chunk(uint8_t* dst, const float (&w)[3
 }
 
 template <int BN, bool PAIR, typename OutT, int NSTAGES = 0>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+__global__ void __launch_bounds__(kThreadsEpi8, 1)
 gemm_fp8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b, const GemmArgs p) {
   using C = Tile<BN, PAIR, NSTAGES>;
   extern __shared__ uint8_t smem_raw[];
@@ -130,7 +137,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
     }
     for (int b = 0; b < 2; ++b) {
       tc5::mbar_init(tfull_bar(b), 1);
-      tc5::mbar_init(tempty_bar(b), PAIR ? 8 : 4);    // the epilogue warps of every CTA that reads this accumulator
+      tc5::mbar_init(tempty_bar(b), PAIR ? 16 : 8);    // the epilogue warps of every CTA that reads this accumulator
     }
     *abort_flag = 0;
     tc5::mbar_fence_init();
@@ -262,9 +269,11 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
     }
   } else {
     // ------------------------------------------------------------------ epilogue (4 warps per CTA)
-    const int q = warp & 3;    // TMEM lane quarter this warp may access
+    const int q = warp & 3;             // TMEM lane quarter this warp may access
+    const int chalf = (warp - 2) >> 2;    // which half of the tile's columns this warp handles
     const float alpha = (*p.scale_inv_a) * (*p.scale_inv_b);
     const float q_scale = p.d8 ? *p.d8_scale : 1.0f;
+    if (p.d8_scale_inv_out != nullptr && blockIdx.x == 0 && threadIdx.x == 64) *p.d8_scale_inv_out = __frcp_rn(q_scale);
     OutT* D = reinterpret_cast<OutT*>(p.d);
     const OutT* R = reinterpret_cast<const OutT*>(p.residual);
     const OutT* G = reinterpret_cast<const OutT*>(p.gelu_src);
@@ -282,12 +291,20 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
       const int n0 = ni * BN;
       const int buf = lt & 1;
       const uint32_t aph = (lt >> 1) & 1;
+      const int row = m0 + q * 32 + lane;
+      if ((R != nullptr || G != nullptr) && row < p.M) {
+        // While the main loop of this tile is still running, pull this thread's slice of the residual / GeLU
+        // source into L2, so that the loads below do not wait for HBM one chunk at a time.
+        const OutT* src = R != nullptr ? R + (int64_t)row * p.ldr + n0 : G + (int64_t)row * p.ldg + n0;
+        const int cols_here = (p.N - n0) < BN ? (p.N - n0) : BN;
+        for (int b = 0; b < cols_here * (int)sizeof(OutT); b += 128)
+          asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const char*>(src) + b));
+      }
       if (!tc5::mbar_wait(tfull_bar(buf), aph, abort_flag, p.status, 1u)) break;
       tc5::fence_after_sync();
-      const int row = m0 + q * 32 + lane;
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN);
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
+      for (int c = chalf * (BN / 64); c < (chalf + 1) * (BN / 64); ++c) {
         uint32_t r[32];
         tc5::tmem_ld32(taddr + (uint32_t)(c * 32), r);
         tc5::tmem_ld_wait();
@@ -301,8 +318,16 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
           if (p.bias != nullptr) {
             if (p.bias_dtype == DT_F32) {
               const float* b = reinterpret_cast<const float*>(p.bias) + col;
+              if (valid == 32 && (reinterpret_cast<uintptr_t>(b) & 15) == 0) {
 #pragma unroll
-              for (int j = 0; j < 32; ++j) if (j < valid) v[j] += __ldg(b + j);
+                for (int j = 0; j < 32; j += 4) {
+                  const float4 t = __ldg(reinterpret_cast<const float4*>(b + j));
+                  v[j] += t.x; v[j + 1] += t.y; v[j + 2] += t.z; v[j + 3] += t.w;
+                }
+              } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) if (j < valid) v[j] += __ldg(b + j);
+              }
             } else if (p.bias_dtype == DT_BF16) {
               const __nv_bfloat16* b = reinterpret_cast<const __nv_bfloat16*>(p.bias) + col;
 #pragma unroll
@@ -384,7 +409,7 @@ int max_pairs(int smem_bytes) {
   if (cached[dev] == 0) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(2 * (unsigned)msamp_sm_count(), 1, 1);
-    cfg.blockDim = dim3(kGemmThreads, 1, 1);
+    cfg.blockDim = dim3(kThreadsEpi8, 1, 1);
     cfg.dynamicSmemBytes = (size_t)smem_bytes;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -424,7 +449,7 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmArgs& p, int 
     if (num_tiles < pairs) pairs = num_tiles;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(2 * (unsigned)pairs, 1, 1);
-    cfg.blockDim = dim3(kGemmThreads, 1, 1);
+    cfg.blockDim = dim3(kThreadsEpi8, 1, 1);
     cfg.dynamicSmemBytes = C::SMEM_BYTES;
     cfg.stream = stream;
     cudaLaunchAttribute attr[2];
@@ -445,7 +470,7 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmArgs& p, int 
   int grid = msamp_sm_count();
   if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
   if (num_tiles < grid) grid = num_tiles;
-  gemm_fp8_kernel<BN, PAIR, OutT, NSTAGES><<<grid, kGemmThreads, C::SMEM_BYTES, stream>>>(ma, mb, p);
+  gemm_fp8_kernel<BN, PAIR, OutT, NSTAGES><<<grid, kThreadsEpi8, C::SMEM_BYTES, stream>>>(ma, mb, p);
   return msamp_check_launch("gemm_fp8_kernel");
 }
 
@@ -468,6 +493,7 @@ struct MsampGemmDesc {
   float* amax_out;
   void* d8;
   const float* d8_scale;
+  float* d8_scale_inv_out;
   int64_t lda, ldb, ldd, ldr, ldg, ld8;
   int M, N, K;
   int a_fmt, b_fmt, d8_fmt;
@@ -510,7 +536,7 @@ MSAMP_API int msamp_gemm_fp8_ex(const MsampGemmDesc* g, void* stream_) {
   GemmArgs p;
   p.d = g->d; p.bias = g->bias; p.residual = g->residual; p.gelu_src = g->gelu_src;
   p.scale_inv_a = g->scale_inv_a; p.scale_inv_b = g->scale_inv_b; p.amax_out = g->amax_out;
-  p.d8 = (uint8_t*)g->d8; p.d8_scale = g->d8_scale;
+  p.d8 = (uint8_t*)g->d8; p.d8_scale = g->d8_scale; p.d8_scale_inv_out = g->d8 ? g->d8_scale_inv_out : nullptr;
   p.status = msamp_device_status_ptr();
   p.stats = g->stats;
   p.ldd = g->ldd; p.ldr = g->ldr; p.ldg = g->ldg; p.ld8 = g->ld8;

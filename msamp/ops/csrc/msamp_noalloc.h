@@ -18,6 +18,10 @@
 //   * The first call on each device looks up the array's device address with cudaGetSymbolAddress
 //     (the array's name is not a device pointer in host code).  That first call should therefore
 //     happen before any stream capture begins on that device.
+//     The address is remembered per device for the life of the process; after cudaDeviceReset (or
+//     any other re-creation of the device's context) it is stale, so reload the library before calling again.
+//   * dy, x, dx and gamma must be 16-byte aligned (the kernels use 16-byte accesses); a misaligned
+//     pointer is rejected with MSAMP_EINVAL (1) before anything is launched.
 //   * The function itself calls no cudaMalloc / cudaFree and no allocating library routine.
 //   * All calls share the one array, which keeps the last call's contents.  Nothing in it has to
 //     start at zero (every slice that is read was written by the same call), but two calls that

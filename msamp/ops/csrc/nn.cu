@@ -1,6 +1,8 @@
 // Non-GEMM kernels of the transformer block: LayerNorm forward/backward, GeLU forward/backward
 // (tanh form), and fused softmax cross-entropy (loss + in-place logit gradient).  All are
 // HBM-bandwidth bound: one pass over the data with 16-byte accesses, statistics in fp32.
+#include <atomic>
+
 #include "common.cuh"
 #include "msamp_noalloc.h"
 
@@ -34,15 +36,37 @@ __device__ __forceinline__ void ld_params(const void* p, int c, float (&o)[N]) {
   }
 }
 
+// Optional quantised output of the forward kernel (all pointers may be null).
+struct LnQuant {
+  uint8_t* y8;             // [rows, cols] e4m3 copy of the output
+  float* scale;            // quantisation scale (read; rewritten from amax_in when that is given)
+  const float* amax_in;    // max|y| from an earlier pass: the scale is derived from it by the power-of-two rule
+  float* amax_out;         // receives max|y| (zeroed by the host wrapper)
+  float* scale_inv_out;    // receives 1 / scale
+};
+
 template <typename T, typename P, int THREADS>
 __global__ void __launch_bounds__(THREADS) layernorm_fwd_kernel(const T* __restrict__ x, const void* __restrict__ gamma,
                                                                  const void* __restrict__ beta, T* __restrict__ y,
                                                                  float* __restrict__ mean_out, float* __restrict__ rstd_out, int rows,
-                                                                 int cols, float eps) {
+                                                                 int cols, float eps, LnQuant q) {
   __shared__ float red[32];
   __shared__ float stat[2];
   constexpr int N = 16 / sizeof(T);
   const int nvec = cols / N;
+  // Optional e4m3 copy of the output (quantised from the values as rounded to T, i.e. the bits a separate
+  // cast of y would produce) and / or max|y|.
+  float q_scale = 1.0f;
+  if (q.scale != nullptr) {
+    q_scale = *q.scale;
+    if (q.amax_in != nullptr) {
+      const float a = *q.amax_in;
+      if ((a > 0.0f) && !isinf(a) && !isnan(a)) q_scale = msamp_compute_scale(a, q_scale, 448.0f, 0);
+      if (blockIdx.x == 0 && threadIdx.x == 0) *q.scale = q_scale;
+    }
+    if (q.scale_inv_out != nullptr && blockIdx.x == 0 && threadIdx.x == 0) *q.scale_inv_out = __frcp_rn(q_scale);
+  }
+  float amax = 0.0f;
   for (int row = blockIdx.x; row < rows; row += gridDim.x) {
     const T* xr = x + (int64_t)row * cols;
     Bytes16 v[LN_VPT];
@@ -83,6 +107,7 @@ __global__ void __launch_bounds__(THREADS) layernorm_fwd_kernel(const T* __restr
       rstd_out[row] = rstd;
     }
     T* yr = y + (int64_t)row * cols;
+    uint8_t* y8r = q.y8 + (int64_t)row * cols;
 #pragma unroll
     for (int k = 0; k < LN_VPT; ++k) {
       int i = threadIdx.x + k * THREADS;
@@ -100,50 +125,96 @@ __global__ void __launch_bounds__(THREADS) layernorm_fwd_kernel(const T* __restr
         T* oe = reinterpret_cast<T*>(&o);
 #pragma unroll
         for (int j = 0; j < N; ++j) oe[j] = from_f32<T>((to_f32<T>(e[j]) - mean) * rstd * g[j] + b[j]);
-        reinterpret_cast<Bytes16*>(yr)[i] = o;
+        if (y != nullptr) reinterpret_cast<Bytes16*>(yr)[i] = o;
+        if (q.amax_out != nullptr || q.y8 != nullptr) {
+          uint16_t o8[N / 2];
+#pragma unroll
+          for (int j = 0; j < N; j += 2) {
+            const float a0 = to_f32<T>(oe[j]), a1 = to_f32<T>(oe[j + 1]);
+            amax = fmaxf(amax, fmaxf(abs_nan_to_inf(a0), abs_nan_to_inf(a1)));
+            o8[j / 2] = f32x2_to_fp8x2<FMT_E4M3>(a0 * q_scale, a1 * q_scale);
+          }
+          if (q.y8 != nullptr) {
+            if (N == 8) reinterpret_cast<Bytes8*>(y8r)[i] = *reinterpret_cast<Bytes8*>(o8);
+            else        reinterpret_cast<uint32_t*>(y8r)[i] = *reinterpret_cast<uint32_t*>(o8);
+          }
+        }
       }
     }
     __syncthreads();
   }
+  if (q.amax_out != nullptr) {
+    amax = block_max(amax, red);
+    if (threadIdx.x == 0) atomic_max_nonneg(q.amax_out, amax);
+  }
 }
 
-// Backward: dx per row; dgamma / dbeta partial sums per CTA (each thread owns fixed columns, whose
-// gamma it keeps in registers for all rows), written to part[gridDim.x][2][cols] and reduced by a
-// second kernel.
-template <typename T, typename P, int THREADS>
-__global__ void __launch_bounds__(THREADS) layernorm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x,
-                                                                 const void* __restrict__ gamma, const float* __restrict__ mean,
-                                                                 const float* __restrict__ rstd, T* __restrict__ dx,
-                                                                 float* __restrict__ part, int rows, int cols) {
+// Block-wide sums of two values at once (one round of barriers); results valid in every thread.
+__device__ __forceinline__ float2 block_sum2(float a, float b, float2* red) {
+  a = warp_sum(a);
+  b = warp_sum(b);
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  if (lane == 0) red[w] = make_float2(a, b);
+  __syncthreads();
+  const int nw = (blockDim.x + 31) >> 5;
+  float2 v = (lane < nw) ? red[lane] : make_float2(0.0f, 0.0f);
+  v.x = warp_sum(v.x);
+  v.y = warp_sum(v.y);
+  __syncthreads();
+  return v;
+}
+
+// Backward: dx per row (+ the skip-connection gradient dres, + max|dx|); dgamma / dbeta partial sums per CTA (each
+// thread owns fixed columns, whose gamma it keeps in registers for all rows), written to part[gridDim.x][2][cols] and
+// reduced by a second kernel.  A CTA of 256 threads owns one row at a time and loads the next row's x, dy and dres
+// while it works on the current one, so that two rows per CTA are in flight.
+constexpr int LN_BWD_THREADS = 256;
+template <typename T, typename P, int VPT>
+__global__ void __launch_bounds__(LN_BWD_THREADS, (VPT <= 2 ? 2 : 1)) layernorm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x,
+                                                                          const void* __restrict__ gamma, const float* __restrict__ mean,
+                                                                          const float* __restrict__ rstd, T* __restrict__ dx,
+                                                                          float* __restrict__ part, int rows, int cols,
+                                                                          const T* __restrict__ dres, float* amax_out) {
+  __shared__ float2 red2[32];
   __shared__ float red[32];
-  __shared__ float stat[2];
   constexpr int N = 16 / sizeof(T);
+  constexpr int THREADS = LN_BWD_THREADS;
   const int nvec = cols / N;
-  float dg[LN_VPT][N], db[LN_VPT][N], gm[LN_VPT][N];
+  float amax = 0.0f;
+  float dg[VPT][N], db[VPT][N], gm[VPT][N];
 #pragma unroll
-  for (int k = 0; k < LN_VPT; ++k) {
+  for (int k = 0; k < VPT; ++k) {
     int i = threadIdx.x + k * THREADS;
 #pragma unroll
     for (int j = 0; j < N; ++j) dg[k][j] = db[k][j] = gm[k][j] = 0.0f;
     if (i < nvec) ld_params<P, N>(gamma, i * N, gm[k]);
   }
-
-  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
-    const T* xr = x + (int64_t)row * cols;
-    const T* dyr = dy + (int64_t)row * cols;
-    const float mu = mean[row], rs = rstd[row];
-    Bytes16 vx[LN_VPT], vd[LN_VPT];
-    float s1 = 0.0f, s2 = 0.0f;    // sum(g*dy), sum(g*dy*xhat)
+  Bytes16 vx[VPT], vd[VPT], vr[VPT], nx[VPT], nd[VPT], nr[VPT];
+  float mu = 0.0f, rs = 0.0f, nmu = 0.0f, nrs = 0.0f;
+  auto load_row = [&](int row, Bytes16 (&ox)[VPT], Bytes16 (&od)[VPT], Bytes16 (&orr)[VPT], float& omu, float& ors) {
+    const Bytes16* xr = reinterpret_cast<const Bytes16*>(x + (int64_t)row * cols);
+    const Bytes16* dyr = reinterpret_cast<const Bytes16*>(dy + (int64_t)row * cols);
+    const Bytes16* rr = reinterpret_cast<const Bytes16*>(dres + (int64_t)row * cols);
 #pragma unroll
-    for (int k = 0; k < LN_VPT; ++k) {
+    for (int k = 0; k < VPT; ++k) {
       int i = threadIdx.x + k * THREADS;
       if (i < nvec) {
-        vx[k] = reinterpret_cast<const Bytes16*>(xr)[i];
-        vd[k] = reinterpret_cast<const Bytes16*>(dyr)[i];
+        ox[k] = xr[i];
+        od[k] = dyr[i];
+        if (dres != nullptr) orr[k] = rr[i];
       }
     }
+    omu = mean[row];
+    ors = rstd[row];
+  };
+  int row = blockIdx.x;
+  if (row < rows) load_row(row, vx, vd, vr, mu, rs);
+  for (; row < rows; row += gridDim.x) {
+    const int next = row + gridDim.x;
+    if (next < rows) load_row(next, nx, nd, nr, nmu, nrs);
+    float s1 = 0.0f, s2 = 0.0f;    // sum(g*dy), sum(g*dy*xhat)
 #pragma unroll
-    for (int k = 0; k < LN_VPT; ++k) {
+    for (int k = 0; k < VPT; ++k) {
       int i = threadIdx.x + k * THREADS;
       if (i < nvec) {
         const T* ex = reinterpret_cast<const T*>(&vx[k]);
@@ -160,36 +231,47 @@ __global__ void __launch_bounds__(THREADS) layernorm_bwd_kernel(const T* __restr
         }
       }
     }
-    s1 = block_sum(s1, red);
-    if (threadIdx.x == 0) stat[0] = s1 / cols;
-    s2 = block_sum(s2, red);
-    if (threadIdx.x == 0) stat[1] = s2 / cols;
-    __syncthreads();
-    const float m1 = stat[0], m2 = stat[1];
+    const float2 tot = block_sum2(s1, s2, red2);
+    const float m1 = tot.x / cols, m2 = tot.y / cols;
     T* dxr = dx + (int64_t)row * cols;
 #pragma unroll
-    for (int k = 0; k < LN_VPT; ++k) {
+    for (int k = 0; k < VPT; ++k) {
       int i = threadIdx.x + k * THREADS;
       if (i < nvec) {
         const T* ex = reinterpret_cast<const T*>(&vx[k]);
         const T* ed = reinterpret_cast<const T*>(&vd[k]);
+        const T* er = reinterpret_cast<const T*>(&vr[k]);
         Bytes16 o;
         T* oe = reinterpret_cast<T*>(&o);
 #pragma unroll
         for (int j = 0; j < N; ++j) {
           float xh = (to_f32<T>(ex[j]) - mu) * rs;
           float gd = to_f32<T>(ed[j]) * gm[k][j];
-          oe[j] = from_f32<T>(rs * (gd - m1 - xh * m2));
+          float r = rs * (gd - m1 - xh * m2);
+          if (dres != nullptr) r += to_f32<T>(er[j]);    // gradient of the skip connection around the LayerNorm branch
+          oe[j] = from_f32<T>(r);
+          if (amax_out != nullptr) amax = fmaxf(amax, abs_nan_to_inf(to_f32<T>(oe[j])));
         }
         reinterpret_cast<Bytes16*>(dxr)[i] = o;
       }
     }
-    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+      vx[k] = nx[k];
+      vd[k] = nd[k];
+      vr[k] = nr[k];
+    }
+    mu = nmu;
+    rs = nrs;
+  }
+  if (amax_out != nullptr) {
+    amax = block_max(amax, red);
+    if (threadIdx.x == 0) atomic_max_nonneg(amax_out, amax);
   }
   float* pg = part + (int64_t)blockIdx.x * 2 * cols;
   float* pb = pg + cols;
 #pragma unroll
-  for (int k = 0; k < LN_VPT; ++k) {
+  for (int k = 0; k < VPT; ++k) {
     int i = threadIdx.x + k * THREADS;
     if (i < nvec) {
 #pragma unroll
@@ -199,6 +281,19 @@ __global__ void __launch_bounds__(THREADS) layernorm_bwd_kernel(const T* __restr
       }
     }
   }
+}
+
+template <typename T, typename P>
+void launch_ln_bwd(int grid, cudaStream_t stream, const void* dy, const void* x, const void* gamma, const float* mean, const float* rstd,
+                   void* dx, float* part, int rows, int cols, const void* dres, float* amax_out) {
+  const int nvec = cols / (16 / (int)sizeof(T));
+  const int vpt = (nvec + LN_BWD_THREADS - 1) / LN_BWD_THREADS;
+  if (vpt <= 1)
+    layernorm_bwd_kernel<T, P, 1><<<grid, LN_BWD_THREADS, 0, stream>>>((const T*)dy, (const T*)x, gamma, mean, rstd, (T*)dx, part, rows, cols, (const T*)dres, amax_out);
+  else if (vpt == 2)
+    layernorm_bwd_kernel<T, P, 2><<<grid, LN_BWD_THREADS, 0, stream>>>((const T*)dy, (const T*)x, gamma, mean, rstd, (T*)dx, part, rows, cols, (const T*)dres, amax_out);
+  else
+    layernorm_bwd_kernel<T, P, 4><<<grid, LN_BWD_THREADS, 0, stream>>>((const T*)dy, (const T*)x, gamma, mean, rstd, (T*)dx, part, rows, cols, (const T*)dres, amax_out);
 }
 
 // Column sums of the per-CTA partials: a block of 32 x 8 threads owns 32 columns; the 8 thread rows
@@ -366,45 +461,70 @@ __global__ void __launch_bounds__(512) xent_bwd_kernel(T* __restrict__ logits, c
 
 MSAMP_API int msamp_layernorm_max_cols(int dtype) { return LN_THREADS * LN_VPT * (dtype == DT_F32 ? 4 : 8); }
 
-MSAMP_API int msamp_layernorm_fwd(const void* x, const void* gamma, const void* beta, int dtype, int pdtype, void* y, float* mean,
-                                  float* rstd, int rows, int cols, float eps, void* stream_) {
+#define MSAMP_LN_ALIGNED(ptr) ((reinterpret_cast<uintptr_t>(ptr) & 15) == 0)
+
+// y (may be null) receives LayerNorm(x) in the activation dtype.  y8 (may be null) receives its e4m3 copy,
+// quantised with *q_scale; with amax_in non-null the scale is first derived from *amax_in by the
+// power-of-two rule and stored to *q_scale; amax_out (nullable, cleared here) receives max|y|;
+// scale_inv_out (nullable) receives 1 / scale.  With y and y8 both null the launch only produces the
+// row statistics and max|y| (the first pass of in-time scaling).
+MSAMP_API int msamp_layernorm_fwd_q(const void* x, const void* gamma, const void* beta, int dtype, int pdtype, void* y, float* mean,
+                                    float* rstd, int rows, int cols, float eps, void* y8, float* q_scale, const float* amax_in,
+                                    float* amax_out, float* scale_inv_out, void* stream_) {
   cudaStream_t stream = (cudaStream_t)stream_;
   MSAMP_REQUIRE(rows >= 0 && cols > 0, "layernorm: bad shape");
   MSAMP_REQUIRE(cols <= msamp_layernorm_max_cols(dtype) && cols % (dtype == DT_F32 ? 4 : 8) == 0,
                 "layernorm: cols=%d must be a multiple of the 16-byte vector and at most %d", cols, msamp_layernorm_max_cols(dtype));
+  MSAMP_REQUIRE(MSAMP_LN_ALIGNED(x) && MSAMP_LN_ALIGNED(y) && MSAMP_LN_ALIGNED(gamma) && MSAMP_LN_ALIGNED(beta) && MSAMP_LN_ALIGNED(y8),
+                "layernorm: x, y, y8, gamma and beta must be 16-byte aligned");
+  MSAMP_REQUIRE(y8 == nullptr || q_scale != nullptr, "layernorm: a quantised output needs its scale");
+  if (amax_out) cudaMemsetAsync(amax_out, 0, sizeof(float), stream);
   if (rows == 0) return MSAMP_OK;
+  LnQuant q;
+  q.y8 = (uint8_t*)y8; q.scale = q_scale; q.amax_in = amax_in; q.amax_out = amax_out; q.scale_inv_out = scale_inv_out;
   const bool narrow = cols <= 128 * LN_VPT * (dtype == DT_F32 ? 4 : 8);
   int cap = msamp_sm_count() * (narrow ? 16 : 8);
   int grid = rows < cap ? rows : cap;
   MSAMP_LN_DISPATCH(dtype, pdtype, T, P, {
     if (narrow)
-      layernorm_fwd_kernel<T, P, 128><<<grid, 128, 0, stream>>>((const T*)x, gamma, beta, (T*)y, mean, rstd, rows, cols, eps);
+      layernorm_fwd_kernel<T, P, 128><<<grid, 128, 0, stream>>>((const T*)x, gamma, beta, (T*)y, mean, rstd, rows, cols, eps, q);
     else
-      layernorm_fwd_kernel<T, P, 256><<<grid, 256, 0, stream>>>((const T*)x, gamma, beta, (T*)y, mean, rstd, rows, cols, eps);
+      layernorm_fwd_kernel<T, P, 256><<<grid, 256, 0, stream>>>((const T*)x, gamma, beta, (T*)y, mean, rstd, rows, cols, eps, q);
   });
   return msamp_check_launch("msamp_layernorm_fwd");
+}
+
+MSAMP_API int msamp_layernorm_fwd(const void* x, const void* gamma, const void* beta, int dtype, int pdtype, void* y, float* mean,
+                                  float* rstd, int rows, int cols, float eps, void* stream_) {
+  return msamp_layernorm_fwd_q(x, gamma, beta, dtype, pdtype, y, mean, rstd, rows, cols, eps, nullptr, nullptr, nullptr, nullptr, nullptr,
+                               stream_);
 }
 
 // part: scratch of msamp_layernorm_bwd_parts() * 2 * cols floats owned by the caller.
 MSAMP_API int msamp_layernorm_bwd_parts() { return msamp_sm_count() * 4; }
 
-MSAMP_API int msamp_layernorm_bwd(const void* dy, const void* x, const void* gamma, int dtype, int pdtype, const float* mean,
-                                  const float* rstd, void* dx, void* dgamma, void* dbeta, float* part, int rows, int cols,
-                                  void* stream_) {
+// dres (nullable, [rows, cols] of the activation dtype) is added to dx: the gradient that reaches x through the skip
+// connection around the LayerNorm branch.  amax_out (nullable, cleared here) receives max|dx| of the stored values.
+MSAMP_API int msamp_layernorm_bwd_ex(const void* dy, const void* x, const void* gamma, int dtype, int pdtype, const float* mean,
+                                     const float* rstd, void* dx, void* dgamma, void* dbeta, float* part, int rows, int cols,
+                                     const void* dres, float* amax_out, void* stream_) {
   cudaStream_t stream = (cudaStream_t)stream_;
   MSAMP_REQUIRE(rows > 0 && cols > 0, "layernorm_bwd: bad shape");
   MSAMP_REQUIRE(cols <= msamp_layernorm_max_cols(dtype) && cols % (dtype == DT_F32 ? 4 : 8) == 0, "layernorm_bwd: unsupported cols=%d", cols);
-  int nparts = msamp_layernorm_bwd_parts();
+  MSAMP_REQUIRE(MSAMP_LN_ALIGNED(dy) && MSAMP_LN_ALIGNED(x) && MSAMP_LN_ALIGNED(dx) && MSAMP_LN_ALIGNED(gamma) && MSAMP_LN_ALIGNED(dres),
+                "layernorm_bwd: dy, x, dx, dres and gamma must be 16-byte aligned");
+  if (amax_out) cudaMemsetAsync(amax_out, 0, sizeof(float), stream);
+  int nparts = msamp_sm_count() * 2;    // two CTAs of 256 threads are resident per SM; never more than msamp_layernorm_bwd_parts()
   int grid = rows < nparts ? rows : nparts;
-  const bool narrow = cols <= 128 * LN_VPT * (dtype == DT_F32 ? 4 : 8);
-  MSAMP_LN_DISPATCH(dtype, pdtype, T, P, {
-    if (narrow)
-      layernorm_bwd_kernel<T, P, 128><<<grid, 128, 0, stream>>>((const T*)dy, (const T*)x, gamma, mean, rstd, (T*)dx, part, rows, cols);
-    else
-      layernorm_bwd_kernel<T, P, 256><<<grid, 256, 0, stream>>>((const T*)dy, (const T*)x, gamma, mean, rstd, (T*)dx, part, rows, cols);
-  });
+  MSAMP_LN_DISPATCH(dtype, pdtype, T, P, { launch_ln_bwd<T, P>(grid, stream, dy, x, gamma, mean, rstd, dx, part, rows, cols, dres, amax_out); });
   layernorm_reduce_kernel<<<(cols + 31) / 32, 256, 0, stream>>>(part, grid, cols, dgamma, dbeta, pdtype);
   return msamp_check_launch("msamp_layernorm_bwd");
+}
+
+MSAMP_API int msamp_layernorm_bwd(const void* dy, const void* x, const void* gamma, int dtype, int pdtype, const float* mean,
+                                  const float* rstd, void* dx, void* dgamma, void* dbeta, float* part, int rows, int cols,
+                                  void* stream_) {
+  return msamp_layernorm_bwd_ex(dy, x, gamma, dtype, pdtype, mean, rstd, dx, dgamma, dbeta, part, rows, cols, nullptr, nullptr, stream_);
 }
 
 // ---- allocation-free LayerNorm backward ---------------------------------------------------------
@@ -423,34 +543,30 @@ MSAMP_API int msamp_layernorm_bwd_static(const void* dy, const void* x, const vo
   }
   MSAMP_REQUIRE(cols <= msamp_layernorm_max_cols(dtype) && cols % (dtype == DT_F32 ? 4 : 8) == 0,
                 "layernorm_bwd_static: unsupported cols=%d", cols);
+  MSAMP_REQUIRE(MSAMP_LN_ALIGNED(dy) && MSAMP_LN_ALIGNED(x) && MSAMP_LN_ALIGNED(dx) && MSAMP_LN_ALIGNED(gamma),
+                "layernorm_bwd_static: dy, x, dx and gamma must be 16-byte aligned");
   // In host code the array's name is only a handle; the device address has to be asked for, once
   // per device, with that device current.
-  static float* scratch_of_device[64] = {nullptr};
+  static std::atomic<float*> scratch_of_device[64];    // zero-initialised; two threads racing here store the same address
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
     msamp_set_error("layernorm_bwd_static: cannot identify the current device");
     return MSAMP_EINVAL;
   }
-  if (scratch_of_device[dev] == nullptr) {
+  if (scratch_of_device[dev].load(std::memory_order_acquire) == nullptr) {
     float* ptr = nullptr;
     cudaError_t e = cudaGetSymbolAddress((void**)&ptr, g_ln_static_part);
     if (e != cudaSuccess || ptr == nullptr) {
       msamp_set_error("layernorm_bwd_static: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
       return MSAMP_ELAUNCH;
     }
-    scratch_of_device[dev] = ptr;
+    scratch_of_device[dev].store(ptr, std::memory_order_release);
   }
-  float* part = scratch_of_device[dev];
+  float* part = scratch_of_device[dev].load(std::memory_order_acquire);
   const int grid = rows < MSAMP_LN_STATIC_PARTS ? rows : MSAMP_LN_STATIC_PARTS;
   // Each of the `grid` CTAs overwrites its whole slice of the scratch and the reduction reads
   // exactly those slices, so leftovers of an earlier call never need clearing.
-  const bool narrow = cols <= 128 * LN_VPT * (dtype == DT_F32 ? 4 : 8);
-  MSAMP_LN_DISPATCH(dtype, pdtype, T, P, {
-    if (narrow)
-      layernorm_bwd_kernel<T, P, 128><<<grid, 128, 0, stream>>>((const T*)dy, (const T*)x, gamma, mean, rstd, (T*)dx, part, rows, cols);
-    else
-      layernorm_bwd_kernel<T, P, 256><<<grid, 256, 0, stream>>>((const T*)dy, (const T*)x, gamma, mean, rstd, (T*)dx, part, rows, cols);
-  });
+  MSAMP_LN_DISPATCH(dtype, pdtype, T, P, { launch_ln_bwd<T, P>(grid, stream, dy, x, gamma, mean, rstd, dx, part, rows, cols, nullptr, nullptr); });
   layernorm_reduce_kernel<<<(cols + 31) / 32, 256, 0, stream>>>(part, grid, cols, dgamma, dbeta, pdtype);
   return msamp_check_launch("msamp_layernorm_bwd_static");
 }

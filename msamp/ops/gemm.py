@@ -24,7 +24,7 @@ class _GemmDesc(ctypes.Structure):
     _fields_ = [
         ('a', ctypes.c_void_p), ('b', ctypes.c_void_p), ('d', ctypes.c_void_p), ('bias', ctypes.c_void_p),
         ('residual', ctypes.c_void_p), ('gelu_src', ctypes.c_void_p), ('scale_inv_a', ctypes.c_void_p),
-        ('scale_inv_b', ctypes.c_void_p), ('amax_out', ctypes.c_void_p), ('d8', ctypes.c_void_p), ('d8_scale', ctypes.c_void_p),
+        ('scale_inv_b', ctypes.c_void_p), ('amax_out', ctypes.c_void_p), ('d8', ctypes.c_void_p), ('d8_scale', ctypes.c_void_p), ('d8_scale_inv_out', ctypes.c_void_p),
         ('lda', ctypes.c_int64), ('ldb', ctypes.c_int64), ('ldd', ctypes.c_int64), ('ldr', ctypes.c_int64), ('ldg', ctypes.c_int64),
         ('ld8', ctypes.c_int64),
         ('M', ctypes.c_int), ('N', ctypes.c_int), ('K', ctypes.c_int), ('a_fmt', ctypes.c_int), ('b_fmt', ctypes.c_int),
@@ -52,7 +52,7 @@ def _fix_operand(t):
 
 def gemm_fp8(a, a_qtype, a_scale_inv, b, b_qtype, b_scale_inv, out_dtype, bias=None, accumulate=False, out=None, amax_out=None,
              max_ctas=0, a_mn=False, b_mn=False, residual=None, gelu_src=None, act=None, out8=None, out8_qtype=None, out8_scale=None,
-             tile=0, stats=None):
+             out8_scale_inv_out=None, tile=0, stats=None):
     """Multiply FP8 byte matrices.
 
     Args:
@@ -70,7 +70,8 @@ def gemm_fp8(a, a_qtype, a_scale_inv, b, b_qtype, b_scale_inv, out_dtype, bias=N
         gelu_src: optional ``[M,N]`` tensor ``h`` of ``out_dtype``; the product is multiplied by ``gelu'(h)``
             (the backward of a GeLU that followed the layer whose input gradient this GEMM computes).
         act: ``None`` or ``'gelu'``: which function of ``D`` ``amax_out`` and ``out8`` describe.
-        out8, out8_qtype, out8_scale: optional uint8 ``[M,N]`` receiving ``quantise(act(D) * out8_scale)``.
+        out8, out8_qtype, out8_scale: optional uint8 ``[M,N]`` receiving ``quantise(act(D) * out8_scale)``;
+            ``out8_scale_inv_out`` (optional) then receives ``1 / out8_scale``.
         tile: 0 = choose, 1 = CTA-pair 256x256 tiles, 2 = single-CTA tiles (CUDA only; for tests and benchmarks).
         stats: optional int64 ``[4 * CTAs]`` CUDA tensor receiving per-CTA cycle counters (producer wait, MMA wait for
             data, MMA wait for TMEM, MMA warp total) for tuning.
@@ -113,6 +114,7 @@ def gemm_fp8(a, a_qtype, a_scale_inv, b, b_qtype, b_scale_inv, out_dtype, bias=N
         g.amax_out = amax_out.data_ptr() if amax_out is not None else None
         g.d8 = out8.data_ptr() if out8 is not None else None
         g.d8_scale = out8_scale.data_ptr() if out8 is not None else None
+        g.d8_scale_inv_out = out8_scale_inv_out.data_ptr() if (out8 is not None and out8_scale_inv_out is not None) else None
         g.lda, g.ldb, g.ldd = a.stride(0), b.stride(0), out.stride(0)
         g.ldr = residual.stride(0) if residual is not None else 0
         g.ldg = gelu_src.stride(0) if gelu_src is not None else 0
@@ -151,4 +153,6 @@ def gemm_fp8(a, a_qtype, a_scale_inv, b, b_qtype, b_scale_inv, out_dtype, bias=N
         if out8 is not None:
             from msamp.ops.cast import _emulate_to_fp8
             out8.copy_(_emulate_to_fp8(w, out8_scale, out8_qtype))
+            if out8_scale_inv_out is not None:
+                torch.reciprocal(out8_scale, out=out8_scale_inv_out)
     return out

@@ -59,6 +59,94 @@ class _LayerNormFn(torch.autograd.Function):
         return dx.view(ctx.shape), dgamma, dbeta, None
 
 
+def _ln_supported(x, weight, bias):
+    cols = x.shape[-1]
+    vec = 4 if x.dtype == torch.float32 else 8
+    return (cols % vec == 0 and cols <= native.lib().msamp_layernorm_max_cols(native.dt(x.dtype))
+            and weight.dtype in (torch.float32, torch.float16, torch.bfloat16) and (bias is None or bias.dtype == weight.dtype))
+
+
+def layer_norm_fwd_raw(x2, weight, bias, eps, want_y=True, y8_scale=None, amax_in=None, amax_out=None, scale_inv_out=None, want_y8=False):
+    """LayerNorm forward without autograd on a contiguous 2-D ``x2``.
+
+    Returns ``(y or None, y8 or None, mean, rstd)``.  ``y8`` is the e4m3 copy of the output quantised with
+    ``y8_scale`` (a 0-d fp32 tensor); with ``amax_in`` the scale is first derived from that amax by the power-of-two
+    rule and written back to ``y8_scale``.  ``amax_out`` receives ``max|y|`` and ``scale_inv_out`` ``1 / scale``.
+    The quantised values are taken from the output as rounded to the dtype of ``x2``, so they equal a separate cast
+    of ``y`` bit for bit.  With ``want_y=False`` and ``want_y8=False`` only the statistics and ``amax_out`` are produced.
+    """
+    rows, cols = x2.shape
+    if x2.is_cuda:
+        if not _ln_supported(x2, weight, bias):
+            raise RuntimeError(f'layer_norm: unsupported shape/dtype on CUDA (cols={cols}, dtype={x2.dtype}, param={weight.dtype})')
+        y = torch.empty_like(x2) if want_y else None
+        y8 = torch.empty((rows, cols), dtype=torch.uint8, device=x2.device) if want_y8 else None
+        mean = torch.empty(rows, dtype=torch.float32, device=x2.device)
+        rstd = torch.empty(rows, dtype=torch.float32, device=x2.device)
+        native.check(
+            native.lib().msamp_layernorm_fwd_q(
+                native.ptr(x2), native.ptr(weight), native.ptr(bias), native.dt(x2.dtype), native.dt(weight.dtype), native.ptr(y),
+                native.ptr(mean), native.ptr(rstd), rows, cols, ctypes.c_float(eps), native.ptr(y8), native.ptr(y8_scale),
+                native.ptr(amax_in), native.ptr(amax_out), native.ptr(scale_inv_out), native.stream()
+            ), 'layernorm_fwd'
+        )
+        return y, y8, mean, rstd
+    from msamp.common.dtype import Dtypes
+    from msamp.ops import cast as _c
+    xf = x2.float()
+    mean = xf.mean(1)
+    var = xf.var(1, unbiased=False)
+    rstd = torch.rsqrt(var + eps)
+    yf = (xf - mean[:, None]) * rstd[:, None] * weight.float()
+    if bias is not None:
+        yf = yf + bias.float()
+    y = yf.to(x2.dtype)
+    y8 = None
+    if amax_out is not None:
+        _c.amax(y, out=amax_out)
+    if want_y8:
+        y8 = _c.cast_to_fp8(y, Dtypes.kfloat8_e4m3, y8_scale, scale_inv_out=scale_inv_out, amax_in=amax_in)
+    return (y if want_y else None), y8, mean, rstd
+
+
+def layer_norm_bwd_raw(dy2, x2, weight, mean, rstd, has_bias, dres=None, amax_out=None):
+    """LayerNorm backward without autograd: returns ``(dx, dgamma, dbeta or None)``.
+
+    ``dres`` (same shape and dtype as ``x2``) is added to ``dx`` in the same pass - the gradient that reaches the
+    input through the skip connection around the normalised branch; ``amax_out`` receives ``max|dx|``.
+    """
+    rows, cols = x2.shape
+    if x2.is_cuda:
+        dx = torch.empty_like(x2)
+        dgamma = torch.empty_like(weight)
+        dbeta = torch.empty_like(weight) if has_bias else None
+        nparts = native.lib().msamp_layernorm_bwd_parts()
+        part = torch.empty(nparts * 2 * cols, dtype=torch.float32, device=x2.device)
+        native.check(
+            native.lib().msamp_layernorm_bwd_ex(
+                native.ptr(dy2), native.ptr(x2), native.ptr(weight), native.dt(x2.dtype), native.dt(weight.dtype), native.ptr(mean),
+                native.ptr(rstd), native.ptr(dx), native.ptr(dgamma), native.ptr(dbeta), native.ptr(part), rows, cols, native.ptr(dres),
+                native.ptr(amax_out), native.stream()
+            ), 'layernorm_bwd'
+        )
+        return dx, dgamma, dbeta
+    from msamp.ops import cast as _c
+    xh = (x2.float() - mean[:, None]) * rstd[:, None]
+    d = dy2.float()
+    gd = d * weight.float()
+    m1 = gd.mean(1, keepdim=True)
+    m2 = (gd * xh).mean(1, keepdim=True)
+    dxf = rstd[:, None] * (gd - m1 - xh * m2)
+    if dres is not None:
+        dxf = dxf + dres.float()
+    dx = dxf.to(x2.dtype)
+    if amax_out is not None:
+        _c.amax(dx, out=amax_out)
+    dgamma = (d * xh).sum(0).to(weight.dtype)
+    dbeta = d.sum(0).to(weight.dtype) if has_bias else None
+    return dx, dgamma, dbeta
+
+
 def layer_norm(x, weight, bias=None, eps=1e-5):
     """LayerNorm over the last dimension."""
     if _use_native(x):
@@ -199,6 +287,55 @@ class _AttentionPackedFn(torch.autograd.Function):
             ), 'attention_bwd'
         )
         return dqkv, None, None
+
+
+def attention_qkv_fwd_raw(qkv, causal=True, scale=None):
+    """Self-attention forward without autograd on a packed ``[B, S, 3, heads, d]`` tensor: returns ``(o [B,S,heads,d], lse or None)``."""
+    B, S, _, nh, d = qkv.shape
+    scale = 1.0 / math.sqrt(d) if scale is None else scale
+    if _use_native(qkv):
+        if qkv.dtype != torch.bfloat16 or d not in (64, 128) or not qkv.is_contiguous() or qkv.data_ptr() % 16:
+            raise RuntimeError(f'attention_qkv: CUDA kernel needs contiguous bf16 with head_dim 64/128 (got {qkv.dtype}, {d})')
+        q, k, v = qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2]
+        o = torch.empty((B, S, nh, d), dtype=qkv.dtype, device=qkv.device)
+        lse = torch.empty((B, nh, S), dtype=torch.float32, device=qkv.device)
+        st = _strides(q) + _strides(k) + _strides(v) + _strides(o) + [0] * 12
+        native.check(
+            _attn_entry(d, 'fwd')(
+                native.ptr(q), native.ptr(k), native.ptr(v), native.ptr(o), native.ptr(lse), _i64x24(*st), B, nh, S, d,
+                ctypes.c_float(scale), int(causal), native.stream()
+            ), 'attention_fwd'
+        )
+        return o, lse
+    with torch.no_grad():
+        return attention(qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2], causal=causal, scale=scale), None
+
+
+def attention_qkv_bwd_raw(qkv, o, lse, d_o, causal=True, scale=None):
+    """Gradient of :func:`attention_qkv_fwd_raw` with respect to the packed ``qkv`` (same layout)."""
+    B, S, _, nh, d = qkv.shape
+    scale = 1.0 / math.sqrt(d) if scale is None else scale
+    if _use_native(qkv):
+        q, k, v = qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2]
+        if d_o.stride(3) != 1 or any(s % 8 for s in d_o.stride()[:3]):
+            d_o = d_o.contiguous()
+        dqkv = torch.empty_like(qkv)
+        dq, dk, dv = dqkv[:, :, 0], dqkv[:, :, 1], dqkv[:, :, 2]
+        delta = torch.empty((B, nh, S), dtype=torch.float32, device=qkv.device)
+        st = _strides(q) + _strides(k) + _strides(v) + _strides(o) + _strides(d_o) + _strides(dq) + _strides(dk) + _strides(dv)
+        native.check(
+            _attn_entry(d, 'bwd')(
+                native.ptr(q), native.ptr(k), native.ptr(v), native.ptr(o), native.ptr(lse), native.ptr(d_o), native.ptr(dq),
+                native.ptr(dk), native.ptr(dv), native.ptr(delta), _i64x24(*st), B, nh, S, d, ctypes.c_float(scale), int(causal),
+                native.stream()
+            ), 'attention_bwd'
+        )
+        return dqkv
+    with torch.enable_grad():
+        leaf = qkv.detach().clone().requires_grad_(True)
+        out = attention(leaf[:, :, 0], leaf[:, :, 1], leaf[:, :, 2], causal=causal, scale=scale)
+        grad, = torch.autograd.grad(out, leaf, d_o)
+    return grad
 
 
 def attention_qkv(qkv, causal=True, scale=None):

@@ -325,6 +325,41 @@ def test_layernorm(dt, shape):
     assert (b.grad - br.grad).abs().max().item() <= tol * math.sqrt(shape[0]) * 2
 
 
+@pytest.mark.parametrize('shape', [(64, 1024), (300, 4096), (17, 8192)])
+def test_layernorm_quantised_output_and_residual_backward(shape):
+    """LayerNorm that emits e4m3 directly == LayerNorm followed by the cast, bit for bit; backward with the skip gradient."""
+    torch.manual_seed(0)
+    x = (torch.randn(*shape, device=DEV) * 2 + 0.5).bfloat16()
+    w = torch.rand(shape[1], device=DEV) + 0.5
+    b = torch.randn(shape[1], device=DEV)
+    y, _, mean, rstd = K.layer_norm_fwd_raw(x, w, b, 1e-5)
+    # delayed regime: given scale, amax recorded
+    scale, am, si = torch.tensor(16.0, device=DEV), torch.zeros((), device=DEV), torch.zeros((), device=DEV)
+    _, y8, mean2, rstd2 = K.layer_norm_fwd_raw(x, w, b, 1e-5, want_y=False, want_y8=True, y8_scale=scale, amax_out=am, scale_inv_out=si)
+    assert torch.equal(y8, cast.cast_to_fp8(y, E4, scale)) and am.item() == y.float().abs().max().item() and si.item() == 1 / 16
+    assert torch.equal(mean, mean2) and torch.equal(rstd, rstd2)
+    # in-time regime: statistics pass, then the scale follows from the amax
+    am2 = torch.zeros((), device=DEV)
+    K.layer_norm_fwd_raw(x, w, b, 1e-5, want_y=False, amax_out=am2)
+    assert am2.item() == am.item()
+    scale2, si2 = torch.ones((), device=DEV), torch.zeros((), device=DEV)
+    _, y8b, _, _ = K.layer_norm_fwd_raw(x, w, b, 1e-5, want_y=False, want_y8=True, y8_scale=scale2, amax_in=am2, scale_inv_out=si2)
+    want_scale = cast.compute_scale(am2, torch.ones((), device=DEV), 448.0)
+    assert scale2.item() == want_scale.item() and si2.item() == 1 / want_scale.item()
+    assert torch.equal(y8b, cast.cast_to_fp8(y, E4, want_scale))
+    # backward: dx = LayerNorm'(dy) + dres, with max|dx|
+    dy, dres = torch.randn_like(y), torch.randn_like(y)
+    dx0, dg0, db0 = K.layer_norm_bwd_raw(dy, x, w, mean, rstd, True)
+    amx = torch.zeros((), device=DEV)
+    dx1, dg1, db1 = K.layer_norm_bwd_raw(dy, x, w, mean, rstd, True, dres=dres, amax_out=amx)
+    ref = K.layer_norm_bwd_raw(dy.cpu(), x.cpu(), w.cpu(), mean.cpu(), rstd.cpu(), True, dres=dres.cpu())[0]
+    assert (dx1.float().cpu() - ref.float()).abs().max().item() <= 4e-2
+    assert (dx1.float() - (dx0.float() + dres.float())).abs().max().item() <= 4e-2
+    assert amx.item() == dx1.float().abs().max().item()
+    assert torch.equal(dg0, dg1) and torch.equal(db0, db1)
+    _status_ok()
+
+
 def test_gelu():
     x = torch.randn(100003, device=DEV, dtype=torch.bfloat16).requires_grad_()
     y = K.gelu(x)

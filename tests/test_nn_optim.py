@@ -353,3 +353,50 @@ def test_gpt_recompute_matches_stored_activations():
     l1, w1 = run(True)
     assert l0 == l1
     assert torch.equal(w0, w1)
+
+
+@pytest.mark.parametrize('regime', ['in-time', 'delayed'])
+def test_fused_sublayers_match_composed_block(regime, monkeypatch):
+    """GPT blocks through msamp.nn.fused_layers against the same blocks composed from layer_norm / F.linear / gelu / +.
+
+    With fp32 activations the two paths differ only in where FP8 rounding happens (GeLU derivative before instead of
+    after a rounding to the activation type is a no-op in fp32), so losses and updated weights agree closely."""
+    import msamp
+    from msamp.common.tensor import ScalingMeta
+    from msamp.models import GPT, gpt_config
+    from msamp.nn import fused_layers, model_state
+
+    def run(fused):
+        model_state.clear()
+        if not fused:
+            monkeypatch.setattr(fused_layers, 'fusable', lambda *mods: False)
+        torch.manual_seed(0)
+        cfg = gpt_config('gpt-tiny', n_layer=2, n_head=2, hidden=64, ffn_hidden=128, vocab_size=128, max_seq=32)
+        model = GPT(cfg, act_dtype=torch.float32)
+        opt = torch.optim.AdamW(model.parameters(), lr=1e-3)
+        model, opt = msamp.initialize(model, opt, 'O2')
+        if regime == 'delayed':
+            for metas in model_state.local_scaling_metas.values():
+                for key in ('input', 'ograd'):
+                    metas[key].amax_counter.fill_(metas[key].window_size)    # past warm-up: scales come from the history
+                    metas[key].scale.fill_(8.0 if key == 'input' else 4096.0)
+        torch.manual_seed(1)
+        tok = torch.randint(0, 128, (2, 32))
+        losses = []
+        for _ in range(3):
+            opt.zero_grad()
+            loss = model(tok, tok)
+            loss.backward()
+            opt.step()
+            losses.append(loss.item())
+        amaxs = {k: v['amaxs'].clone() for k, v in model_state.flattened_scaling_metas.items()}
+        return losses, torch.cat([p.float().reshape(-1) for p in model.parameters()]), amaxs
+
+    l0, w0, a0 = run(True)
+    l1, w1, a1 = run(False)
+    monkeypatch.undo()
+    assert all(abs(x - y) <= 2e-3 * abs(y) for x, y in zip(l0, l1)), (l0, l1)
+    assert (w0 - w1).abs().max().item() <= 5e-3
+    for k in a0:    # both paths record the same statistics for the delayed scales
+        assert torch.allclose(a0[k], a1[k], rtol=0.1, atol=1e-6), k
+    assert l0[-1] < l0[0]
