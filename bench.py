@@ -31,7 +31,9 @@ def parse():
     ap.add_argument('--gpus', type=int, default=1)
     ap.add_argument('--steps', type=int, default=6)
     ap.add_argument('--warmup', type=int, default=3)
-    ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
+    ap.add_argument('--impl', default='ours', choices=['ours', 'reference', 'unfused'],
+                    help="'unfused' = the reference's step sequence re-stated on library kernels (benchmarks/unfused_baseline.py): a same-box "
+                         "comparison point, not the reference")
     ap.add_argument('--model', default='gpt-7b')
     ap.add_argument('--micro-batch', type=int, default=4)
     ap.add_argument('--seq', type=int, default=2048)
@@ -150,7 +152,17 @@ def main():
     full_shard = False
     dp = world // tp
     torch.manual_seed(1234)
-    if tp > 1:
+    if args.impl == 'unfused':
+        # library-kernel re-statement of the reference's step (data parallel only)
+        sys.path.insert(0, os.path.join(ROOT, 'benchmarks'))
+        from unfused_baseline import UnfusedGPT, UnfusedTrainer
+        if tp > 1 or args.model == 'gpt-30b' or args.accum > 1:
+            raise SystemExit('--impl unfused covers the data-parallel GPT configurations only')
+        grp = dist.group.WORLD if world > 1 else None
+        model = UnfusedGPT(cfg, dev, grp)
+        trainer = UnfusedTrainer(model, lr=1e-4, betas=(0.9, 0.95), wd=0.1, group=grp)
+        data_rank = rank
+    elif tp > 1:
         # Megatron-style tensor + sequence parallelism inside groups of `tp` adjacent ranks, sharded optimizer over the rest
         from msamp.megatron import parallel_state as mpu
         from msamp.models import ParallelGPT
@@ -280,7 +292,7 @@ def main():
             'ms_per_step': ms / args.steps, 'higher_is_better': True, 'scaling': 'weak',
             'vs_baseline': (value / (base * world)) if (base and not reduced) else None,
             'dtype': 'fp8 GEMM (e4m3/e5m2) with bf16 activations', 'data': 'synthetic uniform token ids, random-init weights N(0,0.02)',
-            'impl': 'ours',
+            'impl': 'ours' if args.impl == 'ours' else 'unfused re-statement of the reference step on library kernels (cuBLASLt FP8, ATen, SDPA, NCCL) - not the reference',
             'config': {
                 'model': args.model, 'layers': cfg.n_layer, 'hidden': cfg.hidden, 'heads': cfg.n_head, 'ffn': cfg.ffn_hidden,
                 'vocab': cfg.vocab_size, 'global_batch': B * dp * accum, 'micro_batch': B, 'grad_accum': accum, 'recompute': bool(args.recompute), 'seq_len': S,
