@@ -67,6 +67,12 @@ class FP8Optimizer:
                 p.grad = None
             else:
                 p.grad.zero_()
+        if self.zero is not None:
+            # parameters this rank does not own are not in the inner optimizer, but their gradients exist here too
+            for p in self.zero.fp8_params:
+                p.grad = None
+            if self.zero.hp_layout:
+                self.zero._clear_hp_grads()
 
     def backward(self, loss, retain_graph=False):
         """Scale the loss and back-propagate."""
@@ -140,7 +146,11 @@ class FP8Optimizer:
             if self.zero.sharded:
                 for i, m in self.zero.masters.items():
                     m.grad = self.zero.fp8_params[i].grad
-                self._unscale_and_clip(self.zero.hp_params, sharded=list(self.zero.masters.values()))
+                if self.zero.world > 1:
+                    # high-precision parameters are sharded as well: each rank unscales and clips what it owns
+                    self._unscale_and_clip([], sharded=list(self.zero.masters.values()) + self.zero._owned_hp())
+                else:
+                    self._unscale_and_clip(self.zero.hp_params, sharded=list(self.zero.masters.values()))
             else:
                 self._unscale_and_clip(params)
             with self.timers.phase(BASIC_STEP):
@@ -148,10 +158,13 @@ class FP8Optimizer:
             with self.timers.phase(UPDATE_FP16):
                 if self.zero.sharded:
                     self.zero._publish_weights()
+                    self.zero._gather_hp_params()
                     for m in self.zero.masters.values():
                         m.grad = None
             for p in self.zero.fp8_params:
                 p.grad = None
+            if self.zero.hp_layout:
+                self.zero._clear_hp_grads()
         else:
             self._unscale_and_clip(params)
             with self.timers.phase(BASIC_STEP):
@@ -169,7 +182,7 @@ class FP8Optimizer:
         sd['optimizer_state_dict'] = self.optimizer.state_dict()
         hp = self.zero.hp_params if self.zero is not None else [p for p in self._all_params() if not isinstance(p, ScalingTensor)]
         sd['fp32_groups_flat'] = [torch.cat([p.detach().float().reshape(-1) for p in hp])] if hp else []
-        sd['fp8_master_groups'] = [[self.zero.masters[i].detach() for i in sorted(self.zero.masters)]] if (self.zero and self.zero.sharded) else []
+        sd['fp8_master_groups'] = [[m.detach() for m in g] for g in self.zero._master_groups()] if (self.zero and self.zero.sharded) else []
         sd['clip_grad'] = self.clip_grad
         return sd
 
@@ -191,6 +204,14 @@ class FP8Optimizer:
                 p.data.copy_(flat[off:off + p.numel()].view_as(p).to(p.dtype))
                 off += p.numel()
         if sd['fp8_master_groups'] and self.zero is not None and self.zero.sharded:
-            for i, saved in zip(sorted(self.zero.masters), sd['fp8_master_groups'][0]):
-                self.zero.masters[i].copy_(saved.to(device=self.zero.device))
+            groups, saved = self.zero._master_groups(), sd['fp8_master_groups']
+            if len(saved) == 1 and len(groups) != 1 and len(saved[0]) == sum(len(g) for g in groups):
+                # files written before the per-group nesting: one list in ascending tensor index
+                pairs = list(zip([self.zero.masters[i] for i in sorted(self.zero.masters)], saved[0]))
+            else:
+                if len(saved) != len(groups) or any(len(a) != len(b) for a, b in zip(saved, groups)):
+                    raise ValueError('fp8 master groups of the checkpoint do not match the optimizer\'s parameter groups')
+                pairs = [(m, t) for gm, gt in zip(groups, saved) for m, t in zip(gm, gt)]
+            for master, tensor in pairs:
+                master.copy_(tensor.to(device=self.zero.device))
             self.zero._publish_weights()

@@ -39,8 +39,9 @@ class FP8DeepSpeedZeroOptimizer(FP8Optimizer):
 
     def state_dict(self):
         sd = super().state_dict()
-        sd['single_partition_of_fp8_groups'] = sd.pop('fp8_master_groups')[0] if sd.get('fp8_master_groups') else []
-        sd['fp8_master_groups'] = [sd['single_partition_of_fp8_groups']]
+        # the reference's key and nesting: a list of param groups, each a list of detached master ScalingTensors
+        # (msamp/deepspeed/runtime/zero/fp8_stage_1_and_2.py:937-960)
+        sd['single_partition_of_fp8_groups'] = sd.get('fp8_master_groups') or []
         sd['partition_count'] = self.partition_count
         sd['zero_stage'] = 2 if self.partition_gradients else 1
         return sd
@@ -50,5 +51,7 @@ class FP8DeepSpeedZeroOptimizer(FP8Optimizer):
             raise ValueError('changing the data-parallel degree of an FP8 ZeRO checkpoint is not supported')
         sd = dict(sd)
         if 'single_partition_of_fp8_groups' in sd:
-            sd['fp8_master_groups'] = [sd['single_partition_of_fp8_groups']]
+            saved = sd['single_partition_of_fp8_groups']
+            nested = bool(saved) and isinstance(saved[0], (list, tuple))
+            sd['fp8_master_groups'] = saved if (nested or not saved) else [saved]    # a flat list is the layout of older files
         super().load_state_dict(sd, load_optimizer_states=load_optimizer_states)

@@ -9,7 +9,7 @@ import torch
 import torch.distributed as dist
 
 from msamp.common.tensor import ScalingTensor
-from msamp.nn.clip_grad import _grad_norm
+from msamp.nn.clip_grad import _grad_norm, _one_device
 
 
 def clip_grad_norm_fp32(parameters, grads_for_norm, max_norm, norm_type=2, model_parallel_group=None):
@@ -43,6 +43,15 @@ def clip_grad_norm_fp32(parameters, grads_for_norm, max_norm, norm_type=2, model
         total = torch.stack(vals).max() if vals else torch.zeros((), device=device)
         if model_parallel_group is not None and dist.is_initialized():
             dist.all_reduce(total, op=dist.ReduceOp.MAX, group=model_parallel_group)
+    elif norm_type == 2.0 and _one_device(list(grads_for_norm) + grads):
+        # one launch for the squared norm of every gradient, one for the clip (replaces apex's multi_tensor_l2norm /
+        # multi_tensor_scale of the reference, clip_grads.py:79-107)
+        from msamp.ops import multi_tensor as _mt
+        stats = _mt.grad_sumsq(list(grads_for_norm), out=torch.zeros(2, dtype=torch.float32, device=device), tag='megatron_norm')
+        if model_parallel_group is not None and dist.is_initialized():
+            dist.all_reduce(stats, op=dist.ReduceOp.SUM, group=model_parallel_group)
+        _mt.clip_by_sumsq(grads, stats[0:1], max_norm, eps=1.0e-6, tag='megatron_clip')
+        return stats[0].sqrt().item()
     else:
         acc = torch.zeros((), dtype=torch.float32, device=device)
         for g in grads_for_norm:

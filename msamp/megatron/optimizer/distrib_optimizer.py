@@ -60,6 +60,8 @@ class FP8DistributedOptimizer:
             p.main_grad.value.zero_()
         for p in self.zero.hp_params:
             p.grad = None
+        if self.zero.hp_layout:
+            self.zero._clear_hp_grads()
 
     def get_loss_scale(self):
         if self.grad_scaler is None:
@@ -83,13 +85,19 @@ class FP8DistributedOptimizer:
     def gather_model_params(self, args=None, timers=None):
         """Publish the updated weights (and their ``scale_inv``) of every owner to all data-parallel ranks."""
         self.zero._publish_weights()
+        self.zero._gather_hp_params()
+
+    def _hp_updated_here(self):
+        """High-precision parameters this rank updates: all of them on one data-parallel rank, else the ones it owns
+        (the sharded optimizer partitions them over the data-parallel group like the FP8 weights)."""
+        return self.zero._owned_hp() if (self.zero.sharded and self.zero.world > 1) else self.zero.hp_params
 
     def _unscale_and_check(self):
         if self.grad_scaler is None:
             return False
         inv = torch.reciprocal(self.grad_scaler.scale).reshape(1)
         self._found_inf.zero_()
-        grads = [m.grad for m in self.zero.masters.values() if m.grad is not None] + [p.grad for p in self.zero.hp_params if p.grad is not None]
+        grads = [m.grad for m in self.zero.masters.values() if m.grad is not None] + [p.grad for p in self._hp_updated_here() if p.grad is not None]
         torch._amp_foreach_non_finite_check_and_unscale_(grads, self._found_inf.reshape(1), inv)
         dist.all_reduce(self._found_inf, op=dist.ReduceOp.MAX, group=mpu.get_model_parallel_group()) if dist.is_initialized() else None
         return bool(self._found_inf.item() > 0)
@@ -106,18 +114,20 @@ class FP8DistributedOptimizer:
             return False, None, None
         grad_norm = None
         if self.clip_grad > 0.0:
-            params = list(self.zero.masters.values()) + self.zero.hp_params
+            hp_here = self._hp_updated_here()
+            params = list(self.zero.masters.values()) + hp_here
             grads_for_norm = [m.grad for m in self.zero.masters.values() if m.grad is not None]
             tp_rank = mpu.get_tensor_model_parallel_rank()
             dp_rank = mpu.get_data_parallel_rank()
-            for p in self.zero.hp_params:
+            owner_counts = self.zero.sharded and self.zero.world > 1
+            for p in hp_here:
                 if p.grad is None:
                     continue
                 is_tp = getattr(p, 'tensor_model_parallel', False)
-                if dp_rank == 0 and (is_tp or tp_rank == 0):    # replicated params count once
+                if (owner_counts or dp_rank == 0) and (is_tp or tp_rank == 0):    # replicated params count once
                     grads_for_norm.append(p.grad)
-            # Every gradient is counted on exactly one rank of the whole job (FP8 gradients on their owner inside the
-            # data-parallel group, replicated ones on data-parallel rank 0 / tensor-parallel rank 0), so the norm is
+            # Every gradient is counted on exactly one rank of the whole job (FP8 and high-precision gradients on their
+            # owner inside the data-parallel group, tensor-parallel replicas on tensor-parallel rank 0), so the norm is
             # summed over all ranks: data-parallel replicas must agree on the clip coefficient.
             group = dist.group.WORLD if dist.is_initialized() and dist.get_world_size() > 1 else None
             grad_norm = clip_grad_norm_fp32(params, grads_for_norm, self.clip_grad, 2, model_parallel_group=group)
@@ -172,9 +182,10 @@ class FP8DistributedOptimizer:
                 'exp_avg_sq': st['exp_avg_sq'].float().cpu() if 'exp_avg_sq' in st else torch.zeros(m.shape),
                 'step': st.get('step', 0),
             }
-        pieces = self._gather_world({'fp8': local})
         hp = {}
         for j, p in enumerate(z.hp_params):
+            if z.hp_owner[j] != z.rank:
+                continue    # states of a sharded high-precision parameter live on its owner
             st = self.optimizer.state.get(p, {})
             hp[j] = {
                 'param': p.detach().float().cpu(),
@@ -182,10 +193,13 @@ class FP8DistributedOptimizer:
                 'exp_avg_sq': st['exp_avg_sq'].float().cpu() if 'exp_avg_sq' in st else torch.zeros(p.shape),
                 'step': st.get('step', 0),
             }
+        pieces = self._gather_world({'fp8': local, 'hp': hp})
         if mpu.get_data_parallel_rank() == 0:
             merged = {}
+            hp = {}
             for piece in pieces:
                 merged.update(piece['fp8'])
+                hp.update(piece['hp'])
             order = sorted(merged)
             state = {0: {
                 torch.uint8: {k: torch.cat([merged[i][k].reshape(-1) for i in order]) if order else torch.zeros(0) for k in ('param', 'exp_avg', 'exp_avg_sq')},
@@ -216,6 +230,9 @@ class FP8DistributedOptimizer:
         for j, p in enumerate(z.hp_params):
             n = p.numel()
             p.data.copy_(bufs[torch.float32]['param'][off:off + n].view(p.shape).to(p.dtype))
+            if z.hp_owner[j] != z.rank:
+                off += n
+                continue
             st = self.optimizer.state[p]
             st['step'] = state['steps']['hp'].get(j, 0)
             st['exp_avg'] = self.optimizer._get_state_tensor(bufs[torch.float32]['exp_avg'][off:off + n].view(p.shape).to(z.device), self.optimizer.exp_avg_dtype)

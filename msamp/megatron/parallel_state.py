@@ -55,6 +55,9 @@ def initialize_model_parallel(tensor_model_parallel_size=1, pipeline_model_paral
 
 
 def destroy_model_parallel():
+    fused = _STATE.get('fused')
+    if fused is not None and hasattr(fused, 'close'):
+        fused.close()    # frees the symmetric (IPC-shared) buffers of the fused GEMM kernels; collective over the group
     _STATE.update(tp=None, dp=None, pp=None, mp=None, tp_size=1, dp_size=1, pp_size=1, fused=None, init=False)
 
 

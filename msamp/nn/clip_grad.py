@@ -19,6 +19,13 @@ def _grad_norm(g, norm_type):
     return torch.linalg.vector_norm(g.detach().float(), norm_type)
 
 
+def _one_device(grads):
+    devs = {(g.value if isinstance(g, ScalingTensor) else g).device for g in grads}
+    ok = all((g.value if isinstance(g, ScalingTensor) else g).is_contiguous() for g in grads)
+    return len(devs) == 1 and ok and all((g.value if isinstance(g, ScalingTensor) else g).dtype in (
+        torch.float32, torch.float16, torch.bfloat16, torch.uint8) for g in grads)
+
+
 @torch.no_grad()
 def clip_grad_norm_(parameters, max_norm, norm_type=2.0, error_if_nonfinite=False):
     """Clip the global gradient norm in place and return the norm before clipping."""
@@ -37,6 +44,17 @@ def clip_grad_norm_(parameters, max_norm, norm_type=2.0, error_if_nonfinite=Fals
             else:
                 norms.append(g.detach().abs().max().float().to(device))
         total = torch.stack(norms).max()
+    elif norm_type == 2.0 and _one_device(grads):
+        # one launch for the norm of all gradients, one for the clip (msamp.ops.multi_tensor)
+        from msamp.ops import multi_tensor as _mt
+        stats = _mt.grad_sumsq(grads, tag='clip_grad_norm_')
+        total = stats[0].sqrt()
+        if error_if_nonfinite and not bool(torch.isfinite(total)):
+            raise RuntimeError(
+                f'The total norm of order {norm_type} for gradients from `parameters` is non-finite, so it cannot be clipped.'
+            )
+        _mt.clip_by_sumsq(grads, stats[0:1], max_norm, tag='clip_grad_norm_')
+        return total
     else:
         total = torch.linalg.vector_norm(torch.stack([_grad_norm(g, norm_type).to(device) for g in grads]), norm_type)
     if error_if_nonfinite and not bool(torch.isfinite(total)):

@@ -51,7 +51,8 @@ struct FusedArgs {
   int rows_per_rank;
   void* rs_out;
   int64_t rs_ldo;
-  unsigned int* counters;            // [2] local scratch words (comm CTAs done, compute CTAs done); left at zero
+  unsigned int* counters;            // local scratch words, all left at zero: [0] comm CTAs done, [1] compute CTAs done,
+                                     // [2 + world * chunks_per_shard] pieces landed per gathered chunk
 };
 
 __device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
@@ -141,7 +142,6 @@ gemm_fused_kernel(const __grid_constant__ FusedMaps maps, const GemmParams p, co
   auto tempty_bar = [&](int b) { return bars + 8u * (2 * C::STAGES + 2 + b); };
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(smem + C::TILE_BYTES + 8 * (2 * C::STAGES + 4));
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
-  unsigned int* chunk_count = reinterpret_cast<unsigned int*>(tmem_holder + 2);    // [8] copy-progress counters of a comm CTA
   int* role_flag = reinterpret_cast<int*>(tmem_holder + 10);
 
   const int warp = threadIdx.x >> 5;
@@ -165,7 +165,6 @@ gemm_fused_kernel(const __grid_constant__ FusedMaps maps, const GemmParams p, co
       tc5::mbar_init(tempty_bar(b), 4);
     }
     *abort_flag = 0;
-    for (int i = 0; i < 8; ++i) chunk_count[i] = 0;
     *role_flag = 0;
     tc5::mbar_fence_init();
   }
@@ -221,9 +220,12 @@ gemm_fused_kernel(const __grid_constant__ FusedMaps maps, const GemmParams p, co
         __threadfence();
         const int mine = (pieces_per_chunk - warp + kWarps - 1) / kWarps;
         if (mine > 0) {
-          unsigned int done = atomicAdd(&chunk_count[it & 7], (unsigned int)mine) + mine;
+          // one counter per chunk (not a small ring shared by chunks): the six warps never synchronise with each
+          // other, so any reuse of a counter could mix the pieces of two chunks
+          unsigned int* cnt = f.counters + 2 + src * f.chunks_per_shard + ch;
+          unsigned int done = atomicAdd(cnt, (unsigned int)mine) + mine;
           if (done == (unsigned int)pieces_per_chunk) {
-            chunk_count[it & 7] = 0;
+            *cnt = 0;
             st_release_gpu(f.chunk_flags + src * f.chunks_per_shard + ch, f.epoch);
           }
         }

@@ -65,7 +65,8 @@ __device__ bool symm_barrier(const PeerTable& pt, int rank, int world, int slot,
     const uint64_t t0 = gtimer();
     uint32_t spins = 0;
     // epochs only grow; compare with wrap-around tolerance
-    while ((int32_t)(ld_acquire_sys(f) - epoch) < 0) {
+    uint32_t seen;
+    while ((int32_t)((seen = ld_acquire_sys(f)) - epoch) < 0) {
       if ((++spins & 0xff) == 0) {
         if (gtimer() - t0 > limit_ns) {
           ok_flag = 0;
@@ -74,6 +75,13 @@ __device__ bool symm_barrier(const PeerTable& pt, int rank, int world, int slot,
         }
         __nanosleep(200);
       }
+    }
+    // A peer can never be ahead of this rank on the same slot when all ranks issue the same sequence of calls
+    // (it cannot leave the call before this rank has arrived).  If it is, this rank skipped a call: report it
+    // instead of letting the flags run out of step silently.
+    if ((int32_t)(seen - epoch) > 0) {
+      ok_flag = 0;
+      if (status) atomicOr(status, 8u);
     }
   }
   __syncthreads();
@@ -104,11 +112,12 @@ constexpr int kReduceThreads = 256;
 constexpr int kReduceChunk = 16384;    // bytes per work item
 
 __global__ void __launch_bounds__(kReduceThreads) symm_grad_reduce_kernel(const ReduceArgs a) {
-  // (1) wait until every rank has finished writing its gradients and metas
-  if (!symm_barrier(a.grads, a.rank, a.world, 0, a.epoch, blockIdx.x == 0, a.limit_ns, a.status)) return;
+  // (1) wait until every rank has finished writing its gradients and metas.  A CTA whose wait gave up skips the
+  // work but still takes part in the completion count below, so that the shared counter returns to zero.
+  const bool ready = symm_barrier(a.grads, a.rank, a.world, 0, a.epoch, blockIdx.x == 0, a.limit_ns, a.status);
 
   const float inv_world = 1.0f / (float)a.world;
-  for (int w = blockIdx.x; w < a.n_work; w += gridDim.x) {
+  for (int w = blockIdx.x; ready && w < a.n_work; w += gridDim.x) {
     const int t = a.work[2 * w];
     const int64_t begin = a.offsets[t] + (int64_t)a.work[2 * w + 1] * kReduceChunk;
     int64_t end = begin + kReduceChunk;
@@ -167,16 +176,21 @@ __global__ void __launch_bounds__(kReduceThreads) symm_grad_reduce_kernel(const 
   }
   // (2) nobody may reuse the buffers (or read broadcast results) before every rank is done
   __syncthreads();
-  // all CTAs of this rank must be finished before the announcement: count them in
-  __shared__ unsigned int last;
+  // all CTAs of this rank must be finished before the announcement: count them in (low half: arrivals, high half:
+  // CTAs that gave up).  Only a complete reduction is announced; after a give-up the peers' waits run out as well
+  // and every rank reports the failure through the status word.
+  __shared__ unsigned int announce;
   if (threadIdx.x == 0) {
     __threadfence_system();
     unsigned int* counter = reinterpret_cast<unsigned int*>(a.grads.flags[a.rank] + (kFlagSlots - 1) * kMaxRanks);
-    last = (atomicAdd(counter, 1u) == gridDim.x - 1) ? 1u : 0u;
-    if (last) *counter = 0u;
+    const unsigned int before = atomicAdd(counter, ready ? 1u : 0x10001u);
+    const bool is_last = (before & 0xffffu) == gridDim.x - 1;
+    announce = (is_last && ready && (before >> 16) == 0u) ? 1u : 0u;
+    if (is_last) *counter = 0u;
   }
   __syncthreads();
-  symm_barrier(a.grads, a.rank, a.world, 1, a.epoch, last != 0, a.limit_ns, a.status);
+  if (!ready) return;
+  symm_barrier(a.grads, a.rank, a.world, 1, a.epoch, announce != 0, a.limit_ns, a.status);
 }
 
 // After the reduce: scale_inv <- agreed value (row 2 -> row 0), for the tensors listed.

@@ -98,6 +98,10 @@ def i64(v):
     return ctypes.c_int64(int(v))
 
 
+def ctypes_float(v):
+    return ctypes.c_float(float(v))
+
+
 def peek_device_status():
     """The device-side error word without clearing it (no synchronisation: the word lives in mapped host memory)."""
     fn = getattr(lib(), 'msamp_peek_device_status', None)

@@ -61,7 +61,7 @@ class FusedGemmContext:
         max_out_bytes: largest full (pre-reduction) output ``M * N * itemsize`` of a ``gemm_rs`` call.
         n_comm: CTAs of the persistent grid used as copy engines in gather modes.
     """
-    def __init__(self, group=None, max_shard_bytes=0, max_out_bytes=0, n_comm=12, wait_seconds=30.0):
+    def __init__(self, group=None, max_shard_bytes=0, max_out_bytes=0, n_comm=12, wait_seconds=5.0):
         self.group = group
         self.world = DistUtil.get_world_size(group)
         self.rank = DistUtil.get_rank(group)
@@ -86,7 +86,25 @@ class FusedGemmContext:
         self.stage = [SymmetricBuffer(max(self.max_out_bytes, 16), group) for _ in range(2)] if max_out_bytes else None
         self.stage_turn = 0
         self.chunk_flags = torch.zeros(self.world * 4096, dtype=torch.int32, device=dev)
-        self.counters = torch.zeros(2, dtype=torch.int32, device=dev)
+        self.counters = torch.zeros(2 + self.world * 4096, dtype=torch.int32, device=dev)    # two CTA counters + one piece counter per chunk
+
+    def reset_after_failure(self):
+        """After a device-side wait gave up (``native.device_status()`` was non-zero): clear the progress counters a
+        kernel may have left half-counted.  The ranks must then agree on the epoch again (``flags.epoch``) on the host."""
+        if self.native:
+            self.counters.zero_()
+
+    def close(self):
+        """Release the symmetric (IPC-shared) buffers.  Collective over the group, after the last fused call."""
+        if not self.native:
+            return
+        if self.world > 1:
+            dist.barrier(group=self.group)
+        for buf in [self.flags, self.shard] + list(self.stage or []):
+            if buf is not None:
+                buf.close()
+        self.flags = self.shard = self.stage = None
+        self.native = False
 
     # ------------------------------------------------------------------ helpers
     def shard_view(self, nbytes):

@@ -54,7 +54,7 @@ class ZeroShardedOptimizer:
         stage: 0 = replicated states (FP8 all-reduce), 1 or 2 = sharded master weights and moments.
         group: data-parallel process group.
     """
-    def __init__(self, model, optimizer, stage=2, group=None, wait_seconds=30.0, model_parallel_group=None):
+    def __init__(self, model, optimizer, stage=2, group=None, wait_seconds=5.0, model_parallel_group=None):
         self.model, self.optimizer, self.stage, self.group = model, optimizer, stage, group
         self.world = DistUtil.get_world_size(group)
         self.rank = DistUtil.get_rank(group)
@@ -76,6 +76,7 @@ class ZeroShardedOptimizer:
         self._build_buffers()
         if self.sharded:
             self._shard_states()
+        self._build_hp_buffers()
 
     # ------------------------------------------------------------------ set-up
     def _alloc(self, nbytes):
@@ -237,22 +238,106 @@ class ZeroShardedOptimizer:
             self.g_flat[lo:hi] = _k._emulate_to_fp8(acc, scale, E4M3)
             self.g_meta_t[0, i] = 1.0 / scale
 
+    # ------------------------------------------------------------------ high-precision parameters
+    def _build_hp_buffers(self):
+        """Flat, persistent buffers for everything that is not an FP8 weight (embeddings, LayerNorms, biases).
+
+        Stage 0 keeps these parameters and their Adam states replicated and all-reduces their gradients in one flat
+        buffer per dtype.  Stages 1 / 2 shard them like stock ZeRO (the reference hands them to DeepSpeed's own
+        partitioning, msamp/deepspeed/runtime/zero/fp8_stage_1_and_2.py:36-68): every tensor gets an owner rank, the
+        flat buffers are laid out as ``world`` equal regions (region r = the tensors owned by rank r), gradients are
+        reduce-scattered so that each region's sum lands on its owner, only the owner keeps optimizer states and
+        updates, and the updated parameters are all-gathered region by region.
+        """
+        self.hp_owner = [self.rank] * len(self.hp_params)
+        self.hp_layout = {}    # dtype -> dict(region=int, params=[(index, offset)], flat_grad, flat_param or None)
+        if self.world == 1 or not self.hp_params:
+            return
+        shard = self.sharded
+        if shard:
+            self.hp_owner = partition_tensors([p.numel() for p in self.hp_params], self.world)
+        by_dtype = {}
+        for k, p in enumerate(self.hp_params):
+            by_dtype.setdefault(p.dtype, []).append(k)
+        for dtype, idxs in by_dtype.items():
+            fill = [0] * self.world
+            place = []
+            for k in idxs:
+                r = self.hp_owner[k] if shard else 0
+                place.append((k, r, fill[r]))
+                fill[r] += _pad16(self.hp_params[k].numel())
+            region = max(max(fill), 16) if shard else max(fill[0], 16)
+            total = region * (self.world if shard else 1)
+            flat_grad = torch.zeros(total, dtype=dtype, device=self.device)
+            flat_param = None
+            params = [(k, r * region + off) for k, r, off in place]
+            if shard:
+                flat_param = torch.zeros(total, dtype=dtype, device=self.device)
+                for k, off in params:
+                    p = self.hp_params[k]
+                    view = flat_param[off:off + p.numel()].view(p.shape)
+                    view.copy_(p.data)
+                    p.data = view
+            self.hp_layout[dtype] = dict(region=region, params=params, flat_grad=flat_grad, flat_param=flat_param)
+        if shard:
+            # the inner optimizer keeps only what this rank owns
+            owned = {id(self.hp_params[k]) for k in range(len(self.hp_params)) if self.hp_owner[k] == self.rank}
+            hp_ids = {id(p) for p in self.hp_params}
+            for group in self.optimizer.param_groups:
+                group['params'] = [p for p in group['params'] if id(p) not in hp_ids or id(p) in owned]
+            for p in list(self.optimizer.state.keys()):
+                if id(p) in hp_ids and id(p) not in owned:
+                    del self.optimizer.state[p]
+
+    def _owned_hp(self):
+        return [self.hp_params[k] for k in range(len(self.hp_params)) if self.hp_owner[k] == self.rank]
+
     def _reduce_hp_grads(self):
         if self.world == 1:
             return
-        by_dtype = {}
+        backend = dist.get_backend(self.group)
+        for dtype, lay in self.hp_layout.items():
+            flat = lay['flat_grad']
+            for k, off in lay['params']:
+                p = self.hp_params[k]
+                view = flat[off:off + p.numel()].view(p.shape)
+                if p.grad is not None and p.grad.data_ptr() != view.data_ptr():
+                    view.copy_(p.grad)
+                p.grad = view
+            region = lay['region']
+            if self.sharded:
+                mine = flat[self.rank * region:(self.rank + 1) * region]
+                if backend == 'nccl':
+                    dist.reduce_scatter_tensor(mine, flat, group=self.group)
+                else:
+                    dist.all_reduce(flat, group=self.group)
+                mine.div_(self.world)
+            else:
+                dist.all_reduce(flat, group=self.group)
+                flat.div_(self.world)
+
+    def _gather_hp_params(self):
+        """Publish the owners' updated high-precision parameters to every rank (stages 1 / 2)."""
+        if self.world == 1 or not self.sharded:
+            return
+        backend = dist.get_backend(self.group)
+        for dtype, lay in self.hp_layout.items():
+            flat, region = lay['flat_param'], lay['region']
+            mine = flat[self.rank * region:(self.rank + 1) * region]
+            if backend == 'nccl':
+                dist.all_gather_into_tensor(flat, mine, group=self.group)
+            else:
+                parts = [torch.empty_like(mine) for _ in range(self.world)]
+                dist.all_gather(parts, mine.clone(), group=self.group)
+                for r, part in enumerate(parts):
+                    if r != self.rank:
+                        flat[r * region:(r + 1) * region].copy_(part)
+
+    def _clear_hp_grads(self):
+        for lay in self.hp_layout.values():
+            lay['flat_grad'].zero_()
         for p in self.hp_params:
-            if p.grad is not None:
-                by_dtype.setdefault(p.grad.dtype, []).append(p.grad)
-        for grads in by_dtype.values():
-            flat = torch.cat([g.reshape(-1) for g in grads])
-            dist.all_reduce(flat, group=self.group)
-            flat.div_(self.world)
-            off = 0
-            for g in grads:
-                k = g.numel()
-                g.copy_(flat[off:off + k].view_as(g))
-                off += k
+            p.grad = None
 
     def _publish_weights(self):
         if self.native:
@@ -302,47 +387,59 @@ class ZeroShardedOptimizer:
         self.optimizer.step()
         if self.sharded:
             self._publish_weights()
+            self._gather_hp_params()
             for m in self.masters.values():
                 m.grad = None
         for p in self.fp8_params:
             p.grad = None
+        if self.hp_layout:
+            self._clear_hp_grads()
 
     def _clip(self, max_norm):
-        from msamp.nn.clip_grad import _grad_norm
-        sq = torch.zeros((), device=self.device)
+        """Global-norm clipping: one multi-tensor launch for this rank's share of the squared norm, the cross-rank sums,
+        one launch that scales (FP8 gradients through their ``scale_inv``)."""
+        from msamp.ops import multi_tensor as _mt
         owned = list(self.masters.values()) if self.sharded else self.fp8_params
-        for p in owned:
-            if p.grad is not None:
-                sq += _grad_norm(p.grad, 2.0)**2
-        if self.sharded and self.world > 1:
-            dist.all_reduce(sq, group=self.group)
         mp_group = getattr(self, 'model_parallel_group', None)
         mp_rank = dist.get_rank(mp_group) if mp_group is not None else 0
-        for p in self.hp_params:
+        hp = self._owned_hp() if (self.sharded and self.world > 1) else self.hp_params
+        counted = [p.grad for p in owned if p.grad is not None]
+        clipped = list(counted)
+        for p in hp:
             if p.grad is None:
                 continue
+            clipped.append(p.grad)
             if mp_group is not None and mp_rank != 0 and not getattr(p, 'tensor_model_parallel', False):
                 continue    # replicated over the model-parallel group: counted on its first rank only
-            sq += _grad_norm(p.grad, 2.0)**2
+            counted.append(p.grad)
+        if not self.sharded and self.world > 1:
+            # replicated states: every rank holds every gradient, so the local sum already is the data-parallel total
+            stats = _mt.grad_sumsq(counted, tag='zero_norm')
+        else:
+            stats = _mt.grad_sumsq(counted, tag='zero_norm')
+            if self.world > 1:
+                dist.all_reduce(stats, group=self.group)
+        if stats.device != self.device:
+            stats = stats.to(self.device)
         if mp_group is not None and dist.get_world_size(mp_group) > 1:
             # the model-parallel ranks hold different shards of the model: one norm, one clip coefficient for all
-            dist.all_reduce(sq, group=mp_group)
-        total = sq.sqrt()
-        coef = torch.clamp(max_norm / (total + 1e-6), max=1.0)
-        for p in owned:
-            if p.grad is not None:
-                p.grad.mul_(coef)
-        for p in self.hp_params:
-            if p.grad is not None:
-                p.grad.mul_(coef.to(p.grad.dtype))
-        return total
+            dist.all_reduce(stats, group=mp_group)
+        _mt.clip_by_sumsq(clipped, stats[0:1], max_norm, tag='zero_clip')
+        return stats[0].sqrt()
 
     # ------------------------------------------------------------------ checkpoint
+    def _master_groups(self):
+        """This rank's master weights as ``[[masters of param group 0], [masters of param group 1], ...]`` in the order of
+        ``optimizer.param_groups`` - the nesting of ``single_partition_of_fp8_groups`` in the reference's checkpoint
+        (msamp/deepspeed/runtime/zero/fp8_stage_1_and_2.py:937-960)."""
+        mine = {id(m) for m in getattr(self, 'masters', {}).values()}
+        return [[p for p in g['params'] if id(p) in mine] for g in self.optimizer.param_groups]
+
     def state_dict(self):
-        """Inner optimizer state plus this rank's master weights, under the reference's key name."""
+        """Inner optimizer state plus this rank's master weights, under the reference's key name and nesting."""
         return {
             'optimizer_state_dict': self.optimizer.state_dict(),
-            'single_partition_of_fp8_groups': [self.masters[i].detach() for i in sorted(getattr(self, 'masters', {}))],
+            'single_partition_of_fp8_groups': [[m.detach() for m in group] for group in self._master_groups()],
             'partition_count': self.world,
             'zero_stage': self.stage,
         }
@@ -351,10 +448,33 @@ class ZeroShardedOptimizer:
         if sd.get('partition_count', self.world) != self.world:
             raise ValueError('loading a sharded optimizer state needs the same data-parallel size')
         self.optimizer.load_state_dict(sd['optimizer_state_dict'])
-        for i, saved in zip(sorted(getattr(self, 'masters', {})), sd['single_partition_of_fp8_groups']):
-            self.masters[i].copy_(saved.to(device=self.device))
+        saved = sd['single_partition_of_fp8_groups']
+        groups = self._master_groups()
+        if saved and not isinstance(saved[0], (list, tuple)):
+            # legacy layout of this library: one flat list in ascending tensor index
+            flat_masters = [self.masters[i] for i in sorted(getattr(self, 'masters', {}))]
+            if len(saved) != len(flat_masters):
+                raise ValueError(f'checkpoint holds {len(saved)} FP8 master weights, this rank owns {len(flat_masters)}')
+            pairs = list(zip(flat_masters, saved))
+        else:
+            if len(saved) != len(groups) or any(len(a) != len(b) for a, b in zip(saved, groups)):
+                raise ValueError('single_partition_of_fp8_groups does not match the optimizer\'s parameter groups: '
+                                 f'{[len(g) for g in saved]} vs {[len(g) for g in groups]}')
+            pairs = [(m, t) for g_m, g_t in zip(groups, saved) for m, t in zip(g_m, g_t)]
+        for master, tensor in pairs:
+            master.copy_(tensor.to(device=self.device))
         if self.sharded:
             self._publish_weights()
+
+    def close(self):
+        """Release the symmetric (IPC-shared) buffers.  Collective: every rank of the group calls it, after its last step."""
+        for name in ('g_buf', 'g_meta', 'w_buf', 'w_meta', 'flags'):
+            buf = getattr(self, name, None)
+            if buf is not None and hasattr(buf, 'close'):
+                if self.world > 1:
+                    dist.barrier(group=self.group)    # nobody may still be reading this rank's memory
+                buf.close()
+                setattr(self, name, None)
 
     # ------------------------------------------------------------------ elastic checkpoint (any data-parallel degree)
     def elastic_state_dict(self):
@@ -368,7 +488,7 @@ class ZeroShardedOptimizer:
         fp8 = {}
         for i, master in getattr(self, 'masters', {}).items():
             fp8[i] = {'master': master.detach(), 'state': dict(self.optimizer.state.get(master, {}))}
-        hp = {k: dict(self.optimizer.state.get(p, {})) for k, p in enumerate(self.hp_params) if p in self.optimizer.state}
+        hp = {k: dict(self.optimizer.state.get(p, {})) for k, p in enumerate(self.hp_params) if p in self.optimizer.state}    # owned ones only when sharded
         groups = [{k: v for k, v in g.items() if k != 'params'} for g in self.optimizer.param_groups]
         return {'fp8': fp8, 'hp': hp, 'param_groups': groups, 'num_fp8': self.n, 'partition_count': self.world}
 
@@ -401,7 +521,7 @@ class ZeroShardedOptimizer:
             if entry['state']:
                 self.optimizer.state[master] = {k: to_dev(v) for k, v in entry['state'].items()}
         for k, p in enumerate(self.hp_params):
-            if k in full['hp'] and full['hp'][k]:
+            if k in full['hp'] and full['hp'][k] and self.hp_owner[k] == self.rank:
                 self.optimizer.state[p] = {key: to_dev(v) for key, v in full['hp'][k].items()}
         for g, saved in zip(self.optimizer.param_groups, full['param_groups']):
             g.update(saved)

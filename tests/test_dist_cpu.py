@@ -100,8 +100,30 @@ def _zero_training(rank, world, stage):
         owned = sum(1 for o in zero.owners if o == rank)
         assert len(zero.masters) == owned and 0 < owned < len(zero.owners)
         sd = zero.state_dict()
-        assert len(sd['single_partition_of_fp8_groups']) == owned
+        # the reference's nesting: one list of master weights per optimizer param group
+        groups = sd['single_partition_of_fp8_groups']
+        assert len(groups) == len(zero.optimizer.param_groups) and all(isinstance(g, list) for g in groups)
+        assert sum(len(g) for g in groups) == owned
         zero.load_state_dict(sd)
+        # a hand-built dictionary of that shape (what a checkpoint written by the reference carries) loads as well,
+        # and so does the flat list older files of this library used
+        before = [m.value.clone() for g in zero._master_groups() for m in g]
+        hand = {'optimizer_state_dict': zero.optimizer.state_dict(), 'partition_count': world, 'zero_stage': stage,
+                'single_partition_of_fp8_groups': [[t.clone() for t in g] for g in groups]}
+        zero.load_state_dict(hand)
+        legacy = dict(hand, single_partition_of_fp8_groups=[zero.masters[i].detach() for i in sorted(zero.masters)])
+        zero.load_state_dict(legacy)
+        after = [m.value for g in zero._master_groups() for m in g]
+        assert all(torch.equal(a, b) for a, b in zip(before, after))
+        bad = dict(hand, single_partition_of_fp8_groups=[g[:-1] for g in groups])
+        try:
+            zero.load_state_dict(bad)
+            raise AssertionError('a checkpoint with a missing master weight must be rejected')
+        except ValueError:
+            pass
+        # high-precision parameters are sharded too: the inner optimizer only holds what this rank owns
+        hp_in_opt = sum(1 for g in zero.optimizer.param_groups for p in g['params'] if any(p is q for q in zero.hp_params))
+        assert hp_in_opt == sum(1 for o in zero.hp_owner if o == rank) < len(zero.hp_params)
     return losses
 
 

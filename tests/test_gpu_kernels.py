@@ -227,6 +227,35 @@ def test_gemm_epilogue_options(tile):
     _status_ok()
 
 
+def test_multi_tensor_norm_and_clip():
+    """One launch for the norm over mixed high-precision / FP8 gradients, one for the clip, against torch on dequantised copies."""
+    from msamp.ops import multi_tensor as mt
+    torch.manual_seed(3)
+    hp = [torch.randn(1000, 37, device=DEV), torch.randn(70001, device=DEV).bfloat16(), torch.randn(300, 300, device=DEV).half(),
+          torch.randn(5, device=DEV)]
+    fp8 = [(torch.randn(513, 129, device=DEV) * 0.01).cast(E4), (torch.randn(100000, device=DEV) * 3).cast(E5)]
+    grads = hp + fp8
+    want = sum(g.float().square().sum() for g in grads)
+    stats = mt.grad_sumsq(grads, tag='test')
+    assert stats[1].item() == 0 and abs(stats[0].item() - want.item()) <= 1e-4 * want.item()
+    before = [g.float().clone() for g in grads]
+    bytes_before = [g.value.clone() for g in fp8]
+    max_norm = 0.25 * want.sqrt().item()
+    mt.clip_by_sumsq(grads, stats[0:1], max_norm, tag='test')
+    coef = max_norm / (want.sqrt().item() + 1e-6)
+    for g, b in zip(grads, before):
+        tol = 1e-2 if (not isinstance(g, torch.Tensor) or g.dtype != torch.float32) else 1e-6
+        assert (g.float() - b * coef).abs().max().item() <= tol * (b.abs().max().item() * coef) + 1e-12
+    assert all(torch.equal(g.value, b) for g, b in zip(fp8, bytes_before))    # FP8 gradients are clipped through scale_inv only
+    # clipping with a generous threshold is a no-op; a non-finite value raises the flag
+    again = [g.float().clone() for g in grads]
+    mt.clip_by_sumsq(grads, mt.grad_sumsq(grads, tag='test')[0:1], 1e9, tag='test')
+    assert all(torch.equal(g.float(), a) for g, a in zip(grads, again))
+    hp[0][3, 3] = float('inf')
+    assert mt.grad_sumsq(grads, tag='test')[1].item() == 1
+    _status_ok()
+
+
 def test_add_to_fp8_bit_exact():
     for q in (E4, E5):
         for dt in (torch.float32, torch.float16, torch.bfloat16):

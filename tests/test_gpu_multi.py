@@ -1,4 +1,6 @@
-"""Multi-GPU tests (run only when at least two GPUs are visible): symmetric memory, fused FP8 reduce, sharded optimizer."""
+"""Multi-GPU tests: symmetric memory, fused FP8 reduce, sharded optimizer, fused GEMM + collective kernels.
+
+Every test runs on 2, 4 and 8 ranks (one process per GPU) and is skipped when fewer GPUs are visible."""
 import pytest
 import torch
 import torch.distributed as dist
@@ -9,6 +11,7 @@ from tests.dist_utils import run_workers
 
 pytestmark = pytest.mark.gpu
 E4M3 = Dtypes.kfloat8_e4m3
+WORLDS = pytest.mark.parametrize('world', [2, 4, 8])
 
 
 def _need(n):
@@ -38,9 +41,63 @@ def _symm_and_barrier(rank, world):
     buf.close()
 
 
-def test_symmetric_memory_and_bounded_barrier():
-    _need(2)
-    run_workers(_symm_and_barrier, 2, backend='nccl')
+@WORLDS
+def test_symmetric_memory_and_bounded_barrier(world):
+    _need(world)
+    run_workers(_symm_and_barrier, world, backend='nccl')
+
+
+def _timeout_then_normal_reduce(rank, world):
+    """Host-injected failure of the fused gradient reduce: the ranks disagree on the epoch, so one side's wait runs out
+    (status bit 1) and the other sees a flag from the future (status bit 3); after the ranks agree again the very next
+    reduce must be correct, i.e. the shared completion counter was left at zero by the CTAs that gave up."""
+    from msamp.ops import native
+    from msamp.parallel.zero import ZeroShardedOptimizer
+    dev = torch.device('cuda', rank)
+    model = _mk_model(dev)
+    opt = torch.optim.AdamW(model.parameters(), lr=1e-2)
+    model, opt = msamp.initialize(model, opt, 'O2')
+    zero = ZeroShardedOptimizer(model, opt, stage=0, wait_seconds=1.0)
+    torch.manual_seed(100 + rank)
+    x = torch.randn(64, 256, device=dev)
+    model(x).square().mean().backward()
+    keep = zero.g_flat.clone()
+    keep_meta = zero.g_meta_t.clone()
+    if rank == 0:
+        zero.flags.epoch += 100    # rank 0 waits for an epoch nobody else announces
+    zero._reduce_fp8_grads()
+    torch.cuda.synchronize()
+    status = native.device_status()
+    assert status & (2 if rank == 0 else 8), status
+    counter = zero.flags.view(torch.int32)[-8:]
+    assert int(counter[0]) == 0    # the completion counter is back at zero
+    # agree on the epoch again (on the host) and restore the inputs: the next reduce is a normal one
+    dist.barrier()
+    zero.flags.epoch = 1000
+    zero.g_flat.copy_(keep)
+    zero.g_meta_t.copy_(keep_meta)
+    torch.cuda.synchronize()
+    dist.barrier()
+    expect = []
+    for i, p in enumerate(zero.fp8_params):
+        lo = zero.offsets[i]
+        g = keep[lo:lo + p.numel()].view(torch.float8_e4m3fn).float() * keep_meta[0, i]
+        dist.all_reduce(g)
+        expect.append(g / world)
+    zero._reduce_fp8_grads()
+    torch.cuda.synchronize()
+    assert native.device_status() == 0
+    for i, (p, e) in enumerate(zip(zero.fp8_params, expect)):
+        lo = zero.offsets[i]
+        got = zero.g_flat[lo:lo + p.numel()].view(torch.float8_e4m3fn).float() * zero.g_meta_t[0, i]
+        assert (got - e).abs().max().item() <= 0.07 * e.abs().max().item() + 1e-8
+    zero.close()
+
+
+@WORLDS
+def test_reduce_recovers_after_timeout_and_detects_desync(world):
+    _need(world)
+    run_workers(_timeout_then_normal_reduce, world, backend='nccl')
 
 
 def _mk_model(dev):
@@ -81,9 +138,10 @@ def _fused_reduce_matches_math(rank, world):
     assert torch.equal(flat, ref)
 
 
-def test_fused_fp8_allreduce():
-    _need(2)
-    run_workers(_fused_reduce_matches_math, 2, backend='nccl')
+@WORLDS
+def test_fused_fp8_allreduce(world):
+    _need(world)
+    run_workers(_fused_reduce_matches_math, world, backend='nccl')
 
 
 def _zero2_training(rank, world):
@@ -119,17 +177,18 @@ def _zero2_training(rank, world):
     assert torch.equal(flat, ref)
 
 
-def test_zero2_training_two_gpus():
-    _need(2)
-    run_workers(_zero2_training, 2, backend='nccl')
+@WORLDS
+def test_zero2_training(world):
+    _need(world)
+    run_workers(_zero2_training, world, backend='nccl')
 
 
-def _fused_gemms(rank, world):
+def _fused_gemms(rank, world, n_comm=4, shapes=((128, 256, 128), (256, 512, 384), (1024, 4096, 1536), (512, 1024, 1000))):
     from msamp.ops import cast, gemm, native
     from msamp.parallel.fused import FusedGemmContext, all_gather_cols, all_gather_rows, reduce_scatter_rows
     dev = torch.device('cuda', rank)
     F8 = Dtypes.qtype_to_float8
-    ctx = FusedGemmContext(max_shard_bytes=8 << 20, max_out_bytes=64 << 20, n_comm=4)
+    ctx = FusedGemmContext(max_shard_bytes=8 << 20, max_out_bytes=64 << 20, n_comm=n_comm, wait_seconds=2.0)
     assert ctx.native
     sinv = torch.tensor(1 / 16.0, device=dev)
     scale = torch.tensor(16.0, device=dev)
@@ -138,7 +197,7 @@ def _fused_gemms(rank, world):
         g = torch.Generator(device=dev).manual_seed(seed)
         return cast.cast_to_fp8(torch.randn(*shape, device=dev, generator=g), E4M3, scale)
 
-    for (rows, K, N) in ((128, 256, 128), (256, 512, 384), (1024, 4096, 1536), (512, 1024, 1000)):
+    for (rows, K, N) in shapes:
         # --- all-gather(rows of A) + GEMM
         a_shard = q((rows, K), 100 + rank)
         b = q((N, K), 7)
@@ -192,11 +251,20 @@ def _fused_gemms(rank, world):
             err = (out.float() - ref).abs().max().item()
             assert err <= 2e-2 * ref.abs().max().item() + 1e-3, ('gemm_rs', rows, K, N, err)    # partials are rounded to bf16 before the sum
     dist.barrier()
+    ctx.close()
 
 
-def test_fused_gemm_collectives_two_gpus():
+@WORLDS
+def test_fused_gemm_collectives(world):
+    _need(world)
+    run_workers(_fused_gemms, world, backend='nccl')
+
+
+@pytest.mark.parametrize('n_comm', [1, 32])
+def test_fused_gemm_copy_cta_extremes(n_comm):
+    """One copy CTA (every chunk through the same CTA) and many (more copy CTAs than chunks for the small shapes)."""
     _need(2)
-    run_workers(_fused_gemms, 2, backend='nccl')
+    run_workers(_fused_gemms, 2, backend='nccl', args=(n_comm, ((128, 256, 128), (512, 1024, 1000))))
 
 
 def _sp_block_fused(rank, world):
@@ -236,9 +304,10 @@ def _sp_block_fused(rank, world):
     mpu.destroy_model_parallel()
 
 
-def test_sequence_parallel_block_fused_kernels():
-    _need(2)
-    run_workers(_sp_block_fused, 2, backend='nccl')
+@WORLDS
+def test_sequence_parallel_block_fused_kernels(world):
+    _need(world)
+    run_workers(_sp_block_fused, world, backend='nccl')
 
 
 def _full_shard_fused(rank, world):
@@ -268,6 +337,7 @@ def _full_shard_fused(rank, world):
     assert torch.equal(s, ref)
 
 
-def test_full_shard_fused_two_gpus():
-    _need(2)
-    run_workers(_full_shard_fused, 2, backend='nccl')
+@WORLDS
+def test_full_shard_fused(world):
+    _need(world)
+    run_workers(_full_shard_fused, world, backend='nccl')
