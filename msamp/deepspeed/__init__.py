@@ -6,7 +6,8 @@ and ``initialize`` builds MS-AMP engines from the same JSON configuration with a
 
     "msamp": {"enabled": true, "opt_level": "O1|O2|O3", "use_te": false}
 
-The engines themselves do not depend on DeepSpeed: ``MSAMPDeepSpeedEngine`` implements the training-loop
+With DeepSpeed installed, ``initialize`` returns a subclass of its ``DeepSpeedEngine`` whose optimizer is one of msamp's FP8
+wrappers (``runtime/adapter.py``).  Without it, the stand-alone engines below are used; they do not depend on DeepSpeed: ``MSAMPDeepSpeedEngine`` implements the training-loop
 surface (``engine(inputs)``, ``engine.backward(loss)``, ``engine.step()``, checkpoints, gradient
 accumulation, clipping, loss scaling, ZeRO stages 0-2 and pipeline parallelism) on msamp's own optimizers
 and fused collectives.
@@ -47,6 +48,15 @@ def initialize(args=None, model=None, optimizer=None, model_parameters=None, tra
         os.environ.setdefault('MASTER_ADDR', '127.0.0.1')
         os.environ.setdefault('MASTER_PORT', '29500')
         torch.distributed.init_process_group('nccl' if torch.cuda.is_available() else 'gloo')
+    from msamp.deepspeed.runtime import adapter
+    if adapter.deepspeed_available() and not isinstance(model, PipelineModule):
+        # DeepSpeed is installed: its own engine and config, subclassed so that the optimizer is msamp's
+        engine_cls, config_cls = adapter.make_engine_class(), adapter.make_config_class()
+        cfg = config_cls(config, mpu)
+        engine = engine_cls(args=args, model=model, optimizer=optimizer, model_parameters=model_parameters, training_data=training_data,
+                            lr_scheduler=lr_scheduler, mpu=mpu, dist_init_required=dist_init_required, collate_fn=collate_fn, config=config,
+                            config_class=cfg)
+        return engine, engine.optimizer, engine.training_dataloader, engine.lr_scheduler
     if mpu is None and isinstance(model, PipelineModule):
         mpu = model    # batch arithmetic counts data-parallel replicas, not pipeline stages
     cfg = MSAMPDeepSpeedConfig(config, mpu)

@@ -34,6 +34,14 @@ class FP8DeepSpeedZeroOptimizer(FP8Optimizer):
     def partition_count(self):
         return self.zero.world
 
+    # DeepSpeed's engine calls these between backward and step; here the (fused) reduction of all gradients happens
+    # inside step(), so they have nothing left to do.
+    def overlapping_partition_gradients_reduce_epilogue(self):
+        return None
+
+    def reduce_gradients(self, pipeline_parallel=False):
+        return None
+
     def has_overflow(self, partition_gradients=True):
         return self.overflow_checker.check(self._all_params())
 

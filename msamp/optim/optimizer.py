@@ -55,8 +55,42 @@ class LBOptimizer(Optimizer):
                 names.append('wgrad')
         for name in names:
             flat = metas[name]
-            _k.roll_windows(flat['amaxs'], flat['scales'], flat['qtype'], margin=0)
+            self._apply_pending_resets(flat)
+            bad = flat.get('_bad_dev')
+            if bad is None or bad.device != flat['amaxs'].device or bad.numel() != flat['amaxs'].shape[0]:
+                bad = flat['_bad_dev'] = torch.zeros(flat['amaxs'].shape[0], dtype=torch.int32, device=flat['amaxs'].device)
+            _k.roll_windows(flat['amaxs'], flat['scales'], flat['qtype'], margin=0, bad_out=bad)
             flat['amax_counters'] += 1
+            # A non-finite amax puts its meta back into warm-up (in-time scaling for `window` steps), as the reference does
+            # (msamp/optim/optimizer.py:100-103).  The step counters live on the host, the flags on the device: on CPU the
+            # reset is immediate; on CUDA the flags travel through pinned memory and are applied once their copy has
+            # finished (at the latest before the next roll), so that no step waits for the device.
+            if bad.is_cuda:
+                host = flat.get('_bad_host')
+                if host is None or host.numel() != bad.numel():
+                    host = flat['_bad_host'] = torch.zeros(bad.numel(), dtype=torch.int32).pin_memory()
+                host.copy_(bad, non_blocking=True)
+                event = torch.cuda.Event()
+                event.record()
+                flat['_bad_pending'] = (host, event)
+            else:
+                flat['_bad_pending'] = (bad.clone(), None)
+                self._apply_pending_resets(flat)
+
+    @staticmethod
+    def _apply_pending_resets(flat, wait=True):
+        pending = flat.get('_bad_pending')
+        if pending is None:
+            return
+        host, event = pending
+        if event is not None:
+            if not wait and not event.query():
+                return
+            event.synchronize()    # the copy was enqueued a whole step ago: this does not stall in practice
+        mask = host.bool()
+        if bool(mask.any()):
+            flat['amax_counters'][mask.to(flat['amax_counters'].device)] = 0
+        flat['_bad_pending'] = None
 
     # ---- bookkeeping that must tolerate ScalingTensor --------------------------------------------
     def zero_grad(self, set_to_none=None):

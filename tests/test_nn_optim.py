@@ -400,3 +400,28 @@ def test_fused_sublayers_match_composed_block(regime, monkeypatch):
     for k in a0:    # both paths record the same statistics for the delayed scales
         assert torch.allclose(a0[k], a1[k], rtol=0.1, atol=1e-6), k
     assert l0[-1] < l0[0]
+
+
+def test_nonfinite_amax_puts_meta_back_into_warmup():
+    """After an inf / NaN amax the meta's step counter restarts, so the layer scales in time again for `window` steps
+    (the reference's rule: amax_counters[mask_inf_nan] = 0)."""
+    import msamp
+    from msamp.nn import model_state
+    torch.manual_seed(0)
+    model = torch.nn.Sequential(torch.nn.Linear(16, 16), torch.nn.Linear(16, 4))
+    opt = torch.optim.AdamW(model.parameters(), lr=1e-3)
+    model, opt = msamp.initialize(model, opt, 'O2')
+    x = torch.randn(8, 16)
+    for _ in range(17):
+        opt.zero_grad()
+        model(x).sum().backward()
+        opt.step()
+    metas = list(model_state.local_scaling_metas.values())
+    assert not metas[0]['input'].is_warmup() and not metas[1]['input'].is_warmup()
+    bad = x.clone()
+    bad[0, 0] = float('inf')
+    opt.zero_grad()
+    model(bad).sum().backward()    # the first layer records amax = inf for its input
+    opt.step()
+    assert metas[0]['input'].is_warmup() and int(metas[0]['input'].amax_counter) == 0
+    assert torch.isfinite(metas[0]['input'].scale).all()
