@@ -80,6 +80,19 @@ class ScalingMeta:
         fp_max = Floating.qfp_max[qtype]
         self.scale.copy_(ScalingMeta.compute_scaling_factor(self.amax[0], self.scale, fp_max, 0))
 
+    def __setstate__(self, state):
+        """Unpickle; a checkpoint written by the reference after a CUDA optimizer step holds ``scale`` / ``scale_inv`` as
+        Python floats (msamp/optim/adamw.py:188-193): they become 0-d fp32 tensors again, next to ``amax``."""
+        self.__dict__.update(state)
+        amax = self.__dict__.get('amax')
+        device = amax.device if torch.is_tensor(amax) else torch.device('cpu')
+        for key in ('scale', 'scale_inv'):
+            v = self.__dict__.get(key)
+            if v is not None and not torch.is_tensor(v):
+                self.__dict__[key] = torch.tensor(float(v), dtype=torch.float32, device=device)
+        self.__dict__.setdefault('group', None)
+        self.__dict__.setdefault('locked', False)
+
     def copy_(self, src):
         """Copy every field of ``src`` except group and lock."""
         self.qtype = src.qtype

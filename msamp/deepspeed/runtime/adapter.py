@@ -90,7 +90,8 @@ def make_engine_class():
             elif callable(client_optimizer):
                 basic = client_optimizer(model_parameters)
             else:
-                basic = self._configure_basic_optimizer(model_parameters)    # DeepSpeed's own builder: its whole optimizer zoo
+                from msamp.deepspeed.runtime.engine import build_over_all_parameters
+                basic = build_over_all_parameters(self._configure_basic_optimizer, model_parameters, self.module)    # DeepSpeed's own builder
             level = self.msamp_optlevel()
             init_level = 'O2' if level == 'O3' else level    # the ZeRO wrapper below provides O3's FP8 weights + fp16 masters
             group = self._dp_group()

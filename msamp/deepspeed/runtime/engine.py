@@ -21,6 +21,23 @@ from msamp.utils.timer import PhaseTimers, nvtx_range
 _OPTIMIZERS = {'adam': torch.optim.Adam, 'adamw': torch.optim.AdamW}
 
 
+def build_over_all_parameters(build, model_parameters, module):
+    """Basic (torch) optimizer over ``model_parameters`` or all parameters of ``module``.
+
+    Models built from ``msamp.te`` modules already hold ScalingParameters, which torch's optimizers reject: the optimizer
+    is then built on the plain tensors and its first group rebound to the full list (``msamp.initialize`` replaces every
+    entry by position anyway)."""
+    params = list(model_parameters) if model_parameters is not None else list(module.parameters())
+    if params and isinstance(params[0], dict):
+        return build(params)
+    plain = [p for p in params if torch.is_tensor(p)]
+    if len(plain) == len(params):
+        return build(params)
+    opt = build(plain if plain else [torch.nn.Parameter(torch.zeros(1))])
+    opt.param_groups[0]['params'] = params
+    return opt
+
+
 class _WarmupLR:
     """Linear warm-up from ``warmup_min_lr`` to ``warmup_max_lr`` over ``warmup_num_steps`` (DeepSpeed's WarmupLR)."""
     def __init__(self, optimizer, warmup_min_lr=0.0, warmup_max_lr=1e-3, warmup_num_steps=1000, **unused):
@@ -78,7 +95,7 @@ class MSAMPDeepSpeedEngine(torch.nn.Module):
         params.pop('torch_adam', None)
         adam_w_mode = params.pop('adam_w_mode', name == 'adamw')
         cls = torch.optim.AdamW if adam_w_mode else torch.optim.Adam
-        return cls(model_parameters if model_parameters is not None else self.module.parameters(), **params)
+        return build_over_all_parameters(lambda ps: cls(ps, **params), model_parameters, self.module)
 
     def _configure_optimizer(self, client_optimizer, model_parameters):
         cfg = self.config

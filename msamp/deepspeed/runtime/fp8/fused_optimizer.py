@@ -56,7 +56,7 @@ class FP8Optimizer:
 
     def _all_params(self):
         if self.zero is not None:
-            return list(self.zero.fp8_params) + list(self.zero.hp_params)
+            return list(self.zero.fp8_params) + list(self.zero.hp_params) + list(self.zero.local_params)
         return [p for g in self.optimizer.param_groups for p in g['params']]
 
     def zero_grad(self, set_to_none=True):
@@ -95,7 +95,7 @@ class FP8Optimizer:
                 return acc
 
             sq = sumsq(params)
-            if self.zero is not None and self.zero.sharded and self.zero.world > 1:
+            if self.zero is not None and self.zero.world > 1 and (self.zero.sharded or sharded):
                 part = sumsq(sharded)
                 part = part if part is not None else torch.zeros((), device=self.zero.device)
                 part = part.float().reshape(1).clone()
@@ -148,11 +148,12 @@ class FP8Optimizer:
                     m.grad = self.zero.fp8_params[i].grad
                 if self.zero.world > 1:
                     # high-precision parameters are sharded as well: each rank unscales and clips what it owns
-                    self._unscale_and_clip([], sharded=list(self.zero.masters.values()) + self.zero._owned_hp())
+                    self._unscale_and_clip([], sharded=list(self.zero.masters.values()) + self.zero._owned_hp() + self.zero.local_params)
                 else:
-                    self._unscale_and_clip(self.zero.hp_params, sharded=list(self.zero.masters.values()))
+                    self._unscale_and_clip(self.zero.hp_params, sharded=list(self.zero.masters.values()) + self.zero.local_params)
             else:
-                self._unscale_and_clip(params)
+                local = {id(p) for p in self.zero.local_params}
+                self._unscale_and_clip([p for p in params if id(p) not in local], sharded=self.zero.local_params)
             with self.timers.phase(BASIC_STEP):
                 self.optimizer.step()
             with self.timers.phase(UPDATE_FP16):

@@ -131,9 +131,9 @@ class _LnLinearFn(torch.autograd.Function):
 
 
 class _MlpSublayerFn(torch.autograd.Function):
-    """``x + fc2(gelu(fc1(layer_norm(x))))``."""
+    """``x + fc2(gelu(fc1(layer_norm(x))))`` (without the ``x +`` when ``add_residual`` is false)."""
     @staticmethod
-    def forward(ctx, x, ln_weight, ln_bias, b1, b2, eps, w1, m1, w2, m2):
+    def forward(ctx, x, ln_weight, ln_bias, b1, b2, eps, w1, m1, w2, m2, add_residual=True):
         model_state.check_metas_in_flat(m1)
         model_state.check_metas_in_flat(m2)
         x = x.contiguous()
@@ -152,7 +152,8 @@ class _MlpSublayerFn(torch.autograd.Function):
             h = _g.gemm_fp8(y8, E4M3, y_sinv, w1_8, E4M3, w1_sinv, dt, bias=b1, amax_out=g_meta.amax[0], act='gelu', out8=g8,
                             out8_qtype=E4M3, out8_scale=g_meta.scale, out8_scale_inv_out=g_meta.scale_inv)
             g_sinv = g_meta.scale_inv.clone()
-        out = _g.gemm_fp8(g8, E4M3, g_sinv, w2_8, E4M3, w2_sinv, dt, bias=b2, residual=x)
+        out = _g.gemm_fp8(g8, E4M3, g_sinv, w2_8, E4M3, w2_sinv, dt, bias=b2, residual=x if add_residual else None)
+        ctx.add_residual = add_residual
         ctx.save_for_backward(x, ln_weight, mean, rstd, y8, y_sinv, h, g8, g_sinv, w1_8, w1_sinv, w2_8, w2_sinv)
         ctx.w1, ctx.m1, ctx.w2, ctx.m2 = w1, m1, w2, m2
         ctx.has_ln_bias = ln_bias is not None
@@ -178,8 +179,8 @@ class _MlpSublayerFn(torch.autograd.Function):
         del dh
         _deliver_wgrad(ctx.w1, m1, dh8, dh_sinv, y8, y_sinv, dt)
         dln = gemm_dgrad(dh8, dh_sinv, w1_8, w1_sinv, dt)
-        dx, dgamma, dbeta = _ln_backward(dln, x, ln_weight, mean, rstd, ctx.has_ln_bias, g)
-        return dx, dgamma, dbeta, db1, db2, None, None, None, None, None
+        dx, dgamma, dbeta = _ln_backward(dln, x, ln_weight, mean, rstd, ctx.has_ln_bias, g if ctx.add_residual else None)
+        return dx, dgamma, dbeta, db1, db2, None, None, None, None, None, None
 
 
 class _AttnSublayerFn(torch.autograd.Function):
@@ -239,11 +240,18 @@ def ln_linear(x, ln, linear):
     return _LnLinearFn.apply(x, ln.weight, ln.bias, linear.bias, ln.eps, linear.weight, linear.scaling_metas)
 
 
-def mlp_sublayer(x, ln, fc1, fc2):
-    """``x + fc2(gelu(fc1(ln(x))))`` for FP8Linear ``fc1`` / ``fc2``, 2-D ``x``."""
+def mlp_sublayer(x, ln, fc1, fc2, residual=True):
+    """``x + fc2(gelu(fc1(ln(x))))`` for FP8Linear ``fc1`` / ``fc2``, 2-D ``x``; ``residual=False`` drops the ``x +``."""
     model_state.ready_to_scale_tensor = True
     return _MlpSublayerFn.apply(x, ln.weight, ln.bias, fc1.bias, fc2.bias, ln.eps, fc1.weight, fc1.scaling_metas, fc2.weight,
-                                fc2.scaling_metas)
+                                fc2.scaling_metas, bool(residual))
+
+
+class ModuleView:
+    """Presents parameters that live under other names (e.g. ``layer_norm_weight``, ``fc1_weight`` of the TE-shaped
+    modules) as the ``weight`` / ``bias`` / ``eps`` / ``scaling_metas`` attributes the sublayer functions read."""
+    def __init__(self, weight, bias=None, eps=None, scaling_metas=None):
+        self.weight, self.bias, self.eps, self.scaling_metas = weight, bias, eps, scaling_metas
 
 
 def attention_sublayer(x, ln, qkv, proj, batch, seq, n_head, causal=True):

@@ -62,7 +62,14 @@ class ZeroShardedOptimizer:
         self.model_parallel_group = model_parallel_group    # gradient-norm clipping sums over it as well
         params = [p for p in model.parameters() if isinstance(p, ScalingParameter)]
         self.fp8_params = params
-        self.hp_params = [p for p in model.parameters() if not isinstance(p, ScalingParameter)]
+        # Expert (MoE) parameters carry ``allreduce = False`` (DeepSpeed's marker): every data-parallel rank holds different
+        # experts, so they are neither reduced over the data-parallel group nor sharded; their gradient norm is summed
+        # over the group like that of any parameter held by one rank only (reference: fp8/fused_optimizer.py:375-397).
+        self.local_params = [p for p in model.parameters() if not isinstance(p, ScalingParameter) and getattr(p, 'allreduce', True) is False]
+        if any(getattr(p, 'allreduce', True) is False for p in params):
+            raise NotImplementedError('FP8 expert weights (ScalingParameter with allreduce=False) are not supported by the sharded optimizer')
+        local_ids = {id(p) for p in self.local_params}
+        self.hp_params = [p for p in model.parameters() if not isinstance(p, ScalingParameter) and id(p) not in local_ids]
         sizes = [p.numel() for p in params]
         self.owners = partition_tensors(sizes, self.world)
         offs = [0]
@@ -412,11 +419,18 @@ class ZeroShardedOptimizer:
             if mp_group is not None and mp_rank != 0 and not getattr(p, 'tensor_model_parallel', False):
                 continue    # replicated over the model-parallel group: counted on its first rank only
             counted.append(p.grad)
+        local = [p.grad for p in self.local_params if p.grad is not None]
+        clipped += local
         if not self.sharded and self.world > 1:
-            # replicated states: every rank holds every gradient, so the local sum already is the data-parallel total
+            # replicated states: every rank holds every gradient, so the local sum already is the data-parallel total;
+            # only the expert parameters (different on every rank) have to be summed over the group
             stats = _mt.grad_sumsq(counted, tag='zero_norm')
+            if self.local_params:
+                extra = _mt.grad_sumsq(local, out=torch.zeros_like(stats), tag='zero_norm_local')
+                dist.all_reduce(extra, group=self.group)
+                stats = stats + extra
         else:
-            stats = _mt.grad_sumsq(counted, tag='zero_norm')
+            stats = _mt.grad_sumsq(counted + local, tag='zero_norm')
             if self.world > 1:
                 dist.all_reduce(stats, group=self.group)
         if stats.device != self.device:

@@ -13,6 +13,7 @@ import torch.nn.functional as F
 from msamp.common.dtype import Dtypes
 from msamp.common.tensor import ScalingMeta
 from msamp.nn.module import ScalingModule
+from msamp.nn import fused_layers as FL
 from msamp.nn.parameter import ScalingParameter
 from msamp.ops import nn as K
 
@@ -74,7 +75,14 @@ class MSAMPLayerNormLinear(ScalingModule):
         self.scaling_metas = _metas(dev)
         self.weight._scaling_metas = self.scaling_metas
 
+    def _views(self):
+        return (FL.ModuleView(self.layer_norm_weight, self.layer_norm_bias, self.eps),
+                FL.ModuleView(self.weight, self.bias, scaling_metas=self.scaling_metas))
+
     def forward(self, x):
+        if not self.return_layernorm_output and isinstance(self.weight, ScalingParameter) and x.dim() == 2:
+            ln, lin = self._views()
+            return FL.ln_linear(x, ln, lin)    # LayerNorm emits e4m3 directly: its output is never stored in 16 bits
         ln = K.layer_norm(x, self.layer_norm_weight, self.layer_norm_bias, self.eps)
         out = F.linear(ln, self.weight, self.bias)
         return (out, ln) if self.return_layernorm_output else out
@@ -100,10 +108,20 @@ class MSAMPLayerNormMLP(ScalingModule):
         self.fc2_weight._scaling_metas = self.fc2_metas
         self._second = _MetaHolder(self.fc2_metas)
 
-    def forward(self, x):
+    def _views(self):
+        return (FL.ModuleView(self.layer_norm_weight, self.layer_norm_bias, self.eps),
+                FL.ModuleView(self.fc1_weight, self.fc1_bias, scaling_metas=self.fc1_metas),
+                FL.ModuleView(self.fc2_weight, self.fc2_bias, scaling_metas=self.fc2_metas))
+
+    def forward(self, x, residual=False):
+        """``fc2(gelu(fc1(layer_norm(x))))``; ``residual=True`` adds ``x`` in the epilogue of the fc2 GEMM."""
+        if isinstance(self.fc1_weight, ScalingParameter) and isinstance(self.fc2_weight, ScalingParameter) and x.dim() == 2:
+            ln, fc1, fc2 = self._views()
+            return FL.mlp_sublayer(x, ln, fc1, fc2, residual=residual)
         ln = K.layer_norm(x, self.layer_norm_weight, self.layer_norm_bias, self.eps)
         h = K.gelu(F.linear(ln, self.fc1_weight, self.fc1_bias))
-        return F.linear(h, self.fc2_weight, self.fc2_bias)
+        out = F.linear(h, self.fc2_weight, self.fc2_bias)
+        return x + out if residual else out
 
 
 class _MetaHolder(torch.nn.Module):
@@ -128,6 +146,13 @@ class MSAMPTransformerLayer(torch.nn.Module):
         # hidden_states: [seq, batch, hidden] as in TE
         s, b, h = hidden_states.shape
         x = hidden_states.transpose(0, 1).contiguous()
+        fused_attention = (not x.is_cuda) or (x.dtype == torch.bfloat16 and self.head_dim in (64, 128))
+        if fused_attention and isinstance(self.layernorm_qkv.weight, ScalingParameter) and isinstance(self.proj.weight, ScalingParameter):
+            # both halves of the block as fused sublayers (msamp.nn.fused_layers)
+            ln, qkv_lin = self.layernorm_qkv._views()
+            x2 = FL.attention_sublayer(x.view(b * s, h), ln, qkv_lin, self.proj, b, s, self.num_heads, causal=self.causal)
+            x2 = self.layernorm_mlp(x2, residual=True)
+            return x2.view(b, s, h).transpose(0, 1).contiguous()
         qkv = self.layernorm_qkv(x.view(b * s, h)).view(b, s, 3, self.num_heads, self.head_dim)
         o = K.attention_qkv(qkv, causal=self.causal) if qkv.is_cuda and qkv.dtype == torch.bfloat16 and self.head_dim in (64, 128) else \
             K.attention(qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2], causal=self.causal) if not qkv.is_cuda else _sdpa(qkv, self.causal)

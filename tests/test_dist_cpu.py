@@ -1,4 +1,5 @@
 """Multi-process logic on CPU with gloo: FP8 collectives, bucketed TensorDist, sharded optimizer, DDP training."""
+import pytest
 import torch
 import torch.distributed as dist
 
@@ -459,3 +460,48 @@ def _ddp_accumulation_no_sync(rank, world):
 
 def test_fp8_ddp_no_sync_accumulation():
     run_workers(_ddp_accumulation_no_sync, 2)
+
+
+def _moe_local_params(rank, world, stage):
+    """Expert parameters (``allreduce = False``) stay local: not averaged over the data-parallel group, their gradient
+    norm is summed over it, and every rank clips with the same coefficient."""
+    import msamp
+    from msamp.deepspeed.runtime.fp8.fused_optimizer import FP8Optimizer
+    torch.manual_seed(0)
+
+    class Net(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.shared = torch.nn.Linear(8, 8)
+            self.expert = torch.nn.Parameter(torch.full((8, ), float(rank + 1)))
+            self.expert.allreduce = False
+
+        def forward(self, x):
+            return (self.shared(x) * self.expert).sum()
+
+    model = Net()
+    opt = torch.optim.AdamW(model.parameters(), lr=1e-2)
+    model, opt = msamp.initialize(model, opt, 'O2')
+    fp8_opt = FP8Optimizer(model, opt, clip_grad=0.5, zero_stage=stage, fp8_master=stage > 0)
+    if fp8_opt.zero is None:
+        from msamp.parallel.zero import ZeroShardedOptimizer
+        fp8_opt.zero = ZeroShardedOptimizer(model, opt, stage=0)
+    assert [id(p) for p in fp8_opt.zero.local_params] == [id(model.expert)]
+    x = torch.randn(4, 8)
+    fp8_opt.backward(model(x))
+    expert_grad = model.expert.grad.clone()
+    fp8_opt.step()
+    norms = [torch.zeros(()) for _ in range(world)]
+    dist.all_gather(norms, fp8_opt.get_global_grad_norm().float().reshape(()))
+    assert all(torch.equal(n, norms[0]) for n in norms)    # one norm for the whole job
+    sq = expert_grad.square().sum().reshape(1)
+    dist.all_reduce(sq)
+    assert norms[0].item()**2 >= sq.item() * 0.999    # the expert part counts every rank's experts
+    vals = [torch.zeros(8) for _ in range(world)]
+    dist.all_gather(vals, model.expert.detach().clone())
+    assert not torch.equal(vals[0], vals[1])    # experts were neither averaged nor broadcast
+
+
+@pytest.mark.parametrize('stage', [0, 2])
+def test_moe_expert_params_stay_local(stage):
+    run_workers(_moe_local_params, 2, args=(stage, ))

@@ -30,6 +30,13 @@ def test_cifar10_deepspeed_config(config):
     assert 'loss' in out
 
 
+def test_cifar10_deepspeed_te_vit():
+    """Vision Transformer on msamp.te.MSAMPTransformerLayer with the ZeRO-2 + O3 + use_te configuration."""
+    out = _run(['examples/cifar10_deepspeed_te.py', '--steps', '3', '--depth', '2', '--hidden', '128',
+                '--deepspeed_config', os.path.join('examples', 'ds_config_zero_te_msamp.json')])
+    assert 'loss' in out
+
+
 def test_gpt_pretrain_tiny():
     out = _run(['examples/gpt_pretrain.py', '--cpu', '--model', 'gpt-tiny', '--steps', '6', '--seq', '64', '--micro-batch', '2'])
     assert "'loss'" in out
