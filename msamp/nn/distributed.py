@@ -9,7 +9,12 @@ is SUM-reduced as FP8 numbers asynchronously; ``scale_inv`` is divided by W so t
 ``_DDPSink`` resets the bucket bookkeeping in forward and waits for the collectives at the end of backward.
 (reference: msamp/nn/distributed.py:18-264)
 
-For the sharded / fused NVLink path see ``msamp.parallel.ZeroShardedOptimizer``.
+On CUDA with NCCL (up to 8 ranks on one NVLink domain) a bucket takes the fused path instead: ONE multi-tensor launch
+quantises the bucket's gradients into a flat buffer in symmetric memory, each rank with its own in-time scale (the amax
+comes from the wgrad GEMM epilogue, so there is no amax collective), and ONE launch of the fused all-reduce kernel
+(``msamp_symm_grad_reduce``, broadcast flavour) pulls every peer's bytes over NVLink, dequantises each with that peer's
+scale, averages in fp32, rounds once and writes the result to every rank - on the side stream, overlapped with the rest
+of backward.  The NCCL path remains for gloo / CPU and as the oracle of the tests.
 """
 import math
 
@@ -46,6 +51,8 @@ class _ScalingTensorReducer:
         self.bucket_unreduced_param_ids = {}
         self.reduction_stream = torch.cuda.Stream(device=self.device) if self.device.type == 'cuda' else None
         self._build_buckets()
+        self.fused = False
+        self._setup_fused()
         for p in parameters:
             p.register_backward_post_hook(self._make_hook(p))
 
@@ -64,6 +71,121 @@ class _ScalingTensorReducer:
                 nbytes = 0
         if nbytes > 0:
             self.bucket_to_range[bucket] = (start, start + nbytes)
+
+    def _setup_fused(self):
+        """Symmetric buffers, per-bucket work lists and re-homed gradient metas for the fused all-reduce kernel."""
+        import os
+        world = dist.get_world_size(self.process_group) if dist.is_initialized() else 1
+        if (self.device.type != 'cuda' or world < 2 or not self.parameters or dist.get_backend(self.process_group) != 'nccl'
+                or os.environ.get('MSAMP_DDP_FUSED', '1') == '0'):
+            return
+        from msamp.ops import native
+        from msamp.parallel.symm import FlagPad, SymmetricBuffer
+        if world > native.lib().msamp_symm_max_ranks():
+            return
+        self.rank, self.world = dist.get_rank(self.process_group), world
+        n = len(self.parameters)
+        # flat layout: buckets in order, tensors of a bucket in bucket order, every tensor padded to 16 bytes
+        self.tensor_offset = [0] * (n + 1)    # indexed by position in the flat order
+        self.flat_index = {}                  # parameter id -> position in the flat order
+        off = 0
+        order = [pid for b in sorted(self.bucket_to_param_ids) for pid in self.bucket_to_param_ids[b]]
+        for k, pid in enumerate(order):
+            self.flat_index[pid] = k
+            self.tensor_offset[k] = off
+            off += (self.parameters[pid].numel() + 15) // 16 * 16
+        self.tensor_offset[n] = off
+        self.g_buf = SymmetricBuffer(max(off, 16), self.process_group)
+        self.g_meta = SymmetricBuffer(3 * n * 4, self.process_group)
+        self.flags = FlagPad(self.process_group)
+        self.g_flat = self.g_buf.view(torch.uint8)
+        self.g_meta_t = self.g_meta.view(torch.float32).view(3, n)
+        self.g_meta_t[0].fill_(1.0)
+        self.offsets_t = torch.tensor(self.tensor_offset, dtype=torch.int64, device=self.device)
+        chunk = native.lib().msamp_symm_chunk_bytes()
+        self.bucket_work, self.bucket_tensors = {}, {}
+        turn = 0
+        for b, pids in self.bucket_to_param_ids.items():
+            work, tensors = [], []
+            for pid in pids:
+                k = self.flat_index[pid]
+                tensors.append(k)
+                nbytes = self.tensor_offset[k + 1] - self.tensor_offset[k]
+                for c in range((nbytes + chunk - 1) // chunk):
+                    if turn % world == self.rank:    # chunks are dealt to the ranks in turn; each reduces its share for everybody
+                        work.append((k, c))
+                    turn += 1
+            self.bucket_work[b] = (torch.tensor(work if work else [(0, 0)], dtype=torch.int32, device=self.device).reshape(-1), len(work))
+            self.bucket_tensors[b] = torch.tensor(tensors, dtype=torch.int32, device=self.device)
+        # the gradient metas' scale_inv / amax move into the symmetric meta rows, where the peers can read them
+        for pid, p in enumerate(self.parameters):
+            meta = p._scaling_metas['wgrad'] if hasattr(p, '_scaling_metas') else None
+            if meta is None or meta.window_size != 1:
+                return    # not an FP8Linear weight: keep the NCCL path
+        for pid, p in enumerate(self.parameters):
+            k = self.flat_index[pid]
+            meta = p._scaling_metas['wgrad']
+            was_locked, meta.locked = meta.locked, False
+            si, am = self.g_meta_t[0, k:k + 1].view(()), self.g_meta_t[1, k:k + 1]
+            si.copy_(meta.scale_inv)
+            am.copy_(meta.amax)
+            meta.scale_inv, meta.amax = si, am
+            meta.locked = was_locked
+        flat = model_state.flattened_scaling_metas
+        if flat is not None and 'wgrad' in flat:
+            flat['wgrad'] = dict(flat['wgrad'], _external=True)
+        self.fused = True
+
+    def _reduce_bucket_fused(self, bucket):
+        import ctypes
+        from msamp.ops import multi_tensor as _mt
+        from msamp.ops import native
+        pids = self.bucket_to_param_ids[bucket]
+        params = [self.parameters[pid] for pid in pids]
+        self.reduction_stream.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(self.reduction_stream):
+            srcs, dsts, scales, sinvs, amaxs, metas = [], [], [], [], [], []
+            for pid, p in zip(pids, params):
+                g = p.grad
+                if isinstance(g, ScalingTensor):
+                    raise RuntimeError('FP8 DDP expects high-precision gradients carrying a .meta (set model_state.use_fp8_ddp)')
+                k = self.flat_index[pid]
+                meta = p._scaling_metas['wgrad']
+                if getattr(g, 'meta', None) is not meta:
+                    _k.amax(g, out=meta.amax[0])    # a gradient that did not come from the wgrad GEMM epilogue
+                g = g.contiguous()
+                g.record_stream(self.reduction_stream)
+                lo = self.tensor_offset[k]
+                srcs.append(g)
+                dsts.append(self.g_flat[lo:lo + g.numel()])
+                scales.append(meta.scale)
+                sinvs.append(meta.scale_inv)
+                amaxs.append(meta.amax[0])
+                metas.append(meta)
+            _mt.cast_to_fp8_multi(srcs, dsts, E4M3, scales, sinvs, amax_ins=amaxs, tag=f'fp8_ddp_bucket{bucket}')
+            work_t, n_work = self.bucket_work[bucket]
+            n = len(self.parameters)
+            native.check(
+                native.lib().msamp_symm_grad_reduce(
+                    self.g_buf.table, self.g_meta.table, self.flags.table, native.ptr(self.offsets_t), native.ptr(work_t), n_work, n,
+                    self.rank, self.world, ctypes.c_uint(self.flags.next_epoch()), 1, ctypes.c_double(5.0), 64, native.stream()    # 64 CTAs: it overlaps backward
+                ), 'symm_grad_reduce'
+            )
+            tensors = self.bucket_tensors[bucket]
+            native.check(
+                native.lib().msamp_symm_commit_meta(native.ptr(self.g_meta_t), n, native.ptr(tensors), tensors.numel(), native.stream()),
+                'symm_commit_meta'
+            )
+            for p, dst, meta in zip(params, dsts, metas):
+                p.grad = ScalingTensor(dst.view(p.shape), meta)
+
+    def close(self):
+        """Release the symmetric buffers of the fused path (collective over the group)."""
+        if self.fused:
+            dist.barrier(group=self.process_group)
+            for buf in (self.g_buf, self.g_meta, self.flags):
+                buf.close()
+            self.fused = False
 
     def reset_buckets(self):
         if self.bucket_unreduced_param_ids:
@@ -97,6 +219,8 @@ class _ScalingTensorReducer:
         return hook
 
     def _reduce_bucket(self, bucket):
+        if self.fused:
+            return self._reduce_bucket_fused(bucket)
         world = dist.get_world_size(self.process_group)
         params = [self.parameters[pid] for pid in self.bucket_to_param_ids[bucket]]
         grads = [p.grad for p in params]

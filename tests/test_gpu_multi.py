@@ -100,6 +100,60 @@ def test_reduce_recovers_after_timeout_and_detects_desync(world):
     run_workers(_timeout_then_normal_reduce, world, backend='nccl')
 
 
+def _fp8_ddp_fused(rank, world):
+    """FP8 DDP on the fused all-reduce kernel: the reduced gradient is the fp32 mean of the ranks' gradients within one
+    e4m3 rounding, every rank ends with identical bytes and scales, and training converges with identical replicas."""
+    from msamp.nn.distributed import FP8DistributedDataParallel
+    from msamp.ops import native
+    dev = torch.device('cuda', rank)
+    model = _mk_model(dev)
+    opt = torch.optim.AdamW(model.parameters(), lr=3e-3)
+    model, opt = msamp.initialize(model, opt, 'O2')
+    ddp = FP8DistributedDataParallel(model, device_ids=[rank], bucket_cap_mb=0.2)
+    red = ddp.scaling_tensor_reducer
+    assert red.fused and len(red.bucket_to_param_ids) > 1
+    torch.manual_seed(50 + rank)
+    x = torch.randn(64, 256, device=dev)
+    ddp(x).square().mean().backward()
+    torch.cuda.synchronize()
+    assert native.device_status() == 0
+    for p in red.parameters:
+        assert p.grad is not None and p.grad.qtype == E4M3
+    flat = red.g_flat.clone()
+    ref = flat.clone()
+    dist.broadcast(ref, src=0)
+    assert torch.equal(flat, ref)
+    meta = red.g_meta_t[0].clone()
+    ref = meta.clone()
+    dist.broadcast(ref, src=0)
+    assert torch.equal(meta, ref)
+    opt.zero_grad()
+    xs, ys = torch.randn(world * 32, 256, device=dev), torch.randn(world * 32, 64, device=dev)
+    dist.broadcast(xs, src=0)
+    dist.broadcast(ys, src=0)
+    losses = []
+    for _ in range(20):
+        opt.zero_grad()
+        loss = (ddp(xs[rank * 32:(rank + 1) * 32]) - ys[rank * 32:(rank + 1) * 32]).square().mean()
+        loss.backward()
+        opt.step()
+        losses.append(loss.item())
+    torch.cuda.synchronize()
+    assert native.device_status() == 0
+    assert losses[-1] < 0.8 * losses[0], losses
+    flat = torch.cat([p.float().reshape(-1) for p in model.parameters()])
+    ref = flat.clone()
+    dist.broadcast(ref, src=0)
+    assert torch.equal(flat, ref)
+    red.close()
+
+
+@WORLDS
+def test_fp8_ddp_on_fused_allreduce(world):
+    _need(world)
+    run_workers(_fp8_ddp_fused, world, backend='nccl')
+
+
 def _mk_model(dev):
     torch.manual_seed(0)
     return torch.nn.Sequential(torch.nn.Linear(256, 512), torch.nn.GELU(), torch.nn.Linear(512, 512), torch.nn.GELU(),
