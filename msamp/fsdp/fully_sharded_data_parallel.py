@@ -3,7 +3,9 @@
 Every FP8Linear weight ``W [N, K]`` is split by rows over the data-parallel group; a rank permanently holds
 only its e4m3 shard ``W_r [N/W, K]`` (and the shard's transpose), its scaled-fp16 master shard and its Adam
 moment shards.  One scale per *tensor* is kept consistent by MAX-reducing the amax over the shards before
-every re-quantisation (the reference's rule, msamp/optim/adamw.py:306-337).
+every re-quantisation (the reference's rule, msamp/optim/adamw.py:306-337).  The e4m3 shards live permanently in
+symmetric (peer-mapped) memory, so the gather kernels read them where they are; everything that is not a sharded
+linear (embeddings, LayerNorms, biases) is sharded ZeRO-style by ``msamp.parallel.hp_shard.HighPrecisionShards``.
 
   forward   y  = x8 · all-gather-rows(W8_r)ᵀ           parameter all-gather fused into the GEMM
   backward  dx = dy8 · all-gather-K(W8ᵀ_r)ᵀ            parameter all-gather (transposed shards) fused into the GEMM
@@ -43,15 +45,15 @@ class _ShardedLinearFn(torch.autograd.Function):
         x_sinv = in_meta.scale_inv.clone()
         w8, w_sinv = module.weight_shard, module.weight_meta.scale_inv
         rows, K = w8.shape
-        fused = fs.ctx if (fs.ctx is not None and fs.ctx.native and rows % 256 == 0) else None
+        fused = fs.ctx if (fs.ctx is not None and fs.ctx.native and rows % 128 == 0 and module.resident) else None
         if fused is not None:
-            view = fused.shard_view(rows * K).view(rows, K)
-            view.copy_(w8)
-            out = fused.ag_rows_gemm(view, E4M3, w_sinv, x8, E4M3, x_sinv, x.dtype, bias=bias if bias is None or bias.dtype == torch.float32 else None,
+            fs.fused_calls += 1
+            out = fused.ag_rows_gemm(w8, E4M3, w_sinv, x8, E4M3, x_sinv, x.dtype, bias=bias if bias is None or bias.dtype == torch.float32 else None,
                                      shard_is='b')
             if bias is not None and bias.dtype != torch.float32:
                 out.add_(bias)
         else:
+            fs.unfused_calls += 1
             out = _g.gemm_fp8(x8, E4M3, x_sinv, all_gather_rows(w8, fs.group), E4M3, w_sinv, x.dtype, bias=bias)
         ctx.module, ctx.x8t, ctx.x_sinv = module, x8t, x_sinv
         ctx.in_shape, ctx.out_dtype = x.shape, x.dtype
@@ -73,21 +75,23 @@ class _ShardedLinearFn(torch.autograd.Function):
         dy_sinv = og_meta.scale_inv
         w8t, w_sinv = module.weight_shard_t, module.weight_meta.scale_inv    # [K, N/W]
         K, n_local = w8t.shape
-        fused_ok = fs.ctx is not None and fs.ctx.native
+        fused_ok = fs.ctx is not None and fs.ctx.native and module.resident
         dx = None
         if ctx.input_requires_grad:
             if fused_ok and n_local % 128 == 0:
-                rows_pad = (K + 255) // 256 * 256
-                view = fs.ctx.shard_view(rows_pad * n_local)[:K * n_local].view(K, n_local)
-                view.copy_(w8t)
-                dx = fs.ctx.ag_k_gemm(dy8, E5M2, dy_sinv, view, E4M3, w_sinv, ctx.out_dtype)
+                fs.fused_calls += 1
+                dx = fs.ctx.ag_k_gemm(dy8, E5M2, dy_sinv, w8t, E4M3, w_sinv, ctx.out_dtype)    # the resident transposed shard, no copy
             else:
+                fs.unfused_calls += 1
                 dx = _g.gemm_fp8(dy8, E5M2, dy_sinv, all_gather_cols(w8t, fs.group), E4M3, w_sinv, ctx.out_dtype)
             dx = dx.view(ctx.in_shape)
-        # weight gradient of the local batch, reduced over ranks; this rank keeps the rows of its shard
+        # weight gradient of the local batch, reduced over ranks; this rank keeps the rows of its shard.  The partial
+        # products cross NVLink as bf16 (half the bytes of fp32; every rank's partial is rounded once before the fp32 sum).
         if fused_ok and n_local % 128 == 0:
-            part = fs.ctx.gemm_rs(dy8t, E5M2, dy_sinv, ctx.x8t, E4M3, ctx.x_sinv, torch.float32)
+            fs.fused_calls += 1
+            part = fs.ctx.gemm_rs(dy8t, E5M2, dy_sinv, ctx.x8t, E4M3, ctx.x_sinv, torch.bfloat16).float()
         else:
+            fs.unfused_calls += 1
             full = _g.gemm_fp8(dy8t, E5M2, dy_sinv, ctx.x8t, E4M3, ctx.x_sinv, torch.float32)
             part = reduce_scatter_rows(full, fs.group)
         part.div_(fs.world)
@@ -129,6 +133,7 @@ class ShardedFP8Linear(ScalingModule):
         self.weight_meta = _meta_from_amax(E4M3, amax, dev)
         self.weight_shard = _k.cast_to_fp8(shard, E4M3, self.weight_meta.scale)
         self.weight_shard_t = _k.transpose_fp8(self.weight_shard)
+        self.resident = False    # True once both copies live in the fused context's symmetric buffer
         self.bias = linear.bias
         self.scaling_metas = linear.scaling_metas if isinstance(linear, FP8Linear) else dict(
             input=ScalingMeta(E4M3, window_size=FP8Linear.DEFAULT_WINDOW_SIZE, device=dev),
@@ -137,6 +142,24 @@ class ShardedFP8Linear(ScalingModule):
         )
         self.master._scaling_metas = self.scaling_metas
         self._holder = torch.nn.Parameter(torch.empty(0, device=dev))
+
+    def resident_bytes(self):
+        """Symmetric memory both FP8 copies need: the shard, and its transpose with the row count rounded up to the
+        256-row tile of the K-gather kernel (whole tiles are copied between ranks)."""
+        rows, K = self.weight_shard.shape
+        pad_k = (K + 255) // 256 * 256
+        return ((rows * K + 1023) // 1024 + (pad_k * rows + 1023) // 1024 + 2) * 1024
+
+    def make_resident(self, ctx):
+        """Move the FP8 shard and its transpose into ``ctx``'s symmetric buffer (every rank in the same order)."""
+        rows, K = self.weight_shard.shape
+        pad_k = (K + 255) // 256 * 256
+        w = ctx.resident_view(rows * K).view(rows, K)
+        wt = ctx.resident_view(pad_k * rows)[:K * rows].view(K, rows)
+        w.copy_(self.weight_shard)
+        wt.copy_(self.weight_shard_t)
+        self.weight_shard, self.weight_shard_t = w, wt
+        self.resident = True
 
     def forward(self, x):
         model_state.ready_to_scale_tensor = True
@@ -153,7 +176,10 @@ class ShardedFP8Linear(ScalingModule):
         self.weight_meta.reset_scaling_factor()
         torch.reciprocal(self.weight_meta.scale, out=self.weight_meta.scale_inv)
         factor = self.weight_meta.scale * self.master.meta.scale_inv
-        self.weight_shard, self.weight_shard_t = _k.cast_transpose_fp8(self.master.value, E4M3, factor)
+        # in place: the shards keep their addresses (peers hold mappings of them).  No peer reads them between the last
+        # fused call of backward and the first of the next forward: every fused call ends with a cross-rank barrier.
+        _k.cast_to_fp8(self.master.value, E4M3, factor, out=self.weight_shard.view(-1))
+        _k.transpose_fp8(self.weight_shard, out=self.weight_shard_t)
 
     def extra_repr(self):
         return f'in_features={self.in_features}, out_features={self.out_features}, shards={self._fsdp.world}'
@@ -181,16 +207,21 @@ class FP8FullyShardedDataParallel(torch.nn.Module):
         self.rank = DistUtil.get_rank(process_group)
         self.ctx = None
         self.sharded = []
-        biggest_shard, biggest_out = 0, 0
+        self.fused_calls = self.unfused_calls = 0    # GEMMs of sharded linears that took / did not take the fused kernels
+        biggest_shard, biggest_out, resident = 0, 0, 0
         module = self._convert(module, min_shard_numel)
         for m in self.sharded:
             rows, K = m.weight_shard.shape
             pad_k = (K + 255) // 256 * 256
             biggest_shard = max(biggest_shard, rows * K, pad_k * rows)
-            biggest_out = max(biggest_out, m.out_features * K * 4)
+            biggest_out = max(biggest_out, m.out_features * K * 2)    # bf16 partial products
+            resident += m.resident_bytes()
         first = self.sharded[0].weight_shard if self.sharded else None
         if first is not None and first.is_cuda and self.world > 1:
-            self.ctx = FusedGemmContext(process_group, biggest_shard, biggest_out)
+            self.ctx = FusedGemmContext(process_group, biggest_shard, biggest_out, resident_bytes=resident)
+            if self.ctx.native:
+                for m in self.sharded:
+                    m.make_resident(self.ctx)
         self.module = module
         model_state.register_scaling_metas(module, None)
         self.hp_params = [p for p in module.parameters() if not isinstance(p, ScalingParameter) and p.numel() > 0]
@@ -198,6 +229,9 @@ class FP8FullyShardedDataParallel(torch.nn.Module):
             src = dist.get_global_rank(process_group, 0) if process_group is not None else 0
             for p in self.hp_params:
                 dist.broadcast(p.data, src=src, group=process_group)
+        from msamp.parallel.hp_shard import HighPrecisionShards
+        dev = first.device if first is not None else (self.hp_params[0].device if self.hp_params else torch.device('cpu'))
+        self.hp = HighPrecisionShards(self.hp_params, process_group, shard=True, device=dev)
 
     def _convert(self, module, min_numel):
         if isinstance(module, (torch.nn.Linear, FP8Linear)) and not getattr(module, 'use_fp32_linear', False):
@@ -214,8 +248,8 @@ class FP8FullyShardedDataParallel(torch.nn.Module):
         return self.module(*args, **kwargs)
 
     def master_parameters(self):
-        """Parameters an optimizer should update: master shards of the sharded linears + replicated parameters."""
-        return [m.master for m in self.sharded] + self.hp_params
+        """Parameters an optimizer should update: master shards of the sharded linears + the high-precision parameters this rank owns."""
+        return [m.master for m in self.sharded] + self.hp.owned()
 
     def build_optimizer(self, torch_cls=torch.optim.AdamW, **kwargs):
         from msamp.optim import LBAdam, LBAdamW
@@ -224,53 +258,38 @@ class FP8FullyShardedDataParallel(torch.nn.Module):
 
     @torch.no_grad()
     def clip_grad_norm_(self, max_norm):
-        """Global-norm clipping: shard gradients count once over the group, replicated ones once per rank. Call after the
-        replicated gradients were averaged (``step`` does both in the right order when given ``clip_grad``)."""
-        from msamp.nn.clip_grad import _grad_norm
+        """Global-norm clipping.  Every gradient is held by exactly one rank here (shards of the linears, owners of the
+        other parameters), so the squared norms are summed over the group.  Call after ``hp.reduce_grads()`` (``step``
+        does both in the right order when given ``clip_grad``)."""
+        from msamp.ops import multi_tensor as _mt
+        grads = [m.master.grad for m in self.sharded if m.master.grad is not None]
+        grads += [p.grad for p in self.hp.owned() if p.grad is not None]
         dev = self.sharded[0].master.device if self.sharded else self.hp_params[0].device
-        sq = torch.zeros(1, dtype=torch.float32, device=dev)
-        for m in self.sharded:
-            if m.master.grad is not None:
-                sq += _grad_norm(m.master.grad, 2.0)**2
+        stats = _mt.grad_sumsq(grads, out=torch.zeros(2, dtype=torch.float32, device=dev), tag='fsdp_norm')
         if self.world > 1:
-            dist.all_reduce(sq, group=self.group)
-        for p in self.hp_params:
-            if p.grad is not None:
-                sq += _grad_norm(p.grad, 2.0)**2
-        total = sq.sqrt()[0]
-        coef = torch.clamp(max_norm / (total + 1e-6), max=1.0)
-        for m in self.sharded:
-            if m.master.grad is not None:
-                m.master.grad.mul_(coef)
-        for p in self.hp_params:
-            if p.grad is not None:
-                p.grad.mul_(coef.to(p.grad.dtype))
-        return total
+            dist.all_reduce(stats, group=self.group)
+        _mt.clip_by_sumsq(grads, stats[0:1], max_norm, tag='fsdp_clip')
+        return stats[0].sqrt()
 
     @torch.no_grad()
     def step(self, optimizer, clip_grad=0.0):
-        """Average the replicated gradients, (clip,) update, re-quantise the shards, clear gradients."""
-        if self.world > 1:
-            grads = [p.grad for p in self.hp_params if p.grad is not None]
-            by_dtype = {}
-            for g in grads:
-                by_dtype.setdefault(g.dtype, []).append(g)
-            for gs in by_dtype.values():
-                flat = torch.cat([g.reshape(-1) for g in gs])
-                dist.all_reduce(flat, group=self.group)
-                flat.div_(self.world)
-                off = 0
-                for g in gs:
-                    g.copy_(flat[off:off + g.numel()].view_as(g))
-                    off += g.numel()
+        """Reduce the high-precision gradients to their owners, (clip,) update, publish the owners' parameters,
+        re-quantise the weight shards, clear gradients."""
+        self.hp.reduce_grads()
         if clip_grad > 0:
             self.clip_grad_norm_(clip_grad)
         optimizer.step()
+        self.hp.gather_params()
         for m in self.sharded:
             m.requantize()
             m.master.grad = None
-        for p in self.hp_params:
-            p.grad = None
+        self.hp.clear_grads()
+
+    def close(self):
+        """Release the symmetric buffers of the fused kernels (collective over the group, after the last step)."""
+        if self.ctx is not None:
+            self.ctx.close()
+            self.ctx = None
 
     def memory_per_rank(self):
         """Bytes of persistent parameter/optimizer storage on this rank for the sharded layers (fp8 W, W^T, fp16 master)."""

@@ -203,14 +203,20 @@ def cast_transpose_fp8(x, qtype, scale, amax_out=None, need_rowmajor=True, scale
     return (out if need_rowmajor else None), out.t().contiguous()
 
 
-def transpose_fp8(x):
-    """Byte transpose of a 2-D FP8 payload."""
+def transpose_fp8(x, out=None):
+    """Byte transpose of a 2-D FP8 payload (into ``out``, a contiguous ``[cols, rows]`` tensor, when given)."""
     assert x.dim() == 2
+    rows, cols = x.shape
+    if out is not None:
+        assert out.shape == (cols, rows) and out.is_contiguous() and out.dtype == x.dtype
     if x.is_cuda:
         x = x.contiguous()
-        rows, cols = x.shape
-        out = torch.empty((cols, rows), dtype=x.dtype, device=x.device)
+        if out is None:
+            out = torch.empty((cols, rows), dtype=x.dtype, device=x.device)
         native.check(native.lib().msamp_transpose_fp8(native.ptr(x), rows, cols, native.ptr(out), native.stream()), 'transpose_fp8')
+        return out
+    if out is not None:
+        out.copy_(x.t())
         return out
     return x.t().contiguous()
 

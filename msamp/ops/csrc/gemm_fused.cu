@@ -564,8 +564,10 @@ MSAMP_API int msamp_gemm_fused(const MsampFusedDesc* d, void* stream_) {
   cudaStream_t stream = (cudaStream_t)stream_;
   MSAMP_REQUIRE(d->M > 0 && d->N > 0 && d->K > 0 && d->K % 16 == 0, "gemm_fused: bad problem M=%d N=%d K=%d", d->M, d->N, d->K);
   MSAMP_REQUIRE(d->world >= 1 && d->world <= kMaxRanks, "gemm_fused: world=%d not supported", d->world);
-  // Only the 128 x 256 tile is used for row gathers (the shard size must be a multiple of the tile).
-  const int bn = (d->N >= 256) ? 256 : 128;
+  // 128 x 256 tiles, except that a row gather of B whose shards are a multiple of 128 but not of 256 rows (e.g. 7168 / 8
+  // = 896 or 21504 / 8 = 2688) uses 128 x 128 tiles: a tile must not straddle two ranks' shards.
+  int bn = (d->N >= 256) ? 256 : 128;
+  if (d->gather == G_B_ROWS && d->shard_rows % 256 != 0) bn = 128;
   FusedMaps maps;
   FusedArgs f = {};
   GemmParams p;

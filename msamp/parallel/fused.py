@@ -57,11 +57,14 @@ class FusedGemmContext:
 
     Args:
         group: process group (all ranks on one NVLink domain).
-        max_shard_bytes: largest operand shard that will be exposed to peers (bytes).
+        max_shard_bytes: largest operand shard that will be exposed to peers in one call (bytes).
+        resident_bytes: size of the symmetric buffer that holds exposed shards (default: one shard of ``max_shard_bytes``).
+            A larger buffer lets shards stay resident (e.g. the FP8 weight shards of a fully sharded model live there
+            permanently, see ``resident_view``), so that no call has to copy its shard in first.
         max_out_bytes: largest full (pre-reduction) output ``M * N * itemsize`` of a ``gemm_rs`` call.
         n_comm: CTAs of the persistent grid used as copy engines in gather modes.
     """
-    def __init__(self, group=None, max_shard_bytes=0, max_out_bytes=0, n_comm=12, wait_seconds=5.0):
+    def __init__(self, group=None, max_shard_bytes=0, max_out_bytes=0, n_comm=12, wait_seconds=5.0, resident_bytes=0):
         self.group = group
         self.world = DistUtil.get_world_size(group)
         self.rank = DistUtil.get_rank(group)
@@ -81,7 +84,9 @@ class FusedGemmContext:
         dev = torch.device('cuda', torch.cuda.current_device())
         self.device = dev
         self.flags = FlagPad(group)
-        self.shard = SymmetricBuffer(max(self.max_shard_bytes, 16), group) if max_shard_bytes else None
+        self.resident_bytes = max(self.max_shard_bytes, (int(resident_bytes) + 1023) // 1024 * 1024)
+        self.resident_used = 0
+        self.shard = SymmetricBuffer(max(self.resident_bytes, 16), group) if max_shard_bytes else None
         self.local = torch.empty((self.world, max(self.max_shard_bytes, 16)), dtype=torch.uint8, device=dev) if max_shard_bytes else None
         self.stage = [SymmetricBuffer(max(self.max_out_bytes, 16), group) for _ in range(2)] if max_out_bytes else None
         self.stage_turn = 0
@@ -111,6 +116,21 @@ class FusedGemmContext:
         """uint8 view of this rank's exposed shard buffer (write the shard here before a gather operator)."""
         assert nbytes <= self.max_shard_bytes, (nbytes, self.max_shard_bytes)
         return self.shard.view(torch.uint8, 0, nbytes)
+
+    def resident_view(self, nbytes):
+        """Reserve ``nbytes`` of the symmetric shard buffer for good and return the uint8 view: a shard written there
+        can be handed to the gather operators in every step without a copy.  Every rank must reserve in the same order."""
+        off = (self.resident_used + 1023) // 1024 * 1024
+        if off + nbytes > self.shard.nbytes:
+            raise RuntimeError(f'resident shard buffer exhausted ({off + nbytes} > {self.shard.nbytes} bytes)')
+        self.resident_used = off + nbytes
+        return self.shard.view(torch.uint8, off, nbytes)
+
+    def _shard_offset(self, t, nbytes):
+        off = t.data_ptr() - self.shard.local_ptr
+        assert 0 <= off and off + nbytes <= self.shard.nbytes and off % 16 == 0, \
+            'the shard must live in FusedGemmContext.shard_view() / resident_view() memory'
+        return off
 
     def _base_desc(self, M, N, K, a_q, b_q, a_sinv, b_sinv, out, bias, amax_out, accumulate):
         d = _Desc()
@@ -158,13 +178,13 @@ class FusedGemmContext:
             M, N = other.shape[0], rows * W
         if out is None:
             out = torch.empty((M, N), dtype=out_dtype, device=shard.device)
-        tile = 128 if shard_is == 'a' else (256 if N >= 256 else 128)
-        if not self.native or rows % tile or K % 16:
+        tile = 128    # B row shards that are not a multiple of 256 rows make the kernel use 128 x 128 tiles
+        if not self.native or rows % tile or K % 16 or rows * K > self.max_shard_bytes:
             full = all_gather_rows(shard, self.group)
             if shard_is == 'a':
                 return _g.gemm_fp8(full, shard_q, shard_sinv, other, other_q, other_sinv, out_dtype, bias=bias, out=out, amax_out=amax_out)
             return _g.gemm_fp8(other, other_q, other_sinv, full, shard_q, shard_sinv, out_dtype, bias=bias, out=out, amax_out=amax_out)
-        assert shard.data_ptr() == self.shard.local_ptr, 'the shard must be written into FusedGemmContext.shard_view()'
+        off = self._shard_offset(shard, rows * K)
         if amax_out is not None:
             amax_out.zero_()
         a_q, b_q = (shard_q, other_q) if shard_is == 'a' else (other_q, shard_q)
@@ -173,8 +193,8 @@ class FusedGemmContext:
         d.gather = G_A_ROWS if shard_is == 'a' else G_B_ROWS
         nbytes = rows * K
         for r in range(W):
-            ptr = self.shard.local_ptr if r == self.rank else self.local[r].data_ptr()
-            d.peer[r] = self.shard.ptrs[r]
+            ptr = self.shard.local_ptr + off if r == self.rank else self.local[r].data_ptr()
+            d.peer[r] = self.shard.ptrs[r] + off
             if shard_is == 'a':
                 d.a[r] = ptr
             else:
@@ -215,15 +235,15 @@ class FusedGemmContext:
         if not self.native or k % 128 or n_pad * k > self.max_shard_bytes:
             full = all_gather_cols(shard_t, self.group)
             return _g.gemm_fp8(a, a_q, a_sinv, full, shard_q, shard_sinv, out_dtype, out=out, accumulate=accumulate, amax_out=amax_out)
-        assert shard_t.data_ptr() == self.shard.local_ptr, 'the shard must be written into FusedGemmContext.shard_view()'
+        off = self._shard_offset(shard_t, n_pad * k)
         if amax_out is not None:
             amax_out.zero_()
         a = a.contiguous()
         d = self._base_desc(M, N, K, a_q, shard_q, a_sinv, shard_sinv, out, None, amax_out, accumulate)
         d.gather = G_B_K
         for r in range(W):
-            d.peer[r] = self.shard.ptrs[r]
-            d.b[r] = self.shard.local_ptr if r == self.rank else self.local[r].data_ptr()
+            d.peer[r] = self.shard.ptrs[r] + off
+            d.b[r] = self.shard.local_ptr + off if r == self.rank else self.local[r].data_ptr()
         d.a[0], d.lda, d.ldb = a.data_ptr(), a.stride(0), k
         d.shard_rows, d.shard_pitch, d.shard_nrows = k, k, N
         self._launch(d, 'ag_k_gemm')

@@ -247,104 +247,25 @@ class ZeroShardedOptimizer:
 
     # ------------------------------------------------------------------ high-precision parameters
     def _build_hp_buffers(self):
-        """Flat, persistent buffers for everything that is not an FP8 weight (embeddings, LayerNorms, biases).
-
-        Stage 0 keeps these parameters and their Adam states replicated and all-reduces their gradients in one flat
-        buffer per dtype.  Stages 1 / 2 shard them like stock ZeRO (the reference hands them to DeepSpeed's own
-        partitioning, msamp/deepspeed/runtime/zero/fp8_stage_1_and_2.py:36-68): every tensor gets an owner rank, the
-        flat buffers are laid out as ``world`` equal regions (region r = the tensors owned by rank r), gradients are
-        reduce-scattered so that each region's sum lands on its owner, only the owner keeps optimizer states and
-        updates, and the updated parameters are all-gathered region by region.
-        """
-        self.hp_owner = [self.rank] * len(self.hp_params)
-        self.hp_layout = {}    # dtype -> dict(region=int, params=[(index, offset)], flat_grad, flat_param or None)
-        if self.world == 1 or not self.hp_params:
-            return
-        shard = self.sharded
-        if shard:
-            self.hp_owner = partition_tensors([p.numel() for p in self.hp_params], self.world)
-        by_dtype = {}
-        for k, p in enumerate(self.hp_params):
-            by_dtype.setdefault(p.dtype, []).append(k)
-        for dtype, idxs in by_dtype.items():
-            fill = [0] * self.world
-            place = []
-            for k in idxs:
-                r = self.hp_owner[k] if shard else 0
-                place.append((k, r, fill[r]))
-                fill[r] += _pad16(self.hp_params[k].numel())
-            region = max(max(fill), 16) if shard else max(fill[0], 16)
-            total = region * (self.world if shard else 1)
-            flat_grad = torch.zeros(total, dtype=dtype, device=self.device)
-            flat_param = None
-            params = [(k, r * region + off) for k, r, off in place]
-            if shard:
-                flat_param = torch.zeros(total, dtype=dtype, device=self.device)
-                for k, off in params:
-                    p = self.hp_params[k]
-                    view = flat_param[off:off + p.numel()].view(p.shape)
-                    view.copy_(p.data)
-                    p.data = view
-            self.hp_layout[dtype] = dict(region=region, params=params, flat_grad=flat_grad, flat_param=flat_param)
-        if shard:
-            # the inner optimizer keeps only what this rank owns
-            owned = {id(self.hp_params[k]) for k in range(len(self.hp_params)) if self.hp_owner[k] == self.rank}
-            hp_ids = {id(p) for p in self.hp_params}
-            for group in self.optimizer.param_groups:
-                group['params'] = [p for p in group['params'] if id(p) not in hp_ids or id(p) in owned]
-            for p in list(self.optimizer.state.keys()):
-                if id(p) in hp_ids and id(p) not in owned:
-                    del self.optimizer.state[p]
+        """Everything that is not an FP8 weight goes through ``HighPrecisionShards``: replicated with one flat gradient
+        all-reduce per dtype at stage 0, sharded like stock ZeRO (owner per tensor, reduce-scatter, all-gather) at stages 1 / 2."""
+        from msamp.parallel.hp_shard import HighPrecisionShards
+        self.hp = HighPrecisionShards(self.hp_params, self.group, shard=self.sharded, device=self.device)
+        self.hp.bind_optimizer(self.optimizer)
+        self.hp_owner, self.hp_layout = self.hp.owner, self.hp.layout
 
     def _owned_hp(self):
-        return [self.hp_params[k] for k in range(len(self.hp_params)) if self.hp_owner[k] == self.rank]
+        return self.hp.owned()
 
     def _reduce_hp_grads(self):
-        if self.world == 1:
-            return
-        backend = dist.get_backend(self.group)
-        for dtype, lay in self.hp_layout.items():
-            flat = lay['flat_grad']
-            for k, off in lay['params']:
-                p = self.hp_params[k]
-                view = flat[off:off + p.numel()].view(p.shape)
-                if p.grad is not None and p.grad.data_ptr() != view.data_ptr():
-                    view.copy_(p.grad)
-                p.grad = view
-            region = lay['region']
-            if self.sharded:
-                mine = flat[self.rank * region:(self.rank + 1) * region]
-                if backend == 'nccl':
-                    dist.reduce_scatter_tensor(mine, flat, group=self.group)
-                else:
-                    dist.all_reduce(flat, group=self.group)
-                mine.div_(self.world)
-            else:
-                dist.all_reduce(flat, group=self.group)
-                flat.div_(self.world)
+        self.hp.reduce_grads()
 
     def _gather_hp_params(self):
         """Publish the owners' updated high-precision parameters to every rank (stages 1 / 2)."""
-        if self.world == 1 or not self.sharded:
-            return
-        backend = dist.get_backend(self.group)
-        for dtype, lay in self.hp_layout.items():
-            flat, region = lay['flat_param'], lay['region']
-            mine = flat[self.rank * region:(self.rank + 1) * region]
-            if backend == 'nccl':
-                dist.all_gather_into_tensor(flat, mine, group=self.group)
-            else:
-                parts = [torch.empty_like(mine) for _ in range(self.world)]
-                dist.all_gather(parts, mine.clone(), group=self.group)
-                for r, part in enumerate(parts):
-                    if r != self.rank:
-                        flat[r * region:(r + 1) * region].copy_(part)
+        self.hp.gather_params()
 
     def _clear_hp_grads(self):
-        for lay in self.hp_layout.values():
-            lay['flat_grad'].zero_()
-        for p in self.hp_params:
-            p.grad = None
+        self.hp.clear_grads()
 
     def _publish_weights(self):
         if self.native:

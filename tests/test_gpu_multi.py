@@ -265,19 +265,18 @@ def _fused_gemms(rank, world, n_comm=4, shapes=((128, 256, 128), (256, 512, 384)
         assert native.device_status() == 0
         assert torch.equal(out, ref), ('ag_rows a', rows, K, N, (out.float() - ref.float()).abs().max().item())
         assert torch.equal(ctx.gathered_rows(rows, K), full)
-        # --- all-gather(rows of B) + GEMM (parameter gather)
-        if N % 256 == 0 or N == 128:
-            pass
-        w_rows = 256
-        w_shard = q((w_rows, K), 200 + rank)
-        x = q((rows, K), 9)
-        view = ctx.shard_view(w_rows * K).view(w_rows, K)
-        view.copy_(w_shard)
-        out = ctx.ag_rows_gemm(view, E4M3, sinv, x, E4M3, sinv, torch.bfloat16, shard_is='b')
-        ref = gemm.gemm_fp8(x, E4M3, sinv, all_gather_rows(w_shard), E4M3, sinv, torch.bfloat16)
-        torch.cuda.synchronize()
-        assert native.device_status() == 0
-        assert torch.equal(out, ref), ('ag_rows b', rows, K)
+        # --- all-gather(rows of B) + GEMM (parameter gather); 384 = 3 x 128 rows per shard forces the 128 x 128 tiles
+        # (a 256-row tile would straddle two ranks' shards), as the 896- and 2688-row shards of a 7168-wide model do
+        for w_rows in (256, 384):
+            w_shard = q((w_rows, K), 200 + rank)
+            x = q((rows, K), 9)
+            view = ctx.shard_view(w_rows * K).view(w_rows, K)
+            view.copy_(w_shard)
+            out = ctx.ag_rows_gemm(view, E4M3, sinv, x, E4M3, sinv, torch.bfloat16, shard_is='b')
+            ref = gemm.gemm_fp8(x, E4M3, sinv, all_gather_rows(w_shard), E4M3, sinv, torch.bfloat16)
+            torch.cuda.synchronize()
+            assert native.device_status() == 0
+            assert torch.equal(out, ref), ('ag_rows b', rows, K, w_rows)
         # --- GEMM with K-gathered B (wgrad shape): D[N, K] = A[N, W*rows] . concat_K(B_r[K, rows])^T
         a_full = q((N, rows * world), 11)
         bt_shard = q((K, rows), 300 + rank)
@@ -369,26 +368,40 @@ def _full_shard_fused(rank, world):
     from msamp.ops import native
     dev = torch.device('cuda', rank)
     torch.manual_seed(0)
-    model = torch.nn.Sequential(torch.nn.Linear(512, 1024), torch.nn.GELU(), torch.nn.Linear(1024, 512)).to(dev)
+    # shards of 384 = 3 x 128 rows (not a multiple of the 256-row tile) and of 128 rows; an embedding-like parameter
+    # that is not a linear gets an owner rank instead of being replicated
+    hidden = 384 * world
+    model = torch.nn.Sequential(torch.nn.Linear(512, hidden), torch.nn.GELU(), torch.nn.Linear(hidden, 128 * world)).to(dev)
+    extra = torch.nn.Parameter(torch.zeros(128 * world, device=dev))
+    model.register_parameter('out_shift', extra)
     fsdp = FP8FullyShardedDataParallel(model)
-    assert fsdp.ctx is not None and fsdp.ctx.native and len(fsdp.sharded) == 2
+    assert fsdp.ctx is not None and fsdp.ctx.native and len(fsdp.sharded) == 2 and all(m.resident for m in fsdp.sharded)
     opt = fsdp.build_optimizer(torch.optim.AdamW, lr=2e-3)
+    n_opt = sum(len(g['params']) for g in opt.param_groups)
+    assert n_opt == 2 + len(fsdp.hp.owned()) < 2 + len(fsdp.hp_params)    # high-precision parameters are sharded too
     torch.manual_seed(5)
     xs = torch.randn(world * 256, 512, device=dev).bfloat16()
-    ys = torch.randn(world * 256, 512, device=dev).bfloat16()
+    ys = torch.randn(world * 256, 128 * world, device=dev).bfloat16()
     losses = []
     for _ in range(15):
-        loss = (fsdp(xs[rank * 256:(rank + 1) * 256]) - ys[rank * 256:(rank + 1) * 256]).float().square().mean()
+        out = fsdp(xs[rank * 256:(rank + 1) * 256]) + extra.to(torch.bfloat16)
+        loss = (out - ys[rank * 256:(rank + 1) * 256]).float().square().mean()
         loss.backward()
-        fsdp.step(opt)
+        fsdp.step(opt, clip_grad=1.0)
         losses.append(loss.item())
     torch.cuda.synchronize()
     assert native.device_status() == 0
+    assert fsdp.unfused_calls == 0 and fsdp.fused_calls == 15 * 2 * 3 - 15    # every GEMM of every sharded linear (no dx for the first)
     assert losses[-1] < 0.9 * losses[0], losses
     s = fsdp.sharded[0].weight_meta.scale.clone()
     ref = s.clone()
     dist.broadcast(ref, src=0)
     assert torch.equal(s, ref)
+    flat = torch.cat([p.detach().float().reshape(-1) for p in fsdp.hp_params])
+    ref = flat.clone()
+    dist.broadcast(ref, src=0)
+    assert torch.equal(flat, ref)    # the owners' updates reached every rank
+    fsdp.close()
 
 
 @WORLDS
