@@ -133,7 +133,8 @@ class _ScalingTensorReducer:
             meta.locked = was_locked
         flat = model_state.flattened_scaling_metas
         if flat is not None and 'wgrad' in flat:
-            flat['wgrad'] = dict(flat['wgrad'], _external=True)
+            # the metas no longer alias model_state's flat wgrad buffers; point its aliasing check at their new home
+            flat['wgrad'] = dict(flat['wgrad'], scales_inv=self.g_meta_t[0], amaxs=self.g_meta_t[1].view(-1, 1), _external=True)
         self.fused = True
 
     def _reduce_bucket_fused(self, bucket):

@@ -39,8 +39,19 @@ struct AdamTensor {
   float l2;              // wd for L2 mode, else 0
   float beta1, beta2, eps, step_size, inv_sqrt_bc2, gsign;
   int tensor_scale;
-  int pad;
+  int g_index;           // fused reduce-scatter: index of this tensor in the ranks' symmetric gradient buffers, else -1
   float red[4];          // stage-1 results: max|p|, max|m|, max|v|
+};
+
+// Symmetric FP8 gradient buffers of the data-parallel group (see symm.cu): with them stage 1 pulls every rank's
+// e4m3 bytes of a tensor this rank owns, dequantises each with that rank's scale, averages in fp32, rounds the
+// mean to e4m3 once (stored locally for stage 2) and feeds the rounded value straight into the Adam arithmetic -
+// the reduce-scatter and the first optimizer pass are one kernel, and the averaged gradient is never read back.
+constexpr int kMaxPeers = 8;
+struct PeerGrads {
+  const uint8_t* data[kMaxPeers];    // flat e4m3 gradient buffer of every rank (same layout everywhere)
+  float* meta[kMaxPeers];            // [3][n_tensors] per rank: scale_inv | amax | result scale_inv
+  int world, rank, n_tensors;
 };
 
 constexpr int kChunk = 32768;    // elements per block
@@ -269,6 +280,103 @@ __device__ __forceinline__ void adam_block(AdamTensor& t, int64_t begin, int64_t
   }
 }
 
+// Stage 1 of a tensor whose gradient still lies, unreduced, in the ranks' symmetric buffers.
+__device__ __forceinline__ void adam_block_reduce(AdamTensor& t, const PeerGrads& pg, int64_t begin, int64_t end, bool first_chunk, float* red) {
+  const float psi = t.p_scale_inv ? *t.p_scale_inv : 1.0f;
+  const float msi = t.m_scale_inv ? *t.m_scale_inv : 1.0f;
+  const float vsi = t.v_scale_inv ? *t.v_scale_inv : 1.0f;
+  const int64_t goff = reinterpret_cast<const uint8_t*>(t.g) - pg.data[pg.rank];    // same offset in every rank's buffer
+  float sinv[kMaxPeers];
+  float amax = 0.0f;
+  const float inv_world = 1.0f / (float)pg.world;
+#pragma unroll
+  for (int r = 0; r < kMaxPeers; ++r) {
+    if (r < pg.world) {
+      sinv[r] = pg.meta[r][t.g_index] * inv_world;
+      amax = fmaxf(amax, abs_nan_to_inf(pg.meta[r][pg.n_tensors + t.g_index]));
+    }
+  }
+  // same rule and the same summation order as the stand-alone reduce kernel, so both paths produce the same bytes
+  const float new_scale = msamp_compute_scale(amax, 1.0f, 448.0f, 0);
+  const float gsi = __frcp_rn(new_scale);
+  if (first_chunk && threadIdx.x == 0) pg.meta[pg.rank][2 * pg.n_tensors + t.g_index] = gsi;
+  uint8_t* gq = reinterpret_cast<uint8_t*>(const_cast<void*>(t.g));
+  float ap = 0.0f, am = 0.0f, av = 0.0f;
+  const bool vec = ((reinterpret_cast<uintptr_t>(t.p) | reinterpret_cast<uintptr_t>(t.g) | reinterpret_cast<uintptr_t>(t.m) |
+                     reinterpret_cast<uintptr_t>(t.v)) & 15) == 0;
+  int64_t done = begin;
+  if (vec) {
+#pragma unroll 2
+    for (int64_t i = begin + (int64_t)threadIdx.x * 8; i + 8 <= end; i += (int64_t)kAdamThreads * 8) {
+      float acc[8], p[8], m[8], v[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] = 0.0f;
+#pragma unroll
+      for (int r = 0; r < kMaxPeers; ++r) {
+        if (r < pg.world) {
+          const int src = (pg.rank + r) % pg.world;    // stagger peers so that the ranks do not all hit one GPU at once
+          const Bytes8 b = *reinterpret_cast<const Bytes8*>(pg.data[src] + goff + i);
+          const uint8_t* e = reinterpret_cast<const uint8_t*>(&b);
+          const float sc = sinv[src];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) acc[j] += fp8_to_f32<FMT_E4M3>(e[j]) * sc;
+        }
+      }
+      load8(t.p, t.p_st, i, p);
+      load8(t.m, t.m_st, i, m);
+      load8(t.v, t.v_st, i, v);
+      Bytes8 q;
+      uint16_t* qe = reinterpret_cast<uint16_t*>(&q);
+#pragma unroll
+      for (int j = 0; j < 8; j += 2) qe[j / 2] = f32x2_to_fp8x2<FMT_E4M3>(acc[j] * new_scale, acc[j + 1] * new_scale);
+      *reinterpret_cast<Bytes8*>(gq + i) = q;    // the reduced gradient, for stage 2
+      const uint8_t* qb = reinterpret_cast<const uint8_t*>(&q);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        Elem e = adam_elem(t, p[j], fp8_to_f32<FMT_E4M3>(qb[j]), m[j], v[j], psi, gsi, msi, vsi);
+        ap = fmaxf(ap, abs_nan_to_inf(e.p));
+        am = fmaxf(am, abs_nan_to_inf(e.m));
+        av = fmaxf(av, abs_nan_to_inf(e.v));
+      }
+    }
+    done = begin + ((end - begin) / 8) * 8;
+  }
+  for (int64_t i = done + threadIdx.x; i < end; i += kAdamThreads) {
+    float acc = 0.0f;
+    for (int r = 0; r < pg.world; ++r) {
+      const int src = (pg.rank + r) % pg.world;
+      acc += fp8_to_f32<FMT_E4M3>(pg.data[src][goff + i]) * sinv[src];
+    }
+    const uint8_t q = f32_to_fp8<FMT_E4M3>(acc * new_scale);
+    gq[i] = q;
+    Elem e = adam_elem(t, load1(t.p, t.p_st, i), fp8_to_f32<FMT_E4M3>(q), load1(t.m, t.m_st, i), load1(t.v, t.v_st, i), psi, gsi, msi, vsi);
+    ap = fmaxf(ap, abs_nan_to_inf(e.p));
+    am = fmaxf(am, abs_nan_to_inf(e.m));
+    av = fmaxf(av, abs_nan_to_inf(e.v));
+  }
+  ap = block_max(ap, red);
+  am = block_max(am, red);
+  av = block_max(av, red);
+  if (threadIdx.x == 0) {
+    atomic_max_nonneg(&t.red[0], ap);
+    atomic_max_nonneg(&t.red[1], am);
+    atomic_max_nonneg(&t.red[2], av);
+  }
+}
+
+__global__ void __launch_bounds__(kAdamThreads) lbadam_reduce_stage1_kernel(AdamTensor* tensors, const int* __restrict__ work, const PeerGrads pg) {
+  __shared__ float red[32];
+  AdamTensor& t = tensors[work[2 * blockIdx.x]];
+  const int chunk = work[2 * blockIdx.x + 1];
+  const int64_t begin = (int64_t)chunk * kChunk;
+  const int64_t end = (begin + kChunk < t.n) ? begin + kChunk : t.n;
+  if (t.g_index >= 0 && t.g_st == ST_E4M3) {
+    adam_block_reduce(t, pg, begin, end, chunk == 0, red);
+  } else {
+    adam_block<1, -1, -1, -1, -1>(t, begin, end, red);    // gradients that were reduced elsewhere (high-precision parameters)
+  }
+}
+
 // block -> (tensor, chunk) map: work[2*b] = tensor index, work[2*b+1] = chunk index
 template <int STAGE>
 __global__ void __launch_bounds__(kAdamThreads) lbadam_kernel(AdamTensor* tensors, const int* __restrict__ work) {
@@ -331,4 +439,25 @@ MSAMP_API int msamp_lbadam_step(void* tensors, int n_tensors, const int* work, i
   lbadam_kernel<2><<<n_blocks, kAdamThreads, 0, stream>>>((AdamTensor*)tensors, work);
   lbadam_finalize_kernel<<<(n_tensors + 127) / 128, 128, 0, stream>>>((AdamTensor*)tensors, n_tensors);
   return msamp_check_launch("msamp_lbadam_step");
+}
+
+// Same step with the FP8 gradient reduce-scatter folded into stage 1.  data / meta: `world` device pointers to the
+// ranks' symmetric gradient and meta buffers (this rank's own at index `rank`); descriptors with g_index >= 0 must
+// have `g` pointing into this rank's buffer and `g_scale_inv` at meta row 2 of that tensor.  The caller has made sure
+// (cross-rank barrier on the stream) that every rank finished writing its gradients and metas.
+MSAMP_API int msamp_lbadam_step_reduce(void* tensors, int n_tensors, const int* work, int n_blocks, void* const* data, void* const* meta,
+                                       int world, int rank, int n_sym_tensors, void* stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  if (n_tensors <= 0 || n_blocks <= 0) return MSAMP_OK;
+  MSAMP_REQUIRE(world >= 1 && world <= kMaxPeers && rank >= 0 && rank < world, "lbadam_step_reduce: bad world=%d rank=%d", world, rank);
+  PeerGrads pg;
+  for (int r = 0; r < kMaxPeers; ++r) {
+    pg.data[r] = r < world ? (const uint8_t*)data[r] : nullptr;
+    pg.meta[r] = r < world ? (float*)meta[r] : nullptr;
+  }
+  pg.world = world; pg.rank = rank; pg.n_tensors = n_sym_tensors;
+  lbadam_reduce_stage1_kernel<<<n_blocks, kAdamThreads, 0, stream>>>((AdamTensor*)tensors, work, pg);
+  lbadam_kernel<2><<<n_blocks, kAdamThreads, 0, stream>>>((AdamTensor*)tensors, work);
+  lbadam_finalize_kernel<<<(n_tensors + 127) / 128, 128, 0, stream>>>((AdamTensor*)tensors, n_tensors);
+  return msamp_check_launch("msamp_lbadam_step_reduce");
 }

@@ -21,7 +21,7 @@ DESC = np.dtype(
         ('p_st', 'i4'), ('g_st', 'i4'), ('m_st', 'i4'), ('v_st', 'i4'),
         ('lr_wd_factor', 'f4'), ('l2', 'f4'), ('beta1', 'f4'), ('beta2', 'f4'), ('eps', 'f4'), ('step_size', 'f4'),
         ('inv_sqrt_bc2', 'f4'), ('gsign', 'f4'),
-        ('tensor_scale', 'i4'), ('pad', 'i4'),
+        ('tensor_scale', 'i4'), ('g_index', 'i4'),
         ('red', 'f4', (4, )),
     ],
     align=False
@@ -74,8 +74,11 @@ class FusedPlan:
         self.work = torch.from_numpy(work).to(self.device)
         self.key = key
 
-    def run(self, entries):
-        """``entries``: list of dicts with p, g, m, v (Tensor/ScalingTensor) and the scalar hyper-parameters."""
+    def run(self, entries, reduce=None):
+        """``entries``: list of dicts with p, g, m, v (Tensor/ScalingTensor) and the scalar hyper-parameters.
+
+        ``reduce`` (optional): ``dict(data_table, meta_table, world, rank, n_tensors)`` of the data-parallel group's symmetric
+        FP8 gradient buffers; entries with ``g_index >= 0`` then have their gradient reduce-scattered inside stage 1."""
         if not entries:
             return
         sizes = [e['p'].numel() for e in entries]
@@ -112,17 +115,25 @@ class FusedPlan:
             r['lr_wd_factor'], r['l2'] = e['lr_wd_factor'], e['l2']
             r['beta1'], r['beta2'], r['eps'] = e['beta1'], e['beta2'], e['eps']
             r['step_size'], r['inv_sqrt_bc2'], r['gsign'] = e['step_size'], 1.0 / e['sqrt_bc2'], e['gsign']
-            r['tensor_scale'], r['pad'] = int(e['tensor_scale']), 0
+            r['tensor_scale'], r['g_index'] = int(e['tensor_scale']), int(e.get('g_index', -1)) if reduce is not None else -1
             r['red'] = 0.0
         self.dev.copy_(host, non_blocking=True)
         event = torch.cuda.Event()
         event.record()
         self.ring[self.slot][2] = event
         self.slot = (self.slot + 1) % len(self.ring)
-        native.check(
-            native.lib().msamp_lbadam_step(native.ptr(self.dev), len(entries), native.ptr(self.work), self.n_blocks, native.stream()),
-            'lbadam_step'
-        )
+        if reduce is not None:
+            native.check(
+                native.lib().msamp_lbadam_step_reduce(
+                    native.ptr(self.dev), len(entries), native.ptr(self.work), self.n_blocks, reduce['data_table'], reduce['meta_table'],
+                    int(reduce['world']), int(reduce['rank']), int(reduce['n_tensors']), native.stream()
+                ), 'lbadam_step_reduce'
+            )
+        else:
+            native.check(
+                native.lib().msamp_lbadam_step(native.ptr(self.dev), len(entries), native.ptr(self.work), self.n_blocks, native.stream()),
+                'lbadam_step'
+            )
         for e in entries:
             pv = e['p'].value if isinstance(e['p'], ScalingTensor) else e['p']
             torch.autograd.graph.increment_version(pv)

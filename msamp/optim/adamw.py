@@ -23,6 +23,9 @@ class LBAdamW(LBAdamWBase):
     ):
         self.tensor_scale = tensor_scale
         self._plans = {}
+        # set by a sharded optimizer: fold the FP8 gradient reduce-scatter into stage 1 of the fused kernel
+        # (dict(index={id(param): tensor index}, data_table, meta_table, world, rank, n_tensors)); consumed by one step
+        self._reduce_in_step = None
         super().__init__(
             params, lr=lr, bias_correction=bias_correction, betas=betas, eps=eps, weight_decay=weight_decay, amsgrad=False,
             maximize=maximize, exp_avg_dtype=exp_avg_dtype, exp_avg_sq_dtype=exp_avg_sq_dtype
@@ -50,9 +53,10 @@ class LBAdamW(LBAdamWBase):
             g = grads[i]
             if not isinstance(g, ScalingTensor) and not g.is_contiguous():
                 g = g.contiguous()
+            reduce = getattr(self, '_reduce_in_step', None)
             entries.append(
                 dict(
-                    p=p, g=g, m=exp_avgs[i], v=exp_avg_sqs[i],
+                    p=p, g=g, m=exp_avgs[i], v=exp_avg_sqs[i], g_index=(reduce['index'].get(id(p), -1) if reduce is not None else -1),
                     lr_wd_factor=(1.0 if self.use_adam else 1.0 - lr * weight_decay), l2=(weight_decay if self.use_adam else 0.0),
                     beta1=beta1, beta2=beta2, eps=eps, step_size=lr / bc1, sqrt_bc2=math.sqrt(bc2), gsign=(-1.0 if maximize else 1.0),
                     tensor_scale=self.tensor_scale
@@ -62,12 +66,13 @@ class LBAdamW(LBAdamWBase):
         plan = self._plans.get(key)
         if plan is None:
             plan = self._plans[key] = FusedPlan(params[0].device)
-        plan.run(entries)
+        plan.run(entries, reduce=getattr(self, '_reduce_in_step', None))
 
     def __getstate__(self):
         d = super().__getstate__() if hasattr(super(), '__getstate__') else self.__dict__.copy()
         d = dict(d)
         d['_plans'] = {}
+        d['_reduce_in_step'] = None
         return d
 
 

@@ -54,7 +54,7 @@ class ZeroShardedOptimizer:
         stage: 0 = replicated states (FP8 all-reduce), 1 or 2 = sharded master weights and moments.
         group: data-parallel process group.
     """
-    def __init__(self, model, optimizer, stage=2, group=None, wait_seconds=5.0, model_parallel_group=None):
+    def __init__(self, model, optimizer, stage=2, group=None, wait_seconds=5.0, model_parallel_group=None, fuse_adam=True):
         self.model, self.optimizer, self.stage, self.group = model, optimizer, stage, group
         self.world = DistUtil.get_world_size(group)
         self.rank = DistUtil.get_rank(group)
@@ -84,6 +84,21 @@ class ZeroShardedOptimizer:
         if self.sharded:
             self._shard_states()
         self._build_hp_buffers()
+        # Stages 1 / 2 on the native path: the FP8 gradient reduce-scatter runs inside stage 1 of the fused Adam kernel
+        # (each owner pulls its tensors' bytes from all ranks while it streams its own parameters and moments).
+        self.fuse_adam = bool(fuse_adam) and self.native and self.sharded and hasattr(optimizer, '_reduce_in_step') \
+            and getattr(optimizer, 'tensor_scale', False)
+        if self.fuse_adam:
+            self._fused_grads = {}
+            for i, m in self.masters.items():
+                p = self.fp8_params[i]
+                # the reduced gradient's scale_inv lands in meta row 2 (row 0 is this rank's own contribution, which the
+                # peers are still reading)
+                meta = ScalingMeta(E4M3, scale=torch.ones((), device=self.device), scale_inv=self.g_meta_t[2, i:i + 1].view(()),
+                                   amax=self.g_meta_t[1, i:i + 1], window_size=1)
+                self._fused_grads[i] = ScalingTensor(p._grad_out, meta)
+            self._reduce_desc = dict(index={id(m): i for i, m in self.masters.items()}, data_table=self.g_buf.table,
+                                     meta_table=self.g_meta.table, world=self.world, rank=self.rank, n_tensors=self.n)
 
     # ------------------------------------------------------------------ set-up
     def _alloc(self, nbytes):
@@ -304,15 +319,28 @@ class ZeroShardedOptimizer:
 
     def reduce_and_step(self, clip_grad=0.0):
         """Call after backward: exchange gradients, update the owned shard, publish weights, clear gradients."""
-        self._reduce_fp8_grads()
-        self._reduce_hp_grads()
-        if self.sharded:
+        fused = self.fuse_adam and clip_grad <= 0    # clipping needs the norm of the reduced gradients before the update
+        if fused:
+            # one cross-rank barrier (all gradients and metas are written), then reduce-scatter + Adam in one kernel
+            self.flags.barrier(slot=3, limit_seconds=self.wait_seconds)
+            self._reduce_hp_grads()
             for i, m in self.masters.items():
-                p = self.fp8_params[i]
-                m.grad = p.grad
-        if clip_grad > 0:
-            self._clip(clip_grad)
-        self.optimizer.step()
+                m.grad = self._fused_grads[i] if self.fp8_params[i].grad is not None else None
+            self.optimizer._reduce_in_step = self._reduce_desc
+            try:
+                self.optimizer.step()
+            finally:
+                self.optimizer._reduce_in_step = None
+        else:
+            self._reduce_fp8_grads()
+            self._reduce_hp_grads()
+            if self.sharded:
+                for i, m in self.masters.items():
+                    p = self.fp8_params[i]
+                    m.grad = p.grad
+            if clip_grad > 0:
+                self._clip(clip_grad)
+            self.optimizer.step()
         if self.sharded:
             self._publish_weights()
             self._gather_hp_params()

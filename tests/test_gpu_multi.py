@@ -198,7 +198,7 @@ def test_fused_fp8_allreduce(world):
     run_workers(_fused_reduce_matches_math, world, backend='nccl')
 
 
-def _zero2_training(rank, world):
+def _zero2_training(rank, world, fuse_adam=True):
     from msamp.ops import native
     from msamp.parallel import DataParallelTrainer
     dev = torch.device('cuda', rank)
@@ -216,6 +216,8 @@ def _zero2_training(rank, world):
 
     wrapped = Wrap(model)
     trainer = DataParallelTrainer(wrapped, opt, zero_stage=2)
+    trainer.zero.fuse_adam = trainer.zero.fuse_adam and fuse_adam
+    assert trainer.zero.fuse_adam == fuse_adam
     torch.manual_seed(7)
     xs, ys = torch.randn(world * 32, 256, device=dev), torch.randn(world * 32, 64, device=dev)
     losses = []
@@ -229,12 +231,76 @@ def _zero2_training(rank, world):
     ref = flat.clone()
     dist.broadcast(ref, src=0)
     assert torch.equal(flat, ref)
+    trainer.zero.close()
+
+
+def _fused_adam_equals_reduce_then_adam(rank, world):
+    """One optimizer step from the same gradients and states, once with the reduce-scatter folded into the Adam kernel and
+    once with the separate reduce kernel: masters, moments and published FP8 weights agree bit for bit."""
+    from msamp.ops import native
+    from msamp.parallel.zero import ZeroShardedOptimizer
+    dev = torch.device('cuda', rank)
+    model = _mk_model(dev)
+    opt = torch.optim.AdamW(model.parameters(), lr=3e-3)
+    model, opt = msamp.initialize(model, opt, 'O2')
+    zero = ZeroShardedOptimizer(model, opt, stage=2)
+    assert zero.fuse_adam
+    torch.manual_seed(100 + rank)
+    x = torch.randn(64, 256, device=dev)
+    model(x).square().mean().backward()
+    torch.cuda.synchronize()
+    dist.barrier()
+    snap = dict(g=zero.g_flat.clone(), gm=zero.g_meta_t.clone(), w=zero.w_flat.clone(), wm=zero.w_meta_t.clone(),
+                masters={i: (m.value.clone(), m.meta.scale.clone(), m.meta.scale_inv.clone(), m.meta.amax.clone()) for i, m in zero.masters.items()},
+                hp=[p.detach().clone() for p in zero.hp_params], hp_grads=[None if p.grad is None else p.grad.clone() for p in zero.hp_params],
+                fp8_grads=[p.grad for p in zero.fp8_params])
+    results = []
+    for fused in (True, False):
+        zero.fuse_adam = fused
+        zero.reduce_and_step()
+        torch.cuda.synchronize()
+        assert native.device_status() == 0
+        dist.barrier()
+        results.append(dict(w=zero.w_flat.clone(), wm=zero.w_meta_t[:2].clone(),
+                            masters={i: m.value.clone() for i, m in zero.masters.items()},
+                            m={i: opt.state[m]['exp_avg'].value.clone() for i, m in zero.masters.items()},
+                            v={i: opt.state[m]['exp_avg_sq'].value.clone() for i, m in zero.masters.items()}))
+        # back to the state before the step
+        opt.state.clear()
+        zero.g_flat.copy_(snap['g'])
+        zero.g_meta_t.copy_(snap['gm'])
+        zero.w_flat.copy_(snap['w'])
+        zero.w_meta_t.copy_(snap['wm'])
+        for i, m in zero.masters.items():
+            val, sc, si, am = snap['masters'][i]
+            m.value.copy_(val)
+            m.meta.scale.copy_(sc)
+            m.meta.scale_inv.copy_(si)
+            m.meta.amax.copy_(am)
+        for p, d, g in zip(zero.hp_params, snap['hp'], snap['hp_grads']):
+            p.data.copy_(d)
+            p.grad = None if g is None else g.clone()
+        for p, g in zip(zero.fp8_params, snap['fp8_grads']):
+            p.grad = g
+        torch.cuda.synchronize()
+        dist.barrier()
+    a, b = results
+    assert torch.equal(a['w'], b['w']) and torch.equal(a['wm'], b['wm'])
+    for i in a['masters']:
+        assert torch.equal(a['masters'][i], b['masters'][i]) and torch.equal(a['m'][i], b['m'][i]) and torch.equal(a['v'][i], b['v'][i])
+    zero.close()
 
 
 @WORLDS
 def test_zero2_training(world):
     _need(world)
-    run_workers(_zero2_training, world, backend='nccl')
+    run_workers(_zero2_training, world, backend='nccl', args=(True, ))
+
+
+@WORLDS
+def test_reduce_scatter_fused_into_adam_is_bit_exact(world):
+    _need(world)
+    run_workers(_fused_adam_equals_reduce_then_adam, world, backend='nccl')
 
 
 def _fused_gemms(rank, world, n_comm=4, shapes=((128, 256, 128), (256, 512, 384), (1024, 4096, 1536), (512, 1024, 1000))):
