@@ -45,6 +45,7 @@ def parse():
     ap.add_argument('--recompute', action='store_true', help='activation recomputation in the GPT blocks (data-parallel model only)')
     ap.add_argument('--accum', type=int, default=1, help='micro-batches per optimizer step (gradient accumulation); global batch = micro-batch x accum x DP')
     ap.add_argument('--full-shard', action='store_true', help='ZeRO-3 / FSDP full shard (default for gpt-30b on more than one GPU)')
+    ap.add_argument('--overlap-comm', action='store_true', help='reduce FP8 gradients bucket by bucket during backward (data-parallel ZeRO runs)')
     ap.add_argument('--tp', type=int, default=0,
                     help='tensor-parallel size with sequence parallelism (0 = 4 for gpt-13b when the world allows it, else 1)')
     return ap.parse_args()
@@ -200,7 +201,7 @@ def main():
         model = GPT(cfg, device=dev)
         opt = torch.optim.AdamW(model.parameters(), lr=1e-4, betas=(0.9, 0.95), weight_decay=0.1)
         model, opt = msamp.initialize(model, opt, args.opt_level)
-        trainer = DataParallelTrainer(model, opt, zero_stage=2 if world > 1 else 0)
+        trainer = DataParallelTrainer(model, opt, zero_stage=2 if world > 1 else 0, overlap_comm=args.overlap_comm)
         data_rank = rank
 
     B, S = args.micro_batch, args.seq

@@ -18,7 +18,7 @@ class DataParallelTrainer:
     high-precision gradients are averaged in flat buckets.
     """
     def __init__(self, model, optimizer, zero_stage=0, group=None, clip_grad=0.0, bucket_elems=64 * 1024 * 1024, after_backward=None,
-                 heartbeat=None, model_parallel_group=None):
+                 heartbeat=None, model_parallel_group=None, overlap_comm=False):
         self.model = model
         # msamp.utils.Heartbeat (optional): checked before every step, so a rank that went silent between steps raises
         # RankFailure on the others before they enter a collective or a fused kernel that would wait for it
@@ -35,7 +35,8 @@ class DataParallelTrainer:
         self.zero = None
         if zero_stage and self.world > 1:
             from msamp.parallel.zero import ZeroShardedOptimizer
-            self.zero = ZeroShardedOptimizer(model, optimizer, stage=zero_stage, group=group, model_parallel_group=model_parallel_group)
+            self.zero = ZeroShardedOptimizer(model, optimizer, stage=zero_stage, group=group, model_parallel_group=model_parallel_group,
+                                             overlap_comm=overlap_comm)
 
     def _sync_grads(self):
         if self.world == 1:
@@ -72,7 +73,9 @@ class DataParallelTrainer:
         self.optimizer.zero_grad(set_to_none=True)
         k = len(micro_batches)
         total = None
-        for inputs in micro_batches:
+        for n_mb, inputs in enumerate(micro_batches):
+            if self.zero is not None and n_mb == k - 1:
+                self.zero.reduce_in_backward(True)    # the last backward of the step may reduce gradients as they appear
             loss = self.model(*inputs)
             if k > 1:
                 loss = loss / k

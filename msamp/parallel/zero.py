@@ -53,8 +53,14 @@ class ZeroShardedOptimizer:
         optimizer: the LBAdam/LBAdamW/DSAdam built for it.
         stage: 0 = replicated states (FP8 all-reduce), 1 or 2 = sharded master weights and moments.
         group: data-parallel process group.
+        fuse_adam: stages 1 / 2: fold the FP8 gradient reduce-scatter into the first pass of the Adam kernel.
+        overlap_comm: reduce the FP8 gradients bucket by bucket on a side stream while backward is still running (the
+            reference reduces from backward hooks as well, msamp/deepspeed/runtime/zero/fp8_stage_1_and_2.py:378-443).
+            The caller says which backward pass is the last of an optimizer step with ``reduce_in_backward(True)``.
+        bucket_bytes: FP8 gradient bytes per bucket of the overlapped reduction.
     """
-    def __init__(self, model, optimizer, stage=2, group=None, wait_seconds=5.0, model_parallel_group=None, fuse_adam=True):
+    def __init__(self, model, optimizer, stage=2, group=None, wait_seconds=5.0, model_parallel_group=None, fuse_adam=True,
+                 overlap_comm=False, bucket_bytes=256 << 20):
         self.model, self.optimizer, self.stage, self.group = model, optimizer, stage, group
         self.world = DistUtil.get_world_size(group)
         self.rank = DistUtil.get_rank(group)
@@ -99,6 +105,102 @@ class ZeroShardedOptimizer:
                 self._fused_grads[i] = ScalingTensor(p._grad_out, meta)
             self._reduce_desc = dict(index={id(m): i for i, m in self.masters.items()}, data_table=self.g_buf.table,
                                      meta_table=self.g_meta.table, world=self.world, rank=self.rank, n_tensors=self.n)
+
+        self.overlap_comm = bool(overlap_comm) and self.native
+        self._overlap_armed = False
+        if self.overlap_comm:
+            self._setup_overlap(bucket_bytes)
+
+    # ------------------------------------------------------------------ overlapped reduction
+    def _setup_overlap(self, bucket_bytes):
+        """Buckets of FP8 parameters in the order their gradients appear (last layer first), the per-bucket work lists of
+        the fused reduce kernel, and a hook on every parameter that launches a bucket once all of its gradients exist."""
+        self.comm_stream = torch.cuda.Stream(device=self.device)
+        chunk = 16384
+        self.buckets = []    # dict(tensors=[i...], work_t, n_work, commit_t, n_commit)
+        cur, size = [], 0
+        for i in reversed(range(self.n)):
+            cur.append(i)
+            size += self.fp8_params[i].numel()
+            if size >= bucket_bytes:
+                self.buckets.append(cur)
+                cur, size = [], 0
+        if cur:
+            self.buckets.append(cur)
+        self.bucket_of = {}
+        built = []
+        for b, tensors in enumerate(self.buckets):
+            work = []
+            for i in tensors:
+                self.bucket_of[i] = b
+                if self.sharded and self.owners[i] != self.rank:
+                    continue
+                if not self.sharded and (i % self.world) != self.rank:
+                    continue    # all-reduce flavour: the tensors of a bucket are dealt to the ranks in turn
+                nb = _pad16(self.fp8_params[i].numel())
+                work += [(i, c) for c in range((nb + chunk - 1) // chunk)]
+            commit = [i for i in tensors if (not self.sharded) or self.owners[i] == self.rank]
+            built.append(dict(
+                tensors=tensors, n_work=len(work), n_commit=len(commit),
+                work_t=torch.tensor(work if work else [(0, 0)], dtype=torch.int32, device=self.device).reshape(-1),
+                commit_t=torch.tensor(commit if commit else [0], dtype=torch.int32, device=self.device)))
+        self.buckets = built
+        self._pending = [set() for _ in self.buckets]
+        self._launched = [False] * len(self.buckets)
+        for i, p in enumerate(self.fp8_params):
+            p.register_backward_post_hook(self._make_overlap_hook(i))
+
+    def _make_overlap_hook(self, i):
+        def hook(*args, **kwargs):
+            if not self._overlap_armed:
+                return
+            b = self.bucket_of[i]
+            self._pending[b].discard(i)
+            if not self._pending[b] and not self._launched[b]:
+                self._launch_bucket(b)
+        return hook
+
+    def reduce_in_backward(self, enabled=True):
+        """Arm (or disarm) the overlapped reduction for the next backward pass: call with True right before the last
+        backward of an optimizer step (gradient accumulation: earlier micro-batches must not be reduced)."""
+        if not self.overlap_comm:
+            return
+        self._overlap_armed = bool(enabled)
+        if enabled:
+            self._pending = [set(b['tensors']) for b in self.buckets]
+            self._launched = [False] * len(self.buckets)
+
+    def _launch_bucket(self, b):
+        from msamp.ops import native
+        bucket = self.buckets[b]
+        self._launched[b] = True
+        self.comm_stream.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(self.comm_stream):
+            epoch = self.flags.next_epoch()
+            # 64 CTAs: the kernel shares the GPU with the GEMMs of the remaining backward pass
+            native.check(
+                native.lib().msamp_symm_grad_reduce(
+                    self.g_buf.table, self.g_meta.table, self.flags.table, native.ptr(self.offsets_t), native.ptr(bucket['work_t']),
+                    bucket['n_work'], self.n, self.rank, self.world, ctypes.c_uint(epoch), 0 if self.sharded else 1,
+                    ctypes.c_double(self.wait_seconds), 64, native.stream()
+                ), 'symm_grad_reduce(bucket)'
+            )
+            native.check(
+                native.lib().msamp_symm_commit_meta(native.ptr(self.g_meta_t), self.n, native.ptr(bucket['commit_t']), bucket['n_commit'],
+                                                    native.stream()), 'symm_commit_meta'
+            )
+
+    def _finish_overlapped(self):
+        """Launch what backward did not (parameters without a gradient keep their bucket open) and join the side stream.
+        Returns True if the FP8 gradients were reduced this way."""
+        if not (self.overlap_comm and self._overlap_armed):
+            return False
+        for b in range(len(self.buckets)):
+            if not self._launched[b]:
+                self._launch_bucket(b)
+        torch.cuda.current_stream().wait_stream(self.comm_stream)
+        self._overlap_armed = False
+        return True
 
     # ------------------------------------------------------------------ set-up
     def _alloc(self, nbytes):
@@ -319,7 +421,8 @@ class ZeroShardedOptimizer:
 
     def reduce_and_step(self, clip_grad=0.0):
         """Call after backward: exchange gradients, update the owned shard, publish weights, clear gradients."""
-        fused = self.fuse_adam and clip_grad <= 0    # clipping needs the norm of the reduced gradients before the update
+        overlapped = self._finish_overlapped()    # gradients already reduced bucket by bucket during backward
+        fused = self.fuse_adam and clip_grad <= 0 and not overlapped    # clipping needs the reduced gradients' norm before the update
         if fused:
             # one cross-rank barrier (all gradients and metas are written), then reduce-scatter + Adam in one kernel
             self.flags.barrier(slot=3, limit_seconds=self.wait_seconds)
@@ -332,7 +435,8 @@ class ZeroShardedOptimizer:
             finally:
                 self.optimizer._reduce_in_step = None
         else:
-            self._reduce_fp8_grads()
+            if not overlapped:
+                self._reduce_fp8_grads()
             self._reduce_hp_grads()
             if self.sharded:
                 for i, m in self.masters.items():

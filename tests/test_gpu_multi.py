@@ -198,7 +198,7 @@ def test_fused_fp8_allreduce(world):
     run_workers(_fused_reduce_matches_math, world, backend='nccl')
 
 
-def _zero2_training(rank, world, fuse_adam=True):
+def _zero2_training(rank, world, fuse_adam=True, overlap=False):
     from msamp.ops import native
     from msamp.parallel import DataParallelTrainer
     dev = torch.device('cuda', rank)
@@ -215,7 +215,10 @@ def _zero2_training(rank, world, fuse_adam=True):
             return (self.m(x) - y).square().mean()
 
     wrapped = Wrap(model)
-    trainer = DataParallelTrainer(wrapped, opt, zero_stage=2)
+    trainer = DataParallelTrainer(wrapped, opt, zero_stage=2, overlap_comm=overlap)
+    if overlap:
+        assert trainer.zero.overlap_comm
+        assert len(trainer.zero.buckets) >= 1
     trainer.zero.fuse_adam = trainer.zero.fuse_adam and fuse_adam
     assert trainer.zero.fuse_adam == fuse_adam
     torch.manual_seed(7)
@@ -295,6 +298,13 @@ def _fused_adam_equals_reduce_then_adam(rank, world):
 def test_zero2_training(world):
     _need(world)
     run_workers(_zero2_training, world, backend='nccl', args=(True, ))
+
+
+@WORLDS
+def test_zero2_reduction_overlapped_with_backward(world):
+    """The FP8 gradients are reduced bucket by bucket from backward hooks on a side stream; replicas agree, the loss falls."""
+    _need(world)
+    run_workers(_zero2_training, world, backend='nccl', args=(True, True))
 
 
 @WORLDS
