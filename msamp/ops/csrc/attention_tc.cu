@@ -20,6 +20,7 @@
 // up, bit 2 (value 4) of the device status word is set and the CTA frees its TMEM and returns.
 //
 // Same arithmetic as the mma.sync kernels in attention.cu, which remain the path for head size 64.
+#include <cstdlib>
 #include <mutex>
 #include <unordered_map>
 
@@ -33,13 +34,15 @@ constexpr float kLn2 = 0.6931471805599453f;
 constexpr unsigned int kStatusBit = 4u;
 
 struct TcParams {
+  const __nv_bfloat16* q;
   __nv_bfloat16* o;
   float* lse;             // [b, h, s] natural-log sum-exp of the scaled scores
   const float* delta;     // [b, h, s] rowsum(dO * O)
   __nv_bfloat16* dq;
   __nv_bfloat16* dk;
   __nv_bfloat16* dv;
-  int64_t o_sb, o_ss, o_sh;    // element strides: batch, sequence, head
+  int64_t q_sb, q_ss, q_sh;    // element strides: batch, sequence, head
+  int64_t o_sb, o_ss, o_sh;
   int64_t dq_sb, dq_ss, dq_sh;
   int64_t dk_sb, dk_ss, dk_sh;
   int64_t dv_sb, dv_ss, dv_sh;
@@ -317,6 +320,292 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     tc5::fence_after_sync();
     // merge the two groups: both halves of every row meet through shared memory (the Q tile is dead by now)
     float* xm = reinterpret_cast<float*>(smem + OFF_Q);    // [2][128] maxima, then [2][128] sums
+    float* xl = xm + 256;
+    xm[wg * 128 + row] = m;
+    xl[wg * 128 + row] = l;
+    asm volatile("bar.sync 1, 256;" ::: "memory");    // reached by all eight softmax warps, also after a failed wait
+    if (ok) {
+      const float m0 = xm[row], m1 = xm[128 + row], l0 = xl[row], l1 = xl[128 + row];
+      const float mm = fmaxf(m0, m1);
+      const float f0 = (m0 == -INFINITY) ? 0.0f : ex2(m0 - mm);
+      const float f1 = (m1 == -INFINITY) ? 0.0f : ex2(m1 - mm);
+      const float lt = l0 * f0 + l1 * f1;
+      const float inv = lt > 0.0f ? 1.0f / lt : 0.0f;
+      const float g0 = f0 * inv, g1 = f1 * inv;
+      const bool two = n_kv > 1;    // with one key tile group 1 never wrote its accumulator
+      __nv_bfloat16* dst = p.o + (int64_t)b * p.o_sb + (int64_t)grow * p.o_ss + (int64_t)h * p.o_sh + wg * 64;
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        uint32_t a0[32], a1[32];
+        float v[32];
+        tc5::tmem_ld32(tlane + TM_O + (uint32_t)wg * 64u + (uint32_t)c * 32u, a0);
+        if (two) tc5::tmem_ld32(tlane + TM_O + 128u + (uint32_t)wg * 64u + (uint32_t)c * 32u, a1);
+        tc5::tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(a0[i]) * g0;
+        if (two) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = fmaf(__uint_as_float(a1[i]), g1, v[i]);
+        }
+        if (grow < p.seqlen) st_row32(dst + c * 32, v);
+      }
+      if (wg == 0 && grow < p.seqlen) p.lse[(int64_t)bh * p.seqlen + grow] = lt > 0.0f ? mm * kLn2 + logf(lt) : -INFINITY;
+    }
+  }
+
+  // ---------------------------------------------------------------------- tear-down
+  __syncwarp();
+  if (*abort_flag) __nanosleep(200000);    // let copies / MMAs in flight finish before smem and TMEM go away
+  tc5::fence_before_sync();
+  __syncthreads();
+  tc5::fence_after_sync();
+  if (warp == 1) tc5::tmem_dealloc(tmem_base, TM_COLS);
+}
+
+// ====================================================================== forward, A operands in tensor memory
+namespace fwd2 {
+constexpr int NKV = 6;                        // ring depth of the K and V tiles in shared memory
+constexpr int NS = 3;                         // score / probability slots in tensor memory (key tile j uses slot j % 3)
+constexpr uint32_t PANEL_KV = 64 * 128;       // [64 key rows][64 bf16]
+constexpr uint32_t TILE_KV = 2 * PANEL_KV;    // 16 KB
+constexpr uint32_t OFF_K = 0, OFF_V = NKV * TILE_KV, OFF_X = OFF_V + NKV * TILE_KV, OFF_BAR = OFF_X + 2048;
+enum { B_Q = 0, B_KF = 1, B_KE = B_KF + NKV, B_VF = B_KE + NKV, B_VE = B_VF + NKV, B_SF = B_VE + NKV, B_PF = B_SF + NS, B_OF = B_PF + NS,
+       B_ACC = B_OF + 2, NBAR = B_ACC + 1 };
+constexpr int SMEM = OFF_BAR + NBAR * 8 + 16 + 1024;
+// columns: three 64-wide score slots, Q as 64 columns of packed bf16 pairs, two 128-wide output accumulators
+constexpr uint32_t TM_S = 0, TM_Q = 192, TM_O = 256, TM_COLS = 512;
+constexpr float kRescaleStep = 8.0f;
+}    // namespace fwd2
+
+// Same schedule as attn_fwd_tc_kernel (two softmax groups on alternating key tiles, one output accumulator per
+// group, lazy rescale, merge at the end), but the A operand of both products lives in tensor memory:
+//   * Q is written once, as packed bf16 pairs, into 64 TMEM columns by the softmax warps (each thread copies half
+//     of its own row from global memory), and S = Q K^T reads it from there;
+//   * the probabilities of a tile are packed to bf16 and stored with tcgen05.st over the first 32 columns of the
+//     score slot they were computed from, and O += P V reads them from there.
+// Only K and V pass through shared memory, so an S step reads 2 KB instead of 6 KB and a PV step 4 KB instead of 8 KB,
+// and the probability tile costs no shared-memory write.  The tensor pipe executes MMAs in issue order, so slot
+// j % 3 may take the scores of tile j + 3 as soon as that MMA is issued after the PV product of tile j: no
+// "slot free" barriers are needed.
+__global__ void __launch_bounds__(kTcThreads, 1)
+attn_fwd_tm_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, const TcParams p) {
+  using namespace fwd2;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = tc5::smem_u32(smem_raw);
+  const uint32_t base = (raw_addr + 1023u) & ~1023u;
+  uint8_t* smem = smem_raw + (base - raw_addr);
+  const uint32_t bars = base + OFF_BAR;
+  auto bar = [&](int i) { return bars + 8u * (uint32_t)i; };
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(smem + OFF_BAR + NBAR * 8);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+  auto wait_warp = [&](uint32_t br, uint32_t ph) {
+    return __all_sync(0xffffffffu, tc5::mbar_wait(br, ph, abort_flag, p.status, kStatusBit)) != 0;
+  };
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int qt = (int)gridDim.x - 1 - (int)blockIdx.x;    // long rows first
+  const int bh = blockIdx.y;
+  const int b = bh / p.heads;
+  const int h = bh - b * p.heads;
+  const int q0 = qt * 128;
+  const int n_all = (p.seqlen + 63) / 64;
+  const int n_kv = p.causal ? min(2 * qt + 2, n_all) : n_all;
+
+  if (threadIdx.x == 0) {
+    tc5::mbar_init(bar(B_Q), 8);
+    for (int s = 0; s < NKV; ++s) {
+      tc5::mbar_init(bar(B_KF + s), 1);
+      tc5::mbar_init(bar(B_KE + s), 1);
+      tc5::mbar_init(bar(B_VF + s), 1);
+      tc5::mbar_init(bar(B_VE + s), 1);
+    }
+    for (int s = 0; s < NS; ++s) {
+      tc5::mbar_init(bar(B_SF + s), 1);
+      tc5::mbar_init(bar(B_PF + s), 4);
+    }
+    tc5::mbar_init(bar(B_OF + 0), 1);
+    tc5::mbar_init(bar(B_OF + 1), 1);
+    tc5::mbar_init(bar(B_ACC), 1);
+    *abort_flag = 0;
+    tc5::mbar_fence_init();
+    tc5::tma_prefetch_desc(&map_k);
+    tc5::tma_prefetch_desc(&map_v);
+  }
+  if (warp == 1) {
+    tc5::tmem_alloc(tc5::smem_u32(tmem_holder), TM_COLS);
+    tc5::tmem_relinquish();
+  }
+  tc5::fence_before_sync();
+  __syncthreads();
+  tc5::fence_after_sync();
+  const uint32_t tmem_base = *tmem_holder;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      for (int j = 0; j < n_kv; ++j) {
+        const int s = j % NKV;
+        const uint32_t ph = (uint32_t)(j / NKV) & 1u;
+        TC_WAIT(bar(B_KE + s), ph ^ 1u);
+        tc5::mbar_arrive_expect_tx(bar(B_KF + s), TILE_KV);
+        tc5::tma_load_4d(base + OFF_K + s * TILE_KV, &map_k, 0, h, j * 64, b, bar(B_KF + s));
+        tc5::tma_load_4d(base + OFF_K + s * TILE_KV + PANEL_KV, &map_k, 64, h, j * 64, b, bar(B_KF + s));
+        TC_WAIT(bar(B_VE + s), ph ^ 1u);
+        tc5::mbar_arrive_expect_tx(bar(B_VF + s), TILE_KV);
+        tc5::tma_load_4d(base + OFF_V + s * TILE_KV, &map_v, 0, h, j * 64, b, bar(B_VF + s));
+        tc5::tma_load_4d(base + OFF_V + s * TILE_KV + PANEL_KV, &map_v, 64, h, j * 64, b, bar(B_VF + s));
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc_s = tc5::idesc_bf16(128, 64, 0, 0);
+      const uint32_t idesc_o = tc5::idesc_bf16(128, 128, 0, 1);
+      // S[j % 3] = Q K_j^T, A = Q from tensor memory (8 columns per K step of 16)
+      auto issue_s = [&](int j) -> bool {
+        const int sl = j % NS, kv = j % NKV;
+        if (!tc5::mbar_wait(bar(B_KF + kv), (uint32_t)(j / NKV) & 1u, abort_flag, p.status, kStatusBit)) return false;
+        tc5::fence_after_sync();
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint32_t offb = (uint32_t)(kk >> 2) * PANEL_KV + (uint32_t)(kk & 3) * 32u;
+          tc5::mma_f16_ta(tmem_base + TM_S + (uint32_t)sl * 64u, tmem_base + TM_Q + (uint32_t)kk * 8u,
+                          tc5::smem_desc_k_sw128(base + OFF_K + kv * TILE_KV + offb), idesc_s, kk ? 1u : 0u);
+        }
+        tc5::mma_commit(bar(B_KE + kv));
+        tc5::mma_commit(bar(B_SF + sl));
+        return true;
+      };
+      do {
+        TC_WAIT(bar(B_Q), 0u);
+        bool ok = true;
+        for (int j = 0; j < NS && j < n_kv; ++j)
+          if (!issue_s(j)) { ok = false; break; }
+        if (!ok) break;
+        for (int j = 0; j < n_kv; ++j) {
+          const int sl = j % NS, kv = j % NKV;
+          if (!tc5::mbar_wait(bar(B_PF + sl), (uint32_t)(j / NS) & 1u, abort_flag, p.status, kStatusBit)) { ok = false; break; }
+          if (!tc5::mbar_wait(bar(B_VF + kv), (uint32_t)(j / NKV) & 1u, abort_flag, p.status, kStatusBit)) { ok = false; break; }
+          tc5::fence_after_sync();
+          // O[j&1] (+)= P_j V_j : A = P from the first 32 columns of its score slot, B = V with the key index as rows
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk) {
+            tc5::mma_f16_ta(tmem_base + TM_O + (uint32_t)(j & 1) * 128u, tmem_base + TM_S + (uint32_t)sl * 64u + (uint32_t)kk * 8u,
+                            tc5::smem_desc_mn_sw128(base + OFF_V + kv * TILE_KV + (uint32_t)kk * 2048u, PANEL_KV), idesc_o,
+                            (j >= 2 || kk) ? 1u : 0u);
+          }
+          tc5::mma_commit(bar(B_VE + kv));
+          tc5::mma_commit(bar(B_OF + (j & 1)));
+          if (j + NS < n_kv && !issue_s(j + NS)) { ok = false; break; }
+        }
+        if (ok) tc5::mma_commit(bar(B_ACC));
+      } while (false);
+    }
+  } else {
+    // ------------------------------------------------------------------ softmax: one thread per query row and group
+    const int qd = warp & 3;           // TMEM lane quarter this warp may access
+    const int wg = (warp - 2) >> 2;    // group 0: even key tiles, group 1: odd key tiles
+    const int row = qd * 32 + lane;
+    const int grow = q0 + row;
+    const uint32_t tlane = tmem_base + ((uint32_t)(qd * 32) << 16);
+    const uint32_t to = tlane + TM_O + (uint32_t)wg * 128u;
+    const float sl = p.scale * kLog2e;
+    const int lim = p.causal ? min(grow, p.seqlen - 1) : p.seqlen - 1;    // last visible column
+    float m = -INFINITY, l = 0.0f;    // reference maximum (log2 units) and row sum of this group
+    bool ok = true;
+
+    {    // this group's half of the Q row: 64 bf16 -> 32 packed columns
+      uint32_t x[32];
+      if (grow < p.seqlen) {
+        const uint4* src = reinterpret_cast<const uint4*>(p.q + (int64_t)b * p.q_sb + (int64_t)grow * p.q_ss + (int64_t)h * p.q_sh + wg * 64);
+#pragma unroll
+        for (int t = 0; t < 8; ++t) {
+          const uint4 u = __ldg(src + t);
+          x[4 * t] = u.x; x[4 * t + 1] = u.y; x[4 * t + 2] = u.z; x[4 * t + 3] = u.w;
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) x[i] = 0u;
+      }
+      tc5::tmem_st32(tlane + TM_Q + (uint32_t)wg * 32u, x);
+      tc5::tmem_st_wait();
+      tc5::fence_before_sync();
+      __syncwarp();
+      if (lane == 0) tc5::mbar_arrive(bar(B_Q));
+    }
+
+    for (int j = wg; j < n_kv; j += 2) {
+      const int s = j % NS;
+      const uint32_t ph = (uint32_t)(j / NS) & 1u;
+      const int k = j >> 1;    // index of this tile within the group
+      if (!wait_warp(bar(B_SF + s), ph)) { ok = false; break; }
+      tc5::fence_after_sync();
+      uint32_t r[2][32];
+      tc5::tmem_ld32(tlane + TM_S + (uint32_t)s * 64u, r[0]);
+      tc5::tmem_ld32(tlane + TM_S + (uint32_t)s * 64u + 32u, r[1]);
+      tc5::tmem_ld_wait();
+      const int col0 = j * 64;
+      const bool need_mask = (p.causal && col0 + 63 > q0) || (col0 + 64 > p.seqlen);
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+      if (need_mask) {
+#pragma unroll
+        for (int i = 0; i < 64; ++i)
+          if (col0 + i <= lim) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(r[i >> 5][i & 31]));
+      } else {
+#pragma unroll
+        for (int i = 0; i < 64; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(r[i >> 5][i & 31]));
+      }
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * sl;    // sl > 0
+      const bool grow_m = mx > m + kRescaleStep || (m == -INFINITY && mx > -INFINITY);
+      if (__any_sync(0xffffffffu, grow_m)) {
+        const float m_new = grow_m ? mx : m;
+        const float corr = (m == -INFINITY) ? 0.0f : ex2(m - m_new);
+        if (k > 0) {
+          // every earlier product of this group must have landed in O before it is rescaled
+          if (!wait_warp(bar(B_OF + wg), (uint32_t)(k - 1) & 1u)) { ok = false; break; }
+          tc5::fence_after_sync();
+#pragma unroll 1
+          for (int c = 0; c < 4; ++c) {
+            uint32_t x[32];
+            tc5::tmem_ld32(to + (uint32_t)c * 32u, x);
+            tc5::tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) x[i] = __float_as_uint(__uint_as_float(x[i]) * corr);
+            tc5::tmem_st32(to + (uint32_t)c * 32u, x);
+          }
+        }
+        l *= corr;
+        m = m_new;
+      }
+      const float m_use = (m == -INFINITY) ? 0.0f : m;
+      float sum4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+      uint32_t pk[32];
+#pragma unroll
+      for (int g = 0; g < 8; ++g) {    // columns 8g .. 8g+7 -> packed columns 4g .. 4g+3
+        float e[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          e[i] = ex2(fmaf(__uint_as_float(r[g >> 2][(g & 3) * 8 + i]), sl, -m_use));
+          if (need_mask && col0 + g * 8 + i > lim) e[i] = 0.0f;
+          sum4[i & 3] += e[i];
+        }
+        pk[4 * g] = pack_bf16(e[0], e[1]);
+        pk[4 * g + 1] = pack_bf16(e[2], e[3]);
+        pk[4 * g + 2] = pack_bf16(e[4], e[5]);
+        pk[4 * g + 3] = pack_bf16(e[6], e[7]);
+      }
+      l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+      tc5::tmem_st32(tlane + TM_S + (uint32_t)s * 64u, pk);
+      tc5::tmem_st_wait();    // also covers the rescaled accumulator
+      tc5::fence_before_sync();
+      __syncwarp();
+      if (lane == 0) tc5::mbar_arrive(bar(B_PF + s));
+    }
+    ok = ok && wait_warp(bar(B_ACC), 0u);
+    tc5::fence_after_sync();
+    // merge the two groups: both halves of every row meet through shared memory
+    float* xm = reinterpret_cast<float*>(smem + OFF_X);    // [2][128] maxima, then [2][128] sums
     float* xl = xm + 256;
     xm[wg * 128 + row] = m;
     xl[wg * 128 + row] = l;
@@ -985,10 +1274,19 @@ MSAMP_API int msamp_attention_tc_fwd(const void* q, const void* k, const void* v
   p.o_sb = strides[9]; p.o_ss = strides[10]; p.o_sh = strides[11];
   p.batch = batch; p.heads = heads; p.seqlen = seqlen; p.causal = causal; p.scale = scale;
   p.status = msamp_device_status_ptr();
-  if ((rc = set_smem(attn_fwd_tc_kernel, fwd::SMEM))) return rc;
   dim3 grid((seqlen + 127) / 128, batch * heads);
-  attn_fwd_tc_kernel<<<grid, kTcThreads, fwd::SMEM, (cudaStream_t)stream_>>>(mq, mk, mv, p);
-  return msamp_check_launch("attn_fwd_tc_kernel");
+  // MSAMP_ATTN_FWD_SMEM=1 selects the kernel that keeps Q and P in shared memory (the default keeps them in TMEM).
+  static const bool smem_operands = [] { const char* e = getenv("MSAMP_ATTN_FWD_SMEM"); return e && e[0] == '1'; }();
+  if (smem_operands) {
+    if ((rc = set_smem(attn_fwd_tc_kernel, fwd::SMEM))) return rc;
+    attn_fwd_tc_kernel<<<grid, kTcThreads, fwd::SMEM, (cudaStream_t)stream_>>>(mq, mk, mv, p);
+    return msamp_check_launch("attn_fwd_tc_kernel");
+  }
+  p.q = (const __nv_bfloat16*)q;
+  p.q_sb = strides[0]; p.q_ss = strides[1]; p.q_sh = strides[2];
+  if ((rc = set_smem(attn_fwd_tm_kernel, fwd2::SMEM))) return rc;
+  attn_fwd_tm_kernel<<<grid, kTcThreads, fwd2::SMEM, (cudaStream_t)stream_>>>(mk, mv, p);
+  return msamp_check_launch("attn_fwd_tm_kernel");
 }
 
 // Same contract as msamp_attention_bwd (attention.cu) for head_dim 128.
