@@ -42,8 +42,12 @@ MSAMP_USE_WEIGHT_DIFFERENTIABLE_GRADIENT_ESTIMATOR = bool(int(os.getenv('MSAMP_U
 MSAMP_USE_ACTIVATION_SIMULATE_FP4 = bool(int(os.getenv('MSAMP_USE_ACTIVATION_SIMULATE_FP4', 0)))
 
 
+# False (or MSAMP_TP_FUSED=0) runs the NCCL collective + plain GEMM composition everywhere: the oracle of the fused kernels.
+USE_FUSED_COLLECTIVES = bool(int(os.getenv('MSAMP_TP_FUSED', 1)))
+
+
 def _fused_ctx(shard_bytes, out_bytes, device):
-    if device.type != 'cuda' or mpu.get_tensor_model_parallel_world_size() == 1:
+    if not USE_FUSED_COLLECTIVES or device.type != 'cuda' or mpu.get_tensor_model_parallel_world_size() == 1:
         return None
     ctx = mpu.get_fused_context(shard_bytes, out_bytes)
     return ctx if ctx.native else None

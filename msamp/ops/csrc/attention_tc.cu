@@ -34,15 +34,13 @@ constexpr float kLn2 = 0.6931471805599453f;
 constexpr unsigned int kStatusBit = 4u;
 
 struct TcParams {
-  const __nv_bfloat16* q;
   __nv_bfloat16* o;
   float* lse;             // [b, h, s] natural-log sum-exp of the scaled scores
   const float* delta;     // [b, h, s] rowsum(dO * O)
   __nv_bfloat16* dq;
   __nv_bfloat16* dk;
   __nv_bfloat16* dv;
-  int64_t q_sb, q_ss, q_sh;    // element strides: batch, sequence, head
-  int64_t o_sb, o_ss, o_sh;
+  int64_t o_sb, o_ss, o_sh;    // element strides: batch, sequence, head
   int64_t dq_sb, dq_ss, dq_sh;
   int64_t dk_sb, dk_ss, dk_sh;
   int64_t dv_sb, dv_ss, dv_sh;
@@ -362,33 +360,36 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
   if (warp == 1) tc5::tmem_dealloc(tmem_base, TM_COLS);
 }
 
-// ====================================================================== forward, A operands in tensor memory
+// ====================================================================== forward, 128-key score tiles, P in tensor memory
 namespace fwd2 {
-constexpr int NKV = 6;                        // ring depth of the K and V tiles in shared memory
-constexpr int NS = 3;                         // score / probability slots in tensor memory (key tile j uses slot j % 3)
-constexpr uint32_t PANEL_KV = 64 * 128;       // [64 key rows][64 bf16]
-constexpr uint32_t TILE_KV = 2 * PANEL_KV;    // 16 KB
-constexpr uint32_t OFF_K = 0, OFF_V = NKV * TILE_KV, OFF_X = OFF_V + NKV * TILE_KV, OFF_BAR = OFF_X + 2048;
-enum { B_Q = 0, B_KF = 1, B_KE = B_KF + NKV, B_VF = B_KE + NKV, B_VE = B_VF + NKV, B_SF = B_VE + NKV, B_PF = B_SF + NS, B_OF = B_PF + NS,
+constexpr int NK = 3;                         // ring depth of the K tiles (128 keys each)
+constexpr int NV = 5;                         // ring depth of the V sub-tiles (64 keys each)
+constexpr uint32_t PANEL_Q = 128 * 128;       // [128 query rows][64 bf16]
+constexpr uint32_t TILE_Q = 2 * PANEL_Q;      // 32 KB
+constexpr uint32_t PANEL_K = 128 * 128;       // [128 key rows][64 bf16]
+constexpr uint32_t TILE_K = 2 * PANEL_K;      // 32 KB
+constexpr uint32_t PANEL_V = 64 * 128;        // [64 key rows][64 bf16]
+constexpr uint32_t TILE_V = 2 * PANEL_V;      // 16 KB
+constexpr uint32_t OFF_Q = 0, OFF_K = TILE_Q, OFF_V = OFF_K + NK * TILE_K, OFF_X = OFF_V + NV * TILE_V, OFF_BAR = OFF_X + 2048;
+enum { B_Q = 0, B_KF = 1, B_KE = B_KF + NK, B_VF = B_KE + NK, B_VE = B_VF + NV, B_SF = B_VE + NV, B_PF = B_SF + 2, B_OF = B_PF + 4,
        B_ACC = B_OF + 2, NBAR = B_ACC + 1 };
 constexpr int SMEM = OFF_BAR + NBAR * 8 + 16 + 1024;
-// columns: three 64-wide score slots, Q as 64 columns of packed bf16 pairs, two 128-wide output accumulators
-constexpr uint32_t TM_S = 0, TM_Q = 192, TM_O = 256, TM_COLS = 512;
+constexpr uint32_t TM_S = 0, TM_O = 256, TM_COLS = 512;    // two 128-column score slots, two 128-column outputs
 constexpr float kRescaleStep = 8.0f;
 }    // namespace fwd2
 
-// Same schedule as attn_fwd_tc_kernel (two softmax groups on alternating key tiles, one output accumulator per
-// group, lazy rescale, merge at the end), but the A operand of both products lives in tensor memory:
-//   * Q is written once, as packed bf16 pairs, into 64 TMEM columns by the softmax warps (each thread copies half
-//     of its own row from global memory), and S = Q K^T reads it from there;
-//   * the probabilities of a tile are packed to bf16 and stored with tcgen05.st over the first 32 columns of the
-//     score slot they were computed from, and O += P V reads them from there.
-// Only K and V pass through shared memory, so an S step reads 2 KB instead of 6 KB and a PV step 4 KB instead of 8 KB,
-// and the probability tile costs no shared-memory write.  The tensor pipe executes MMAs in issue order, so slot
-// j % 3 may take the scores of tile j + 3 as soon as that MMA is issued after the PV product of tile j: no
-// "slot free" barriers are needed.
+// Measured on this part: a 128 x N x 16 bf16 tcgen05.mma costs about 70 cycles for N = 64 as well as for N = 128 (the
+// A operand, 4 KB, is fed at 64 B/clk whatever N is), wherever A comes from.  S = Q K^T is therefore issued over 128
+// keys at a time (8 MMAs per 128 keys instead of 16).  The two softmax groups split every 128-key score tile by
+// columns: group g owns keys [128 J + 64 g, 128 J + 64 g + 64) of tile J, with its own output accumulator O_g,
+// reference maximum and row sum, exactly as if the groups took alternating 64-key tiles; the halves are merged once
+// at the end.  Probabilities are packed to bf16 and stored with tcgen05.st over the first 32 columns of the 64-column
+// half they were computed from, and O_g += P V reads them from tensor memory (no shared-memory round trip for P).
+// The tensor pipe executes MMAs in issue order, so slot J & 1 may take the scores of tile J + 2 as soon as that MMA is
+// issued after both PV products of tile J: no "slot free" barriers are needed.
 __global__ void __launch_bounds__(kTcThreads, 1)
-attn_fwd_tm_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, const TcParams p) {
+attn_fwd_tm_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                   const __grid_constant__ CUtensorMap map_v, const TcParams p) {
   using namespace fwd2;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = tc5::smem_u32(smem_raw);
@@ -410,25 +411,28 @@ attn_fwd_tm_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
   const int h = bh - b * p.heads;
   const int q0 = qt * 128;
   const int n_all = (p.seqlen + 63) / 64;
-  const int n_kv = p.causal ? min(2 * qt + 2, n_all) : n_all;
+  const int n_kv = p.causal ? min(2 * qt + 2, n_all) : n_all;    // 64-key sub-tiles with a visible key
+  const int n_t = (n_kv + 1) >> 1;                               // 128-key tiles; a trailing odd sub-tile is fully masked
 
   if (threadIdx.x == 0) {
-    tc5::mbar_init(bar(B_Q), 8);
-    for (int s = 0; s < NKV; ++s) {
+    tc5::mbar_init(bar(B_Q), 1);
+    for (int s = 0; s < NK; ++s) {
       tc5::mbar_init(bar(B_KF + s), 1);
       tc5::mbar_init(bar(B_KE + s), 1);
+    }
+    for (int s = 0; s < NV; ++s) {
       tc5::mbar_init(bar(B_VF + s), 1);
       tc5::mbar_init(bar(B_VE + s), 1);
     }
-    for (int s = 0; s < NS; ++s) {
-      tc5::mbar_init(bar(B_SF + s), 1);
-      tc5::mbar_init(bar(B_PF + s), 4);
-    }
+    tc5::mbar_init(bar(B_SF + 0), 1);
+    tc5::mbar_init(bar(B_SF + 1), 1);
+    for (int s = 0; s < 4; ++s) tc5::mbar_init(bar(B_PF + s), 4);
     tc5::mbar_init(bar(B_OF + 0), 1);
     tc5::mbar_init(bar(B_OF + 1), 1);
     tc5::mbar_init(bar(B_ACC), 1);
     *abort_flag = 0;
     tc5::mbar_fence_init();
+    tc5::tma_prefetch_desc(&map_q);
     tc5::tma_prefetch_desc(&map_k);
     tc5::tma_prefetch_desc(&map_v);
   }
@@ -444,60 +448,71 @@ attn_fwd_tm_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
-      for (int j = 0; j < n_kv; ++j) {
-        const int s = j % NKV;
-        const uint32_t ph = (uint32_t)(j / NKV) & 1u;
-        TC_WAIT(bar(B_KE + s), ph ^ 1u);
-        tc5::mbar_arrive_expect_tx(bar(B_KF + s), TILE_KV);
-        tc5::tma_load_4d(base + OFF_K + s * TILE_KV, &map_k, 0, h, j * 64, b, bar(B_KF + s));
-        tc5::tma_load_4d(base + OFF_K + s * TILE_KV + PANEL_KV, &map_k, 64, h, j * 64, b, bar(B_KF + s));
-        TC_WAIT(bar(B_VE + s), ph ^ 1u);
-        tc5::mbar_arrive_expect_tx(bar(B_VF + s), TILE_KV);
-        tc5::tma_load_4d(base + OFF_V + s * TILE_KV, &map_v, 0, h, j * 64, b, bar(B_VF + s));
-        tc5::tma_load_4d(base + OFF_V + s * TILE_KV + PANEL_KV, &map_v, 64, h, j * 64, b, bar(B_VF + s));
+      tc5::mbar_arrive_expect_tx(bar(B_Q), TILE_Q);
+      tc5::tma_load_4d(base + OFF_Q, &map_q, 0, h, q0, b, bar(B_Q));
+      tc5::tma_load_4d(base + OFF_Q + PANEL_Q, &map_q, 64, h, q0, b, bar(B_Q));
+      bool ok = true;
+      for (int t = 0; t < n_t && ok; ++t) {
+        const int ks = t % NK;
+        TC_WAIT(bar(B_KE + ks), ((uint32_t)(t / NK) & 1u) ^ 1u);
+        tc5::mbar_arrive_expect_tx(bar(B_KF + ks), TILE_K);
+        tc5::tma_load_4d(base + OFF_K + ks * TILE_K, &map_k, 0, h, t * 128, b, bar(B_KF + ks));
+        tc5::tma_load_4d(base + OFF_K + ks * TILE_K + PANEL_K, &map_k, 64, h, t * 128, b, bar(B_KF + ks));
+        for (int g = 0; g < 2; ++g) {
+          const int j = 2 * t + g;
+          const int vs = j % NV;
+          if (!tc5::mbar_wait(bar(B_VE + vs), ((uint32_t)(j / NV) & 1u) ^ 1u, abort_flag, p.status, kStatusBit)) { ok = false; break; }
+          tc5::mbar_arrive_expect_tx(bar(B_VF + vs), TILE_V);
+          tc5::tma_load_4d(base + OFF_V + vs * TILE_V, &map_v, 0, h, j * 64, b, bar(B_VF + vs));
+          tc5::tma_load_4d(base + OFF_V + vs * TILE_V + PANEL_V, &map_v, 64, h, j * 64, b, bar(B_VF + vs));
+        }
       }
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      const uint32_t idesc_s = tc5::idesc_bf16(128, 64, 0, 0);
+      const uint32_t idesc_s = tc5::idesc_bf16(128, 128, 0, 0);
       const uint32_t idesc_o = tc5::idesc_bf16(128, 128, 0, 1);
-      // S[j % 3] = Q K_j^T, A = Q from tensor memory (8 columns per K step of 16)
-      auto issue_s = [&](int j) -> bool {
-        const int sl = j % NS, kv = j % NKV;
-        if (!tc5::mbar_wait(bar(B_KF + kv), (uint32_t)(j / NKV) & 1u, abort_flag, p.status, kStatusBit)) return false;
+      // S[t & 1] = Q K_t^T over 128 keys
+      auto issue_s = [&](int t) -> bool {
+        const int ks = t % NK;
+        if (!tc5::mbar_wait(bar(B_KF + ks), (uint32_t)(t / NK) & 1u, abort_flag, p.status, kStatusBit)) return false;
         tc5::fence_after_sync();
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
-          const uint32_t offb = (uint32_t)(kk >> 2) * PANEL_KV + (uint32_t)(kk & 3) * 32u;
-          tc5::mma_f16_ta(tmem_base + TM_S + (uint32_t)sl * 64u, tmem_base + TM_Q + (uint32_t)kk * 8u,
-                          tc5::smem_desc_k_sw128(base + OFF_K + kv * TILE_KV + offb), idesc_s, kk ? 1u : 0u);
+          const uint32_t off = (uint32_t)(kk >> 2) * PANEL_Q + (uint32_t)(kk & 3) * 32u;    // PANEL_K == PANEL_Q
+          tc5::mma_f16(tmem_base + TM_S + (uint32_t)(t & 1) * 128u, tc5::smem_desc_k_sw128(base + OFF_Q + off),
+                       tc5::smem_desc_k_sw128(base + OFF_K + ks * TILE_K + off), idesc_s, kk ? 1u : 0u);
         }
-        tc5::mma_commit(bar(B_KE + kv));
-        tc5::mma_commit(bar(B_SF + sl));
+        tc5::mma_commit(bar(B_KE + ks));
+        tc5::mma_commit(bar(B_SF + (t & 1)));
         return true;
       };
       do {
         TC_WAIT(bar(B_Q), 0u);
         bool ok = true;
-        for (int j = 0; j < NS && j < n_kv; ++j)
-          if (!issue_s(j)) { ok = false; break; }
+        for (int t = 0; t < 2 && t < n_t; ++t)
+          if (!issue_s(t)) { ok = false; break; }
         if (!ok) break;
-        for (int j = 0; j < n_kv; ++j) {
-          const int sl = j % NS, kv = j % NKV;
-          if (!tc5::mbar_wait(bar(B_PF + sl), (uint32_t)(j / NS) & 1u, abort_flag, p.status, kStatusBit)) { ok = false; break; }
-          if (!tc5::mbar_wait(bar(B_VF + kv), (uint32_t)(j / NKV) & 1u, abort_flag, p.status, kStatusBit)) { ok = false; break; }
-          tc5::fence_after_sync();
-          // O[j&1] (+)= P_j V_j : A = P from the first 32 columns of its score slot, B = V with the key index as rows
+        for (int t = 0; t < n_t && ok; ++t) {
+          for (int g = 0; g < 2; ++g) {
+            const int j = 2 * t + g;
+            const int vs = j % NV;
+            if (!tc5::mbar_wait(bar(B_PF + (t & 1) * 2 + g), (uint32_t)(t >> 1) & 1u, abort_flag, p.status, kStatusBit)) { ok = false; break; }
+            if (!tc5::mbar_wait(bar(B_VF + vs), (uint32_t)(j / NV) & 1u, abort_flag, p.status, kStatusBit)) { ok = false; break; }
+            tc5::fence_after_sync();
+            // O_g (+)= P V : A = P from the first 32 columns of its half of the score slot, B = V with the key index as rows
 #pragma unroll
-          for (int kk = 0; kk < 4; ++kk) {
-            tc5::mma_f16_ta(tmem_base + TM_O + (uint32_t)(j & 1) * 128u, tmem_base + TM_S + (uint32_t)sl * 64u + (uint32_t)kk * 8u,
-                            tc5::smem_desc_mn_sw128(base + OFF_V + kv * TILE_KV + (uint32_t)kk * 2048u, PANEL_KV), idesc_o,
-                            (j >= 2 || kk) ? 1u : 0u);
+            for (int kk = 0; kk < 4; ++kk) {
+              tc5::mma_f16_ta(tmem_base + TM_O + (uint32_t)g * 128u,
+                              tmem_base + TM_S + (uint32_t)(t & 1) * 128u + (uint32_t)g * 64u + (uint32_t)kk * 8u,
+                              tc5::smem_desc_mn_sw128(base + OFF_V + vs * TILE_V + (uint32_t)kk * 2048u, PANEL_V), idesc_o,
+                              (t > 0 || kk) ? 1u : 0u);
+            }
+            tc5::mma_commit(bar(B_VE + vs));
+            tc5::mma_commit(bar(B_OF + g));
           }
-          tc5::mma_commit(bar(B_VE + kv));
-          tc5::mma_commit(bar(B_OF + (j & 1)));
-          if (j + NS < n_kv && !issue_s(j + NS)) { ok = false; break; }
+          if (ok && t + 2 < n_t && !issue_s(t + 2)) ok = false;
         }
         if (ok) tc5::mma_commit(bar(B_ACC));
       } while (false);
@@ -505,7 +520,7 @@ attn_fwd_tm_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
   } else {
     // ------------------------------------------------------------------ softmax: one thread per query row and group
     const int qd = warp & 3;           // TMEM lane quarter this warp may access
-    const int wg = (warp - 2) >> 2;    // group 0: even key tiles, group 1: odd key tiles
+    const int wg = (warp - 2) >> 2;    // group g: second index of the 64-key halves it owns
     const int row = qd * 32 + lane;
     const int grow = q0 + row;
     const uint32_t tlane = tmem_base + ((uint32_t)(qd * 32) << 16);
@@ -515,37 +530,15 @@ attn_fwd_tm_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
     float m = -INFINITY, l = 0.0f;    // reference maximum (log2 units) and row sum of this group
     bool ok = true;
 
-    {    // this group's half of the Q row: 64 bf16 -> 32 packed columns
-      uint32_t x[32];
-      if (grow < p.seqlen) {
-        const uint4* src = reinterpret_cast<const uint4*>(p.q + (int64_t)b * p.q_sb + (int64_t)grow * p.q_ss + (int64_t)h * p.q_sh + wg * 64);
-#pragma unroll
-        for (int t = 0; t < 8; ++t) {
-          const uint4 u = __ldg(src + t);
-          x[4 * t] = u.x; x[4 * t + 1] = u.y; x[4 * t + 2] = u.z; x[4 * t + 3] = u.w;
-        }
-      } else {
-#pragma unroll
-        for (int i = 0; i < 32; ++i) x[i] = 0u;
-      }
-      tc5::tmem_st32(tlane + TM_Q + (uint32_t)wg * 32u, x);
-      tc5::tmem_st_wait();
-      tc5::fence_before_sync();
-      __syncwarp();
-      if (lane == 0) tc5::mbar_arrive(bar(B_Q));
-    }
-
-    for (int j = wg; j < n_kv; j += 2) {
-      const int s = j % NS;
-      const uint32_t ph = (uint32_t)(j / NS) & 1u;
-      const int k = j >> 1;    // index of this tile within the group
-      if (!wait_warp(bar(B_SF + s), ph)) { ok = false; break; }
+    for (int t = 0; t < n_t; ++t) {
+      const uint32_t ts = tlane + TM_S + (uint32_t)(t & 1) * 128u + (uint32_t)wg * 64u;
+      if (!wait_warp(bar(B_SF + (t & 1)), (uint32_t)(t >> 1) & 1u)) { ok = false; break; }
       tc5::fence_after_sync();
       uint32_t r[2][32];
-      tc5::tmem_ld32(tlane + TM_S + (uint32_t)s * 64u, r[0]);
-      tc5::tmem_ld32(tlane + TM_S + (uint32_t)s * 64u + 32u, r[1]);
+      tc5::tmem_ld32(ts, r[0]);
+      tc5::tmem_ld32(ts + 32u, r[1]);
       tc5::tmem_ld_wait();
-      const int col0 = j * 64;
+      const int col0 = (2 * t + wg) * 64;
       const bool need_mask = (p.causal && col0 + 63 > q0) || (col0 + 64 > p.seqlen);
       float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
       if (need_mask) {
@@ -561,9 +554,9 @@ attn_fwd_tm_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
       if (__any_sync(0xffffffffu, grow_m)) {
         const float m_new = grow_m ? mx : m;
         const float corr = (m == -INFINITY) ? 0.0f : ex2(m - m_new);
-        if (k > 0) {
+        if (t > 0) {
           // every earlier product of this group must have landed in O before it is rescaled
-          if (!wait_warp(bar(B_OF + wg), (uint32_t)(k - 1) & 1u)) { ok = false; break; }
+          if (!wait_warp(bar(B_OF + wg), (uint32_t)(t - 1) & 1u)) { ok = false; break; }
           tc5::fence_after_sync();
 #pragma unroll 1
           for (int c = 0; c < 4; ++c) {
@@ -596,11 +589,11 @@ attn_fwd_tm_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
         pk[4 * g + 3] = pack_bf16(e[6], e[7]);
       }
       l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
-      tc5::tmem_st32(tlane + TM_S + (uint32_t)s * 64u, pk);
+      tc5::tmem_st32(ts, pk);
       tc5::tmem_st_wait();    // also covers the rescaled accumulator
       tc5::fence_before_sync();
       __syncwarp();
-      if (lane == 0) tc5::mbar_arrive(bar(B_PF + s));
+      if (lane == 0) tc5::mbar_arrive(bar(B_PF + (t & 1) * 2 + wg));
     }
     ok = ok && wait_warp(bar(B_ACC), 0u);
     tc5::fence_after_sync();
@@ -618,21 +611,17 @@ attn_fwd_tm_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
       const float lt = l0 * f0 + l1 * f1;
       const float inv = lt > 0.0f ? 1.0f / lt : 0.0f;
       const float g0 = f0 * inv, g1 = f1 * inv;
-      const bool two = n_kv > 1;    // with one key tile group 1 never wrote its accumulator
+      // both accumulators were written (a group whose keys are all masked accumulated zeros)
       __nv_bfloat16* dst = p.o + (int64_t)b * p.o_sb + (int64_t)grow * p.o_ss + (int64_t)h * p.o_sh + wg * 64;
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
         uint32_t a0[32], a1[32];
         float v[32];
         tc5::tmem_ld32(tlane + TM_O + (uint32_t)wg * 64u + (uint32_t)c * 32u, a0);
-        if (two) tc5::tmem_ld32(tlane + TM_O + 128u + (uint32_t)wg * 64u + (uint32_t)c * 32u, a1);
+        tc5::tmem_ld32(tlane + TM_O + 128u + (uint32_t)wg * 64u + (uint32_t)c * 32u, a1);
         tc5::tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(a0[i]) * g0;
-        if (two) {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = fmaf(__uint_as_float(a1[i]), g1, v[i]);
-        }
+        for (int i = 0; i < 32; ++i) v[i] = fmaf(__uint_as_float(a1[i]), g1, __uint_as_float(a0[i]) * g0);
         if (grow < p.seqlen) st_row32(dst + c * 32, v);
       }
       if (wg == 0 && grow < p.seqlen) p.lse[(int64_t)bh * p.seqlen + grow] = lt > 0.0f ? mm * kLn2 + logf(lt) : -INFINITY;
@@ -1275,17 +1264,18 @@ MSAMP_API int msamp_attention_tc_fwd(const void* q, const void* k, const void* v
   p.batch = batch; p.heads = heads; p.seqlen = seqlen; p.causal = causal; p.scale = scale;
   p.status = msamp_device_status_ptr();
   dim3 grid((seqlen + 127) / 128, batch * heads);
-  // MSAMP_ATTN_FWD_SMEM=1 selects the kernel that keeps Q and P in shared memory (the default keeps them in TMEM).
+  // MSAMP_ATTN_FWD_SMEM=1 selects the kernel with 64-key score tiles and P in shared memory (default: 128-key score
+  // tiles, P in tensor memory).
   static const bool smem_operands = [] { const char* e = getenv("MSAMP_ATTN_FWD_SMEM"); return e && e[0] == '1'; }();
   if (smem_operands) {
     if ((rc = set_smem(attn_fwd_tc_kernel, fwd::SMEM))) return rc;
     attn_fwd_tc_kernel<<<grid, kTcThreads, fwd::SMEM, (cudaStream_t)stream_>>>(mq, mk, mv, p);
     return msamp_check_launch("attn_fwd_tc_kernel");
   }
-  p.q = (const __nv_bfloat16*)q;
-  p.q_sb = strides[0]; p.q_ss = strides[1]; p.q_sh = strides[2];
+  CUtensorMap mk128;
+  if ((rc = make_map4(k, batch, heads, seqlen, strides[3], strides[4], strides[5], 128, &mk128))) return rc;
   if ((rc = set_smem(attn_fwd_tm_kernel, fwd2::SMEM))) return rc;
-  attn_fwd_tm_kernel<<<grid, kTcThreads, fwd2::SMEM, (cudaStream_t)stream_>>>(mk, mv, p);
+  attn_fwd_tm_kernel<<<grid, kTcThreads, fwd2::SMEM, (cudaStream_t)stream_>>>(mq, mk128, mv, p);
   return msamp_check_launch("attn_fwd_tm_kernel");
 }
 

@@ -5,6 +5,7 @@ handles travel through ``torch.distributed`` object collectives.  Kernels receiv
 pointers and address peers directly over NVLink.
 """
 import ctypes
+import os
 
 import torch
 import torch.distributed as dist
@@ -12,6 +13,8 @@ import torch.distributed as dist
 from msamp.common.utils.dist import DistUtil
 from msamp.ops import native
 
+_SKEW_US = float(os.getenv('MSAMP_DEBUG_SKEW_US', '0') or 0)
+_SKEW_REVERSE = os.getenv('MSAMP_DEBUG_SKEW_ORDER', '') == 'reverse'
 _TYPESTR = {torch.uint8: '|u1', torch.float32: '<f4', torch.float16: '<f2', torch.int32: '<i4', torch.int64: '<i8'}
 
 
@@ -22,8 +25,21 @@ class _Exposed:
         self._owner = owner
 
 
+class GuardCorruption(RuntimeError):
+    """A guard region next to a symmetric buffer no longer holds its pattern: some kernel (local or a peer's) wrote
+    outside the buffer."""
+
+
 class SymmetricBuffer:
-    """``nbytes`` of zero-initialised device memory on every rank of ``group``, with peer pointers."""
+    """``nbytes`` of zero-initialised device memory on every rank of ``group``, with peer pointers.
+
+    The allocation is ``GUARD`` bytes larger on either side; the two guard regions are filled with ``GUARD_BYTE`` and
+    never handed to a kernel.  ``check_guards()`` (also run by ``close()``) copies them to the host and raises
+    ``GuardCorruption`` when a byte changed, which is how an out-of-range peer store shows up without a memory checker.
+    """
+    GUARD = 4096
+    GUARD_BYTE = 0xA5
+
     def __init__(self, nbytes, group=None):
         self.group = group
         self.world = DistUtil.get_world_size(group)
@@ -32,8 +48,13 @@ class SymmetricBuffer:
         lib = native.lib()
         ptr = ctypes.c_void_p()
         handle = ctypes.create_string_buffer(64)
-        native.check(lib.msamp_symm_alloc(ctypes.c_size_t(self.nbytes), ctypes.byref(ptr), handle), 'symm_alloc')
-        self.local_ptr = ptr.value
+        native.check(lib.msamp_symm_alloc(ctypes.c_size_t(self.nbytes + 2 * self.GUARD), ctypes.byref(ptr), handle), 'symm_alloc')
+        self._base_ptr = ptr.value
+        self.local_ptr = self._base_ptr + self.GUARD
+        self._device = torch.device('cuda', torch.cuda.current_device())
+        for g in self._guard_views():
+            g.fill_(self.GUARD_BYTE)
+        torch.cuda.current_stream().synchronize()    # peers may map and write the buffer right after the handle exchange
         self.ptrs = [None] * self.world
         self.ptrs[self.rank] = self.local_ptr
         self._opened = []
@@ -45,11 +66,25 @@ class SymmetricBuffer:
                     continue
                 peer = ctypes.c_void_p()
                 native.check(lib.msamp_symm_open(ctypes.c_char_p(h), ctypes.byref(peer)), f'symm_open(rank {r})')
-                self.ptrs[r] = peer.value
+                self.ptrs[r] = peer.value + self.GUARD
                 self._opened.append(peer.value)
             dist.barrier(group=group)
         self.table = (ctypes.c_void_p * self.world)(*self.ptrs)
-        self._device = torch.device('cuda', torch.cuda.current_device())
+
+    def _guard_views(self):
+        return [torch.as_tensor(_Exposed(self._base_ptr, self.GUARD, torch.uint8, self), device=self._device),
+                torch.as_tensor(_Exposed(self.local_ptr + self.nbytes, self.GUARD, torch.uint8, self), device=self._device)]
+
+    def check_guards(self):
+        """Raise ``GuardCorruption`` if a byte of either guard region changed (synchronises the current stream)."""
+        if not self.local_ptr:
+            return
+        for name, g in zip(('before', 'after'), self._guard_views()):
+            bad = (g != self.GUARD_BYTE).nonzero()
+            if bad.numel():
+                first = int(bad[0])
+                raise GuardCorruption(f'rank {self.rank}: {bad.numel()} byte(s) of the guard {name} a {self.nbytes}-byte symmetric buffer '
+                                      f'were overwritten (first at guard offset {first})')
 
     def view(self, dtype, byte_offset=0, numel=None):
         """Tensor aliasing this rank's copy of the buffer."""
@@ -67,8 +102,12 @@ class SymmetricBuffer:
             lib.msamp_symm_close(ctypes.c_void_p(p))
         self._opened = []
         if self.local_ptr:
-            lib.msamp_symm_free(ctypes.c_void_p(self.local_ptr))
-            self.local_ptr = 0
+            try:
+                self.check_guards()
+            finally:
+                lib.msamp_symm_free(ctypes.c_void_p(self._base_ptr))
+                self.local_ptr = 0
+                self._base_ptr = 0
 
 
 class FlagPad(SymmetricBuffer):
@@ -78,6 +117,16 @@ class FlagPad(SymmetricBuffer):
         self.epoch = 0
 
     def next_epoch(self):
+        """Advance the epoch; every cross-rank launch calls this right before it is enqueued.
+
+        Debug schedules: with ``MSAMP_DEBUG_SKEW_US=<n>`` rank ``r`` first enqueues an idle spin of ``n * r`` microseconds
+        (``MSAMP_DEBUG_SKEW_ORDER=reverse``: ``n * (world - 1 - r)``) on the launching stream, so the ranks reach every
+        in-kernel flag exchange in a fixed, skewed order.  Two opposite orders shake out protocols that only work when
+        the ranks happen to arrive together."""
+        if _SKEW_US:
+            k = (self.world - 1 - self.rank) if _SKEW_REVERSE else self.rank
+            if k:
+                torch.cuda._sleep(int(_SKEW_US * k * 1500))    # cycles; about a microsecond per 1500 at the clocks seen under load
         self.epoch += 1
         return self.epoch
 

@@ -38,7 +38,17 @@ def _symm_and_barrier(rank, world):
     assert native.device_status() & 2
     assert mine.sum().item() == (rank + 1) * mine.numel()
     dist.barrier()
+    # guard regions on either side of the buffer: intact after the writes above, and a changed byte is reported
+    from msamp.parallel.symm import GuardCorruption
+    buf.check_guards()
+    flags.check_guards()
+    after = buf._guard_views()[1]
+    after[7] = 0    # host-injected: what an out-of-range store of a kernel would leave behind
+    with pytest.raises(GuardCorruption):
+        buf.check_guards()
+    after[7] = buf.GUARD_BYTE
     buf.close()
+    flags.close()
 
 
 @WORLDS
@@ -190,6 +200,7 @@ def _fused_reduce_matches_math(rank, world):
     ref = flat.clone()
     dist.broadcast(ref, src=0)
     assert torch.equal(flat, ref)
+    zero.close()    # also checks the guard regions around the symmetric buffers
 
 
 @WORLDS
@@ -396,8 +407,30 @@ def test_fused_gemm_copy_cta_extremes(n_comm):
     run_workers(_fused_gemms, 2, backend='nccl', args=(n_comm, ((128, 256, 128), (512, 1024, 1000))))
 
 
+def _skewed(rank, world):
+    from msamp.parallel import symm
+    assert symm._SKEW_US == 300.0
+    _fused_reduce_matches_math(rank, world)
+    _fused_gemms(rank, world, 4, ((128, 256, 128), (512, 1024, 1000)))
+    _fused_adam_equals_reduce_then_adam(rank, world)
+
+
+@pytest.mark.parametrize('order', ['forward', 'reverse'])
+def test_rank_skewed_schedules(order, monkeypatch):
+    """The cross-rank kernels under two deterministic, opposite arrival orders (rank r enters every cross-rank launch
+    300 us x r late, or 300 us x (world - 1 - r) late)."""
+    world = 4 if torch.cuda.is_available() and torch.cuda.device_count() >= 4 else 2
+    _need(world)
+    monkeypatch.setenv('MSAMP_DEBUG_SKEW_US', '300')
+    monkeypatch.setenv('MSAMP_DEBUG_SKEW_ORDER', order)
+    run_workers(_skewed, world, backend='nccl')
+
+
 def _sp_block_fused(rank, world):
-    from msamp.megatron import ColumnParallelLinear, RowParallelLinear, parallel_state as mpu
+    """A sequence-parallel MLP block (column-parallel, GeLU, row-parallel) on the fused gather-GEMM / GEMM-reduce-scatter
+    kernels against (a) the SAME FP8 computation composed of NCCL collectives and the plain GEMM, which it must match
+    within the rounding of the bf16 partial sums, and (b) fp32 math, loosely (FP8 quantisation error)."""
+    from msamp.megatron import ColumnParallelLinear, RowParallelLinear, layers, parallel_state as mpu
     from msamp.ops import native
     mpu.initialize_model_parallel(tensor_model_parallel_size=world)
     dev = torch.device('cuda', rank)
@@ -407,29 +440,51 @@ def _sp_block_fused(rank, world):
     full_w2 = (torch.randn(H, F, device=dev) * 0.05)
     x_full = torch.randn(S, B, H, device=dev)
     g_full = torch.randn(S, B, H, device=dev)
-    col = ColumnParallelLinear(H, F, bias=True, sequence_parallel=True, device=dev)
-    row = RowParallelLinear(F, H, bias=True, sequence_parallel=True, device=dev)
     fs = F // world
-    with torch.no_grad():
-        col.weight.copy_(full_w1[rank * fs:(rank + 1) * fs].cast(col.weight.qtype))
-        row.weight.copy_(full_w2[:, rank * fs:(rank + 1) * fs].contiguous().cast(row.weight.qtype))
     sl = slice(rank * (S // world), (rank + 1) * (S // world))
-    x = x_full[sl].bfloat16().clone().requires_grad_()
-    y = row(torch.nn.functional.gelu(col(x)))
-    ctx = mpu.get_fused_context()
-    assert ctx.native
-    y.backward(g_full[sl].bfloat16())
-    torch.cuda.synchronize()
-    assert native.device_status() == 0
+
+    def run(fused):
+        layers.USE_FUSED_COLLECTIVES = fused
+        torch.manual_seed(1)
+        col = ColumnParallelLinear(H, F, bias=True, sequence_parallel=True, device=dev)
+        row = RowParallelLinear(F, H, bias=True, sequence_parallel=True, device=dev)
+        with torch.no_grad():
+            col.weight.copy_(full_w1[rank * fs:(rank + 1) * fs].cast(col.weight.qtype))
+            row.weight.copy_(full_w2[:, rank * fs:(rank + 1) * fs].contiguous().cast(row.weight.qtype))
+        x = x_full[sl].bfloat16().clone().requires_grad_()
+        y = row(torch.nn.functional.gelu(col(x)))
+        if fused:
+            assert mpu.get_fused_context().native
+        y.backward(g_full[sl].bfloat16())
+        torch.cuda.synchronize()
+        assert native.device_status() == 0
+        return y.detach().float(), x.grad.float(), col.weight.grad.float(), row.weight.grad.float()
+
+    try:
+        fused = run(True)
+        plain = run(False)
+    finally:
+        layers.USE_FUSED_COLLECTIVES = True
+    # (a) same FP8 operands, same products: only the order / precision of the cross-rank sums differs (fp32 in the fused
+    # epilogue, bf16 in NCCL), and a weight gradient may land on the other side of one e4m3 rounding boundary
+    names = ('y', 'dx', 'wgrad_col', 'wgrad_row')
+    tols = (0.02, 0.02, 0.07, 0.07)
+    for name, a, b, tol in zip(names, fused, plain, tols):
+        scale = b.abs().max().item()
+        assert (a - b).abs().max().item() <= tol * scale + 1e-6, (name, (a - b).abs().max().item(), scale)
+        if name.startswith('wgrad'):
+            assert (a != b).float().mean().item() < 0.02, (name, (a != b).float().mean().item())
+    # (b) fp32 math
+    y, dx, wg1, wg2 = fused
     w1 = full_w1.clone().requires_grad_()
     w2 = full_w2.clone().requires_grad_()
     ref_x = x_full.clone().requires_grad_()
     ref = torch.nn.functional.gelu(ref_x @ w1.t()) @ w2.t()
     ref.backward(g_full)
-    assert (y.float() - ref[sl]).abs().max().item() < 0.1 * ref.abs().max().item() + 0.02    # two chained FP8 GEMMs
-    assert (x.grad.float() - ref_x.grad[sl]).abs().max().item() < 0.25 * ref_x.grad.abs().max().item()
-    assert (col.weight.grad.float() - w1.grad[rank * fs:(rank + 1) * fs]).abs().max().item() < 0.15 * w1.grad.abs().max().item()
-    assert (row.weight.grad.float() - w2.grad[:, rank * fs:(rank + 1) * fs]).abs().max().item() < 0.15 * w2.grad.abs().max().item()
+    assert (y - ref[sl]).abs().max().item() < 0.1 * ref.abs().max().item() + 0.02    # two chained FP8 GEMMs
+    assert (dx - ref_x.grad[sl]).abs().max().item() < 0.25 * ref_x.grad.abs().max().item()
+    assert (wg1 - w1.grad[rank * fs:(rank + 1) * fs]).abs().max().item() < 0.15 * w1.grad.abs().max().item()
+    assert (wg2 - w2.grad[:, rank * fs:(rank + 1) * fs]).abs().max().item() < 0.15 * w2.grad.abs().max().item()
     mpu.destroy_model_parallel()
 
 
