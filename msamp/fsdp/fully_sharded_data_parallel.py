@@ -288,6 +288,13 @@ class FP8FullyShardedDataParallel(torch.nn.Module):
     def close(self):
         """Release the symmetric buffers of the fused kernels (collective over the group, after the last step)."""
         if self.ctx is not None:
+            if self.ctx.native:
+                torch.cuda.synchronize()
+                for m in self.sharded:    # resident shards alias the symmetric buffer: keep the values in ordinary memory
+                    if getattr(m, 'resident', False):
+                        m.weight_shard, m.weight_shard_t = m.weight_shard.clone(), m.weight_shard_t.clone()
+                        m.resident = False
+                torch.cuda.synchronize()
             self.ctx.close()
             self.ctx = None
 

@@ -9,13 +9,26 @@ import torch.distributed as dist
 _STATE = {'tp': None, 'dp': None, 'pp': None, 'mp': None, 'tp_size': 1, 'dp_size': 1, 'pp_size': 1, 'fused': None, 'init': False}
 
 
+_CORE = [None, False]    # [megatron.core.parallel_state or None, import attempted]
+
+
 def _core():
-    try:
-        from megatron.core import parallel_state as ps    # type: ignore
-        if ps.model_parallel_is_initialized():
-            return ps
-    except Exception:
-        pass
+    """Megatron-LM's own parallel state when it is importable and initialised.  The import is attempted once: a failed
+    import walks ``sys.path`` every time, and this function sits on the path of every tensor-parallel linear."""
+    if not _CORE[1]:
+        _CORE[1] = True
+        try:
+            from megatron.core import parallel_state as ps    # type: ignore
+            _CORE[0] = ps
+        except Exception:
+            _CORE[0] = None
+    ps = _CORE[0]
+    if ps is not None:
+        try:
+            if ps.model_parallel_is_initialized():
+                return ps
+        except Exception:
+            pass
     return None
 
 

@@ -183,6 +183,22 @@ class _ScalingTensorReducer:
     def close(self):
         """Release the symmetric buffers of the fused path (collective over the group)."""
         if self.fused:
+            torch.cuda.synchronize()
+            # the wgrad metas' scale_inv / amax and model_state's flat wgrad tables alias the symmetric meta rows: move them
+            # into ordinary memory first (values kept), or the next re-flattening of the registry would read freed memory
+            for p in self.parameters:
+                meta = p._scaling_metas['wgrad'] if hasattr(p, '_scaling_metas') else None
+                if meta is not None:
+                    was_locked, meta.locked = meta.locked, False
+                    meta.scale_inv, meta.amax = meta.scale_inv.clone(), meta.amax.clone()
+                    meta.locked = was_locked
+                if isinstance(p.grad, ScalingTensor):
+                    p.grad = None
+            flat = model_state.flattened_scaling_metas
+            if flat is not None and flat.get('wgrad', {}).get('_external'):
+                model_state.reflatten()
+            self.g_meta_t = None
+            torch.cuda.synchronize()
             dist.barrier(group=self.process_group)
             for buf in (self.g_buf, self.g_meta, self.flags):
                 buf.close()

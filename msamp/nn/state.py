@@ -134,14 +134,19 @@ class ModelState:
                 key = f'{name}_{i}'
                 i += 1
             self._local_scaling_metas[key] = metas
-        all_metas = list(self._local_scaling_metas.values())
-        if not all_metas:
-            return
-        self._flattened_scaling_metas = {k: self._flatten_scaling_metas([m[k] for m in all_metas]) for k in all_metas[0].keys()}
+        all_metas = self.reflatten()
         for metas in all_metas:
             for m in metas.values():
                 m.group = group
             self.check_metas_in_flat(metas)
+
+    def reflatten(self):
+        """Rebuild the flat buffers from the current tensors of every registered meta (values kept).  Also the way back
+        for metas whose tensors were moved elsewhere (e.g. into symmetric memory that is about to be freed)."""
+        all_metas = list(self._local_scaling_metas.values())
+        if all_metas:
+            self._flattened_scaling_metas = {k: self._flatten_scaling_metas([m[k] for m in all_metas]) for k in all_metas[0].keys()}
+        return all_metas
 
 
 model_state = ModelState()

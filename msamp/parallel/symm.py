@@ -97,17 +97,31 @@ class SymmetricBuffer:
         return torch.as_tensor(_Exposed(self.local_ptr + byte_offset, numel, dtype, self), device=self._device)
 
     def close(self):
+        """Unmap the peers' copies and free this rank's.  Collective over the group: every rank calls it, after the last
+        kernel that may touch any rank's copy has completed (callers put a barrier before it).
+
+        Freeing exported memory while a peer still has it mapped is undefined behaviour in CUDA IPC (a later allocation
+        that reuses the range can lose its backing when the peer unmaps), so the ranks meet once more between "every rank
+        has closed its mappings" and "every rank frees its own allocation".  A guard violation is raised only after the
+        memory is released, so a rank that found one does not leave the others waiting in that barrier."""
         lib = native.lib()
+        err = None
+        if self.local_ptr:
+            try:
+                self.check_guards()
+            except GuardCorruption as e:
+                err = e
         for p in self._opened:
             lib.msamp_symm_close(ctypes.c_void_p(p))
         self._opened = []
         if self.local_ptr:
-            try:
-                self.check_guards()
-            finally:
-                lib.msamp_symm_free(ctypes.c_void_p(self._base_ptr))
-                self.local_ptr = 0
-                self._base_ptr = 0
+            if self.world > 1 and dist.is_available() and dist.is_initialized():
+                dist.barrier(group=self.group)
+            lib.msamp_symm_free(ctypes.c_void_p(self._base_ptr))
+            self.local_ptr = 0
+            self._base_ptr = 0
+        if err is not None:
+            raise err
 
 
 class FlagPad(SymmetricBuffer):

@@ -533,8 +533,38 @@ class ZeroShardedOptimizer:
         if self.sharded:
             self._publish_weights()
 
+    def _rehome(self):
+        """Move everything that aliases the symmetric buffers (the FP8 weights and their scale_inv / amax, the wgrad metas'
+        scale_inv / amax, the gradient views, model_state's flat wgrad tables) into ordinary device memory, values kept.
+        Without this the model, and the process-wide meta registry that is re-flattened whenever another model registers,
+        would keep reading memory that ``close()`` is about to free."""
+        for p in self.fp8_params:
+            metas = getattr(p, '_scaling_metas', None) or {}
+            meta = metas.get('wgrad')
+            if meta is not None:
+                was_locked, meta.locked = meta.locked, False
+                meta.scale_inv, meta.amax = meta.scale_inv.clone(), meta.amax.clone()
+                meta.locked = was_locked
+            p._grad_out = None
+            if p.grad is not None:
+                p.grad = None
+            if self.sharded and getattr(self, 'w_buf', None) is not None:
+                p.value = p.value.clone()
+                p.meta.scale_inv, p.meta.amax = p.meta.scale_inv.clone(), p.meta.amax.clone()
+                p._fp8_cache = None
+        self._fused_grads = {}
+        flat = model_state.flattened_scaling_metas
+        if flat is not None and flat.get('wgrad', {}).get('_external'):
+            model_state.reflatten()
+        self.g_flat = self.g_meta_t = self.w_flat = self.w_meta_t = None
+
     def close(self):
-        """Release the symmetric (IPC-shared) buffers.  Collective: every rank of the group calls it, after its last step."""
+        """Release the symmetric (IPC-shared) buffers.  Collective: every rank of the group calls it, after its last step.
+        The model keeps its FP8 weights (copied to ordinary memory); the optimizer can no longer step."""
+        if self.native and getattr(self, 'g_buf', None) is not None:
+            torch.cuda.synchronize(self.device)
+            self._rehome()
+            torch.cuda.synchronize(self.device)
         for name in ('g_buf', 'g_meta', 'w_buf', 'w_meta', 'flags'):
             buf = getattr(self, name, None)
             if buf is not None and hasattr(buf, 'close'):
