@@ -1,6 +1,8 @@
 """Multi-GPU tests: symmetric memory, fused FP8 reduce, sharded optimizer, fused GEMM + collective kernels.
 
 Every test runs on 2, 4 and 8 ranks (one process per GPU) and is skipped when fewer GPUs are visible."""
+import os
+
 import pytest
 import torch
 import torch.distributed as dist
@@ -11,7 +13,8 @@ from tests.dist_utils import run_workers
 
 pytestmark = pytest.mark.gpu
 E4M3 = Dtypes.kfloat8_e4m3
-WORLDS = pytest.mark.parametrize('world', [2, 4, 8])
+# MSAMP_TEST_WORLDS narrows the rank counts (a box with eight GPUs is expensive: see test_all_scenarios_in_one_group)
+WORLDS = pytest.mark.parametrize('world', [int(w) for w in os.getenv('MSAMP_TEST_WORLDS', '2,4,8').split(',') if w])
 
 
 def _need(n):
@@ -539,3 +542,26 @@ def _full_shard_fused(rank, world):
 def test_full_shard_fused(world):
     _need(world)
     run_workers(_full_shard_fused, world, backend='nccl')
+
+
+def _all_scenarios(rank, world):
+    """Every multi-rank scenario of this file in ONE process group, one after the other (each frees its symmetric buffers
+    before the next allocates its own)."""
+    from msamp.nn import model_state
+    scenarios = [_symm_and_barrier, _timeout_then_normal_reduce, _fp8_ddp_fused, _fused_reduce_matches_math, _zero2_training,
+                 lambda r, w: _zero2_training(r, w, True, True), _fused_adam_equals_reduce_then_adam, _fused_gemms, _sp_block_fused,
+                 _full_shard_fused]
+    for fn in scenarios:
+        fn(rank, world)
+        torch.cuda.synchronize()
+        dist.barrier()
+        model_state.clear()
+
+
+@pytest.mark.parametrize('world', [int(w) for w in os.getenv('MSAMP_TEST_COMBINED_WORLDS', '4,8').split(',') if w])
+def test_all_scenarios_in_one_group(world):
+    """The per-scenario tests above spawn a process group each; at four and eight ranks this test runs them all in one
+    group, which costs a fraction of the GPU time and additionally covers allocate / free / re-allocate of the symmetric
+    buffers in one process."""
+    _need(world)
+    run_workers(_all_scenarios, world, backend='nccl')
