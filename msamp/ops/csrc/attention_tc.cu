@@ -1156,6 +1156,517 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
   if (warp == 1) tc5::tmem_dealloc(tmem_base, TM_COLS);
 }
 
+// ========================================================================= dK / dV, 128-query tiles, dS^T in tensor memory
+namespace dkv2 {
+constexpr uint32_t PANEL = 128 * 128;      // [128 rows][64 bf16]
+constexpr uint32_t TILE = 2 * PANEL;       // 32 KB: 128 rows x 128 bf16
+constexpr int NSQ = 2;                     // Q / dO stages (a stage is read by the first and by the last MMA of its tile)
+constexpr uint32_t OFF_K = 0, OFF_V = TILE, OFF_Q = 2 * TILE, OFF_DO = OFF_Q + NSQ * TILE, OFF_PT = OFF_DO + NSQ * TILE,
+                   OFF_LSE = OFF_PT + TILE, OFF_BAR = OFF_LSE + NSQ * 2 * 128 * 4;
+enum { B_KV = 0, B_QF = 1, B_QE = B_QF + NSQ, B_SF = B_QE + NSQ, B_SE = B_SF + 1, B_DF = B_SE + 1, B_PF = B_DF + 1, B_PE = B_PF + 1,
+       B_ACC = B_PE + 1, NBAR = B_ACC + 1 };
+// seven 32 KB tiles leave 3 KB of the 227 KB: the dynamic array is declared 128-byte aligned, so rounding its start up to
+// 1024 bytes costs at most 896
+constexpr int SMEM = OFF_BAR + NBAR * 8 + 16 + 896;
+static_assert(SMEM <= 227 * 1024, "dK/dV kernel: shared memory");
+constexpr uint32_t TM_ST = 0, TM_DPT = 128, TM_DV = 256, TM_DK = 384, TM_COLS = 512;
+}    // namespace dkv2
+
+// dK and dV for 128 key rows; query tiles of 128, so that S^T = K Q^T and dP^T = V dO^T are N = 128 products (an M = 128
+// bf16 MMA costs the same for N = 64).  Tensor memory holds exactly S^T, dP^T, dV and dK (4 x 128 columns).  The eight
+// softmax warps split a tile by columns (group g: queries 64 g .. 64 g + 63).  S^T is read into registers and released
+// at once, so the scores of the next tile are computed during the arithmetic of this one; P^T goes to shared memory (A
+// operand of dV += P^T dO); dS^T is packed to bf16 and stored over the dP^T columns it came from (A operand of
+// dK += dS^T Q, read from tensor memory).  dP^T of the next tile is issued after dK of this one (in-order tensor pipe).
+__global__ void __launch_bounds__(kTcThreads, 1)
+attn_bwd_dkdv_tm_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                        const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do, const TcParams p) {
+  using namespace dkv2;
+  extern __shared__ __align__(128) uint8_t smem_raw128[];
+  const uint32_t raw_addr = tc5::smem_u32(smem_raw128);
+  const uint32_t base = (raw_addr + 1023u) & ~1023u;
+  uint8_t* smem = smem_raw128 + (base - raw_addr);
+  const uint32_t bars = base + OFF_BAR;
+  auto bar = [&](int i) { return bars + 8u * (uint32_t)i; };
+  float* s_lse = reinterpret_cast<float*>(smem + OFF_LSE);    // [NSQ][128] log2-scaled lse, then [NSQ][128] delta
+  float* s_delta = s_lse + NSQ * 128;
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(smem + OFF_BAR + NBAR * 8);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+  auto wait_warp = [&](uint32_t br, uint32_t ph) {
+    return __all_sync(0xffffffffu, tc5::mbar_wait(br, ph, abort_flag, p.status, kStatusBit)) != 0;
+  };
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int kt = blockIdx.x;    // key tile 0 has the most query tiles under a causal mask and starts first
+  const int bh = blockIdx.y;
+  const int b = bh / p.heads;
+  const int h = bh - b * p.heads;
+  const int k0 = kt * 128;
+  const int nq_all = (p.seqlen + 127) / 128;
+  const int t_first = p.causal ? kt : 0;
+  const int n_q = nq_all - t_first;    // >= 1 because k0 < seqlen
+
+  if (threadIdx.x == 0) {
+    tc5::mbar_init(bar(B_KV), 1);
+    for (int s = 0; s < NSQ; ++s) {
+      tc5::mbar_init(bar(B_QF + s), 2);    // TMA bytes + the lse/delta rows written by warp 0
+      tc5::mbar_init(bar(B_QE + s), 9);    // last MMA that reads the stage + eight softmax warps
+    }
+    tc5::mbar_init(bar(B_SF), 1);
+    tc5::mbar_init(bar(B_SE), 8);
+    tc5::mbar_init(bar(B_DF), 1);
+    tc5::mbar_init(bar(B_PF), 8);
+    tc5::mbar_init(bar(B_PE), 1);
+    tc5::mbar_init(bar(B_ACC), 1);
+    *abort_flag = 0;
+    tc5::mbar_fence_init();
+    tc5::tma_prefetch_desc(&map_q);
+    tc5::tma_prefetch_desc(&map_k);
+    tc5::tma_prefetch_desc(&map_v);
+    tc5::tma_prefetch_desc(&map_do);
+  }
+  if (warp == 1) {
+    tc5::tmem_alloc(tc5::smem_u32(tmem_holder), TM_COLS);
+    tc5::tmem_relinquish();
+  }
+  tc5::fence_before_sync();
+  __syncthreads();
+  tc5::fence_after_sync();
+  const uint32_t tmem_base = *tmem_holder;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ producer (whole warp: lane 0 issues TMA)
+    if (lane == 0) {
+      tc5::mbar_arrive_expect_tx(bar(B_KV), 2 * TILE);
+      tc5::tma_load_4d(base + OFF_K, &map_k, 0, h, k0, b, bar(B_KV));
+      tc5::tma_load_4d(base + OFF_K + PANEL, &map_k, 64, h, k0, b, bar(B_KV));
+      tc5::tma_load_4d(base + OFF_V, &map_v, 0, h, k0, b, bar(B_KV));
+      tc5::tma_load_4d(base + OFF_V + PANEL, &map_v, 64, h, k0, b, bar(B_KV));
+    }
+    const float* glse = p.lse + (int64_t)bh * p.seqlen;
+    const float* gdelta = p.delta + (int64_t)bh * p.seqlen;
+    for (int t = 0; t < n_q; ++t) {
+      const int s = t % NSQ;
+      const uint32_t ph = (uint32_t)(t / NSQ) & 1u;
+      const int qrow0 = (t_first + t) * 128;
+      TC_WAIT(bar(B_QE + s), ph ^ 1u);
+      if (lane == 0) {
+        tc5::mbar_arrive_expect_tx(bar(B_QF + s), 2 * TILE);
+        tc5::tma_load_4d(base + OFF_Q + s * TILE, &map_q, 0, h, qrow0, b, bar(B_QF + s));
+        tc5::tma_load_4d(base + OFF_Q + s * TILE + PANEL, &map_q, 64, h, qrow0, b, bar(B_QF + s));
+        tc5::tma_load_4d(base + OFF_DO + s * TILE, &map_do, 0, h, qrow0, b, bar(B_QF + s));
+        tc5::tma_load_4d(base + OFF_DO + s * TILE + PANEL, &map_do, 64, h, qrow0, b, bar(B_QF + s));
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int r = lane + 32 * i;
+        const bool in = qrow0 + r < p.seqlen;
+        s_lse[s * 128 + r] = in ? glse[qrow0 + r] * kLog2e : INFINITY;    // +inf makes the probability exactly zero
+        s_delta[s * 128 + r] = in ? gdelta[qrow0 + r] : 0.0f;
+      }
+      __syncwarp();
+      if (lane == 0) tc5::mbar_arrive(bar(B_QF + s));
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc_s = tc5::idesc_bf16(128, 128, 0, 0);
+      const uint32_t idesc_acc = tc5::idesc_bf16(128, 128, 0, 1);
+      auto issue_st = [&](int t) -> bool {    // S^T = K Q_t^T
+        const int st = t % NSQ;
+        if (t > 0 && !tc5::mbar_wait(bar(B_SE), (uint32_t)(t - 1) & 1u, abort_flag, p.status, kStatusBit)) return false;
+        if (!tc5::mbar_wait(bar(B_QF + st), (uint32_t)(t / NSQ) & 1u, abort_flag, p.status, kStatusBit)) return false;
+        tc5::fence_after_sync();
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint32_t off = (uint32_t)(kk >> 2) * PANEL + (uint32_t)(kk & 3) * 32u;
+          tc5::mma_f16(tmem_base + TM_ST, tc5::smem_desc_k_sw128(base + OFF_K + off), tc5::smem_desc_k_sw128(base + OFF_Q + st * TILE + off),
+                       idesc_s, kk ? 1u : 0u);
+        }
+        tc5::mma_commit(bar(B_SF));
+        return true;
+      };
+      auto issue_dpt = [&](int t) {    // dP^T = V dO_t^T (the stage was waited for by issue_st(t))
+        const int st = t % NSQ;
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint32_t off = (uint32_t)(kk >> 2) * PANEL + (uint32_t)(kk & 3) * 32u;
+          tc5::mma_f16(tmem_base + TM_DPT, tc5::smem_desc_k_sw128(base + OFF_V + off), tc5::smem_desc_k_sw128(base + OFF_DO + st * TILE + off),
+                       idesc_s, kk ? 1u : 0u);
+        }
+        tc5::mma_commit(bar(B_DF));
+      };
+      do {
+        TC_WAIT(bar(B_KV), 0u);
+        if (!issue_st(0)) break;
+        issue_dpt(0);
+        bool ok = true;
+        for (int t = 0; t < n_q; ++t) {
+          const int st = t % NSQ;
+          // the scores of the next tile go first when their operands are already there (the usual case); otherwise they
+          // follow dK of this tile, so that a late Q / dO stage does not hold up the products that are ready
+          bool pending = t + 1 < n_q;
+          if (pending && tc5::mbar_test(bar(B_SE), (uint32_t)t & 1u) &&
+              tc5::mbar_test(bar(B_QF + (t + 1) % NSQ), (uint32_t)((t + 1) / NSQ) & 1u)) {
+            if (!issue_st(t + 1)) { ok = false; break; }
+            pending = false;
+          }
+          if (!tc5::mbar_wait(bar(B_PF), (uint32_t)t & 1u, abort_flag, p.status, kStatusBit)) { ok = false; break; }
+          tc5::fence_after_sync();
+          // dV += P^T dO_t : A = P^T from shared memory (K-major over the 128 queries), B = dO read MN-major
+#pragma unroll
+          for (int kk = 0; kk < 8; ++kk) {
+            tc5::mma_f16(tmem_base + TM_DV, tc5::smem_desc_k_sw128(base + OFF_PT + (uint32_t)(kk >> 2) * PANEL + (uint32_t)(kk & 3) * 32u),
+                         tc5::smem_desc_mn_sw128(base + OFF_DO + st * TILE + (uint32_t)kk * 2048u, PANEL), idesc_acc, (t | kk) ? 1u : 0u);
+          }
+          tc5::mma_commit(bar(B_PE));
+          // dK += dS^T Q_t : A = dS^T from tensor memory (group g: 32 packed columns at the start of its half), B = Q MN-major
+#pragma unroll
+          for (int kk = 0; kk < 8; ++kk) {
+            tc5::mma_f16_ta(tmem_base + TM_DK, tmem_base + TM_DPT + (uint32_t)(kk >> 2) * 64u + (uint32_t)(kk & 3) * 8u,
+                            tc5::smem_desc_mn_sw128(base + OFF_Q + st * TILE + (uint32_t)kk * 2048u, PANEL), idesc_acc, (t | kk) ? 1u : 0u);
+          }
+          tc5::mma_commit(bar(B_QE + st));
+          if (pending && !issue_st(t + 1)) { ok = false; break; }
+          if (t + 1 < n_q) issue_dpt(t + 1);
+        }
+        if (ok) tc5::mma_commit(bar(B_ACC));
+      } while (false);
+    }
+  } else {
+    // ------------------------------------------------------------------ one thread per key row and query half
+    const int qd = warp & 3;
+    const int wg = (warp - 2) >> 2;    // group g: queries 64 g .. 64 g + 63 of every tile
+    const int row = qd * 32 + lane;
+    const int grow = k0 + row;
+    const uint32_t tlane = tmem_base + ((uint32_t)(qd * 32) << 16);
+    const float sl = p.scale * kLog2e;
+    const uint32_t prow = base + OFF_PT + (uint32_t)wg * PANEL + (uint32_t)row * 128u;
+    const uint32_t swz = (uint32_t)(row & 7);
+    bool ok = true;
+    for (int t = 0; t < n_q; ++t) {
+      const int st = t % NSQ;
+      const int qrow0 = (t_first + t) * 128 + wg * 64;    // first query of this group's half
+      if (!wait_warp(bar(B_QF + st), (uint32_t)(t / NSQ) & 1u)) { ok = false; break; }
+      if (!wait_warp(bar(B_SF), (uint32_t)t & 1u)) { ok = false; break; }
+      tc5::fence_after_sync();
+      const bool need_mask = p.causal && (qrow0 < k0 + 128);
+      const float4* lse2 = reinterpret_cast<const float4*>(s_lse + st * 128 + wg * 64);
+      const float4* dlt = reinterpret_cast<const float4*>(s_delta + st * 128 + wg * 64);
+      uint32_t rs[2][32], rd[2][32];
+      tc5::tmem_ld32(tlane + TM_ST + (uint32_t)wg * 64u, rs[0]);
+      tc5::tmem_ld32(tlane + TM_ST + (uint32_t)wg * 64u + 32u, rs[1]);
+      tc5::tmem_ld_wait();
+      tc5::fence_before_sync();
+      __syncwarp();
+      if (lane == 0) tc5::mbar_arrive(bar(B_SE));    // the score tile may take tile t + 1
+      if (!wait_warp(bar(B_DF), (uint32_t)t & 1u)) { ok = false; break; }
+      tc5::fence_after_sync();
+      tc5::tmem_ld32(tlane + TM_DPT + (uint32_t)wg * 64u, rd[0]);
+      tc5::tmem_ld32(tlane + TM_DPT + (uint32_t)wg * 64u + 32u, rd[1]);
+      tc5::tmem_ld_wait();
+      if (t > 0 && !wait_warp(bar(B_PE), (uint32_t)(t - 1) & 1u)) { ok = false; break; }    // dV of the previous tile has read P^T
+      uint32_t pk[32];
+#pragma unroll
+      for (int g = 0; g < 8; ++g) {    // 16-byte chunk g = queries 8g .. 8g+7 of this half
+        float e[8], ds[8];
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+          const float4 l4 = lse2[g * 2 + hh];
+          const float4 d4 = dlt[g * 2 + hh];
+          const float la[4] = {l4.x, l4.y, l4.z, l4.w};
+          const float da[4] = {d4.x, d4.y, d4.z, d4.w};
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const int i = hh * 4 + u;
+            const int ql = g * 8 + i;
+            float ev = ex2(fmaf(__uint_as_float(rs[ql >> 5][ql & 31]), sl, -la[u]));
+            if (need_mask && qrow0 + ql < grow) ev = 0.0f;
+            e[i] = ev;
+            ds[i] = ev * (__uint_as_float(rd[ql >> 5][ql & 31]) - da[u]);
+          }
+        }
+        st_shared_v4(prow + ((((uint32_t)g) ^ swz) << 4), pack_bf16(e[0], e[1]), pack_bf16(e[2], e[3]), pack_bf16(e[4], e[5]),
+                     pack_bf16(e[6], e[7]));
+        pk[4 * g] = pack_bf16(ds[0], ds[1]);
+        pk[4 * g + 1] = pack_bf16(ds[2], ds[3]);
+        pk[4 * g + 2] = pack_bf16(ds[4], ds[5]);
+        pk[4 * g + 3] = pack_bf16(ds[6], ds[7]);
+      }
+      tc5::tmem_st32(tlane + TM_DPT + (uint32_t)wg * 64u, pk);
+      tc5::tmem_st_wait();
+      tc5::fence_before_sync();
+      fence_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        tc5::mbar_arrive(bar(B_PF));
+        tc5::mbar_arrive(bar(B_QE + st));
+      }
+    }
+    if (ok && wait_warp(bar(B_ACC), 0u)) {
+      tc5::fence_after_sync();
+      __nv_bfloat16* dv = p.dv + (int64_t)b * p.dv_sb + (int64_t)grow * p.dv_ss + (int64_t)h * p.dv_sh;
+      __nv_bfloat16* dk = p.dk + (int64_t)b * p.dk_sb + (int64_t)grow * p.dk_ss + (int64_t)h * p.dk_sh;
+      // group 0 stores dV, group 1 stores dK
+      __nv_bfloat16* dst = wg == 0 ? dv : dk;
+      const float f = wg == 0 ? 1.0f : p.scale;
+      const uint32_t tsrc = tlane + (wg == 0 ? TM_DV : TM_DK);
+#pragma unroll
+      for (int c = 0; c < 4; c += 2) {
+        uint32_t r0[32], r1[32];
+        float v[32];
+        tc5::tmem_ld32(tsrc + (uint32_t)c * 32u, r0);
+        tc5::tmem_ld32(tsrc + (uint32_t)c * 32u + 32u, r1);
+        tc5::tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r0[i]) * f;
+        if (grow < p.seqlen) st_row32(dst + c * 32, v);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r1[i]) * f;
+        if (grow < p.seqlen) st_row32(dst + c * 32 + 32, v);
+      }
+    }
+  }
+
+  __syncwarp();
+  if (*abort_flag) __nanosleep(200000);
+  tc5::fence_before_sync();
+  __syncthreads();
+  tc5::fence_after_sync();
+  if (warp == 1) tc5::tmem_dealloc(tmem_base, TM_COLS);
+}
+
+// ================================================================================ dQ, 128-key tiles, dS in tensor memory
+namespace dqk2 {
+constexpr uint32_t PANEL = 128 * 128;      // [128 rows][64 bf16]: one 64-wide slice of the head dimension
+constexpr uint32_t TILE = 2 * PANEL;       // 32 KB: 128 rows x 128 bf16
+constexpr int NK = 3;    // K tiles: read by the first (S) and by the last (dQ) MMA of their step, so three are alive
+constexpr int NV = 2;    // V tiles: read by dP only
+constexpr uint32_t OFF_Q = 0, OFF_DO = TILE, OFF_K = 2 * TILE, OFF_V = OFF_K + NK * TILE, OFF_BAR = OFF_V + NV * TILE;
+enum { B_Q = 0, B_KF = 1, B_KE = B_KF + NK, B_VF = B_KE + NK, B_VE = B_VF + NV, B_SF = B_VE + NV, B_SE = B_SF + 1, B_DF = B_SE + 1,
+       B_PF = B_DF + 2, B_ACC = B_PF + 2, NBAR = B_ACC + 1 };
+constexpr int SMEM = OFF_BAR + NBAR * 8 + 16 + 1024;
+// one 128-column score tile, two 128-column dP tiles (dS is written over the dP tile it came from), dQ
+constexpr uint32_t TM_S = 0, TM_DP = 128, TM_DQ = 384, TM_COLS = 512;
+}    // namespace dqk2
+
+// dQ for 128 query rows; key tiles of 128 (an M = 128 bf16 MMA costs the same ~70 cycles for N = 64 and N = 128, so the
+// two score products S = Q K^T and dP = dO V^T are issued over 128 keys at a time).  The eight softmax warps split every
+// tile by columns (group g: keys [128 T + 64 g, + 64)).  S is read into registers and its tile released at once; dS is
+// packed to bf16 and stored with tcgen05.st over the dP columns it was computed from (group g: the first 32 columns of
+// its 64-column half), from where dQ += dS K reads it as the A operand: no shared-memory round trip, and the two dP tiles
+// alternate so that dP of tile T + 1 is computed while dS of tile T is still being consumed.  The tensor pipe executes
+// MMAs in issue order, so dP(T + 2) may overwrite tile T & 1 once it is issued after dQ(T).
+__global__ void __launch_bounds__(kTcThreads, 1)
+attn_bwd_dq_tm_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                      const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do, const TcParams p) {
+  using namespace dqk2;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = tc5::smem_u32(smem_raw);
+  const uint32_t base = (raw_addr + 1023u) & ~1023u;
+  uint8_t* smem = smem_raw + (base - raw_addr);
+  const uint32_t bars = base + OFF_BAR;
+  auto bar = [&](int i) { return bars + 8u * (uint32_t)i; };
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(smem + OFF_BAR + NBAR * 8);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+  auto wait_warp = [&](uint32_t br, uint32_t ph) {
+    return __all_sync(0xffffffffu, tc5::mbar_wait(br, ph, abort_flag, p.status, kStatusBit)) != 0;
+  };
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int qt = (int)gridDim.x - 1 - (int)blockIdx.x;
+  const int bh = blockIdx.y;
+  const int b = bh / p.heads;
+  const int h = bh - b * p.heads;
+  const int q0 = qt * 128;
+  const int nk_all = (p.seqlen + 63) / 64;
+  const int n_kv = p.causal ? min(2 * qt + 2, nk_all) : nk_all;    // 64-key halves with a visible key
+  const int n_t = (n_kv + 1) >> 1;                                 // 128-key tiles; a trailing odd half is fully masked
+
+  if (threadIdx.x == 0) {
+    tc5::mbar_init(bar(B_Q), 1);
+    for (int s = 0; s < NK; ++s) {
+      tc5::mbar_init(bar(B_KF + s), 1);
+      tc5::mbar_init(bar(B_KE + s), 1);
+    }
+    for (int s = 0; s < NV; ++s) {
+      tc5::mbar_init(bar(B_VF + s), 1);
+      tc5::mbar_init(bar(B_VE + s), 1);
+    }
+    tc5::mbar_init(bar(B_SF), 1);
+    tc5::mbar_init(bar(B_SE), 8);
+    for (int s = 0; s < 2; ++s) {
+      tc5::mbar_init(bar(B_DF + s), 1);
+      tc5::mbar_init(bar(B_PF + s), 8);
+    }
+    tc5::mbar_init(bar(B_ACC), 1);
+    *abort_flag = 0;
+    tc5::mbar_fence_init();
+    tc5::tma_prefetch_desc(&map_q);
+    tc5::tma_prefetch_desc(&map_k);
+    tc5::tma_prefetch_desc(&map_v);
+    tc5::tma_prefetch_desc(&map_do);
+  }
+  if (warp == 1) {
+    tc5::tmem_alloc(tc5::smem_u32(tmem_holder), TM_COLS);
+    tc5::tmem_relinquish();
+  }
+  tc5::fence_before_sync();
+  __syncthreads();
+  tc5::fence_after_sync();
+  const uint32_t tmem_base = *tmem_holder;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      tc5::mbar_arrive_expect_tx(bar(B_Q), 2 * TILE);
+      tc5::tma_load_4d(base + OFF_Q, &map_q, 0, h, q0, b, bar(B_Q));
+      tc5::tma_load_4d(base + OFF_Q + PANEL, &map_q, 64, h, q0, b, bar(B_Q));
+      tc5::tma_load_4d(base + OFF_DO, &map_do, 0, h, q0, b, bar(B_Q));
+      tc5::tma_load_4d(base + OFF_DO + PANEL, &map_do, 64, h, q0, b, bar(B_Q));
+      for (int t = 0; t < n_t; ++t) {
+        const int ks = t % NK, vs = t % NV;
+        TC_WAIT(bar(B_KE + ks), ((uint32_t)(t / NK) & 1u) ^ 1u);
+        tc5::mbar_arrive_expect_tx(bar(B_KF + ks), TILE);
+        tc5::tma_load_4d(base + OFF_K + ks * TILE, &map_k, 0, h, t * 128, b, bar(B_KF + ks));
+        tc5::tma_load_4d(base + OFF_K + ks * TILE + PANEL, &map_k, 64, h, t * 128, b, bar(B_KF + ks));
+        TC_WAIT(bar(B_VE + vs), ((uint32_t)(t / NV) & 1u) ^ 1u);
+        tc5::mbar_arrive_expect_tx(bar(B_VF + vs), TILE);
+        tc5::tma_load_4d(base + OFF_V + vs * TILE, &map_v, 0, h, t * 128, b, bar(B_VF + vs));
+        tc5::tma_load_4d(base + OFF_V + vs * TILE + PANEL, &map_v, 64, h, t * 128, b, bar(B_VF + vs));
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc_s = tc5::idesc_bf16(128, 128, 0, 0);
+      const uint32_t idesc_acc = tc5::idesc_bf16(128, 128, 0, 1);
+      // S = Q K_t^T (single tile, released by the softmax warps as soon as they hold it in registers) and
+      // dP[t & 1] = dO V_t^T
+      auto issue_s = [&](int t) -> bool {
+        const int ks = t % NK, vs = t % NV;
+        if (t > 0 && !tc5::mbar_wait(bar(B_SE), (uint32_t)(t - 1) & 1u, abort_flag, p.status, kStatusBit)) return false;
+        if (!tc5::mbar_wait(bar(B_KF + ks), (uint32_t)(t / NK) & 1u, abort_flag, p.status, kStatusBit)) return false;
+        tc5::fence_after_sync();
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint32_t off = (uint32_t)(kk >> 2) * PANEL + (uint32_t)(kk & 3) * 32u;
+          tc5::mma_f16(tmem_base + TM_S, tc5::smem_desc_k_sw128(base + OFF_Q + off), tc5::smem_desc_k_sw128(base + OFF_K + ks * TILE + off),
+                       idesc_s, kk ? 1u : 0u);
+        }
+        tc5::mma_commit(bar(B_SF));
+        if (!tc5::mbar_wait(bar(B_VF + vs), (uint32_t)(t / NV) & 1u, abort_flag, p.status, kStatusBit)) return false;
+        tc5::fence_after_sync();
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint32_t off = (uint32_t)(kk >> 2) * PANEL + (uint32_t)(kk & 3) * 32u;
+          tc5::mma_f16(tmem_base + TM_DP + (uint32_t)(t & 1) * 128u, tc5::smem_desc_k_sw128(base + OFF_DO + off),
+                       tc5::smem_desc_k_sw128(base + OFF_V + vs * TILE + off), idesc_s, kk ? 1u : 0u);
+        }
+        tc5::mma_commit(bar(B_VE + vs));
+        tc5::mma_commit(bar(B_DF + (t & 1)));
+        return true;
+      };
+      do {
+        TC_WAIT(bar(B_Q), 0u);
+        if (!issue_s(0)) break;
+        bool ok = true;
+        for (int t = 0; t < n_t; ++t) {
+          if (t + 1 < n_t && !issue_s(t + 1)) { ok = false; break; }
+          const int ks = t % NK;
+          if (!tc5::mbar_wait(bar(B_PF + (t & 1)), (uint32_t)(t >> 1) & 1u, abort_flag, p.status, kStatusBit)) { ok = false; break; }
+          tc5::fence_after_sync();
+          // dQ += dS K_t : A = dS from tensor memory (group g wrote keys 64 g .. 64 g + 63 as 32 packed columns at the start
+          // of its half), B = the K tile with the key index as rows (MN-major)
+#pragma unroll
+          for (int kk = 0; kk < 8; ++kk) {
+            tc5::mma_f16_ta(tmem_base + TM_DQ,
+                            tmem_base + TM_DP + (uint32_t)(t & 1) * 128u + (uint32_t)(kk >> 2) * 64u + (uint32_t)(kk & 3) * 8u,
+                            tc5::smem_desc_mn_sw128(base + OFF_K + ks * TILE + (uint32_t)kk * 2048u, PANEL), idesc_acc, (t | kk) ? 1u : 0u);
+          }
+          tc5::mma_commit(bar(B_KE + ks));
+        }
+        if (ok) tc5::mma_commit(bar(B_ACC));
+      } while (false);
+    }
+  } else {
+    const int qd = warp & 3;
+    const int wg = (warp - 2) >> 2;    // group g: the g-th 64-key half of every tile
+    const int row = qd * 32 + lane;
+    const int grow = q0 + row;
+    const uint32_t tlane = tmem_base + ((uint32_t)(qd * 32) << 16);
+    const float sl = p.scale * kLog2e;
+    const bool in = grow < p.seqlen;
+    const float lse2 = in ? p.lse[(int64_t)bh * p.seqlen + grow] * kLog2e : INFINITY;
+    const float dlt = in ? p.delta[(int64_t)bh * p.seqlen + grow] : 0.0f;
+    const int lim = p.causal ? min(grow, p.seqlen - 1) : p.seqlen - 1;
+    bool ok = true;
+    for (int t = 0; t < n_t; ++t) {
+      const int col0 = (2 * t + wg) * 64;
+      const uint32_t tdp = tlane + TM_DP + (uint32_t)(t & 1) * 128u + (uint32_t)wg * 64u;
+      if (!wait_warp(bar(B_SF), (uint32_t)t & 1u)) { ok = false; break; }
+      tc5::fence_after_sync();
+      const bool need_mask = (p.causal && col0 + 63 > q0) || (col0 + 64 > p.seqlen);
+      uint32_t rs[2][32], rd[2][32];
+      tc5::tmem_ld32(tlane + TM_S + (uint32_t)wg * 64u, rs[0]);
+      tc5::tmem_ld32(tlane + TM_S + (uint32_t)wg * 64u + 32u, rs[1]);
+      tc5::tmem_ld_wait();
+      tc5::fence_before_sync();
+      __syncwarp();
+      if (lane == 0) tc5::mbar_arrive(bar(B_SE));    // the score tile may take tile t + 1
+      if (!wait_warp(bar(B_DF + (t & 1)), (uint32_t)(t >> 1) & 1u)) { ok = false; break; }
+      tc5::fence_after_sync();
+      tc5::tmem_ld32(tdp, rd[0]);
+      tc5::tmem_ld32(tdp + 32u, rd[1]);
+      tc5::tmem_ld_wait();
+      uint32_t pk[32];
+#pragma unroll
+      for (int g = 0; g < 8; ++g) {    // keys 8g .. 8g+7 of this half -> packed columns 4g .. 4g+3
+        float ds[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int c = g * 8 + i;
+          float e = ex2(fmaf(__uint_as_float(rs[c >> 5][c & 31]), sl, -lse2));
+          if (need_mask && col0 + c > lim) e = 0.0f;
+          ds[i] = e * (__uint_as_float(rd[c >> 5][c & 31]) - dlt);
+        }
+        pk[4 * g] = pack_bf16(ds[0], ds[1]);
+        pk[4 * g + 1] = pack_bf16(ds[2], ds[3]);
+        pk[4 * g + 2] = pack_bf16(ds[4], ds[5]);
+        pk[4 * g + 3] = pack_bf16(ds[6], ds[7]);
+      }
+      tc5::tmem_st32(tdp, pk);
+      tc5::tmem_st_wait();
+      tc5::fence_before_sync();
+      __syncwarp();
+      if (lane == 0) tc5::mbar_arrive(bar(B_PF + (t & 1)));
+    }
+    if (ok && wait_warp(bar(B_ACC), 0u)) {
+      tc5::fence_after_sync();
+      __nv_bfloat16* dq = p.dq + (int64_t)b * p.dq_sb + (int64_t)grow * p.dq_ss + (int64_t)h * p.dq_sh;
+      // each group stores one half of the row
+      uint32_t r0[32], r1[32];
+      float v[32];
+      tc5::tmem_ld32(tlane + TM_DQ + (uint32_t)wg * 64u, r0);
+      tc5::tmem_ld32(tlane + TM_DQ + (uint32_t)wg * 64u + 32u, r1);
+      tc5::tmem_ld_wait();
+#pragma unroll
+      for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r0[i]) * p.scale;
+      if (in) st_row32(dq + wg * 64, v);
+#pragma unroll
+      for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r1[i]) * p.scale;
+      if (in) st_row32(dq + wg * 64 + 32, v);
+    }
+  }
+
+  __syncwarp();
+  if (*abort_flag) __nanosleep(200000);
+  tc5::fence_before_sync();
+  __syncthreads();
+  tc5::fence_after_sync();
+  if (warp == 1) tc5::tmem_dealloc(tmem_base, TM_COLS);
+}
+
 // ---- host side -----------------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -1311,9 +1822,18 @@ MSAMP_API int msamp_attention_tc_bwd(const void* q, const void* k, const void* v
     if ((rc = make_map4(k, batch, heads, seqlen, strides[3], strides[4], strides[5], 128, &mk))) return rc;
     if ((rc = make_map4(v, batch, heads, seqlen, strides[6], strides[7], strides[8], 128, &mv))) return rc;
     if ((rc = make_map4(d_o, batch, heads, seqlen, strides[12], strides[13], strides[14], 64, &mdo))) return rc;
-    if ((rc = set_smem(attn_bwd_dkdv_tc_kernel, dkv::SMEM))) return rc;
     dim3 grid((seqlen + 127) / 128, batch * heads);
-    attn_bwd_dkdv_tc_kernel<<<grid, kTcThreads, dkv::SMEM, stream>>>(mq, mk, mv, mdo, p);
+    static const bool smem_operands = [] { const char* e = getenv("MSAMP_ATTN_BWD_SMEM"); return e && e[0] == '1'; }();
+    if (smem_operands) {
+      if ((rc = set_smem(attn_bwd_dkdv_tc_kernel, dkv::SMEM))) return rc;
+      attn_bwd_dkdv_tc_kernel<<<grid, kTcThreads, dkv::SMEM, stream>>>(mq, mk, mv, mdo, p);
+    } else {
+      CUtensorMap mq128, mdo128;
+      if ((rc = make_map4(q, batch, heads, seqlen, strides[0], strides[1], strides[2], 128, &mq128))) return rc;
+      if ((rc = make_map4(d_o, batch, heads, seqlen, strides[12], strides[13], strides[14], 128, &mdo128))) return rc;
+      if ((rc = set_smem(attn_bwd_dkdv_tm_kernel, dkv2::SMEM))) return rc;
+      attn_bwd_dkdv_tm_kernel<<<grid, kTcThreads, dkv2::SMEM, stream>>>(mq128, mk, mv, mdo128, p);
+    }
   }
   {
     CUtensorMap mq, mk, mv, mdo;
@@ -1321,9 +1841,19 @@ MSAMP_API int msamp_attention_tc_bwd(const void* q, const void* k, const void* v
     if ((rc = make_map4(k, batch, heads, seqlen, strides[3], strides[4], strides[5], 64, &mk))) return rc;
     if ((rc = make_map4(v, batch, heads, seqlen, strides[6], strides[7], strides[8], 64, &mv))) return rc;
     if ((rc = make_map4(d_o, batch, heads, seqlen, strides[12], strides[13], strides[14], 128, &mdo))) return rc;
-    if ((rc = set_smem(attn_bwd_dq_tc_kernel, dqk::SMEM))) return rc;
     dim3 grid((seqlen + 127) / 128, batch * heads);
-    attn_bwd_dq_tc_kernel<<<grid, kTcThreads, dqk::SMEM, stream>>>(mq, mk, mv, mdo, p);
+    // MSAMP_ATTN_BWD_SMEM=1 selects the kernels with 64-wide score tiles and the second operand in shared memory
+    static const bool smem_operands = [] { const char* e = getenv("MSAMP_ATTN_BWD_SMEM"); return e && e[0] == '1'; }();
+    if (smem_operands) {
+      if ((rc = set_smem(attn_bwd_dq_tc_kernel, dqk::SMEM))) return rc;
+      attn_bwd_dq_tc_kernel<<<grid, kTcThreads, dqk::SMEM, stream>>>(mq, mk, mv, mdo, p);
+    } else {
+      CUtensorMap mk128, mv128;
+      if ((rc = make_map4(k, batch, heads, seqlen, strides[3], strides[4], strides[5], 128, &mk128))) return rc;
+      if ((rc = make_map4(v, batch, heads, seqlen, strides[6], strides[7], strides[8], 128, &mv128))) return rc;
+      if ((rc = set_smem(attn_bwd_dq_tm_kernel, dqk2::SMEM))) return rc;
+      attn_bwd_dq_tm_kernel<<<grid, kTcThreads, dqk2::SMEM, stream>>>(mq, mk128, mv128, mdo, p);
+    }
   }
   return msamp_check_launch("attn_bwd_tc kernels");
 }
