@@ -63,7 +63,9 @@ struct Tile {
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int STAGES = NSTAGES ? NSTAGES : (PAIR ? 6 : ((BN == 256) ? 4 : 6));
   static constexpr int TILE_BYTES = STAGES * STAGE_BYTES;
-  static constexpr int SMEM_BYTES = TILE_BYTES + 256 + 1024;    // barriers + manual alignment slack
+  static constexpr int STAGING_OFF = TILE_BYTES + 256;          // after the barriers: 4 KB per epilogue warp
+  static constexpr int SMEM_BYTES = STAGING_OFF + 8 * 4096 + 1024;    // + manual alignment slack
+  static_assert(SMEM_BYTES <= 227 * 1024, "GEMM shared memory");
   static constexpr int TMEM_COLS = 2 * BN;                       // two accumulator buffers
   static constexpr uint32_t TX_BYTES = PAIR ? 2 * STAGE_BYTES : STAGE_BYTES;
 };
@@ -282,6 +284,12 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
     const bool vec_g = G && ((reinterpret_cast<uintptr_t>(G) & 15) == 0) && ((p.ldg * sizeof(OutT)) % 16 == 0);
     const bool vec_8 = p.d8 && ((reinterpret_cast<uintptr_t>(p.d8) & 15) == 0) && (p.ld8 % 16 == 0);
     const uint32_t tempty_remote = PAIR ? tc5::map_to_cta(tempty_bar(0), 0) : 0u;
+    // 16-bit outputs of full tiles go through a per-warp staging buffer of 32 rows x 128 bytes: the thread that owns a
+    // row writes its 64 converted columns there (16-byte pieces XOR-swizzled by row), then the warp writes the rows out
+    // with every store instruction covering four complete 128-byte lines.  Storing straight from the row-per-thread
+    // layout touches 32 different lines with 16 bytes each per instruction, which cost 11 % of the GEMM on N >= 12288.
+    const uint32_t stage = base + (uint32_t)C::STAGING_OFF + (uint32_t)(warp - 2) * 4096u;
+    const bool staged_ok = sizeof(OutT) == 2 && vec_ok;
     float amax = 0.0f;
     uint32_t lt = 0;
     for (int tile = first_tile; tile < num_tiles; tile += tile_step, ++lt) {
@@ -292,6 +300,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
       const int buf = lt & 1;
       const uint32_t aph = (lt >> 1) & 1;
       const int row = m0 + q * 32 + lane;
+      const bool full_tile = staged_ok && (m0 + q * 32 + 32 <= p.M) && (n0 + BN <= p.N);    // uniform over the warp
       if ((R != nullptr || G != nullptr) && row < p.M) {
         // While the main loop of this tile is still running, pull this thread's slice of the residual / GeLU
         // source into L2, so that the loads below do not wait for HBM one chunk at a time.
@@ -351,7 +360,42 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
             for (int j = 0; j < 32; ++j) v[j] *= gelu_grad_f(h[j]);
           }
           OutT* dst = D + (int64_t)row * p.ldd + col;
-          store_chunk<OutT>(dst, v, vec_ok, valid);
+          if constexpr (sizeof(OutT) == 2) {
+            if (full_tile) {
+              const uint32_t srow = stage + (uint32_t)lane * 128u;
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                Bytes16 o;
+                OutT* e = reinterpret_cast<OutT*>(&o);
+#pragma unroll
+                for (int t = 0; t < 8; ++t) e[t] = from_f32<OutT>(v[8 * j + t]);
+                const uint32_t piece = (uint32_t)((c & 1) * 4 + j);
+                const uint4 u = *reinterpret_cast<const uint4*>(&o);
+                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(srow + ((piece ^ (uint32_t)(lane & 7)) << 4)), "r"(u.x),
+                             "r"(u.y), "r"(u.z), "r"(u.w)
+                             : "memory");
+              }
+              if (c & 1) {
+                __syncwarp();
+                const uint32_t piece = (uint32_t)(lane & 7);
+                OutT* out0 = D + (int64_t)(m0 + q * 32) * p.ldd + (col - 32) + piece * 8;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                  const uint32_t r = (uint32_t)(lane >> 3) + 4u * (uint32_t)i;
+                  uint4 u;
+                  asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                               : "=r"(u.x), "=r"(u.y), "=r"(u.z), "=r"(u.w)
+                               : "r"(stage + r * 128u + ((piece ^ (r & 7u)) << 4)));
+                  *reinterpret_cast<uint4*>(out0 + (int64_t)r * p.ldd) = u;
+                }
+                __syncwarp();
+              }
+            } else {
+              store_chunk<OutT>(dst, v, vec_ok, valid);
+            }
+          } else {
+            store_chunk<OutT>(dst, v, vec_ok, valid);
+          }
           if (p.amax_out != nullptr || p.d8 != nullptr) {
             // statistics and the quantised copy are taken from the values as stored (rounded to the
             // output type), so that they equal what a separate pass over D would produce
