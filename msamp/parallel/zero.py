@@ -241,6 +241,14 @@ class ZeroShardedOptimizer:
         flat = model_state.flattened_scaling_metas
         if flat is not None and 'wgrad' in flat:
             flat['wgrad'] = dict(flat['wgrad'], scales_inv=g_meta[0], amaxs=g_meta[1].view(-1, 1), _external=True)
+        # every offset a kernel will add to a (peer) base pointer, checked against the buffer it indexes: the kernels read
+        # 16-byte vectors up to the padded end of a tensor and three fp32 meta rows of n entries
+        for i, p in enumerate(self.fp8_params):
+            lo, hi = self.offsets[i], self.offsets[i] + _pad16(p.numel())
+            if lo % 16 or hi > g_flat.numel() or (i + 1 < len(self.offsets) and hi > self.offsets[i + 1]):
+                raise RuntimeError(f'gradient buffer layout: tensor {i} covers [{lo}, {hi}) of {g_flat.numel()} bytes')
+        if g_meta.numel() < 3 * max(n, 1):
+            raise RuntimeError('gradient meta rows are too short')
         work = []
         chunk = 16384
         for i, p in enumerate(self.fp8_params):
