@@ -52,6 +52,7 @@ struct GemmArgs {
   int a_mn, b_mn;             // 1: that operand is stored [K, M] / [K, N]
   int act;                    // 0: identity, 1: amax_out and d8 refer to gelu(D)
   int group_m;                // row tiles per rasterisation group (see tile_to_mn); 0 means all of them
+  int tma_store;              // 1: tma_d describes D and full 16-bit tiles are stored through it
 };
 
 template <int BN, bool PAIR, int NSTAGES = 0>
@@ -63,7 +64,7 @@ struct Tile {
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int STAGES = NSTAGES ? NSTAGES : (PAIR ? 6 : ((BN == 256) ? 4 : 6));
   static constexpr int TILE_BYTES = STAGES * STAGE_BYTES;
-  static constexpr int STAGING_OFF = TILE_BYTES + 256;          // after the barriers: 4 KB per epilogue warp
+  static constexpr int STAGING_OFF = TILE_BYTES + 1024;         // after the barriers, 1024-byte aligned: 4 KB per epilogue warp
   static constexpr int SMEM_BYTES = STAGING_OFF + 8 * 4096 + 1024;    // + manual alignment slack
   static_assert(SMEM_BYTES <= 227 * 1024, "GEMM shared memory");
   static constexpr int TMEM_COLS = 2 * BN;                       // two accumulator buffers
@@ -105,7 +106,8 @@ __device__ __forceinline__ void store_fp8_chunk(uint8_t* dst, const float (&w)[3
 
 template <int BN, bool PAIR, typename OutT, int NSTAGES = 0>
 __global__ void __launch_bounds__(kThreadsEpi8, 1)
-gemm_fp8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b, const GemmArgs p) {
+gemm_fp8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+                const __grid_constant__ CUtensorMap tma_d, const GemmArgs p) {
   using C = Tile<BN, PAIR, NSTAGES>;
   extern __shared__ uint8_t smem_raw[];
   // 128B-swizzled tiles need 1024-byte alignment (the offset is the same in both CTAs of a pair).
@@ -289,7 +291,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
     // with every store instruction covering four complete 128-byte lines.  Storing straight from the row-per-thread
     // layout touches 32 different lines with 16 bytes each per instruction, which cost 11 % of the GEMM on N >= 12288.
     const uint32_t stage = base + (uint32_t)C::STAGING_OFF + (uint32_t)(warp - 2) * 4096u;
-    const bool staged_ok = sizeof(OutT) == 2 && vec_ok;
+    const bool staged_ok = sizeof(OutT) == 2 && vec_ok && p.tma_store != 0;
     float amax = 0.0f;
     uint32_t lt = 0;
     for (int tile = first_tile; tile < num_tiles; tile += tile_step, ++lt) {
@@ -376,17 +378,14 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
                              : "memory");
               }
               if (c & 1) {
+                // the staging rows are laid out exactly as a 128-byte-swizzled TMA box of 32 rows x 128 bytes: one thread
+                // hands them to the TMA unit, which writes complete lines without occupying the load/store path
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 __syncwarp();
-                const uint32_t piece = (uint32_t)(lane & 7);
-                OutT* out0 = D + (int64_t)(m0 + q * 32) * p.ldd + (col - 32) + piece * 8;
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                  const uint32_t r = (uint32_t)(lane >> 3) + 4u * (uint32_t)i;
-                  uint4 u;
-                  asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
-                               : "=r"(u.x), "=r"(u.y), "=r"(u.z), "=r"(u.w)
-                               : "r"(stage + r * 128u + ((piece ^ (r & 7u)) << 4)));
-                  *reinterpret_cast<uint4*>(out0 + (int64_t)r * p.ldd) = u;
+                if (lane == 0) {
+                  tc5::tma_store_2d(&tma_d, stage, (col - 32) * (int)sizeof(OutT), m0 + q * 32);
+                  tc5::bulk_commit_group();
+                  tc5::bulk_wait_read<0>();    // the buffer is rewritten by the next 64 columns
                 }
                 __syncwarp();
               }
@@ -424,6 +423,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
         else      tc5::mbar_arrive(tempty_bar(buf));
       }
     }
+    if (lane == 0) tc5::bulk_wait_all<0>();    // TMA stores of this warp have landed before the CTA goes away
     if (p.amax_out != nullptr) {
       amax = warp_max(amax);
       if (lane == 0) atomic_max_nonneg(p.amax_out, amax);
@@ -473,7 +473,7 @@ int max_pairs(int smem_bytes) {
 }
 
 template <int BN, bool PAIR, typename OutT, int NSTAGES = 0>
-int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmArgs& p, int max_ctas, cudaStream_t stream) {
+int launch(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& md, const GemmArgs& p, int max_ctas, cudaStream_t stream) {
   using C = Tile<BN, PAIR, NSTAGES>;
   static bool configured[64] = {false};
   int dev = 0;
@@ -503,7 +503,7 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmArgs& p, int 
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_fp8_kernel<BN, PAIR, OutT, NSTAGES>, ma, mb, p);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_fp8_kernel<BN, PAIR, OutT, NSTAGES>, ma, mb, md, p);
     if (e != cudaSuccess) {
       msamp_set_error("gemm_fp8 pair kernel launch: %s", cudaGetErrorString(e));
       cudaGetLastError();
@@ -514,7 +514,7 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmArgs& p, int 
   int grid = msamp_sm_count();
   if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
   if (num_tiles < grid) grid = num_tiles;
-  gemm_fp8_kernel<BN, PAIR, OutT, NSTAGES><<<grid, kThreadsEpi8, C::SMEM_BYTES, stream>>>(ma, mb, p);
+  gemm_fp8_kernel<BN, PAIR, OutT, NSTAGES><<<grid, kThreadsEpi8, C::SMEM_BYTES, stream>>>(ma, mb, md, p);
   return msamp_check_launch("gemm_fp8_kernel");
 }
 
@@ -577,7 +577,20 @@ MSAMP_API int msamp_gemm_fp8_ex(const MsampGemmDesc* g, void* stream_) {
   if (g->b_mn) rc = make_map(g->b, K, N, g->ldb, BK, &mb);
   else         rc = make_map(g->b, N, K, g->ldb, pair ? bn / 2 : bn, &mb);
   if (rc) return rc;
+  // 16-bit outputs of full tiles are written by TMA from the epilogue's staging buffers: a byte view of D with boxes of
+  // 32 rows x 128 bytes.  Without it (fp32 output, unaligned D) the map argument is a placeholder that is never used.
+  CUtensorMap md = ma;
+  int tma_store = 0;
+  {
+    const int esize = g->out_dtype == DT_F32 ? 4 : 2;
+    if (esize == 2 && (reinterpret_cast<uintptr_t>(g->d) & 15) == 0 && (g->ldd * esize) % 16 == 0 && N >= 128 &&
+        make_map(g->d, M, (int64_t)N * esize, g->ldd * esize, 32, &md) == MSAMP_OK)
+      tma_store = 1;
+    else
+      md = ma;
+  }
   GemmArgs p;
+  p.tma_store = tma_store;
   p.d = g->d; p.bias = g->bias; p.residual = g->residual; p.gelu_src = g->gelu_src;
   p.scale_inv_a = g->scale_inv_a; p.scale_inv_b = g->scale_inv_b; p.amax_out = g->amax_out;
   p.d8 = (uint8_t*)g->d8; p.d8_scale = g->d8_scale; p.d8_scale_inv_out = g->d8 ? g->d8_scale_inv_out : nullptr;
@@ -594,9 +607,9 @@ MSAMP_API int msamp_gemm_fp8_ex(const MsampGemmDesc* g, void* stream_) {
     p.group_m = grp >= num_m ? num_m : (int)grp;
   }
   MSAMP_DISPATCH_HP(g->out_dtype, T, {
-    if (pair) return launch<256, true, T>(ma, mb, p, g->max_ctas, stream);
-    if (bn == 256) return launch<256, false, T>(ma, mb, p, g->max_ctas, stream);
-    return launch<128, false, T>(ma, mb, p, g->max_ctas, stream);
+    if (pair) return launch<256, true, T>(ma, mb, md, p, g->max_ctas, stream);
+    if (bn == 256) return launch<256, false, T>(ma, mb, md, p, g->max_ctas, stream);
+    return launch<128, false, T>(ma, mb, md, p, g->max_ctas, stream);
   });
   return MSAMP_OK;
 }
