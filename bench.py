@@ -306,6 +306,9 @@ def main():
             'peak_mem_gib_per_gpu': peak_mem,
             'host_enqueue_ms_per_step': host_enqueue_ms, 'clocks': clocks, 'e2e': e2e, 'gpu_launches': launches, 'device_status': status,
         }
+        if full_shard:
+            # GEMMs of the sharded linears that ran the fused gather / reduce-scatter kernels vs the NCCL + plain GEMM form
+            out['fused_gemm_calls'], out['unfused_gemm_calls'] = int(fsdp.fused_calls), int(fsdp.unfused_calls)
         print(json.dumps(out))
     if world > 1:
         dist.destroy_process_group()
