@@ -637,6 +637,312 @@ attn_fwd_tm_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
   if (warp == 1) tc5::tmem_dealloc(tmem_base, TM_COLS);
 }
 
+// ================================================================= forward, persistent CTAs over (query tile, batch, head)
+namespace fwd3 {
+using namespace fwd2;    // same tiles, rings and tensor-memory layout
+constexpr uint32_t OFF_X3 = OFF_V + NV * TILE_V;          // two merge buffers of 2 KB (alternating work items)
+constexpr uint32_t OFF_BAR3 = OFF_X3 + 4096;
+enum { B3_QE = NBAR, B3_OE = NBAR + 1, B3_X = NBAR + 2, NBAR3 = NBAR + 3 };
+constexpr int SMEM3 = OFF_BAR3 + NBAR3 * 8 + 16 + 1024;
+}    // namespace fwd3
+
+// The schedule of attn_fwd_tm_kernel with one CTA per SM that walks a list of work items (query tile, batch * head),
+// longest rows first, item i of CTA c = c + i * gridDim.x.  Every ring (K, V, score slots) and every barrier keeps
+// running across items, so the TMA warp loads Q, K and V of the next item while the softmax warps are still in the
+// epilogue of the current one, and the MMA warp has the first two score tiles of the next item ready when they return:
+// the ~8 k cycles of prologue and epilogue per item (of ~23 k on average for sequence 2048) are hidden.  Two extra
+// barriers order the reuse: B3_QE (all score MMAs of an item issued and complete: the Q tile may be overwritten) and
+// B3_OE (the softmax warps have read both output accumulators: the first PV product of the next item may overwrite them);
+// B3_X is where the eight softmax warps meet before the two groups' partial results are merged.
+__global__ void __launch_bounds__(kTcThreads, 1)
+attn_fwd_ps_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                   const __grid_constant__ CUtensorMap map_v, const TcParams p, int n_qt, int n_items) {
+  using namespace fwd3;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = tc5::smem_u32(smem_raw);
+  const uint32_t base = (raw_addr + 1023u) & ~1023u;
+  uint8_t* smem = smem_raw + (base - raw_addr);
+  const uint32_t bars = base + OFF_BAR3;
+  auto bar = [&](int i) { return bars + 8u * (uint32_t)i; };
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(smem + OFF_BAR3 + NBAR3 * 8);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+  auto wait_warp = [&](uint32_t br, uint32_t ph) {
+    return __all_sync(0xffffffffu, tc5::mbar_wait(br, ph, abort_flag, p.status, kStatusBit)) != 0;
+  };
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int bh_total = p.batch * p.heads;
+  const int n_all = (p.seqlen + 63) / 64;
+  // work item -> (query tile, batch * head) and its number of 128-key tiles
+  auto item_qt = [&](int item) { return n_qt - 1 - item / bh_total; };
+  auto item_tiles = [&](int qt) {
+    const int n_kv = p.causal ? min(2 * qt + 2, n_all) : n_all;
+    return (n_kv + 1) >> 1;
+  };
+
+  if (threadIdx.x == 0) {
+    tc5::mbar_init(bar(B_Q), 1);
+    for (int s = 0; s < NK; ++s) {
+      tc5::mbar_init(bar(B_KF + s), 1);
+      tc5::mbar_init(bar(B_KE + s), 1);
+    }
+    for (int s = 0; s < NV; ++s) {
+      tc5::mbar_init(bar(B_VF + s), 1);
+      tc5::mbar_init(bar(B_VE + s), 1);
+    }
+    tc5::mbar_init(bar(B_SF + 0), 1);
+    tc5::mbar_init(bar(B_SF + 1), 1);
+    for (int s = 0; s < 4; ++s) tc5::mbar_init(bar(B_PF + s), 4);
+    tc5::mbar_init(bar(B_OF + 0), 1);
+    tc5::mbar_init(bar(B_OF + 1), 1);
+    tc5::mbar_init(bar(B_ACC), 1);
+    tc5::mbar_init(bar(B3_QE), 1);
+    tc5::mbar_init(bar(B3_OE), 8);
+    tc5::mbar_init(bar(B3_X), 8);
+    *abort_flag = 0;
+    tc5::mbar_fence_init();
+    tc5::tma_prefetch_desc(&map_q);
+    tc5::tma_prefetch_desc(&map_k);
+    tc5::tma_prefetch_desc(&map_v);
+  }
+  if (warp == 1) {
+    tc5::tmem_alloc(tc5::smem_u32(tmem_holder), TM_COLS);
+    tc5::tmem_relinquish();
+  }
+  tc5::fence_before_sync();
+  __syncthreads();
+  tc5::fence_after_sync();
+  const uint32_t tmem_base = *tmem_holder;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int gt = 0;    // 128-key tiles loaded so far (all items)
+      bool ok = true;
+      int it = 0;
+      for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++it) {
+        const int qt = item_qt(item);
+        const int bh = item % bh_total;
+        const int b = bh / p.heads, h = bh - b * p.heads;
+        const int n_t = item_tiles(qt);
+        if (it > 0 && !tc5::mbar_wait(bar(B3_QE), (uint32_t)(it - 1) & 1u, abort_flag, p.status, kStatusBit)) break;
+        tc5::mbar_arrive_expect_tx(bar(B_Q), TILE_Q);
+        tc5::tma_load_4d(base + OFF_Q, &map_q, 0, h, qt * 128, b, bar(B_Q));
+        tc5::tma_load_4d(base + OFF_Q + PANEL_Q, &map_q, 64, h, qt * 128, b, bar(B_Q));
+        for (int t = 0; t < n_t && ok; ++t, ++gt) {
+          const int ks = gt % NK;
+          if (!tc5::mbar_wait(bar(B_KE + ks), ((uint32_t)(gt / NK) & 1u) ^ 1u, abort_flag, p.status, kStatusBit)) { ok = false; break; }
+          tc5::mbar_arrive_expect_tx(bar(B_KF + ks), TILE_K);
+          tc5::tma_load_4d(base + OFF_K + ks * TILE_K, &map_k, 0, h, t * 128, b, bar(B_KF + ks));
+          tc5::tma_load_4d(base + OFF_K + ks * TILE_K + PANEL_K, &map_k, 64, h, t * 128, b, bar(B_KF + ks));
+          for (int g = 0; g < 2; ++g) {
+            const int gj = 2 * gt + g;    // 64-key sub-tiles loaded so far
+            const int vs = gj % NV;
+            if (!tc5::mbar_wait(bar(B_VE + vs), ((uint32_t)(gj / NV) & 1u) ^ 1u, abort_flag, p.status, kStatusBit)) { ok = false; break; }
+            tc5::mbar_arrive_expect_tx(bar(B_VF + vs), TILE_V);
+            tc5::tma_load_4d(base + OFF_V + vs * TILE_V, &map_v, 0, h, (2 * t + g) * 64, b, bar(B_VF + vs));
+            tc5::tma_load_4d(base + OFF_V + vs * TILE_V + PANEL_V, &map_v, 64, h, (2 * t + g) * 64, b, bar(B_VF + vs));
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc_s = tc5::idesc_bf16(128, 128, 0, 0);
+      const uint32_t idesc_o = tc5::idesc_bf16(128, 128, 0, 1);
+      auto issue_s = [&](int gs) -> bool {    // S[gs & 1] = Q K^T for the gs-th tile of this CTA
+        const int ks = gs % NK;
+        if (!tc5::mbar_wait(bar(B_KF + ks), (uint32_t)(gs / NK) & 1u, abort_flag, p.status, kStatusBit)) return false;
+        tc5::fence_after_sync();
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint32_t off = (uint32_t)(kk >> 2) * PANEL_Q + (uint32_t)(kk & 3) * 32u;
+          tc5::mma_f16(tmem_base + TM_S + (uint32_t)(gs & 1) * 128u, tc5::smem_desc_k_sw128(base + OFF_Q + off),
+                       tc5::smem_desc_k_sw128(base + OFF_K + ks * TILE_K + off), idesc_s, kk ? 1u : 0u);
+        }
+        tc5::mma_commit(bar(B_KE + ks));
+        tc5::mma_commit(bar(B_SF + (gs & 1)));
+        return true;
+      };
+      int g0 = 0;    // tiles of earlier items
+      bool ok = true;
+      int it = 0;
+      for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++it) {
+        const int n_t = item_tiles(item_qt(item));
+        if (!tc5::mbar_wait(bar(B_Q), (uint32_t)it & 1u, abort_flag, p.status, kStatusBit)) { ok = false; break; }
+        for (int t = 0; t < 2 && t < n_t; ++t)
+          if (!issue_s(g0 + t)) { ok = false; break; }
+        if (!ok) break;
+        if (n_t <= 2) tc5::mma_commit(bar(B3_QE));    // every score product of this item has been issued
+        // the softmax warps must have read the previous item's accumulators before they are overwritten
+        if (it > 0 && !tc5::mbar_wait(bar(B3_OE), (uint32_t)(it - 1) & 1u, abort_flag, p.status, kStatusBit)) { ok = false; break; }
+        for (int t = 0; t < n_t && ok; ++t) {
+          const int gs = g0 + t;
+          for (int g = 0; g < 2; ++g) {
+            const int gj = 2 * gs + g;
+            const int vs = gj % NV;
+            if (!tc5::mbar_wait(bar(B_PF + (gs & 1) * 2 + g), (uint32_t)(gs >> 1) & 1u, abort_flag, p.status, kStatusBit)) { ok = false; break; }
+            if (!tc5::mbar_wait(bar(B_VF + vs), (uint32_t)(gj / NV) & 1u, abort_flag, p.status, kStatusBit)) { ok = false; break; }
+            tc5::fence_after_sync();
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk) {
+              tc5::mma_f16_ta(tmem_base + TM_O + (uint32_t)g * 128u,
+                              tmem_base + TM_S + (uint32_t)(gs & 1) * 128u + (uint32_t)g * 64u + (uint32_t)kk * 8u,
+                              tc5::smem_desc_mn_sw128(base + OFF_V + vs * TILE_V + (uint32_t)kk * 2048u, PANEL_V), idesc_o,
+                              (t > 0 || kk) ? 1u : 0u);
+            }
+            tc5::mma_commit(bar(B_VE + vs));
+            tc5::mma_commit(bar(B_OF + g));
+          }
+          if (ok && t + 2 < n_t) {
+            if (!issue_s(gs + 2)) { ok = false; break; }
+            if (t + 3 == n_t) tc5::mma_commit(bar(B3_QE));
+          }
+        }
+        if (ok) tc5::mma_commit(bar(B_ACC));
+        g0 += n_t;
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ softmax: one thread per query row and group
+    const int qd = warp & 3;           // TMEM lane quarter this warp may access
+    const int wg = (warp - 2) >> 2;    // group g: second index of the 64-key halves it owns
+    const int row = qd * 32 + lane;
+    const uint32_t tlane = tmem_base + ((uint32_t)(qd * 32) << 16);
+    const uint32_t to = tlane + TM_O + (uint32_t)wg * 128u;
+    const float sl = p.scale * kLog2e;
+    int g0 = 0;
+    bool ok = true;
+    int it = 0;
+    for (int item = blockIdx.x; item < n_items; item += gridDim.x, ++it) {
+      const int qt = item_qt(item);
+      const int bh = item % bh_total;
+      const int b = bh / p.heads, h = bh - b * p.heads;
+      const int n_t = item_tiles(qt);
+      const int q0 = qt * 128;
+      const int grow = q0 + row;
+      const int lim = p.causal ? min(grow, p.seqlen - 1) : p.seqlen - 1;    // last visible column
+      float m = -INFINITY, l = 0.0f;    // reference maximum (log2 units) and row sum of this group
+      for (int t = 0; t < n_t; ++t) {
+        const int gs = g0 + t;
+        const uint32_t ts = tlane + TM_S + (uint32_t)(gs & 1) * 128u + (uint32_t)wg * 64u;
+        if (!wait_warp(bar(B_SF + (gs & 1)), (uint32_t)(gs >> 1) & 1u)) { ok = false; break; }
+        tc5::fence_after_sync();
+        uint32_t r[2][32];
+        tc5::tmem_ld32(ts, r[0]);
+        tc5::tmem_ld32(ts + 32u, r[1]);
+        tc5::tmem_ld_wait();
+        const int col0 = (2 * t + wg) * 64;
+        const bool need_mask = (p.causal && col0 + 63 > q0) || (col0 + 64 > p.seqlen);
+        float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+        if (need_mask) {
+#pragma unroll
+          for (int i = 0; i < 64; ++i)
+            if (col0 + i <= lim) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(r[i >> 5][i & 31]));
+        } else {
+#pragma unroll
+          for (int i = 0; i < 64; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(r[i >> 5][i & 31]));
+        }
+        const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * sl;    // sl > 0
+        const bool grow_m = mx > m + kRescaleStep || (m == -INFINITY && mx > -INFINITY);
+        if (__any_sync(0xffffffffu, grow_m)) {
+          const float m_new = grow_m ? mx : m;
+          const float corr = (m == -INFINITY) ? 0.0f : ex2(m - m_new);
+          if (t > 0) {
+            // every earlier product of this group and item must have landed in O before it is rescaled
+            if (!wait_warp(bar(B_OF + wg), (uint32_t)(gs - 1) & 1u)) { ok = false; break; }
+            tc5::fence_after_sync();
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+              uint32_t x[32];
+              tc5::tmem_ld32(to + (uint32_t)c * 32u, x);
+              tc5::tmem_ld_wait();
+#pragma unroll
+              for (int i = 0; i < 32; ++i) x[i] = __float_as_uint(__uint_as_float(x[i]) * corr);
+              tc5::tmem_st32(to + (uint32_t)c * 32u, x);
+            }
+          }
+          l *= corr;
+          m = m_new;
+        }
+        const float m_use = (m == -INFINITY) ? 0.0f : m;
+        float sum4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        uint32_t pk[32];
+#pragma unroll
+        for (int g = 0; g < 8; ++g) {    // columns 8g .. 8g+7 -> packed columns 4g .. 4g+3
+          float e[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            e[i] = ex2(fmaf(__uint_as_float(r[g >> 2][(g & 3) * 8 + i]), sl, -m_use));
+            if (need_mask && col0 + g * 8 + i > lim) e[i] = 0.0f;
+            sum4[i & 3] += e[i];
+          }
+          pk[4 * g] = pack_bf16(e[0], e[1]);
+          pk[4 * g + 1] = pack_bf16(e[2], e[3]);
+          pk[4 * g + 2] = pack_bf16(e[4], e[5]);
+          pk[4 * g + 3] = pack_bf16(e[6], e[7]);
+        }
+        l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+        tc5::tmem_st32(ts, pk);
+        tc5::tmem_st_wait();    // also covers the rescaled accumulator
+        tc5::fence_before_sync();
+        __syncwarp();
+        if (lane == 0) tc5::mbar_arrive(bar(B_PF + (gs & 1) * 2 + wg));
+      }
+      ok = ok && wait_warp(bar(B_ACC), (uint32_t)it & 1u);
+      tc5::fence_after_sync();
+      // merge the two groups through shared memory (two buffers, alternating items: a warp that is already in the next
+      // item's merge cannot overwrite values another warp still reads)
+      float* xm = reinterpret_cast<float*>(smem + OFF_X3 + (uint32_t)(it & 1) * 2048u);    // [2][128] maxima, then [2][128] sums
+      float* xl = xm + 256;
+      if (!ok) break;
+      xm[wg * 128 + row] = m;
+      xl[wg * 128 + row] = l;
+      // the eight warps meet on an mbarrier (bounded wait) rather than on a named barrier: a warp that gave up on an
+      // earlier wait leaves without arriving, and the others then give up here instead of waiting for it for ever
+      __syncwarp();
+      if (lane == 0) tc5::mbar_arrive(bar(B3_X));
+      if (!wait_warp(bar(B3_X), (uint32_t)it & 1u)) { ok = false; break; }
+      const float m0 = xm[row], m1 = xm[128 + row], l0 = xl[row], l1 = xl[128 + row];
+      const float mm = fmaxf(m0, m1);
+      const float f0 = (m0 == -INFINITY) ? 0.0f : ex2(m0 - mm);
+      const float f1 = (m1 == -INFINITY) ? 0.0f : ex2(m1 - mm);
+      const float lt = l0 * f0 + l1 * f1;
+      const float inv = lt > 0.0f ? 1.0f / lt : 0.0f;
+      const float gg0 = f0 * inv, gg1 = f1 * inv;
+      uint32_t a0[2][32], a1[2][32];
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        tc5::tmem_ld32(tlane + TM_O + (uint32_t)wg * 64u + (uint32_t)c * 32u, a0[c]);
+        tc5::tmem_ld32(tlane + TM_O + 128u + (uint32_t)wg * 64u + (uint32_t)c * 32u, a1[c]);
+      }
+      tc5::tmem_ld_wait();
+      tc5::fence_before_sync();
+      __syncwarp();
+      if (lane == 0) tc5::mbar_arrive(bar(B3_OE));    // the accumulators may take the next item
+      __nv_bfloat16* dst = p.o + (int64_t)b * p.o_sb + (int64_t)grow * p.o_ss + (int64_t)h * p.o_sh + wg * 64;
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        float v[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = fmaf(__uint_as_float(a1[c][i]), gg1, __uint_as_float(a0[c][i]) * gg0);
+        if (grow < p.seqlen) st_row32(dst + c * 32, v);
+      }
+      if (wg == 0 && grow < p.seqlen) p.lse[(int64_t)bh * p.seqlen + grow] = lt > 0.0f ? mm * kLn2 + logf(lt) : -INFINITY;
+      g0 += n_t;
+    }
+  }
+
+  // ---------------------------------------------------------------------- tear-down
+  __syncwarp();
+  if (*abort_flag) __nanosleep(200000);    // let copies / MMAs in flight finish before smem and TMEM go away
+  tc5::fence_before_sync();
+  __syncthreads();
+  tc5::fence_after_sync();
+  if (warp == 1) tc5::tmem_dealloc(tmem_base, TM_COLS);
+}
+
 // ===================================================================================== delta = rowsum(dO * O)
 struct DeltaParams {
   const __nv_bfloat16* o;
@@ -1785,9 +2091,19 @@ MSAMP_API int msamp_attention_tc_fwd(const void* q, const void* k, const void* v
   }
   CUtensorMap mk128;
   if ((rc = make_map4(k, batch, heads, seqlen, strides[3], strides[4], strides[5], 128, &mk128))) return rc;
-  if ((rc = set_smem(attn_fwd_tm_kernel, fwd2::SMEM))) return rc;
-  attn_fwd_tm_kernel<<<grid, kTcThreads, fwd2::SMEM, (cudaStream_t)stream_>>>(mq, mk128, mv, p);
-  return msamp_check_launch("attn_fwd_tm_kernel");
+  // MSAMP_ATTN_FWD_PERSIST=1 runs persistent CTAs over the work items instead of one CTA per (query tile, batch, head)
+  static const bool persistent = [] { const char* e = getenv("MSAMP_ATTN_FWD_PERSIST"); return e && e[0] == '1'; }();
+  if (!persistent) {
+    if ((rc = set_smem(attn_fwd_tm_kernel, fwd2::SMEM))) return rc;
+    attn_fwd_tm_kernel<<<grid, kTcThreads, fwd2::SMEM, (cudaStream_t)stream_>>>(mq, mk128, mv, p);
+    return msamp_check_launch("attn_fwd_tm_kernel");
+  }
+  const int n_qt = (seqlen + 127) / 128;
+  const int n_items = n_qt * batch * heads;
+  const int ctas = n_items < msamp_sm_count() ? n_items : msamp_sm_count();
+  if ((rc = set_smem(attn_fwd_ps_kernel, fwd3::SMEM3))) return rc;
+  attn_fwd_ps_kernel<<<ctas, kTcThreads, fwd3::SMEM3, (cudaStream_t)stream_>>>(mq, mk128, mv, p, n_qt, n_items);
+  return msamp_check_launch("attn_fwd_ps_kernel");
 }
 
 // Same contract as msamp_attention_bwd (attention.cu) for head_dim 128.
