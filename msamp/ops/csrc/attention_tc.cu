@@ -675,6 +675,13 @@ attn_fwd_ps_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
   const int n_all = (p.seqlen + 63) / 64;
   // work item -> (query tile, batch * head) and its number of 128-key tiles
   auto item_qt = [&](int item) { return n_qt - 1 - item / bh_total; };
+  // items are sorted by falling length; CTA c takes one item per wave of gridDim.x items, walking even waves upwards
+  // and odd waves downwards, so that the per-CTA sums stay within about one tile of each other
+  const int n_waves = (n_items + (int)gridDim.x - 1) / (int)gridDim.x;
+  auto item_at = [&](int w) {
+    const int c = (w & 1) ? (int)gridDim.x - 1 - (int)blockIdx.x : (int)blockIdx.x;
+    return w * (int)gridDim.x + c;
+  };
   auto item_tiles = [&](int qt) {
     const int n_kv = p.causal ? min(2 * qt + 2, n_all) : n_all;
     return (n_kv + 1) >> 1;
@@ -720,7 +727,9 @@ attn_fwd_ps_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       int gt = 0;    // 128-key tiles loaded so far (all items)
       bool ok = true;
       int it = 0;
-      for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++it) {
+      for (int w = 0; w < n_waves && ok; ++w) {
+        const int item = item_at(w);
+        if (item >= n_items) continue;
         const int qt = item_qt(item);
         const int bh = item % bh_total;
         const int b = bh / p.heads, h = bh - b * p.heads;
@@ -744,6 +753,7 @@ attn_fwd_ps_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             tc5::tma_load_4d(base + OFF_V + vs * TILE_V + PANEL_V, &map_v, 64, h, (2 * t + g) * 64, b, bar(B_VF + vs));
           }
         }
+        ++it;
       }
     }
   } else if (warp == 1) {
@@ -768,7 +778,9 @@ attn_fwd_ps_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       int g0 = 0;    // tiles of earlier items
       bool ok = true;
       int it = 0;
-      for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++it) {
+      for (int w = 0; w < n_waves && ok; ++w) {
+        const int item = item_at(w);
+        if (item >= n_items) continue;
         const int n_t = item_tiles(item_qt(item));
         if (!tc5::mbar_wait(bar(B_Q), (uint32_t)it & 1u, abort_flag, p.status, kStatusBit)) { ok = false; break; }
         for (int t = 0; t < 2 && t < n_t; ++t)
@@ -802,6 +814,7 @@ attn_fwd_ps_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         }
         if (ok) tc5::mma_commit(bar(B_ACC));
         g0 += n_t;
+        ++it;
       }
     }
   } else {
@@ -815,7 +828,9 @@ attn_fwd_ps_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     int g0 = 0;
     bool ok = true;
     int it = 0;
-    for (int item = blockIdx.x; item < n_items; item += gridDim.x, ++it) {
+    for (int w = 0; w < n_waves; ++w) {
+      const int item = item_at(w);
+      if (item >= n_items) continue;
       const int qt = item_qt(item);
       const int bh = item % bh_total;
       const int b = bh / p.heads, h = bh - b * p.heads;
@@ -931,6 +946,7 @@ attn_fwd_ps_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       }
       if (wg == 0 && grow < p.seqlen) p.lse[(int64_t)bh * p.seqlen + grow] = lt > 0.0f ? mm * kLn2 + logf(lt) : -INFINITY;
       g0 += n_t;
+      ++it;
     }
   }
 
@@ -2091,8 +2107,8 @@ MSAMP_API int msamp_attention_tc_fwd(const void* q, const void* k, const void* v
   }
   CUtensorMap mk128;
   if ((rc = make_map4(k, batch, heads, seqlen, strides[3], strides[4], strides[5], 128, &mk128))) return rc;
-  // MSAMP_ATTN_FWD_PERSIST=1 runs persistent CTAs over the work items instead of one CTA per (query tile, batch, head)
-  static const bool persistent = [] { const char* e = getenv("MSAMP_ATTN_FWD_PERSIST"); return e && e[0] == '1'; }();
+  // MSAMP_ATTN_FWD_PERSIST=0 launches one CTA per (query tile, batch, head) instead of persistent CTAs
+  static const bool persistent = [] { const char* e = getenv("MSAMP_ATTN_FWD_PERSIST"); return !(e && e[0] == '0'); }();
   if (!persistent) {
     if ((rc = set_smem(attn_fwd_tm_kernel, fwd2::SMEM))) return rc;
     attn_fwd_tm_kernel<<<grid, kTcThreads, fwd2::SMEM, (cudaStream_t)stream_>>>(mq, mk128, mv, p);
