@@ -232,6 +232,54 @@ class FP8FullyShardedDataParallel(torch.nn.Module):
         from msamp.parallel.hp_shard import HighPrecisionShards
         dev = first.device if first is not None else (self.hp_params[0].device if self.hp_params else torch.device('cpu'))
         self.hp = HighPrecisionShards(self.hp_params, process_group, shard=True, device=dev)
+        self._flatten_weight_metas(dev)
+
+    def _flatten_weight_metas(self, dev):
+        """Put the scalars that the re-quantisation of the weight shards reads and writes (the masters' amax and scale_inv,
+        the shards' amax, scale and scale_inv) into flat vectors, each meta keeping a view: one MAX all-reduce, one
+        vectorised scale computation and one multi-tensor cast then serve all sharded linears of a step."""
+        n = len(self.sharded)
+        if n == 0:
+            return
+        f = lambda fill: torch.full((n, ), fill, dtype=torch.float32, device=dev)    # noqa: E731
+        self._m_amax, self._m_sinv = f(0.0), f(1.0)
+        self._w_amax, self._w_scale, self._w_sinv, self._factor = f(0.0), f(1.0), f(1.0), f(1.0)
+        for i, m in enumerate(self.sharded):
+            for meta, amax, scale, sinv in ((m.master.meta, self._m_amax, None, self._m_sinv), (m.weight_meta, self._w_amax, self._w_scale, self._w_sinv)):
+                was_locked, meta.locked = meta.locked, False
+                amax[i:i + 1].copy_(meta.amax[0:1])
+                meta.amax = amax[i:i + 1]
+                sinv[i].copy_(meta.scale_inv)
+                meta.scale_inv = sinv[i:i + 1].view(())
+                if scale is not None:
+                    scale[i].copy_(meta.scale)
+                    meta.scale = scale[i:i + 1].view(())
+                meta.locked = was_locked
+        self._factor_views = [self._factor[i:i + 1].view(()) for i in range(n)]
+
+    @torch.no_grad()
+    def _requantize_all(self):
+        """Master shards -> e4m3 shards (and their transposes), every tensor with its tensor-wide scale: the amax of
+        every master is agreed across the shards by ONE MAX all-reduce, the scales come from one vectorised application of
+        the power-of-two rule, and one multi-tensor launch casts all shards (``ShardedFP8Linear.requantize`` is the
+        per-module form of the same arithmetic)."""
+        ms = self.sharded
+        if not ms:
+            return
+        from msamp.common.dtype import Floating
+        from msamp.ops import multi_tensor as _mt
+        self._w_amax.copy_(self._m_amax)
+        if self.world > 1:
+            dist.all_reduce(self._w_amax, op=dist.ReduceOp.MAX, group=self.group)
+        self._w_scale.copy_(ScalingMeta.compute_scaling_factor(self._w_amax, self._w_scale, Floating.qfp_max[E4M3], 0))
+        torch.reciprocal(self._w_scale, out=self._w_sinv)
+        torch.mul(self._w_scale, self._m_sinv, out=self._factor)
+        # in place: the shards keep their addresses (peers hold mappings of them).  No peer reads them between the last
+        # fused call of backward and the first of the next forward: every fused call ends with a cross-rank barrier.
+        _mt.cast_to_fp8_multi([m.master.value.view(-1) for m in ms], [m.weight_shard.view(-1) for m in ms], E4M3, self._factor_views,
+                              tag='fsdp_requant')
+        for m in ms:
+            _k.transpose_fp8(m.weight_shard, out=m.weight_shard_t)
 
     def _convert(self, module, min_numel):
         if isinstance(module, (torch.nn.Linear, FP8Linear)) and not getattr(module, 'use_fp32_linear', False):
@@ -280,8 +328,8 @@ class FP8FullyShardedDataParallel(torch.nn.Module):
             self.clip_grad_norm_(clip_grad)
         optimizer.step()
         self.hp.gather_params()
+        self._requantize_all()
         for m in self.sharded:
-            m.requantize()
             m.master.grad = None
         self.hp.clear_grads()
 
