@@ -647,7 +647,7 @@ constexpr int SMEM3 = OFF_BAR3 + NBAR3 * 8 + 16 + 1024;
 }    // namespace fwd3
 
 // The schedule of attn_fwd_tm_kernel with one CTA per SM that walks a list of work items (query tile, batch * head),
-// longest rows first, item i of CTA c = c + i * gridDim.x.  Every ring (K, V, score slots) and every barrier keeps
+// grouped by head and by falling length (see item_qt below).  Every ring (K, V, score slots) and every barrier keeps
 // running across items, so the TMA warp loads Q, K and V of the next item while the softmax warps are still in the
 // epilogue of the current one, and the MMA warp has the first two score tiles of the next item ready when they return:
 // the ~8 k cycles of prologue and epilogue per item (of ~23 k on average for sequence 2048) are hidden.  Two extra
@@ -674,7 +674,21 @@ attn_fwd_ps_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
   const int bh_total = p.batch * p.heads;
   const int n_all = (p.seqlen + 63) / 64;
   // work item -> (query tile, batch * head) and its number of 128-key tiles
-  auto item_qt = [&](int item) { return n_qt - 1 - item / bh_total; };
+  // Items are ordered in groups of G (batch, head) pairs, inside a group by falling query tile (= falling length), so
+  // that the CTAs of a few consecutive waves work on the same heads: a head's K and V (1 MB at sequence 2048) are read
+  // from HBM by its longest rows and found in L2 by the others (with all heads of one query-tile level in a wave the
+  // kernel read K / V 3.9 times).  G * n_qt is about four waves, which the snake walk below balances exactly.
+  const int G = max(1, (4 * (int)gridDim.x) / n_qt);
+  auto item_qt = [&](int item) {
+    const int g = item / (G * n_qt);
+    const int hg = min(G, bh_total - g * G);
+    return n_qt - 1 - (item - g * G * n_qt) / hg;
+  };
+  auto item_bh = [&](int item) {
+    const int g = item / (G * n_qt);
+    const int hg = min(G, bh_total - g * G);
+    return g * G + (item - g * G * n_qt) % hg;
+  };
   // items are sorted by falling length; CTA c takes one item per wave of gridDim.x items, walking even waves upwards
   // and odd waves downwards, so that the per-CTA sums stay within about one tile of each other
   const int n_waves = (n_items + (int)gridDim.x - 1) / (int)gridDim.x;
@@ -731,7 +745,7 @@ attn_fwd_ps_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         const int item = item_at(w);
         if (item >= n_items) continue;
         const int qt = item_qt(item);
-        const int bh = item % bh_total;
+        const int bh = item_bh(item);
         const int b = bh / p.heads, h = bh - b * p.heads;
         const int n_t = item_tiles(qt);
         if (it > 0 && !tc5::mbar_wait(bar(B3_QE), (uint32_t)(it - 1) & 1u, abort_flag, p.status, kStatusBit)) break;
@@ -832,7 +846,7 @@ attn_fwd_ps_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       const int item = item_at(w);
       if (item >= n_items) continue;
       const int qt = item_qt(item);
-      const int bh = item % bh_total;
+      const int bh = item_bh(item);
       const int b = bh / p.heads, h = bh - b * p.heads;
       const int n_t = item_tiles(qt);
       const int q0 = qt * 128;
