@@ -2003,6 +2003,595 @@ attn_bwd_dq_tm_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
   if (warp == 1) tc5::tmem_dealloc(tmem_base, TM_COLS);
 }
 
+// ============================================================================ dQ, persistent CTAs over the work items
+namespace dqk3 {
+using namespace dqk2;
+enum { B3_QE = NBAR, B3_OE = NBAR + 1, NBAR3 = NBAR + 2 };
+constexpr int SMEM3 = OFF_BAR + NBAR3 * 8 + 16 + 1024;
+}    // namespace dqk3
+
+// Work item -> (level, batch * head) for the persistent attention kernels: groups of G heads, inside a group by rising
+// level (level 0 is the longest row), so that consecutive waves work on the same heads (their K / V or Q / dO stay in
+// L2) and a walk that alternates direction per wave gives every CTA the same amount of work per group.
+struct ItemOrder {
+  int n_lv, bh_total, G;
+  __device__ __forceinline__ void decode(int item, int& level, int& bh) const {
+    const int g = item / (G * n_lv);
+    const int hg = min(G, bh_total - g * G);
+    const int j = item - g * G * n_lv;
+    level = j / hg;
+    bh = g * G + j % hg;
+  }
+};
+
+// attn_bwd_dq_tm_kernel with one CTA per SM walking the (query tile, batch * head) items.  Rings, the score tile and
+// the dP tiles keep running across items (one global tile counter), so Q / dO / K / V of the next item are loaded and
+// its first score products issued while the softmax warps still store dQ of the current one.  B3_QE: the score products
+// of an item are complete, Q and dO may be overwritten; B3_OE: the softmax warps have read dQ, the accumulator may be
+// overwritten by the first product of the next item.
+__global__ void __launch_bounds__(kTcThreads, 1)
+attn_bwd_dq_ps_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                      const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do, const TcParams p, int n_qt,
+                      int n_items) {
+  using namespace dqk3;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = tc5::smem_u32(smem_raw);
+  const uint32_t base = (raw_addr + 1023u) & ~1023u;
+  uint8_t* smem = smem_raw + (base - raw_addr);
+  const uint32_t bars = base + OFF_BAR;
+  auto bar = [&](int i) { return bars + 8u * (uint32_t)i; };
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(smem + OFF_BAR + NBAR3 * 8);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+  auto wait_warp = [&](uint32_t br, uint32_t ph) {
+    return __all_sync(0xffffffffu, tc5::mbar_wait(br, ph, abort_flag, p.status, kStatusBit)) != 0;
+  };
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int nk_all = (p.seqlen + 63) / 64;
+  const ItemOrder order{n_qt, p.batch * p.heads, max(1, (4 * (int)gridDim.x) / n_qt)};
+  const int n_waves = (n_items + (int)gridDim.x - 1) / (int)gridDim.x;
+  auto item_at = [&](int w) {
+    const int c = (w & 1) ? (int)gridDim.x - 1 - (int)blockIdx.x : (int)blockIdx.x;
+    return w * (int)gridDim.x + c;
+  };
+  auto tiles_of = [&](int qt) {
+    const int n_kv = p.causal ? min(2 * qt + 2, nk_all) : nk_all;
+    return (n_kv + 1) >> 1;
+  };
+
+  if (threadIdx.x == 0) {
+    tc5::mbar_init(bar(B_Q), 1);
+    for (int s = 0; s < NK; ++s) {
+      tc5::mbar_init(bar(B_KF + s), 1);
+      tc5::mbar_init(bar(B_KE + s), 1);
+    }
+    for (int s = 0; s < NV; ++s) {
+      tc5::mbar_init(bar(B_VF + s), 1);
+      tc5::mbar_init(bar(B_VE + s), 1);
+    }
+    tc5::mbar_init(bar(B_SF), 1);
+    tc5::mbar_init(bar(B_SE), 8);
+    for (int s = 0; s < 2; ++s) {
+      tc5::mbar_init(bar(B_DF + s), 1);
+      tc5::mbar_init(bar(B_PF + s), 8);
+    }
+    tc5::mbar_init(bar(B_ACC), 1);
+    tc5::mbar_init(bar(B3_QE), 1);
+    tc5::mbar_init(bar(B3_OE), 8);
+    *abort_flag = 0;
+    tc5::mbar_fence_init();
+    tc5::tma_prefetch_desc(&map_q);
+    tc5::tma_prefetch_desc(&map_k);
+    tc5::tma_prefetch_desc(&map_v);
+    tc5::tma_prefetch_desc(&map_do);
+  }
+  if (warp == 1) {
+    tc5::tmem_alloc(tc5::smem_u32(tmem_holder), TM_COLS);
+    tc5::tmem_relinquish();
+  }
+  tc5::fence_before_sync();
+  __syncthreads();
+  tc5::fence_after_sync();
+  const uint32_t tmem_base = *tmem_holder;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int gt = 0, it = 0;
+      bool ok = true;
+      for (int w = 0; w < n_waves && ok; ++w) {
+        const int item = item_at(w);
+        if (item >= n_items) continue;
+        int level, bh;
+        order.decode(item, level, bh);
+        const int qt = n_qt - 1 - level;
+        const int b = bh / p.heads, h = bh - b * p.heads;
+        const int n_t = tiles_of(qt);
+        if (it > 0 && !tc5::mbar_wait(bar(B3_QE), (uint32_t)(it - 1) & 1u, abort_flag, p.status, kStatusBit)) break;
+        tc5::mbar_arrive_expect_tx(bar(B_Q), 2 * TILE);
+        tc5::tma_load_4d(base + OFF_Q, &map_q, 0, h, qt * 128, b, bar(B_Q));
+        tc5::tma_load_4d(base + OFF_Q + PANEL, &map_q, 64, h, qt * 128, b, bar(B_Q));
+        tc5::tma_load_4d(base + OFF_DO, &map_do, 0, h, qt * 128, b, bar(B_Q));
+        tc5::tma_load_4d(base + OFF_DO + PANEL, &map_do, 64, h, qt * 128, b, bar(B_Q));
+        for (int t = 0; t < n_t; ++t, ++gt) {
+          const int ks = gt % NK, vs = gt % NV;
+          if (!tc5::mbar_wait(bar(B_KE + ks), ((uint32_t)(gt / NK) & 1u) ^ 1u, abort_flag, p.status, kStatusBit)) { ok = false; break; }
+          tc5::mbar_arrive_expect_tx(bar(B_KF + ks), TILE);
+          tc5::tma_load_4d(base + OFF_K + ks * TILE, &map_k, 0, h, t * 128, b, bar(B_KF + ks));
+          tc5::tma_load_4d(base + OFF_K + ks * TILE + PANEL, &map_k, 64, h, t * 128, b, bar(B_KF + ks));
+          if (!tc5::mbar_wait(bar(B_VE + vs), ((uint32_t)(gt / NV) & 1u) ^ 1u, abort_flag, p.status, kStatusBit)) { ok = false; break; }
+          tc5::mbar_arrive_expect_tx(bar(B_VF + vs), TILE);
+          tc5::tma_load_4d(base + OFF_V + vs * TILE, &map_v, 0, h, t * 128, b, bar(B_VF + vs));
+          tc5::tma_load_4d(base + OFF_V + vs * TILE + PANEL, &map_v, 64, h, t * 128, b, bar(B_VF + vs));
+        }
+        ++it;
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc_s = tc5::idesc_bf16(128, 128, 0, 0);
+      const uint32_t idesc_acc = tc5::idesc_bf16(128, 128, 0, 1);
+      // S = Q K^T and dP[gt & 1] = dO V^T for the gt-th tile of this CTA
+      auto issue_s = [&](int gt) -> bool {
+        const int ks = gt % NK, vs = gt % NV;
+        if (gt > 0 && !tc5::mbar_wait(bar(B_SE), (uint32_t)(gt - 1) & 1u, abort_flag, p.status, kStatusBit)) return false;
+        if (!tc5::mbar_wait(bar(B_KF + ks), (uint32_t)(gt / NK) & 1u, abort_flag, p.status, kStatusBit)) return false;
+        tc5::fence_after_sync();
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint32_t off = (uint32_t)(kk >> 2) * PANEL + (uint32_t)(kk & 3) * 32u;
+          tc5::mma_f16(tmem_base + TM_S, tc5::smem_desc_k_sw128(base + OFF_Q + off), tc5::smem_desc_k_sw128(base + OFF_K + ks * TILE + off),
+                       idesc_s, kk ? 1u : 0u);
+        }
+        tc5::mma_commit(bar(B_SF));
+        if (!tc5::mbar_wait(bar(B_VF + vs), (uint32_t)(gt / NV) & 1u, abort_flag, p.status, kStatusBit)) return false;
+        tc5::fence_after_sync();
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint32_t off = (uint32_t)(kk >> 2) * PANEL + (uint32_t)(kk & 3) * 32u;
+          tc5::mma_f16(tmem_base + TM_DP + (uint32_t)(gt & 1) * 128u, tc5::smem_desc_k_sw128(base + OFF_DO + off),
+                       tc5::smem_desc_k_sw128(base + OFF_V + vs * TILE + off), idesc_s, kk ? 1u : 0u);
+        }
+        tc5::mma_commit(bar(B_VE + vs));
+        tc5::mma_commit(bar(B_DF + (gt & 1)));
+        return true;
+      };
+      int g0 = 0, it = 0;
+      bool ok = true;
+      for (int w = 0; w < n_waves && ok; ++w) {
+        const int item = item_at(w);
+        if (item >= n_items) continue;
+        int level, bh;
+        order.decode(item, level, bh);
+        const int n_t = tiles_of(n_qt - 1 - level);
+        if (!tc5::mbar_wait(bar(B_Q), (uint32_t)it & 1u, abort_flag, p.status, kStatusBit)) { ok = false; break; }
+        if (!issue_s(g0)) { ok = false; break; }
+        if (n_t == 1) tc5::mma_commit(bar(B3_QE));
+        if (it > 0 && !tc5::mbar_wait(bar(B3_OE), (uint32_t)(it - 1) & 1u, abort_flag, p.status, kStatusBit)) { ok = false; break; }
+        for (int t = 0; t < n_t; ++t) {
+          const int gt = g0 + t;
+          if (t + 1 < n_t) {
+            if (!issue_s(gt + 1)) { ok = false; break; }
+            if (t + 2 == n_t) tc5::mma_commit(bar(B3_QE));    // every score product of this item is issued
+          }
+          const int ks = gt % NK;
+          if (!tc5::mbar_wait(bar(B_PF + (gt & 1)), (uint32_t)(gt >> 1) & 1u, abort_flag, p.status, kStatusBit)) { ok = false; break; }
+          tc5::fence_after_sync();
+#pragma unroll
+          for (int kk = 0; kk < 8; ++kk) {
+            tc5::mma_f16_ta(tmem_base + TM_DQ,
+                            tmem_base + TM_DP + (uint32_t)(gt & 1) * 128u + (uint32_t)(kk >> 2) * 64u + (uint32_t)(kk & 3) * 8u,
+                            tc5::smem_desc_mn_sw128(base + OFF_K + ks * TILE + (uint32_t)kk * 2048u, PANEL), idesc_acc, (t | kk) ? 1u : 0u);
+          }
+          tc5::mma_commit(bar(B_KE + ks));
+        }
+        if (!ok) break;
+        tc5::mma_commit(bar(B_ACC));
+        g0 += n_t;
+        ++it;
+      }
+    }
+  } else {
+    const int qd = warp & 3;
+    const int wg = (warp - 2) >> 2;    // group g: the g-th 64-key half of every tile
+    const int row = qd * 32 + lane;
+    const uint32_t tlane = tmem_base + ((uint32_t)(qd * 32) << 16);
+    const float sl = p.scale * kLog2e;
+    int g0 = 0, it = 0;
+    bool ok = true;
+    for (int w = 0; w < n_waves && ok; ++w) {
+      const int item = item_at(w);
+      if (item >= n_items) continue;
+      int level, bh;
+      order.decode(item, level, bh);
+      const int qt = n_qt - 1 - level;
+      const int b = bh / p.heads, h = bh - b * p.heads;
+      const int n_t = tiles_of(qt);
+      const int q0 = qt * 128;
+      const int grow = q0 + row;
+      const bool in = grow < p.seqlen;
+      const float lse2 = in ? p.lse[(int64_t)bh * p.seqlen + grow] * kLog2e : INFINITY;
+      const float dlt = in ? p.delta[(int64_t)bh * p.seqlen + grow] : 0.0f;
+      const int lim = p.causal ? min(grow, p.seqlen - 1) : p.seqlen - 1;
+      for (int t = 0; t < n_t; ++t) {
+        const int gt = g0 + t;
+        const int col0 = (2 * t + wg) * 64;
+        const uint32_t tdp = tlane + TM_DP + (uint32_t)(gt & 1) * 128u + (uint32_t)wg * 64u;
+        if (!wait_warp(bar(B_SF), (uint32_t)gt & 1u)) { ok = false; break; }
+        tc5::fence_after_sync();
+        const bool need_mask = (p.causal && col0 + 63 > q0) || (col0 + 64 > p.seqlen);
+        uint32_t rs[2][32], rd[2][32];
+        tc5::tmem_ld32(tlane + TM_S + (uint32_t)wg * 64u, rs[0]);
+        tc5::tmem_ld32(tlane + TM_S + (uint32_t)wg * 64u + 32u, rs[1]);
+        tc5::tmem_ld_wait();
+        tc5::fence_before_sync();
+        __syncwarp();
+        if (lane == 0) tc5::mbar_arrive(bar(B_SE));    // the score tile may take the next tile
+        if (!wait_warp(bar(B_DF + (gt & 1)), (uint32_t)(gt >> 1) & 1u)) { ok = false; break; }
+        tc5::fence_after_sync();
+        tc5::tmem_ld32(tdp, rd[0]);
+        tc5::tmem_ld32(tdp + 32u, rd[1]);
+        tc5::tmem_ld_wait();
+        uint32_t pk[32];
+#pragma unroll
+        for (int g = 0; g < 8; ++g) {    // keys 8g .. 8g+7 of this half -> packed columns 4g .. 4g+3
+          float ds[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int c = g * 8 + i;
+            float e = ex2(fmaf(__uint_as_float(rs[c >> 5][c & 31]), sl, -lse2));
+            if (need_mask && col0 + c > lim) e = 0.0f;
+            ds[i] = e * (__uint_as_float(rd[c >> 5][c & 31]) - dlt);
+          }
+          pk[4 * g] = pack_bf16(ds[0], ds[1]);
+          pk[4 * g + 1] = pack_bf16(ds[2], ds[3]);
+          pk[4 * g + 2] = pack_bf16(ds[4], ds[5]);
+          pk[4 * g + 3] = pack_bf16(ds[6], ds[7]);
+        }
+        tc5::tmem_st32(tdp, pk);
+        tc5::tmem_st_wait();
+        tc5::fence_before_sync();
+        __syncwarp();
+        if (lane == 0) tc5::mbar_arrive(bar(B_PF + (gt & 1)));
+      }
+      if (!ok || !wait_warp(bar(B_ACC), (uint32_t)it & 1u)) { ok = false; break; }
+      tc5::fence_after_sync();
+      __nv_bfloat16* dq = p.dq + (int64_t)b * p.dq_sb + (int64_t)grow * p.dq_ss + (int64_t)h * p.dq_sh;
+      // each group stores one half of the row
+      uint32_t r0[32], r1[32];
+      float v[32];
+      tc5::tmem_ld32(tlane + TM_DQ + (uint32_t)wg * 64u, r0);
+      tc5::tmem_ld32(tlane + TM_DQ + (uint32_t)wg * 64u + 32u, r1);
+      tc5::tmem_ld_wait();
+      tc5::fence_before_sync();
+      __syncwarp();
+      if (lane == 0) tc5::mbar_arrive(bar(B3_OE));    // the accumulator may take the next item
+#pragma unroll
+      for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r0[i]) * p.scale;
+      if (in) st_row32(dq + wg * 64, v);
+#pragma unroll
+      for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r1[i]) * p.scale;
+      if (in) st_row32(dq + wg * 64 + 32, v);
+      g0 += n_t;
+      ++it;
+    }
+  }
+
+  __syncwarp();
+  if (*abort_flag) __nanosleep(200000);
+  tc5::fence_before_sync();
+  __syncthreads();
+  tc5::fence_after_sync();
+  if (warp == 1) tc5::tmem_dealloc(tmem_base, TM_COLS);
+}
+
+// ====================================================================== dK / dV, persistent CTAs over the work items
+namespace dkv3 {
+using namespace dkv2;
+enum { B3_KVE = NBAR, B3_OE = NBAR + 1, NBAR3 = NBAR + 2 };
+constexpr int SMEM3 = OFF_BAR + NBAR3 * 8 + 16 + 896;
+static_assert(SMEM3 <= 227 * 1024, "persistent dK/dV kernel: shared memory");
+}    // namespace dkv3
+
+// attn_bwd_dkdv_tm_kernel with one CTA per SM walking the (key tile, batch * head) items; the Q / dO stages, the score
+// tiles and all barriers keep running across items (one global query-tile counter).  B3_KVE: every S^T / dP^T product of
+// an item is complete, K and V may be overwritten by the next item's; B3_OE: the softmax warps have read dV and dK, the
+// first products of the next item may overwrite the accumulators.
+__global__ void __launch_bounds__(kTcThreads, 1)
+attn_bwd_dkdv_ps_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                        const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do, const TcParams p, int n_kt,
+                        int n_items) {
+  using namespace dkv3;
+  extern __shared__ __align__(128) uint8_t smem_raw128[];
+  const uint32_t raw_addr = tc5::smem_u32(smem_raw128);
+  const uint32_t base = (raw_addr + 1023u) & ~1023u;
+  uint8_t* smem = smem_raw128 + (base - raw_addr);
+  const uint32_t bars = base + OFF_BAR;
+  auto bar = [&](int i) { return bars + 8u * (uint32_t)i; };
+  float* s_lse = reinterpret_cast<float*>(smem + OFF_LSE);    // [NSQ][128] log2-scaled lse, then [NSQ][128] delta
+  float* s_delta = s_lse + NSQ * 128;
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(smem + OFF_BAR + NBAR3 * 8);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+  auto wait_warp = [&](uint32_t br, uint32_t ph) {
+    return __all_sync(0xffffffffu, tc5::mbar_wait(br, ph, abort_flag, p.status, kStatusBit)) != 0;
+  };
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int nq_all = (p.seqlen + 127) / 128;
+  const ItemOrder order{n_kt, p.batch * p.heads, max(1, (4 * (int)gridDim.x) / n_kt)};
+  const int n_waves = (n_items + (int)gridDim.x - 1) / (int)gridDim.x;
+  auto item_at = [&](int w) {
+    const int c = (w & 1) ? (int)gridDim.x - 1 - (int)blockIdx.x : (int)blockIdx.x;
+    return w * (int)gridDim.x + c;
+  };
+
+  if (threadIdx.x == 0) {
+    tc5::mbar_init(bar(B_KV), 1);
+    for (int s = 0; s < NSQ; ++s) {
+      tc5::mbar_init(bar(B_QF + s), 2);    // TMA bytes + the lse/delta rows written by warp 0
+      tc5::mbar_init(bar(B_QE + s), 9);    // last MMA that reads the stage + eight softmax warps
+    }
+    tc5::mbar_init(bar(B_SF), 1);
+    tc5::mbar_init(bar(B_SE), 8);
+    tc5::mbar_init(bar(B_DF), 1);
+    tc5::mbar_init(bar(B_PF), 8);
+    tc5::mbar_init(bar(B_PE), 1);
+    tc5::mbar_init(bar(B_ACC), 1);
+    tc5::mbar_init(bar(B3_KVE), 1);
+    tc5::mbar_init(bar(B3_OE), 8);
+    *abort_flag = 0;
+    tc5::mbar_fence_init();
+    tc5::tma_prefetch_desc(&map_q);
+    tc5::tma_prefetch_desc(&map_k);
+    tc5::tma_prefetch_desc(&map_v);
+    tc5::tma_prefetch_desc(&map_do);
+  }
+  if (warp == 1) {
+    tc5::tmem_alloc(tc5::smem_u32(tmem_holder), TM_COLS);
+    tc5::tmem_relinquish();
+  }
+  tc5::fence_before_sync();
+  __syncthreads();
+  tc5::fence_after_sync();
+  const uint32_t tmem_base = *tmem_holder;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ producer (whole warp: lane 0 issues TMA)
+    int gq = 0, it = 0;
+    bool ok = true;
+    for (int w = 0; w < n_waves && ok; ++w) {
+      const int item = item_at(w);
+      if (item >= n_items) continue;
+      int kt, bh;
+      order.decode(item, kt, bh);
+      const int b = bh / p.heads, h = bh - b * p.heads;
+      const int k0 = kt * 128;
+      const int t_first = p.causal ? kt : 0;
+      const int n_q = nq_all - t_first;
+      if (it > 0 && !__all_sync(0xffffffffu, tc5::mbar_wait(bar(B3_KVE), (uint32_t)(it - 1) & 1u, abort_flag, p.status, kStatusBit))) break;
+      if (lane == 0) {
+        tc5::mbar_arrive_expect_tx(bar(B_KV), 2 * TILE);
+        tc5::tma_load_4d(base + OFF_K, &map_k, 0, h, k0, b, bar(B_KV));
+        tc5::tma_load_4d(base + OFF_K + PANEL, &map_k, 64, h, k0, b, bar(B_KV));
+        tc5::tma_load_4d(base + OFF_V, &map_v, 0, h, k0, b, bar(B_KV));
+        tc5::tma_load_4d(base + OFF_V + PANEL, &map_v, 64, h, k0, b, bar(B_KV));
+      }
+      const float* glse = p.lse + (int64_t)bh * p.seqlen;
+      const float* gdelta = p.delta + (int64_t)bh * p.seqlen;
+      for (int t = 0; t < n_q; ++t, ++gq) {
+        const int s = gq % NSQ;
+        const int qrow0 = (t_first + t) * 128;
+        if (!__all_sync(0xffffffffu, tc5::mbar_wait(bar(B_QE + s), ((uint32_t)(gq / NSQ) & 1u) ^ 1u, abort_flag, p.status, kStatusBit))) { ok = false; break; }
+        if (lane == 0) {
+          tc5::mbar_arrive_expect_tx(bar(B_QF + s), 2 * TILE);
+          tc5::tma_load_4d(base + OFF_Q + s * TILE, &map_q, 0, h, qrow0, b, bar(B_QF + s));
+          tc5::tma_load_4d(base + OFF_Q + s * TILE + PANEL, &map_q, 64, h, qrow0, b, bar(B_QF + s));
+          tc5::tma_load_4d(base + OFF_DO + s * TILE, &map_do, 0, h, qrow0, b, bar(B_QF + s));
+          tc5::tma_load_4d(base + OFF_DO + s * TILE + PANEL, &map_do, 64, h, qrow0, b, bar(B_QF + s));
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int r = lane + 32 * i;
+          const bool in = qrow0 + r < p.seqlen;
+          s_lse[s * 128 + r] = in ? glse[qrow0 + r] * kLog2e : INFINITY;    // +inf makes the probability exactly zero
+          s_delta[s * 128 + r] = in ? gdelta[qrow0 + r] : 0.0f;
+        }
+        __syncwarp();
+        if (lane == 0) tc5::mbar_arrive(bar(B_QF + s));
+      }
+      ++it;
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc_s = tc5::idesc_bf16(128, 128, 0, 0);
+      const uint32_t idesc_acc = tc5::idesc_bf16(128, 128, 0, 1);
+      auto issue_st = [&](int gq) -> bool {    // S^T = K Q^T for the gq-th query tile of this CTA
+        const int st = gq % NSQ;
+        if (gq > 0 && !tc5::mbar_wait(bar(B_SE), (uint32_t)(gq - 1) & 1u, abort_flag, p.status, kStatusBit)) return false;
+        if (!tc5::mbar_wait(bar(B_QF + st), (uint32_t)(gq / NSQ) & 1u, abort_flag, p.status, kStatusBit)) return false;
+        tc5::fence_after_sync();
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint32_t off = (uint32_t)(kk >> 2) * PANEL + (uint32_t)(kk & 3) * 32u;
+          tc5::mma_f16(tmem_base + TM_ST, tc5::smem_desc_k_sw128(base + OFF_K + off), tc5::smem_desc_k_sw128(base + OFF_Q + st * TILE + off),
+                       idesc_s, kk ? 1u : 0u);
+        }
+        tc5::mma_commit(bar(B_SF));
+        return true;
+      };
+      auto issue_dpt = [&](int gq) {    // dP^T = V dO^T (the stage was waited for by issue_st(gq))
+        const int st = gq % NSQ;
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint32_t off = (uint32_t)(kk >> 2) * PANEL + (uint32_t)(kk & 3) * 32u;
+          tc5::mma_f16(tmem_base + TM_DPT, tc5::smem_desc_k_sw128(base + OFF_V + off), tc5::smem_desc_k_sw128(base + OFF_DO + st * TILE + off),
+                       idesc_s, kk ? 1u : 0u);
+        }
+        tc5::mma_commit(bar(B_DF));
+      };
+      int g0 = 0, it = 0;
+      bool ok = true;
+      for (int w = 0; w < n_waves && ok; ++w) {
+        const int item = item_at(w);
+        if (item >= n_items) continue;
+        int kt, bh;
+        order.decode(item, kt, bh);
+        const int n_q = nq_all - (p.causal ? kt : 0);
+        if (!tc5::mbar_wait(bar(B_KV), (uint32_t)it & 1u, abort_flag, p.status, kStatusBit)) { ok = false; break; }
+        if (!issue_st(g0)) { ok = false; break; }
+        issue_dpt(g0);
+        if (n_q == 1) tc5::mma_commit(bar(B3_KVE));
+        if (it > 0 && !tc5::mbar_wait(bar(B3_OE), (uint32_t)(it - 1) & 1u, abort_flag, p.status, kStatusBit)) { ok = false; break; }
+        for (int t = 0; t < n_q; ++t) {
+          const int gq = g0 + t;
+          const int st = gq % NSQ;
+          bool pending = t + 1 < n_q;
+          if (pending && tc5::mbar_test(bar(B_SE), (uint32_t)gq & 1u) &&
+              tc5::mbar_test(bar(B_QF + (gq + 1) % NSQ), (uint32_t)((gq + 1) / NSQ) & 1u)) {
+            if (!issue_st(gq + 1)) { ok = false; break; }
+            pending = false;
+          }
+          if (!tc5::mbar_wait(bar(B_PF), (uint32_t)gq & 1u, abort_flag, p.status, kStatusBit)) { ok = false; break; }
+          tc5::fence_after_sync();
+#pragma unroll
+          for (int kk = 0; kk < 8; ++kk) {
+            tc5::mma_f16(tmem_base + TM_DV, tc5::smem_desc_k_sw128(base + OFF_PT + (uint32_t)(kk >> 2) * PANEL + (uint32_t)(kk & 3) * 32u),
+                         tc5::smem_desc_mn_sw128(base + OFF_DO + st * TILE + (uint32_t)kk * 2048u, PANEL), idesc_acc, (t | kk) ? 1u : 0u);
+          }
+          tc5::mma_commit(bar(B_PE));
+#pragma unroll
+          for (int kk = 0; kk < 8; ++kk) {
+            tc5::mma_f16_ta(tmem_base + TM_DK, tmem_base + TM_DPT + (uint32_t)(kk >> 2) * 64u + (uint32_t)(kk & 3) * 8u,
+                            tc5::smem_desc_mn_sw128(base + OFF_Q + st * TILE + (uint32_t)kk * 2048u, PANEL), idesc_acc, (t | kk) ? 1u : 0u);
+          }
+          tc5::mma_commit(bar(B_QE + st));
+          if (pending && !issue_st(gq + 1)) { ok = false; break; }
+          if (t + 1 < n_q) {
+            issue_dpt(gq + 1);
+            if (t + 2 == n_q) tc5::mma_commit(bar(B3_KVE));    // every S^T / dP^T product of this item is issued
+          }
+        }
+        if (!ok) break;
+        tc5::mma_commit(bar(B_ACC));
+        g0 += n_q;
+        ++it;
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ one thread per key row and query half
+    const int qd = warp & 3;
+    const int wg = (warp - 2) >> 2;    // group g: queries 64 g .. 64 g + 63 of every tile
+    const int row = qd * 32 + lane;
+    const uint32_t tlane = tmem_base + ((uint32_t)(qd * 32) << 16);
+    const float sl = p.scale * kLog2e;
+    const uint32_t prow = base + OFF_PT + (uint32_t)wg * PANEL + (uint32_t)row * 128u;
+    const uint32_t swz = (uint32_t)(row & 7);
+    int g0 = 0, it = 0;
+    bool ok = true;
+    for (int w = 0; w < n_waves && ok; ++w) {
+      const int item = item_at(w);
+      if (item >= n_items) continue;
+      int kt, bh;
+      order.decode(item, kt, bh);
+      const int b = bh / p.heads, h = bh - b * p.heads;
+      const int k0 = kt * 128;
+      const int grow = k0 + row;
+      const int t_first = p.causal ? kt : 0;
+      const int n_q = nq_all - t_first;
+      for (int t = 0; t < n_q; ++t) {
+        const int gq = g0 + t;
+        const int st = gq % NSQ;
+        const int qrow0 = (t_first + t) * 128 + wg * 64;    // first query of this group's half
+        if (!wait_warp(bar(B_QF + st), (uint32_t)(gq / NSQ) & 1u)) { ok = false; break; }
+        if (!wait_warp(bar(B_SF), (uint32_t)gq & 1u)) { ok = false; break; }
+        tc5::fence_after_sync();
+        const bool need_mask = p.causal && (qrow0 < k0 + 128);
+        const float4* lse2 = reinterpret_cast<const float4*>(s_lse + st * 128 + wg * 64);
+        const float4* dlt = reinterpret_cast<const float4*>(s_delta + st * 128 + wg * 64);
+        uint32_t rs[2][32], rd[2][32];
+        tc5::tmem_ld32(tlane + TM_ST + (uint32_t)wg * 64u, rs[0]);
+        tc5::tmem_ld32(tlane + TM_ST + (uint32_t)wg * 64u + 32u, rs[1]);
+        tc5::tmem_ld_wait();
+        tc5::fence_before_sync();
+        __syncwarp();
+        if (lane == 0) tc5::mbar_arrive(bar(B_SE));    // the score tile may take the next tile
+        if (!wait_warp(bar(B_DF), (uint32_t)gq & 1u)) { ok = false; break; }
+        tc5::fence_after_sync();
+        tc5::tmem_ld32(tlane + TM_DPT + (uint32_t)wg * 64u, rd[0]);
+        tc5::tmem_ld32(tlane + TM_DPT + (uint32_t)wg * 64u + 32u, rd[1]);
+        tc5::tmem_ld_wait();
+        if (gq > 0 && !wait_warp(bar(B_PE), (uint32_t)(gq - 1) & 1u)) { ok = false; break; }    // dV of the previous tile has read P^T
+        uint32_t pk[32];
+#pragma unroll
+        for (int g = 0; g < 8; ++g) {    // 16-byte chunk g = queries 8g .. 8g+7 of this half
+          float e[8], ds[8];
+#pragma unroll
+          for (int hh = 0; hh < 2; ++hh) {
+            const float4 l4 = lse2[g * 2 + hh];
+            const float4 d4 = dlt[g * 2 + hh];
+            const float la[4] = {l4.x, l4.y, l4.z, l4.w};
+            const float da[4] = {d4.x, d4.y, d4.z, d4.w};
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              const int i = hh * 4 + u;
+              const int ql = g * 8 + i;
+              float ev = ex2(fmaf(__uint_as_float(rs[ql >> 5][ql & 31]), sl, -la[u]));
+              if (need_mask && qrow0 + ql < grow) ev = 0.0f;
+              e[i] = ev;
+              ds[i] = ev * (__uint_as_float(rd[ql >> 5][ql & 31]) - da[u]);
+            }
+          }
+          st_shared_v4(prow + ((((uint32_t)g) ^ swz) << 4), pack_bf16(e[0], e[1]), pack_bf16(e[2], e[3]), pack_bf16(e[4], e[5]),
+                       pack_bf16(e[6], e[7]));
+          pk[4 * g] = pack_bf16(ds[0], ds[1]);
+          pk[4 * g + 1] = pack_bf16(ds[2], ds[3]);
+          pk[4 * g + 2] = pack_bf16(ds[4], ds[5]);
+          pk[4 * g + 3] = pack_bf16(ds[6], ds[7]);
+        }
+        tc5::tmem_st32(tlane + TM_DPT + (uint32_t)wg * 64u, pk);
+        tc5::tmem_st_wait();
+        tc5::fence_before_sync();
+        fence_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          tc5::mbar_arrive(bar(B_PF));
+          tc5::mbar_arrive(bar(B_QE + st));
+        }
+      }
+      if (!ok || !wait_warp(bar(B_ACC), (uint32_t)it & 1u)) { ok = false; break; }
+      tc5::fence_after_sync();
+      // group 0 stores dV, group 1 stores dK: read the whole accumulator first, so that it is free for the next item
+      __nv_bfloat16* dst = wg == 0 ? p.dv + (int64_t)b * p.dv_sb + (int64_t)grow * p.dv_ss + (int64_t)h * p.dv_sh
+                                   : p.dk + (int64_t)b * p.dk_sb + (int64_t)grow * p.dk_ss + (int64_t)h * p.dk_sh;
+      const float f = wg == 0 ? 1.0f : p.scale;
+      const uint32_t tsrc = tlane + (wg == 0 ? TM_DV : TM_DK);
+      uint32_t acc[4][32];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tc5::tmem_ld32(tsrc + (uint32_t)c * 32u, acc[c]);
+      tc5::tmem_ld_wait();
+      tc5::fence_before_sync();
+      __syncwarp();
+      if (lane == 0) tc5::mbar_arrive(bar(B3_OE));
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        float v[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(acc[c][i]) * f;
+        if (grow < p.seqlen) st_row32(dst + c * 32, v);
+      }
+      g0 += n_q;
+      ++it;
+    }
+  }
+
+  __syncwarp();
+  if (*abort_flag) __nanosleep(200000);
+  tc5::fence_before_sync();
+  __syncthreads();
+  tc5::fence_after_sync();
+  if (warp == 1) tc5::tmem_dealloc(tmem_base, TM_COLS);
+}
+
 // ---- host side -----------------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -2177,8 +2766,17 @@ MSAMP_API int msamp_attention_tc_bwd(const void* q, const void* k, const void* v
       CUtensorMap mq128, mdo128;
       if ((rc = make_map4(q, batch, heads, seqlen, strides[0], strides[1], strides[2], 128, &mq128))) return rc;
       if ((rc = make_map4(d_o, batch, heads, seqlen, strides[12], strides[13], strides[14], 128, &mdo128))) return rc;
-      if ((rc = set_smem(attn_bwd_dkdv_tm_kernel, dkv2::SMEM))) return rc;
-      attn_bwd_dkdv_tm_kernel<<<grid, kTcThreads, dkv2::SMEM, stream>>>(mq128, mk, mv, mdo128, p);
+      static const bool persistent = [] { const char* e = getenv("MSAMP_ATTN_BWD_PERSIST"); return !(e && e[0] == '0'); }();
+      if (persistent) {
+        const int n_kt = (seqlen + 127) / 128;
+        const int n_items = n_kt * batch * heads;
+        const int ctas = n_items < msamp_sm_count() ? n_items : msamp_sm_count();
+        if ((rc = set_smem(attn_bwd_dkdv_ps_kernel, dkv3::SMEM3))) return rc;
+        attn_bwd_dkdv_ps_kernel<<<ctas, kTcThreads, dkv3::SMEM3, stream>>>(mq128, mk, mv, mdo128, p, n_kt, n_items);
+      } else {
+        if ((rc = set_smem(attn_bwd_dkdv_tm_kernel, dkv2::SMEM))) return rc;
+        attn_bwd_dkdv_tm_kernel<<<grid, kTcThreads, dkv2::SMEM, stream>>>(mq128, mk, mv, mdo128, p);
+      }
     }
   }
   {
@@ -2197,8 +2795,18 @@ MSAMP_API int msamp_attention_tc_bwd(const void* q, const void* k, const void* v
       CUtensorMap mk128, mv128;
       if ((rc = make_map4(k, batch, heads, seqlen, strides[3], strides[4], strides[5], 128, &mk128))) return rc;
       if ((rc = make_map4(v, batch, heads, seqlen, strides[6], strides[7], strides[8], 128, &mv128))) return rc;
-      if ((rc = set_smem(attn_bwd_dq_tm_kernel, dqk2::SMEM))) return rc;
-      attn_bwd_dq_tm_kernel<<<grid, kTcThreads, dqk2::SMEM, stream>>>(mq, mk128, mv128, mdo, p);
+      // MSAMP_ATTN_BWD_PERSIST=0: one CTA per (tile, batch, head) instead of persistent CTAs over the work items
+      static const bool persistent = [] { const char* e = getenv("MSAMP_ATTN_BWD_PERSIST"); return !(e && e[0] == '0'); }();
+      if (persistent) {
+        const int n_qt = (seqlen + 127) / 128;
+        const int n_items = n_qt * batch * heads;
+        const int ctas = n_items < msamp_sm_count() ? n_items : msamp_sm_count();
+        if ((rc = set_smem(attn_bwd_dq_ps_kernel, dqk3::SMEM3))) return rc;
+        attn_bwd_dq_ps_kernel<<<ctas, kTcThreads, dqk3::SMEM3, stream>>>(mq, mk128, mv128, mdo, p, n_qt, n_items);
+      } else {
+        if ((rc = set_smem(attn_bwd_dq_tm_kernel, dqk2::SMEM))) return rc;
+        attn_bwd_dq_tm_kernel<<<grid, kTcThreads, dqk2::SMEM, stream>>>(mq, mk128, mv128, mdo, p);
+      }
     }
   }
   return msamp_check_launch("attn_bwd_tc kernels");
