@@ -488,6 +488,44 @@ def test_attention_more_work_items_than_sms(causal):
     assert torch.equal(o2, o) and torch.equal(qkv2.grad, qkv.grad)
 
 
+_ATTN_VARIANT_SCRIPT = """
+import math, sys, torch
+sys.path.insert(0, %r)
+from msamp.ops import native, nn as K
+torch.manual_seed(3)
+B, S, H, d = 2, 640, 4, 128
+qkv = torch.randn(B, S, 3, H, d, device='cuda').bfloat16().requires_grad_()
+o = K.attention_qkv(qkv, causal=True)
+do = torch.randn_like(o)
+o.backward(do)
+assert native.device_status() == 0
+ref = qkv.detach().float().requires_grad_()
+q, k, v = (ref[:, :, i].permute(0, 2, 1, 3) for i in range(3))
+s = (q @ k.transpose(-1, -2)) / math.sqrt(d)
+s = s.masked_fill(torch.ones(S, S, dtype=torch.bool, device='cuda').triu(1), float('-inf'))
+r = (torch.softmax(s, -1) @ v).permute(0, 2, 1, 3)
+r.backward(do.float())
+assert (o.float() - r).abs().max().item() <= 3e-2
+assert (qkv.grad.float() - ref.grad).abs().max().item() <= 3e-2 * max(1.0, ref.grad.abs().max().item())
+print('ok')
+"""
+
+
+@pytest.mark.parametrize('env', [{'MSAMP_ATTN_FWD_PERSIST': '0', 'MSAMP_ATTN_BWD_PERSIST': '0'},
+                                 {'MSAMP_ATTN_FWD_SMEM': '1', 'MSAMP_ATTN_BWD_SMEM': '1'}])
+def test_attention_kernel_variants(env):
+    """The earlier attention kernels stay selectable through environment variables that are read once per process
+    (one CTA per work item instead of persistent CTAs; 64-wide score tiles with P / dS in shared memory): each
+    combination runs in a fresh process against the fp32 reference."""
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    res = subprocess.run([sys.executable, '-c', _ATTN_VARIANT_SCRIPT % root], env=dict(os.environ, **env), capture_output=True, text=True,
+                         timeout=300)
+    assert res.returncode == 0 and 'ok' in res.stdout, res.stderr[-2000:]
+
+
 def test_cross_entropy():
     torch.manual_seed(0)
     rows, vocab = 300, 50304
