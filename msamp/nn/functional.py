@@ -88,6 +88,7 @@ def weight_fp8(weight):
     sinv = torch.empty_like(meta.scale_inv)
     w8 = _k.cast_to_fp8(w2d, E4M3, meta.scale_inv, scale_inv_out=sinv, amax_in=meta.amax[0], rescale=True)
     weight._fp8_cache1 = (key, w8, sinv)
+    weight._wants_fp8_copy = True    # the fused Adam step will deliver the copy of the updated weight (msamp/optim/adamw.py)
     return w8, sinv
 
 

@@ -33,6 +33,8 @@ struct AdamTensor {
   float* v_scale;
   float* v_scale_inv;
   float* v_amax;
+  uint8_t* w8;            // optional: e4m3 copy of the NEW parameter (scaled-fp16 parameters only), written by stage 2
+  float* w8_scale_inv;    // 1 / scale of that copy (written when the metas are published)
   int64_t n;
   int p_st, g_st, m_st, v_st;
   float lr_wd_factor;    // 1 - lr * wd (decoupled) or 1
@@ -221,8 +223,12 @@ __device__ __forceinline__ void adam_block(AdamTensor& t, int64_t begin, int64_t
     if (t.v_scale) vs = t.tensor_scale ? msamp_compute_scale(t.red[2], 1.0f, st_max(v_st), 0) : 1.0f;
   }
 
+  // e4m3 copy of the new parameter: scale from the power-of-two rule on max|p| (stage 1), applied to the payload that is
+  // stored with scale ps, i.e. payload * (s8 / ps) - the arithmetic of re-quantising the stored tensor
+  uint8_t* w8 = (STAGE == 2 && p_st == ST_F16 && t.p_scale) ? t.w8 : nullptr;
+  const float w8_factor = w8 ? msamp_compute_scale(t.red[0], 1.0f, 448.0f, 0) * __frcp_rn(ps) : 0.0f;
   const bool vec = ((reinterpret_cast<uintptr_t>(t.p) | reinterpret_cast<uintptr_t>(t.g) | reinterpret_cast<uintptr_t>(t.m) |
-                     reinterpret_cast<uintptr_t>(t.v)) & 15) == 0;
+                     reinterpret_cast<uintptr_t>(t.v) | reinterpret_cast<uintptr_t>(w8)) & 15) == 0;
   float ap = 0.0f, am = 0.0f, av = 0.0f;
   if (vec) {
 #pragma unroll 2
@@ -249,6 +255,17 @@ __device__ __forceinline__ void adam_block(AdamTensor& t, int64_t begin, int64_t
         store8(t.p, p_st, i, p);
         store8(t.m, m_st, i, m);
         store8(t.v, v_st, i, v);
+        if (w8 != nullptr) {
+          // the e4m3 copy is taken from the parameter AS STORED (rounded to fp16), with the factor a separate cast of the
+          // stored tensor would use, so it equals that cast bit for bit
+          uint16_t o8[4];
+#pragma unroll
+          for (int j = 0; j < 8; j += 2) {
+            const float a = __half2float(__float2half_rn(sat(p[j], 65504.0f))), b = __half2float(__float2half_rn(sat(p[j + 1], 65504.0f)));
+            o8[j / 2] = f32x2_to_fp8x2<FMT_E4M3>(a * w8_factor, b * w8_factor);
+          }
+          *reinterpret_cast<uint2*>(w8 + i) = *reinterpret_cast<const uint2*>(o8);
+        }
       }
     }
   }
@@ -265,6 +282,7 @@ __device__ __forceinline__ void adam_block(AdamTensor& t, int64_t begin, int64_t
         store1(t.p, p_st, i, e.p * ps);
         store1(t.m, m_st, i, e.m * ms);
         store1(t.v, v_st, i, e.v * vs);
+        if (w8 != nullptr) w8[i] = f32_to_fp8<FMT_E4M3>(__half2float(__float2half_rn(sat(e.p * ps, 65504.0f))) * w8_factor);
       }
     }
   }
@@ -410,6 +428,7 @@ __global__ void lbadam_finalize_kernel(AdamTensor* tensors, int n) {
     *t.p_scale = s;
     *t.p_scale_inv = __frcp_rn(s);
     if (t.p_amax) *t.p_amax = t.red[0];
+    if (t.w8 && t.w8_scale_inv && t.p_st == ST_F16) *t.w8_scale_inv = __frcp_rn(msamp_compute_scale(t.red[0], 1.0f, 448.0f, 0));
   }
   if (t.m_scale) {
     float s = t.tensor_scale ? msamp_compute_scale(t.red[1], 1.0f, st_max(t.m_st), 0) : 1.0f;

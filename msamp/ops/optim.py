@@ -17,6 +17,7 @@ DESC = np.dtype(
         ('g_scale_inv', 'u8'),
         ('m_scale', 'u8'), ('m_scale_inv', 'u8'), ('m_amax', 'u8'),
         ('v_scale', 'u8'), ('v_scale_inv', 'u8'), ('v_amax', 'u8'),
+        ('w8', 'u8'), ('w8_scale_inv', 'u8'),
         ('n', 'i8'),
         ('p_st', 'i4'), ('g_st', 'i4'), ('m_st', 'i4'), ('v_st', 'i4'),
         ('lr_wd_factor', 'f4'), ('l2', 'f4'), ('beta1', 'f4'), ('beta2', 'f4'), ('eps', 'f4'), ('step_size', 'f4'),
@@ -26,7 +27,7 @@ DESC = np.dtype(
     ],
     align=False
 )
-assert DESC.itemsize == 192
+assert DESC.itemsize == 208
 
 
 def _storage(t):
@@ -110,6 +111,8 @@ class FusedPlan:
                 r['v_scale'], r['v_scale_inv'], r['v_amax'] = vmeta.scale.data_ptr(), vmeta.scale_inv.data_ptr(), vmeta.amax.data_ptr()
             else:
                 r['v_scale'] = r['v_scale_inv'] = r['v_amax'] = 0
+            w8 = e.get('w8')
+            r['w8'], r['w8_scale_inv'] = (w8[0].data_ptr(), w8[1].data_ptr()) if w8 is not None else (0, 0)
             r['n'] = sizes[i]
             r['p_st'], r['g_st'], r['m_st'], r['v_st'] = pst, gst, mst, vst
             r['lr_wd_factor'], r['l2'] = e['lr_wd_factor'], e['l2']

@@ -54,9 +54,19 @@ class LBAdamW(LBAdamWBase):
             if not isinstance(g, ScalingTensor) and not g.is_contiguous():
                 g = g.contiguous()
             reduce = getattr(self, '_reduce_in_step', None)
+            # A scaled-fp16 weight whose forward asked for an e4m3 copy (msamp.nn.functional.weight_fp8) gets that copy
+            # from stage 2 of this kernel, which holds the new values anyway: the forward then finds it in its cache and the
+            # separate re-quantisation pass over every weight (3 bytes per parameter and step) disappears.
+            w8 = None
+            if getattr(p, '_wants_fp8_copy', False) and isinstance(p, ScalingTensor) and p.meta.qtype == Dtypes.kfloat16 \
+                    and p.value.dim() >= 2:
+                w8 = getattr(p, '_adam_w8', None)
+                if w8 is None or w8[0].numel() != p.numel() or w8[0].device != p.value.device:
+                    w8 = p._adam_w8 = (torch.empty(p.numel(), dtype=torch.uint8, device=p.value.device),
+                                       torch.empty((), dtype=torch.float32, device=p.value.device))
             entries.append(
                 dict(
-                    p=p, g=g, m=exp_avgs[i], v=exp_avg_sqs[i], g_index=(reduce['index'].get(id(p), -1) if reduce is not None else -1),
+                    p=p, g=g, m=exp_avgs[i], v=exp_avg_sqs[i], w8=w8, g_index=(reduce['index'].get(id(p), -1) if reduce is not None else -1),
                     lr_wd_factor=(1.0 if self.use_adam else 1.0 - lr * weight_decay), l2=(weight_decay if self.use_adam else 0.0),
                     beta1=beta1, beta2=beta2, eps=eps, step_size=lr / bc1, sqrt_bc2=math.sqrt(bc2), gsign=(-1.0 if maximize else 1.0),
                     tensor_scale=self.tensor_scale
@@ -67,6 +77,12 @@ class LBAdamW(LBAdamWBase):
         if plan is None:
             plan = self._plans[key] = FusedPlan(params[0].device)
         plan.run(entries, reduce=getattr(self, '_reduce_in_step', None))
+        for e in entries:
+            if e['w8'] is not None:
+                p, (w8, sinv) = e['p'], e['w8']
+                val = p.value
+                key = (val.data_ptr(), val._version, p.meta.scale_inv._version, p.meta.scale_inv.data_ptr())
+                p._fp8_cache1 = (key, w8.view(-1, val.shape[-1]), sinv)
 
     def __getstate__(self):
         d = super().__getstate__() if hasattr(super(), '__getstate__') else self.__dict__.copy()
