@@ -170,13 +170,26 @@ class _MlpSublayerFn(torch.autograd.Function):
         # fc2
         dy8, dy_sinv, db2 = _quantize_ograd(g, m2['ograd'], ctx.b2_dtype is not None, ctx.b2_dtype)
         _deliver_wgrad(ctx.w2, m2, dy8, dy_sinv, g8, g_sinv, dt)
-        # dgrad of fc2 with the GeLU derivative applied in the epilogue, max|dh| reduced on the way
-        dh_amax = torch.empty((), dtype=torch.float32, device=x.device)
-        dh = gemm_dgrad(dy8, dy_sinv, w2_8, w2_sinv, dt, gelu_src=h, amax_out=dh_amax)
-        setattr(dh, _AMAX_HINT, dh_amax)
+        # dgrad of fc2 with the GeLU derivative applied in the epilogue
+        og = m1['ograd']
+        if og.is_in_time_scaling():
+            # in-time scaling: the scale of dh follows from its amax, which the epilogue reduces on the way; the
+            # quantisation (and the bias gradient) is a second pass over dh
+            dh_amax = torch.empty((), dtype=torch.float32, device=x.device)
+            dh = gemm_dgrad(dy8, dy_sinv, w2_8, w2_sinv, dt, gelu_src=h, amax_out=dh_amax)
+            setattr(dh, _AMAX_HINT, dh_amax)
+            dh8, dh_sinv, db1 = _quantize_ograd(dh, og, ctx.b1_dtype is not None, ctx.b1_dtype)
+            del dh
+        else:
+            # delayed scaling: the scale is known beforehand, so the epilogue writes the e5m2 operand of the next two GEMMs,
+            # the amax for the history and the column sums (= the bias gradient of fc1) itself; dh in bf16 is never stored
+            dh8 = torch.empty((dy8.shape[0], h.shape[1]), dtype=torch.uint8, device=x.device)
+            colsum = torch.empty(h.shape[1], dtype=torch.float32, device=x.device) if ctx.b1_dtype is not None else None
+            gemm_dgrad(dy8, dy_sinv, w2_8, w2_sinv, dt, gelu_src=h, amax_out=og.amax[0], out8=dh8, out8_qtype=E5M2, out8_scale=og.scale,
+                       out8_scale_inv_out=og.scale_inv, colsum_out=colsum, store_out=False)
+            dh_sinv = og.scale_inv.clone()
+            db1 = colsum.to(ctx.b1_dtype) if colsum is not None else None
         # fc1
-        dh8, dh_sinv, db1 = _quantize_ograd(dh, m1['ograd'], ctx.b1_dtype is not None, ctx.b1_dtype)
-        del dh
         _deliver_wgrad(ctx.w1, m1, dh8, dh_sinv, y8, y_sinv, dt)
         dln = gemm_dgrad(dh8, dh_sinv, w1_8, w1_sinv, dt)
         dx, dgamma, dbeta = _ln_backward(dln, x, ln_weight, mean, rstd, ctx.has_ln_bias, g if ctx.add_residual else None)

@@ -53,6 +53,8 @@ struct GemmArgs {
   int act;                    // 0: identity, 1: amax_out and d8 refer to gelu(D)
   int group_m;                // row tiles per rasterisation group (see tile_to_mn); 0 means all of them
   int tma_store;              // 1: tma_d describes D and full 16-bit tiles are stored through it
+  float* colsum;              // optional [N] fp32: += column sums of D as stored (a bias gradient); zeroed by the caller
+  int no_d;                   // 1: D itself is not written (only amax_out / d8 / colsum are wanted)
 };
 
 template <int BN, bool PAIR, int NSTAGES = 0>
@@ -102,6 +104,14 @@ __device__ __forceinline__ void store_fp8_chunk(uint8_t* dst, const float (&w)[3
     for (int j = 0; j < 32; ++j)
       if (j < valid) dst[j] = f32_to_fp8<FMT>(w[j] * scale);
   }
+}
+
+// Ragged tiles and fp32 outputs: every thread adds its row's values (as rounded to the output type) to the column sums.
+template <typename OutT>
+__device__ __forceinline__ void colsum_chunk(float* cs, const float (&v)[32], int valid) {
+#pragma unroll
+  for (int j = 0; j < 32; ++j)
+    if (j < valid) atomicAdd(cs + j, to_f32<OutT>(from_f32<OutT>(v[j])));
 }
 
 template <int BN, bool PAIR, typename OutT, int NSTAGES = 0>
@@ -291,7 +301,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
     // with every store instruction covering four complete 128-byte lines.  Storing straight from the row-per-thread
     // layout touches 32 different lines with 16 bytes each per instruction, which cost 11 % of the GEMM on N >= 12288.
     const uint32_t stage = base + (uint32_t)C::STAGING_OFF + (uint32_t)(warp - 2) * 4096u;
-    const bool staged_ok = sizeof(OutT) == 2 && vec_ok && p.tma_store != 0;
+    const bool staged_ok = sizeof(OutT) == 2 && ((vec_ok && p.tma_store != 0) || p.no_d != 0);
     float amax = 0.0f;
     uint32_t lt = 0;
     for (int tile = first_tile; tile < num_tiles; tile += tile_step, ++lt) {
@@ -382,18 +392,37 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
                 // hands them to the TMA unit, which writes complete lines without occupying the load/store path
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 __syncwarp();
-                if (lane == 0) {
+                if (lane == 0 && !p.no_d) {
                   tc5::tma_store_2d(&tma_d, stage, (col - 32) * (int)sizeof(OutT), m0 + q * 32);
                   tc5::bulk_commit_group();
-                  tc5::bulk_wait_read<0>();    // the buffer is rewritten by the next 64 columns
                 }
+                if (p.colsum != nullptr) {
+                  // column sums of the 32 staged rows: lane L owns columns 2L and 2L + 1 of the 64-column group and walks
+                  // down the rows (one 4-byte word per row; a row's 32 words are a permutation of its 128 bytes, so the
+                  // reads of a warp are conflict free)
+                  float s0 = 0.0f, s1 = 0.0f;
+                  const uint32_t piece = (uint32_t)lane >> 2, word = ((uint32_t)lane & 3u) * 4u;
+#pragma unroll 8
+                  for (uint32_t r = 0; r < 32; ++r) {
+                    uint32_t wv;
+                    asm volatile("ld.shared.b32 %0, [%1];" : "=r"(wv) : "r"(stage + r * 128u + ((piece ^ (r & 7u)) << 4) + word));
+                    const OutT* e2 = reinterpret_cast<const OutT*>(&wv);
+                    s0 += to_f32<OutT>(e2[0]);
+                    s1 += to_f32<OutT>(e2[1]);
+                  }
+                  atomicAdd(p.colsum + (col - 32) + 2 * lane, s0);
+                  atomicAdd(p.colsum + (col - 32) + 2 * lane + 1, s1);
+                }
+                if (lane == 0 && !p.no_d) tc5::bulk_wait_read<0>();    // the buffer is rewritten by the next 64 columns
                 __syncwarp();
               }
             } else {
-              store_chunk<OutT>(dst, v, vec_ok, valid);
+              if (!p.no_d) store_chunk<OutT>(dst, v, vec_ok, valid);
+              if (p.colsum != nullptr) colsum_chunk<OutT>(p.colsum + col, v, valid);
             }
           } else {
-            store_chunk<OutT>(dst, v, vec_ok, valid);
+            if (!p.no_d) store_chunk<OutT>(dst, v, vec_ok, valid);
+            if (p.colsum != nullptr) colsum_chunk<OutT>(p.colsum + col, v, valid);
           }
           if (p.amax_out != nullptr || p.d8 != nullptr) {
             // statistics and the quantised copy are taken from the values as stored (rounded to the
@@ -547,6 +576,7 @@ struct MsampGemmDesc {
   int max_ctas;
   int tile;
   unsigned long long* stats;    // optional tuning counters, 4 per CTA (see GemmArgs)
+  float* colsum;                // optional [N] fp32, += column sums of D as stored; zeroed by the caller
 };
 
 MSAMP_API int msamp_gemm_fp8_ex(const MsampGemmDesc* g, void* stream_) {
@@ -558,7 +588,10 @@ MSAMP_API int msamp_gemm_fp8_ex(const MsampGemmDesc* g, void* stream_) {
                 "msamp_gemm_fp8: the contiguous dimension of each operand must be a multiple of 16");
   MSAMP_REQUIRE((reinterpret_cast<uintptr_t>(g->a) & 15) == 0 && (reinterpret_cast<uintptr_t>(g->b) & 15) == 0,
                 "msamp_gemm_fp8: operands must be 16-byte aligned");
-  MSAMP_REQUIRE(g->scale_inv_a && g->scale_inv_b && g->d, "msamp_gemm_fp8: null pointer");
+  MSAMP_REQUIRE(g->scale_inv_a && g->scale_inv_b, "msamp_gemm_fp8: null pointer");
+  MSAMP_REQUIRE(g->d != nullptr || g->d8 != nullptr || g->amax_out != nullptr || g->colsum != nullptr,
+                "msamp_gemm_fp8: no output requested");
+  MSAMP_REQUIRE(g->d != nullptr || (g->residual == nullptr), "msamp_gemm_fp8: a residual needs the output it is added to");
   MSAMP_REQUIRE(g->d8 == nullptr || g->d8_scale != nullptr, "msamp_gemm_fp8: a quantised copy needs its scale");
   const int sms = msamp_sm_count();
   // Tile choice: single-CTA 128x256 tiles when those fill the device, else 128x128.  The CTA-pair kernel moves a
@@ -583,7 +616,7 @@ MSAMP_API int msamp_gemm_fp8_ex(const MsampGemmDesc* g, void* stream_) {
   int tma_store = 0;
   {
     const int esize = g->out_dtype == DT_F32 ? 4 : 2;
-    if (esize == 2 && (reinterpret_cast<uintptr_t>(g->d) & 15) == 0 && (g->ldd * esize) % 16 == 0 && N >= 128 &&
+    if (g->d != nullptr && esize == 2 && (reinterpret_cast<uintptr_t>(g->d) & 15) == 0 && (g->ldd * esize) % 16 == 0 && N >= 128 &&
         make_map(g->d, M, (int64_t)N * esize, g->ldd * esize, 32, &md) == MSAMP_OK)
       tma_store = 1;
     else
@@ -591,6 +624,8 @@ MSAMP_API int msamp_gemm_fp8_ex(const MsampGemmDesc* g, void* stream_) {
   }
   GemmArgs p;
   p.tma_store = tma_store;
+  p.colsum = g->colsum;
+  p.no_d = g->d == nullptr ? 1 : 0;
   p.d = g->d; p.bias = g->bias; p.residual = g->residual; p.gelu_src = g->gelu_src;
   p.scale_inv_a = g->scale_inv_a; p.scale_inv_b = g->scale_inv_b; p.amax_out = g->amax_out;
   p.d8 = (uint8_t*)g->d8; p.d8_scale = g->d8_scale; p.d8_scale_inv_out = g->d8 ? g->d8_scale_inv_out : nullptr;

@@ -30,6 +30,7 @@ class _GemmDesc(ctypes.Structure):
         ('M', ctypes.c_int), ('N', ctypes.c_int), ('K', ctypes.c_int), ('a_fmt', ctypes.c_int), ('b_fmt', ctypes.c_int),
         ('d8_fmt', ctypes.c_int), ('a_mn', ctypes.c_int), ('b_mn', ctypes.c_int), ('out_dtype', ctypes.c_int),
         ('bias_dtype', ctypes.c_int), ('act', ctypes.c_int), ('max_ctas', ctypes.c_int), ('tile', ctypes.c_int), ('stats', ctypes.c_void_p),
+        ('colsum', ctypes.c_void_p),
     ]
 
 
@@ -52,7 +53,7 @@ def _fix_operand(t):
 
 def gemm_fp8(a, a_qtype, a_scale_inv, b, b_qtype, b_scale_inv, out_dtype, bias=None, accumulate=False, out=None, amax_out=None,
              max_ctas=0, a_mn=False, b_mn=False, residual=None, gelu_src=None, act=None, out8=None, out8_qtype=None, out8_scale=None,
-             out8_scale_inv_out=None, tile=0, stats=None):
+             out8_scale_inv_out=None, tile=0, stats=None, colsum_out=None, store_out=True):
     """Multiply FP8 byte matrices.
 
     Args:
@@ -72,6 +73,9 @@ def gemm_fp8(a, a_qtype, a_scale_inv, b, b_qtype, b_scale_inv, out_dtype, bias=N
         act: ``None`` or ``'gelu'``: which function of ``D`` ``amax_out`` and ``out8`` describe.
         out8, out8_qtype, out8_scale: optional uint8 ``[M,N]`` receiving ``quantise(act(D) * out8_scale)``;
             ``out8_scale_inv_out`` (optional) then receives ``1 / out8_scale``.
+        colsum_out: optional fp32 ``[N]`` receiving the column sums of ``D`` as stored (the bias gradient when ``D`` is the
+            output gradient of a biased layer); it is overwritten.
+        store_out: ``False`` skips ``D`` itself (returns ``None``) when only ``amax_out`` / ``out8`` / ``colsum_out`` are wanted.
         tile: 0 = choose, 1 = CTA-pair 256x256 tiles, 2 = single-CTA tiles (CUDA only; for tests and benchmarks).
         stats: optional int64 ``[4 * CTAs]`` CUDA tensor receiving per-CTA cycle counters (producer wait, MMA wait for
             data, MMA wait for TMEM, MMA warp total) for tuning.
@@ -84,10 +88,17 @@ def gemm_fp8(a, a_qtype, a_scale_inv, b, b_qtype, b_scale_inv, out_dtype, bias=N
         raise ValueError('accumulate=True needs an output tensor')
     if accumulate and residual is not None:
         raise ValueError('accumulate and residual exclude each other')
-    if out is None:
+    if not store_out:
+        if out is not None or accumulate or residual is not None:
+            raise ValueError('store_out=False excludes out, accumulate and residual')
+        if amax_out is None and out8 is None and colsum_out is None:
+            raise ValueError('store_out=False needs another output')
+    elif out is None:
         out = torch.empty((M, N), dtype=out_dtype, device=a.device)
     else:
         assert out.shape == (M, N) and out.dtype == out_dtype and out.stride(1) == 1
+    if colsum_out is not None:
+        assert colsum_out.shape == (N, ) and colsum_out.dtype == torch.float32 and colsum_out.is_contiguous()
     if accumulate:
         residual = out
     for t in (residual, gelu_src):
@@ -105,8 +116,11 @@ def gemm_fp8(a, a_qtype, a_scale_inv, b, b_qtype, b_scale_inv, out_dtype, bias=N
             K += pad
         if amax_out is not None:
             amax_out.zero_()
+        if colsum_out is not None:
+            colsum_out.zero_()
         g = _GemmDesc()
-        g.a, g.b, g.d = a.data_ptr(), b.data_ptr(), out.data_ptr()
+        g.a, g.b, g.d = a.data_ptr(), b.data_ptr(), (out.data_ptr() if out is not None else None)
+        g.colsum = colsum_out.data_ptr() if colsum_out is not None else None
         g.bias = bias.data_ptr() if bias is not None else None
         g.residual = residual.data_ptr() if residual is not None else None
         g.gelu_src = gelu_src.data_ptr() if gelu_src is not None else None
@@ -115,7 +129,7 @@ def gemm_fp8(a, a_qtype, a_scale_inv, b, b_qtype, b_scale_inv, out_dtype, bias=N
         g.d8 = out8.data_ptr() if out8 is not None else None
         g.d8_scale = out8_scale.data_ptr() if out8 is not None else None
         g.d8_scale_inv_out = out8_scale_inv_out.data_ptr() if (out8 is not None and out8_scale_inv_out is not None) else None
-        g.lda, g.ldb, g.ldd = a.stride(0), b.stride(0), out.stride(0)
+        g.lda, g.ldb, g.ldd = a.stride(0), b.stride(0), (out.stride(0) if out is not None else N)
         g.ldr = residual.stride(0) if residual is not None else 0
         g.ldg = gelu_src.stride(0) if gelu_src is not None else 0
         g.ld8 = out8.stride(0) if out8 is not None else 0
@@ -143,9 +157,13 @@ def gemm_fp8(a, a_qtype, a_scale_inv, b, b_qtype, b_scale_inv, out_dtype, bias=N
         res = res + residual.float()
     if gelu_src is not None:
         res = res * _gelu_tanh_grad(gelu_src.float())
-    out.copy_(res.to(out_dtype))
+    stored = res.to(out_dtype)
+    if out is not None:
+        out.copy_(stored)
+    if colsum_out is not None:
+        colsum_out.copy_(stored.float().sum(0))
     if amax_out is not None or out8 is not None:
-        w = out.float()
+        w = stored.float()
         if act == 'gelu':
             w = _gelu_tanh(w).to(out_dtype).float()
         if amax_out is not None:

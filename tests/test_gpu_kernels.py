@@ -224,6 +224,30 @@ def test_gemm_epilogue_options(tile):
     g = K.gelu(d)    # the stand-alone kernel on the stored values
     assert am.item() == g.float().abs().max().item()
     assert torch.equal(out8, cast.cast_to_fp8(g, E4, q_scale))
+    # backward of fc2 in the delayed regime: e5m2 copy of D = product x gelu'(h), its amax and its column sums (the bias
+    # gradient of fc1) from one launch that does not store D itself; ragged and full tiles (513 rows, 768 / 800 columns)
+    for mm, nn in ((m, n), (513, 800)):
+        a2, sia2 = _mk(mm, k, E4)
+        b2, sib2 = _mk(nn, k, E4)
+        h2 = torch.randn(mm, nn, device=DEV).bfloat16()
+        d_ref = gemm.gemm_fp8(a2, E4, sia2, b2, E4, sib2, torch.bfloat16, gelu_src=h2, tile=tile)
+        am = torch.zeros((), device=DEV)
+        cs = torch.full((nn, ), 7.0, device=DEV)
+        q5 = torch.tensor(64.0, device=DEV)
+        sinv = torch.zeros((), device=DEV)
+        out5 = torch.empty(mm, nn, dtype=torch.uint8, device=DEV)
+        none = gemm.gemm_fp8(a2, E4, sia2, b2, E4, sib2, torch.bfloat16, gelu_src=h2, amax_out=am, out8=out5, out8_qtype=E5, out8_scale=q5,
+                             out8_scale_inv_out=sinv, colsum_out=cs, store_out=False, tile=tile)
+        assert none is None
+        assert am.item() == d_ref.float().abs().max().item() and sinv.item() == 1.0 / 64.0
+        assert torch.equal(out5, cast.cast_to_fp8(d_ref, E5, q5))
+        want_cs = d_ref.float().sum(0)
+        assert (cs - want_cs).abs().max().item() <= 1e-3 * d_ref.float().abs().sum(0).max().item() + 1e-6
+        # with D stored as well the same sums come out
+        cs2 = torch.empty(nn, device=DEV)
+        d2 = gemm.gemm_fp8(a2, E4, sia2, b2, E4, sib2, torch.bfloat16, gelu_src=h2, colsum_out=cs2, tile=tile)
+        assert torch.equal(d2, d_ref)
+        assert (cs2 - want_cs).abs().max().item() <= 1e-3 * d_ref.float().abs().sum(0).max().item() + 1e-6
     _status_ok()
 
 
