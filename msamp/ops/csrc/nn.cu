@@ -2,9 +2,11 @@
 // (tanh form), and fused softmax cross-entropy (loss + in-place logit gradient).  All are
 // HBM-bandwidth bound: one pass over the data with 16-byte accesses, statistics in fp32.
 #include <atomic>
+#include <type_traits>
 
 #include "common.cuh"
 #include "msamp_noalloc.h"
+#include "tcgen05.cuh"
 
 namespace {
 
@@ -283,6 +285,152 @@ __global__ void __launch_bounds__(LN_BWD_THREADS, (VPT <= 2 ? 2 : 1)) layernorm_
   }
 }
 
+// LayerNorm backward for 16-bit rows, fed by bulk copies (cp.async.bulk, global -> shared, completion on an mbarrier).
+// The register-prefetching kernel above keeps one row per CTA in flight beyond the current one, which at two resident
+// CTAs per SM is about a third of the bytes HBM needs in flight (it ran at 2.1-2.8 TB/s); here one thread keeps
+// LN_BULK_STAGES - 1 rows (x, dy and the skip-connection gradient) of every CTA on their way while the CTA works on the
+// current one.  Each CTA takes a contiguous block of rows, whose mean / rstd it reads into shared memory once.
+// Same arithmetic and outputs as layernorm_bwd_kernel.  A wait that gives up sets bit 16 of the device status word.
+constexpr int LN_BULK_STAGES = 4;
+constexpr int LN_BULK_MAX_ROWS = 512;    // rows per CTA whose statistics fit the static shared arrays
+template <typename T, typename P, int VPT>
+__global__ void __launch_bounds__(LN_BWD_THREADS, 2)
+layernorm_bwd_bulk_kernel(const T* __restrict__ dy, const T* __restrict__ x, const void* __restrict__ gamma, const float* __restrict__ mean,
+                          const float* __restrict__ rstd, T* __restrict__ dx, float* __restrict__ part, int rows, int cols,
+                          const T* __restrict__ dres, float* amax_out, int rows_per_cta, unsigned int* status) {
+  extern __shared__ __align__(128) uint8_t ln_ring[];
+  __shared__ float2 red2[32];
+  __shared__ float red[32];
+  __shared__ float s_mean[LN_BULK_MAX_ROWS], s_rstd[LN_BULK_MAX_ROWS];
+  __shared__ __align__(8) uint64_t bar_mem[LN_BULK_STAGES];
+  __shared__ int abort_word;
+  constexpr int N = 16 / sizeof(T);
+  constexpr int THREADS = LN_BWD_THREADS;
+  const int nvec = cols / N;
+  const uint32_t row_bytes = (uint32_t)cols * (uint32_t)sizeof(T);
+  const uint32_t stage_bytes = 3u * row_bytes;    // x | dy | dres
+  const uint32_t ring = tc5::smem_u32(ln_ring);
+  const uint32_t bars = tc5::smem_u32(bar_mem);
+  volatile int* abort_flag = &abort_word;
+  const int r0 = blockIdx.x * rows_per_cta;
+  const int n = min(rows - r0, rows_per_cta);    // >= 1: the grid is sized from rows_per_cta
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < LN_BULK_STAGES; ++s) tc5::mbar_init(bars + 8u * s, 1);
+    abort_word = 0;
+    tc5::mbar_fence_init();
+  }
+  for (int i = threadIdx.x; i < n; i += THREADS) {
+    s_mean[i] = mean[r0 + i];
+    s_rstd[i] = rstd[r0 + i];
+  }
+  __syncthreads();
+  auto issue = [&](int j) {    // thread 0: bring row r0 + j into stage j % LN_BULK_STAGES
+    const uint32_t b = bars + 8u * (uint32_t)(j % LN_BULK_STAGES);
+    const uint32_t dst = ring + (uint32_t)(j % LN_BULK_STAGES) * stage_bytes;
+    const int64_t off = (int64_t)(r0 + j) * cols;
+    tc5::mbar_arrive_expect_tx(b, (dres != nullptr ? 3u : 2u) * row_bytes);
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(x + off),
+                 "r"(row_bytes), "r"(b)
+                 : "memory");
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst + row_bytes),
+                 "l"(dy + off), "r"(row_bytes), "r"(b)
+                 : "memory");
+    if (dres != nullptr)
+      asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst + 2u * row_bytes),
+                   "l"(dres + off), "r"(row_bytes), "r"(b)
+                   : "memory");
+  };
+  if (threadIdx.x == 0)
+    for (int j = 0; j < LN_BULK_STAGES - 1 && j < n; ++j) issue(j);
+  float amax = 0.0f;
+  float dg[VPT][N], db[VPT][N], gm[VPT][N];
+#pragma unroll
+  for (int k = 0; k < VPT; ++k) {
+    int i = threadIdx.x + k * THREADS;
+#pragma unroll
+    for (int j = 0; j < N; ++j) dg[k][j] = db[k][j] = gm[k][j] = 0.0f;
+    if (i < nvec) ld_params<P, N>(gamma, i * N, gm[k]);
+  }
+  bool ok = true;
+  for (int it = 0; it < n; ++it) {
+    // every thread has finished row it - 1: its stage takes row it + LN_BULK_STAGES - 1.  Also the place where the CTA
+    // agrees to stop after a wait that gave up.
+    if (__syncthreads_or(!ok)) break;
+    if (threadIdx.x == 0 && it + LN_BULK_STAGES - 1 < n) issue(it + LN_BULK_STAGES - 1);
+    const int st = it % LN_BULK_STAGES;
+    ok = tc5::mbar_wait(bars + 8u * (uint32_t)st, (uint32_t)(it / LN_BULK_STAGES) & 1u, abort_flag, status, 16u);
+    const uint8_t* sx = ln_ring + (size_t)st * stage_bytes;
+    const Bytes16* xs = reinterpret_cast<const Bytes16*>(sx);
+    const Bytes16* ds = reinterpret_cast<const Bytes16*>(sx + row_bytes);
+    const Bytes16* rs_ = reinterpret_cast<const Bytes16*>(sx + 2u * row_bytes);
+    const float mu = s_mean[it], rs = s_rstd[it];
+    Bytes16 vx[VPT], vd[VPT], vr[VPT];
+    float s1 = 0.0f, s2 = 0.0f;    // sum(g*dy), sum(g*dy*xhat)
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+      int i = threadIdx.x + k * THREADS;
+      if (i < nvec) {
+        vx[k] = xs[i];
+        vd[k] = ds[i];
+        if (dres != nullptr) vr[k] = rs_[i];
+        const T* ex = reinterpret_cast<const T*>(&vx[k]);
+        const T* ed = reinterpret_cast<const T*>(&vd[k]);
+#pragma unroll
+        for (int j = 0; j < N; ++j) {
+          float xh = (to_f32<T>(ex[j]) - mu) * rs;
+          float d = to_f32<T>(ed[j]);
+          float gd = d * gm[k][j];
+          s1 += gd;
+          s2 += gd * xh;
+          dg[k][j] += d * xh;
+          db[k][j] += d;
+        }
+      }
+    }
+    const float2 tot = block_sum2(s1, s2, red2);
+    const float m1 = tot.x / cols, m2 = tot.y / cols;
+    T* dxr = dx + (int64_t)(r0 + it) * cols;
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+      int i = threadIdx.x + k * THREADS;
+      if (i < nvec) {
+        const T* ex = reinterpret_cast<const T*>(&vx[k]);
+        const T* ed = reinterpret_cast<const T*>(&vd[k]);
+        const T* er = reinterpret_cast<const T*>(&vr[k]);
+        Bytes16 o;
+        T* oe = reinterpret_cast<T*>(&o);
+#pragma unroll
+        for (int j = 0; j < N; ++j) {
+          float xh = (to_f32<T>(ex[j]) - mu) * rs;
+          float gd = to_f32<T>(ed[j]) * gm[k][j];
+          float r = rs * (gd - m1 - xh * m2);
+          if (dres != nullptr) r += to_f32<T>(er[j]);
+          oe[j] = from_f32<T>(r);
+          if (amax_out != nullptr) amax = fmaxf(amax, abs_nan_to_inf(to_f32<T>(oe[j])));
+        }
+        reinterpret_cast<Bytes16*>(dxr)[i] = o;
+      }
+    }
+  }
+  if (amax_out != nullptr) {
+    amax = block_max(amax, red);
+    if (threadIdx.x == 0) atomic_max_nonneg(amax_out, amax);
+  }
+  float* pg = part + (int64_t)blockIdx.x * 2 * cols;
+  float* pb = pg + cols;
+#pragma unroll
+  for (int k = 0; k < VPT; ++k) {
+    int i = threadIdx.x + k * THREADS;
+    if (i < nvec) {
+#pragma unroll
+      for (int j = 0; j < N; ++j) {
+        pg[i * N + j] = dg[k][j];
+        pb[i * N + j] = db[k][j];
+      }
+    }
+  }
+}
+
 template <typename T, typename P>
 void launch_ln_bwd(int grid, cudaStream_t stream, const void* dy, const void* x, const void* gamma, const float* mean, const float* rstd,
                    void* dx, float* part, int rows, int cols, const void* dres, float* amax_out) {
@@ -459,6 +607,36 @@ __global__ void __launch_bounds__(512) xent_bwd_kernel(T* __restrict__ logits, c
     else { msamp_set_error("layernorm: parameters must be fp32 or match the activation dtype"); return MSAMP_EDTYPE; } \
   })
 
+template <typename T, typename P>
+int launch_ln_bwd_bulk_p(int grid, size_t ring_bytes, cudaStream_t stream, const void* dy, const void* x, const void* gamma, const float* mean,
+                         const float* rstd, void* dx, float* part, int rows, int cols, const void* dres, float* amax_out, int rpc) {
+  const int vpt = (cols / 8 + LN_BWD_THREADS - 1) / LN_BWD_THREADS;
+  unsigned int* status = msamp_device_status_ptr();
+#define MSAMP_LN_BULK(VPT_)                                                                                                              \
+  {                                                                                                                                      \
+    auto kern = layernorm_bwd_bulk_kernel<T, P, VPT_>;                                                                                   \
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ring_bytes) != cudaSuccess) {                       \
+      msamp_set_error("layernorm_bwd: cannot reserve %zu bytes of shared memory", ring_bytes);                                           \
+      return MSAMP_ELAUNCH;                                                                                                              \
+    }                                                                                                                                    \
+    kern<<<grid, LN_BWD_THREADS, ring_bytes, stream>>>((const T*)dy, (const T*)x, gamma, mean, rstd, (T*)dx, part, rows, cols, (const T*)dres, \
+                                                        amax_out, rpc, status);                                                          \
+  }
+  if (vpt <= 1) MSAMP_LN_BULK(1) else MSAMP_LN_BULK(2)
+#undef MSAMP_LN_BULK
+  return MSAMP_OK;
+}
+template <typename T>
+int launch_ln_bwd_bulk(int pdtype, int grid, size_t ring_bytes, cudaStream_t stream, const void* dy, const void* x, const void* gamma,
+                       const float* mean, const float* rstd, void* dx, float* part, int rows, int cols, const void* dres, float* amax_out,
+                       int rpc) {
+  const int own = sizeof(T) == 2 && std::is_same<T, __half>::value ? DT_F16 : DT_BF16;
+  if (pdtype == DT_F32) return launch_ln_bwd_bulk_p<T, float>(grid, ring_bytes, stream, dy, x, gamma, mean, rstd, dx, part, rows, cols, dres, amax_out, rpc);
+  if (pdtype == own) return launch_ln_bwd_bulk_p<T, T>(grid, ring_bytes, stream, dy, x, gamma, mean, rstd, dx, part, rows, cols, dres, amax_out, rpc);
+  msamp_set_error("layernorm: parameters must be fp32 or match the activation dtype");
+  return MSAMP_EDTYPE;
+}
+
 MSAMP_API int msamp_layernorm_max_cols(int dtype) { return LN_THREADS * LN_VPT * (dtype == DT_F32 ? 4 : 8); }
 
 #define MSAMP_LN_ALIGNED(ptr) ((reinterpret_cast<uintptr_t>(ptr) & 15) == 0)
@@ -516,6 +694,23 @@ MSAMP_API int msamp_layernorm_bwd_ex(const void* dy, const void* x, const void* 
   if (amax_out) cudaMemsetAsync(amax_out, 0, sizeof(float), stream);
   int nparts = msamp_sm_count() * 2;    // two CTAs of 256 threads are resident per SM; never more than msamp_layernorm_bwd_parts()
   int grid = rows < nparts ? rows : nparts;
+  // the bulk-copy kernel: 16-bit data, one or two vectors per thread, enough rows per CTA to fill its ring, statistics that
+  // fit its shared arrays
+  {
+    const int rpc = (rows + nparts - 1) / nparts;
+    const int nvec16 = cols / 8;
+    const size_t ring_bytes = (size_t)LN_BULK_STAGES * 3 * cols * 2;
+    if (dtype != DT_F32 && nvec16 <= 2 * LN_BWD_THREADS && rpc >= LN_BULK_STAGES && rpc <= LN_BULK_MAX_ROWS && ring_bytes <= 100 * 1024 &&
+        (cols * 2) % 16 == 0) {
+      const int grid_b = (rows + rpc - 1) / rpc;
+      int rc = MSAMP_OK;
+      if (dtype == DT_BF16) rc = launch_ln_bwd_bulk<__nv_bfloat16>(pdtype, grid_b, ring_bytes, stream, dy, x, gamma, mean, rstd, dx, part, rows, cols, dres, amax_out, rpc);
+      else                  rc = launch_ln_bwd_bulk<__half>(pdtype, grid_b, ring_bytes, stream, dy, x, gamma, mean, rstd, dx, part, rows, cols, dres, amax_out, rpc);
+      if (rc) return rc;
+      layernorm_reduce_kernel<<<(cols + 31) / 32, 256, 0, stream>>>(part, grid_b, cols, dgamma, dbeta, pdtype);
+      return msamp_check_launch("msamp_layernorm_bwd (bulk)");
+    }
+  }
   MSAMP_LN_DISPATCH(dtype, pdtype, T, P, { launch_ln_bwd<T, P>(grid, stream, dy, x, gamma, mean, rstd, dx, part, rows, cols, dres, amax_out); });
   layernorm_reduce_kernel<<<(cols + 31) / 32, 256, 0, stream>>>(part, grid, cols, dgamma, dbeta, pdtype);
   return msamp_check_launch("msamp_layernorm_bwd");

@@ -61,7 +61,8 @@ MSAMP_API const char* msamp_last_error() { return g_error; }
 
 // Returns the accumulated device status bits and clears them. Bit 0: a bounded wait in a GEMM
 // pipeline gave up; bit 1: a peer-flag wait gave up; bit 2: an attention pipeline wait gave up; bit 3: the ranks'
-// sequences of fused calls ran out of step (a peer's flag was ahead of this rank's epoch).
+// sequences of fused calls ran out of step (a peer's flag was ahead of this rank's epoch); bit 4: a wait on the bulk-copy
+// ring of a streaming kernel (LayerNorm backward) gave up.
 MSAMP_API unsigned int msamp_read_device_status() {
   unsigned int* p = msamp_device_status_ptr();
   if (!p) return 0;

@@ -356,7 +356,7 @@ def test_fused_adam_matches_definition(p_kind, state_dtypes, use_adam):
 
 
 @pytest.mark.parametrize('dt', [torch.bfloat16, torch.float32])
-@pytest.mark.parametrize('shape', [(64, 256), (1000, 4096), (7, 1024), (3, 8192)])
+@pytest.mark.parametrize('shape', [(64, 256), (1000, 4096), (7, 1024), (3, 8192), (2500, 4096), (1300, 1024)])    # the last two: bulk-copy backward
 def test_layernorm(dt, shape):
     if dt == torch.float32 and shape[1] > 4096:
         pytest.skip('rows of fp32 data are limited to 4096 columns')
@@ -378,7 +378,7 @@ def test_layernorm(dt, shape):
     assert (b.grad - br.grad).abs().max().item() <= tol * math.sqrt(shape[0]) * 2
 
 
-@pytest.mark.parametrize('shape', [(64, 1024), (300, 4096), (17, 8192)])
+@pytest.mark.parametrize('shape', [(64, 1024), (300, 4096), (17, 8192), (2500, 4096), (1500, 2048)])
 def test_layernorm_quantised_output_and_residual_backward(shape):
     """LayerNorm that emits e4m3 directly == LayerNorm followed by the cast, bit for bit; backward with the skip gradient."""
     torch.manual_seed(0)
