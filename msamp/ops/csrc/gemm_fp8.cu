@@ -228,10 +228,24 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
       // 32 rows of 128 bytes for an MN-major tile (encoded in units of 16 bytes).
       const uint64_t a_step = p.a_mn ? (uint64_t)(32 * 128 / 16) : 2ull;
       const uint64_t b_step = p.b_mn ? (uint64_t)(32 * 128 / 16) : 2ull;
-      uint32_t it = 0;
       uint32_t lt = 0;
       long long w_data = 0, w_tmem = 0;
       const long long t_begin = p.stats ? clock64() : 0;
+      // The tensor pipe buffers next to nothing.  An M = 128, N = 256, K = 32 MMA runs for 128 cycles, and whatever
+      // the issuing thread does between two MMAs beyond about 60 cycles leaves the pipe idle for as long
+      // (benchmarks/mma_fp8_shapes.cu: a delay of X cycles per K block costs X cycles per K block; commits and
+      // fences are free).  A blocking wait on a stage's barrier between two K blocks costs 100-140 cycles even when
+      // the data arrived long ago, which held this loop at 155 cycles per MMA with no loads and no epilogue at all.
+      // So the barrier of the NEXT stage is probed, without blocking, before the last MMA of the current K block is
+      // issued: the probe's latency overlaps with that issue, and the blocking wait is taken only when the probe
+      // failed (133 cycles per MMA in the same experiment).  Polling in a loop instead (here or in the producer)
+      // is much worse than the suspending wait: it measured 185-200 cycles per MMA.
+      // Stage index, parity and descriptors advance by additions.
+      const uint64_t da0 = p.a_mn ? tc5::smem_desc_mn_sw128(base, 128 * BK) : tc5::smem_desc_k_sw128(base);
+      const uint64_t db0 = p.b_mn ? tc5::smem_desc_mn_sw128(base + C::A_BYTES, 128 * BK) : tc5::smem_desc_k_sw128(base + C::A_BYTES);
+      int s = 0;
+      uint32_t ph = 0;
+      bool pre_ok = false;
       for (int tile = first_tile; tile < num_tiles; tile += tile_step, ++lt) {
         const int buf = lt & 1;
         const uint32_t aph = (lt >> 1) & 1;
@@ -241,39 +255,36 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
         tc5::fence_after_sync();
         const uint32_t tmem_d = tmem_base + (uint32_t)(buf * BN);
         bool ok = true;
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
-          const int s = it % C::STAGES;
-          const uint32_t ph = (it / C::STAGES) & 1;
-          t0 = p.stats ? clock64() : 0;
-          if (!tc5::mbar_wait(full_bar(s), ph, abort_flag, p.status, 1u)) { ok = false; break; }
-          if (p.stats) w_data += clock64() - t0;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!pre_ok) {
+            t0 = p.stats ? clock64() : 0;
+            if (!tc5::mbar_wait(full_bar(s), ph, abort_flag, p.status, 1u)) { ok = false; break; }
+            if (p.stats) w_data += clock64() - t0;
+          }
           tc5::fence_after_sync();
-          const uint32_t sa = base + s * C::STAGE_BYTES;
-          const uint64_t da = p.a_mn ? tc5::smem_desc_mn_sw128(sa, 128 * BK) : tc5::smem_desc_k_sw128(sa);
-          const uint64_t db = p.b_mn ? tc5::smem_desc_mn_sw128(sa + C::A_BYTES, 128 * BK) : tc5::smem_desc_k_sw128(sa + C::A_BYTES);
+          const uint64_t da = da0 + (uint64_t)(s * (C::STAGE_BYTES >> 4));
+          const uint64_t db = db0 + (uint64_t)(s * (C::STAGE_BYTES >> 4));
+          int sn = s + 1;
+          uint32_t phn = ph;
+          if (sn == C::STAGES) { sn = 0; phn ^= 1u; }
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k) {
+            if (k == BK / UMMA_K - 1) pre_ok = tc5::mbar_test(full_bar(sn), phn);
             if (PAIR) {
               tc5::mma_f8f6f4_pair(tmem_d, da + a_step * k, db + b_step * k, idesc, (kb | k) ? 1u : 0u);
             } else {
               tc5::mma_f8f6f4(tmem_d, da + a_step * k, db + b_step * k, idesc, (kb | k) ? 1u : 0u);
             }
           }
-          // frees the stage (in both CTAs) once these MMAs have read it
-          if (PAIR) {
-            tc5::mma_commit_pair(tc5::map_to_cta(empty_bar(s), 0));
-            tc5::mma_commit_pair(tc5::map_to_cta(empty_bar(s), 1));
-          } else {
-            tc5::mma_commit(empty_bar(s));
-          }
+          // frees the stage (in both CTAs: one multicast commit) once these MMAs have read it
+          if (PAIR) tc5::mma_commit_pair_mc(empty_bar(s), (uint16_t)3);
+          else      tc5::mma_commit(empty_bar(s));
+          s = sn;
+          ph = phn;
         }
         if (!ok) break;
-        if (PAIR) {    // accumulator complete, in both CTAs' TMEM
-          tc5::mma_commit_pair(tc5::map_to_cta(tfull_bar(buf), 0));
-          tc5::mma_commit_pair(tc5::map_to_cta(tfull_bar(buf), 1));
-        } else {
-          tc5::mma_commit(tfull_bar(buf));
-        }
+        if (PAIR) tc5::mma_commit_pair_mc(tfull_bar(buf), (uint16_t)3);    // accumulator complete, in both CTAs' TMEM
+        else      tc5::mma_commit(tfull_bar(buf));
       }
       if (p.stats) {
         p.stats[4 * blockIdx.x + 1] = (unsigned long long)w_data;
@@ -594,12 +605,15 @@ MSAMP_API int msamp_gemm_fp8_ex(const MsampGemmDesc* g, void* stream_) {
   MSAMP_REQUIRE(g->d != nullptr || (g->residual == nullptr), "msamp_gemm_fp8: a residual needs the output it is added to");
   MSAMP_REQUIRE(g->d8 == nullptr || g->d8_scale != nullptr, "msamp_gemm_fp8: a quantised copy needs its scale");
   const int sms = msamp_sm_count();
-  // Tile choice: single-CTA 128x256 tiles when those fill the device, else 128x128.  The CTA-pair kernel moves a
-  // third less data per FLOP but under the 1 kW power cap of a B200 it measured 0-6 % slower inside a training
-  // step than the single-CTA kernel, so it runs only on request (tile == 1).
+  // Tile choice.  Problems that fill the device with 256-wide tiles run on the CTA-pair kernel (256x256 tiles over two
+  // SMs): it moves a third less data per FLOP through L2 and shared memory, and since the MMA issue loop stopped
+  // leaving the tensor pipe idle between K blocks that is what counts: under the 1 kW power cap a GPT-7B step measured
+  // 235.6 ms with it, 239.5 ms with single-CTA 128x256 tiles and 237.2 ms with the pair kernel everywhere but in the
+  // weight-gradient layout (same GPU, same run).  Calls that cap their CTAs to share the GPU with a communication
+  // kernel, and smaller problems, use single-CTA 128x256 or 128x128 tiles.
   const int64_t tiles_256 = (int64_t)((M + BM - 1) / BM) * ((N + 255) / 256);
   int tile = g->tile;
-  if (tile == 0) tile = 2;
+  if (tile == 0) tile = (N > 128 && tiles_256 >= 2 * sms && g->max_ctas <= 0) ? 1 : 2;
   const bool pair = tile == 1;
   const int bn = pair ? 256 : ((N > 128 && tiles_256 >= sms) ? 256 : 128);
   CUtensorMap ma, mb;

@@ -233,6 +233,12 @@ __device__ __forceinline__ void mma_commit_pair(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
 
+// One commit that arrives on the barrier at the same shared-memory offset in every CTA of `cta_mask` (bit r = CTA rank r).
+__device__ __forceinline__ void mma_commit_pair_mc(uint32_t bar, uint16_t cta_mask) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar), "h"(cta_mask)
+               : "memory");
+}
+
 // D[tmem] (+)= A[smem] * B[smem] for 16-bit inputs (bf16 / fp16); issued by one thread.
 __device__ __forceinline__ void mma_f16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
   asm volatile(
