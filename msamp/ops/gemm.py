@@ -15,7 +15,7 @@ from msamp.common.dtype import Dtypes
 from msamp.ops import native
 
 _F8 = Dtypes.qtype_to_float8
-# MSAMP_GEMM_TILE=1|2 forces the CTA-pair or the single-CTA kernel for every call that does not choose itself (tuning aid)
+# MSAMP_GEMM_TILE=1|2 forces the CTA-pair or the single-CTA kernel for every call that does not choose itself; 0 lets the library choose
 _DEFAULT_TILE = int(os.environ.get('MSAMP_GEMM_TILE', '0'))
 
 
