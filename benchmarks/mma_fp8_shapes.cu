@@ -17,7 +17,7 @@ using namespace tc5;
 // 3 the same with the non-blocking test_wait, 4 the wait without the fence, 5 wait + fence after the second MMA of the K block
 // instead, 6 / 7 a chain of 16 / 64 dependent integer multiply-adds, >= 16 a busy delay of EXTRA cycles on clock64.
 template <int N, int PER_COMMIT, int EXTRA>
-__global__ void __launch_bounds__(128, 1) k(long long* out, int n_mma) {
+__global__ void __launch_bounds__(128, 1) k(long long* out, int n_mma, int mn) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
@@ -46,12 +46,14 @@ __global__ void __launch_bounds__(128, 1) k(long long* out, int n_mma) {
   const uint32_t tm = holder;
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   if (warp == 1 && lane == 0) {
-    const uint32_t idesc = idesc_f8(128, N, 0, 0, 0, 0);
+    // mn: both operands MN-major (the layout of the weight-gradient GEMM: [k rows][128 bytes of M or N] panels)
+    const uint32_t idesc = idesc_f8(128, N, 0, 0, mn, mn);
     const long long t0 = clock64();
     for (int j = 0; j < n_mma; ++j) {
       const uint32_t sa = base + (uint32_t)((j >> 2) & 3) * STAGE;
-      const uint64_t da = smem_desc_k_sw128(sa) + 2ull * (j & 3);
-      const uint64_t db = smem_desc_k_sw128(sa + 128 * 128) + 2ull * (j & 3);
+      const uint64_t da = mn ? smem_desc_mn_sw128(sa, 128 * 128) + (uint64_t)(32 * 128 / 16) * (j & 3) : smem_desc_k_sw128(sa) + 2ull * (j & 3);
+      const uint64_t db = mn ? smem_desc_mn_sw128(sa + 128 * 128, 128 * 128) + (uint64_t)(32 * 128 / 16) * (j & 3)
+                             : smem_desc_k_sw128(sa + 128 * 128) + 2ull * (j & 3);
       mma_f8f6f4(tm + (uint32_t)(((j >> 7) & 1) * N), da, db, idesc, (j & 127) ? 1u : 0u);
       if ((j % PER_COMMIT) == PER_COMMIT - 1) mma_commit(bar + 8);    // arrivals nobody waits for
       if ((j & 3) == 1 && EXTRA == 5) {    // the same wait, but in the middle of the K block
@@ -177,10 +179,10 @@ void run_pair(long long* d, int n_mma) {
 }
 
 template <int N, int PER_COMMIT, int EXTRA = 0>
-void run(long long* d, int n_mma) {
+void run(long long* d, int n_mma, int mn = 0) {
   constexpr int SMEM = 4 * (128 * 128 + N * 128) + 2048;
   cudaFuncSetAttribute(k<N, PER_COMMIT, EXTRA>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
-  for (int rep = 0; rep < 2; ++rep) k<N, PER_COMMIT, EXTRA><<<148, 128, SMEM>>>(d, n_mma);
+  for (int rep = 0; rep < 2; ++rep) k<N, PER_COMMIT, EXTRA><<<148, 128, SMEM>>>(d, n_mma, mn);
   cudaError_t e = cudaDeviceSynchronize();
   long long h[2 * 148];
   cudaMemcpy(h, d, sizeof(h), cudaMemcpyDeviceToHost);
@@ -189,8 +191,8 @@ void run(long long* d, int n_mma) {
     issue += (double)h[2 * i] / 148;
     total += (double)h[2 * i + 1] / 148;
   }
-  printf("128 x %3d x 32 e4m3, commit every %3d MMAs, extra %3d: err=%d, %.1f cycles per MMA until all issued, %.1f until all complete; %.0f multiply-adds per cycle\n",
-         N, PER_COMMIT, EXTRA, (int)e, issue / n_mma, total / n_mma, 128.0 * N * 32 * n_mma / total);
+  printf("128 x %3d x 32 e4m3%s, commit every %3d MMAs, extra %3d: err=%d, %.1f cycles per MMA until all issued, %.1f until all complete; %.0f multiply-adds per cycle\n",
+         N, mn ? " (A, B MN-major)" : "", PER_COMMIT, EXTRA, (int)e, issue / n_mma, total / n_mma, 128.0 * N * 32 * n_mma / total);
 }
 
 int main() {
@@ -203,6 +205,8 @@ int main() {
   run<256, 1>(d, n);
   run<256, 16>(d, n);
   run<256, 128>(d, n);
+  run<256, 4>(d, n, 1);
+  run<128, 4>(d, n, 1);
   run_pair(d, n);
   run<256, 4, 1>(d, n);
   run<256, 4, 2>(d, n);
