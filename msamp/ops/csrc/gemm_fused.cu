@@ -318,7 +318,15 @@ gemm_fused_kernel(const __grid_constant__ FusedMaps maps, const GemmParams p, co
     // ================================================================== MMA issuer
     if (lane == 0) {
       const uint32_t idesc = tc5::idesc_f8(BM, BN, p.a_fmt, p.b_fmt);
-      uint32_t it = 0, lt = 0;
+      uint32_t lt = 0;
+      // As in gemm_fp8.cu: the tensor pipe idles for whatever this thread does between two MMAs, and a blocking wait on
+      // a stage barrier costs 100-140 cycles even when the data is there.  The barrier of the next stage is probed
+      // without blocking before the last MMA of a K block; the blocking wait runs only when the probe failed.
+      const uint64_t da0 = tc5::smem_desc_k_sw128(base);
+      const uint64_t db0 = tc5::smem_desc_k_sw128(base + C::A_BYTES);
+      int s = 0;
+      uint32_t ph = 0;
+      bool pre_ok = false;
       for (int tile = cta; tile < num_tiles; tile += ncta, ++lt) {
         const int buf = lt & 1;
         const uint32_t aph = (lt >> 1) & 1;
@@ -326,18 +334,22 @@ gemm_fused_kernel(const __grid_constant__ FusedMaps maps, const GemmParams p, co
         tc5::fence_after_sync();
         const uint32_t tmem_d = tmem_base + (uint32_t)(buf * BN);
         bool ok = true;
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
-          const int s = it % C::STAGES;
-          const uint32_t ph = (it / C::STAGES) & 1;
-          if (!tc5::mbar_wait(full_bar(s), ph, abort_flag, p.status, 1u)) { ok = false; break; }
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!pre_ok && !tc5::mbar_wait(full_bar(s), ph, abort_flag, p.status, 1u)) { ok = false; break; }
           tc5::fence_after_sync();
-          const uint32_t sa = base + s * C::STAGE_BYTES;
-          const uint64_t da = tc5::smem_desc_k_sw128(sa);
-          const uint64_t db = tc5::smem_desc_k_sw128(sa + C::A_BYTES);
+          const uint64_t da = da0 + (uint64_t)(s * (C::STAGE_BYTES >> 4));
+          const uint64_t db = db0 + (uint64_t)(s * (C::STAGE_BYTES >> 4));
+          int sn = s + 1;
+          uint32_t phn = ph;
+          if (sn == C::STAGES) { sn = 0; phn ^= 1u; }
 #pragma unroll
-          for (int k = 0; k < BK / UMMA_K; ++k)
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            if (k == BK / UMMA_K - 1) pre_ok = tc5::mbar_test(full_bar(sn), phn);
             tc5::mma_f8f6f4(tmem_d, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc, (kb | k) ? 1u : 0u);
+          }
           tc5::mma_commit(empty_bar(s));
+          s = sn;
+          ph = phn;
         }
         if (!ok) break;
         tc5::mma_commit(tfull_bar(buf));
