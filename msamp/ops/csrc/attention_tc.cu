@@ -808,8 +808,10 @@ attn_fwd_ps_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
           for (int g = 0; g < 2; ++g) {
             const int gj = 2 * gs + g;
             const int vs = gj % NV;
-            if (!tc5::mbar_wait(bar(B_PF + (gs & 1) * 2 + g), (uint32_t)(gs >> 1) & 1u, abort_flag, p.status, kStatusBit)) { ok = false; break; }
+            // the data barrier first: a wait costs 100+ cycles even when its phase completed long ago, and this one
+            // then passes while the softmax warps are still at work on P
             if (!tc5::mbar_wait(bar(B_VF + vs), (uint32_t)(gj / NV) & 1u, abort_flag, p.status, kStatusBit)) { ok = false; break; }
+            if (!tc5::mbar_wait(bar(B_PF + (gs & 1) * 2 + g), (uint32_t)(gs >> 1) & 1u, abort_flag, p.status, kStatusBit)) { ok = false; break; }
             tc5::fence_after_sync();
 #pragma unroll
             for (int kk = 0; kk < 4; ++kk) {
@@ -2133,8 +2135,11 @@ attn_bwd_dq_ps_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
       // S = Q K^T and dP[gt & 1] = dO V^T for the gt-th tile of this CTA
       auto issue_s = [&](int gt) -> bool {
         const int ks = gt % NK, vs = gt % NV;
-        if (gt > 0 && !tc5::mbar_wait(bar(B_SE), (uint32_t)(gt - 1) & 1u, abort_flag, p.status, kStatusBit)) return false;
+        // data barriers first (they pass while the softmax warps still hold S), so that the two products are issued back
+        // to back once S is free: a wait between them idles the tensor pipe for 100+ cycles even when V is there
         if (!tc5::mbar_wait(bar(B_KF + ks), (uint32_t)(gt / NK) & 1u, abort_flag, p.status, kStatusBit)) return false;
+        if (!tc5::mbar_wait(bar(B_VF + vs), (uint32_t)(gt / NV) & 1u, abort_flag, p.status, kStatusBit)) return false;
+        if (gt > 0 && !tc5::mbar_wait(bar(B_SE), (uint32_t)(gt - 1) & 1u, abort_flag, p.status, kStatusBit)) return false;
         tc5::fence_after_sync();
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
@@ -2143,8 +2148,6 @@ attn_bwd_dq_ps_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                        idesc_s, kk ? 1u : 0u);
         }
         tc5::mma_commit(bar(B_SF));
-        if (!tc5::mbar_wait(bar(B_VF + vs), (uint32_t)(gt / NV) & 1u, abort_flag, p.status, kStatusBit)) return false;
-        tc5::fence_after_sync();
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
           const uint32_t off = (uint32_t)(kk >> 2) * PANEL + (uint32_t)(kk & 3) * 32u;
@@ -2407,8 +2410,8 @@ attn_bwd_dkdv_ps_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       const uint32_t idesc_acc = tc5::idesc_bf16(128, 128, 0, 1);
       auto issue_st = [&](int gq) -> bool {    // S^T = K Q^T for the gq-th query tile of this CTA
         const int st = gq % NSQ;
+        if (!tc5::mbar_wait(bar(B_QF + st), (uint32_t)(gq / NSQ) & 1u, abort_flag, p.status, kStatusBit)) return false;    // data first
         if (gq > 0 && !tc5::mbar_wait(bar(B_SE), (uint32_t)(gq - 1) & 1u, abort_flag, p.status, kStatusBit)) return false;
-        if (!tc5::mbar_wait(bar(B_QF + st), (uint32_t)(gq / NSQ) & 1u, abort_flag, p.status, kStatusBit)) return false;
         tc5::fence_after_sync();
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
