@@ -7,13 +7,14 @@
 // written.  The per-tensor scale_inv factors are read from device memory (no host synchronisation).
 //
 // Two persistent, warp-specialised kernels share the code below:
-//   * single-CTA kernel (default): 128 x 256 tiles (128 x 128 when those would not fill the device).
-//   * CTA-pair kernel (on request): a cluster of two CTAs on the two SMs of a TPC computes a 256 x 256
-//     tile with tcgen05.mma.cta_group::2.  Each CTA loads its own 128 rows of A and its own 128
-//     rows of B with its own TMA (no multicast), i.e. 32 KB per 128-byte K block instead of the
-//     48 KB a single CTA needs for 128 x 256.  The even CTA issues the MMAs for both.
+//   * CTA-pair kernel (default when the problem fills the device): a cluster of two CTAs on the two SMs of a
+//     TPC computes a 256 x 256 tile with tcgen05.mma.cta_group::2.  Each CTA loads its own 128 rows of A
+//     and its own 128 rows of B with its own TMA (no multicast), i.e. 32 KB per 128-byte K block instead
+//     of the 48 KB a single CTA needs for 128 x 256.  The even CTA issues the MMAs for both.
+//   * single-CTA kernel (smaller problems, and calls that cap their CTAs): 128 x 256 tiles, or 128 x 128
+//     when those would not fill the device.
 // Roles:  warp 0 TMA producer (ring of shared-memory stages), warp 1 TMEM allocation + MMA issue,
-// warps 2..5 epilogue (tcgen05.ld the fp32 accumulator, scale, bias / residual / GeLU derivative,
+// warps 2..9 epilogue (tcgen05.ld the fp32 accumulator, scale, bias / residual / GeLU derivative,
 // convert, store, optional max|D| and optional quantised copy).  Two accumulator buffers in TMEM
 // let the epilogue of tile i overlap the main loop of tile i+1.  Every wait on an mbarrier is
 // bounded; when one gives up the CTA sets the device status word, lets its outstanding copies land,
